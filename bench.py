@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Benchmark of the int8 paged decode attention (the headline workload).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one decode-attention call over a batch of 64 sequences (32 query heads, 8 KV heads,
+head_dim 128, 16-token pages, contexts uniform in [512, 4096], page tables drawn from a
+200k-page int8 pool with a (multiplier, shift) per token and KV head).  Inputs are synthetic
+and seeded.  With N > 1 every rank holds its own pool and batch (independent sequences, no
+collective on the data path: weak scaling) and the rate is the sum over ranks.
+
+The script prints ONE JSON line:
+  value      tokens/s with everything resident in HBM (CUDA-event time over the K steps, max over ranks)
+  e2e        the same rate through the C ABI with the step's inputs (queries, their scales, page table,
+             lengths) coming from pinned host memory and the int8 result copied back, every step; the
+             KV pool is the cache itself and stays resident
+  roofline   algorithmic bytes of one launch / mean kernel time, against the measured HBM copy peak
+  cpu_baseline  the CPU oracle (numpy port of the reference arithmetic) timed on this host
+
+``--impl reference`` times only the CPU oracle port on the host cores (the reference's attention is
+Python/torch code that cannot travel with this repository; its arithmetic is restated in oracle/).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(batch=64, q_heads=32, kv_heads=8, head_dim=128, page=16, ctx_lo=512, ctx_hi=4096, pool_pages=200_000)
+METRIC = "int8 paged decode attention throughput (decode tokens/s; HBM GB/s in roofline)"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
+# profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES = None
+
+
+def draw_lens(seed: int) -> np.ndarray:
+    return np.random.default_rng(seed).integers(WORKLOAD["ctx_lo"], WORKLOAD["ctx_hi"] + 1, WORKLOAD["batch"])
+
+
+def algorithmic_bytes(lens: np.ndarray) -> int:
+    """Minimum HBM traffic of one launch: K and V codes, their scales, page ids, q in, int8 out."""
+    w = WORKLOAD
+    per_seq = lens.astype(np.int64) * w["kv_heads"] * w["head_dim"] * 2 + lens.astype(np.int64) * w["kv_heads"] * 2 * 5 \
+        + ((lens + 15) // 16).astype(np.int64) * 4
+    return int(per_seq.sum() + w["batch"] * w["q_heads"] * w["head_dim"] * 2)
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------- CPU oracle leg
+def cpu_oracle_rate(seed: int, n_seq: int, repeats: int = 1):
+    """Tokens/s of the numpy oracle on the first ``n_seq`` sequences of the seeded batch."""
+    from oracle import attention as oattn
+    w = WORKLOAD
+    lens = draw_lens(seed)[:n_seq]
+    rng = np.random.default_rng(seed + 1)
+    n_pg = (lens + 15) // 16
+    pool = oattn.PagedKV(int(n_pg.sum()), w["kv_heads"], w["head_dim"])
+    pool.k_codes[:] = rng.integers(-127, 128, pool.k_codes.shape, dtype=np.int8)
+    pool.v_codes[:] = rng.integers(-127, 128, pool.v_codes.shape, dtype=np.int8)
+    pool.meta[:, :, 0:32] = rng.integers(2**30, 2**31, pool.meta[:, :, 0:32].shape)
+    pool.meta[:, :, 32:36].view(np.int8)[:] = rng.integers(35, 39, (pool.P, pool.H, 16))
+    pool.meta[:, :, 36:40].view(np.int8)[:] = rng.integers(33, 38, (pool.P, pool.H, 16))
+    perm = rng.permutation(pool.P)
+    tables, off = [], 0
+    for n in n_pg:
+        tables.append(perm[off:off + n]); off += n
+    q = rng.integers(-127, 128, (n_seq, w["q_heads"], w["head_dim"]), dtype=np.int8)
+    qm = rng.integers(2**30, 2**31, (n_seq, w["q_heads"])); qs = rng.integers(43, 46, (n_seq, w["q_heads"]))
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        out = oattn.paged_attention(q, qm, qs, pool, tables, lens, [1] * n_seq)
+        oattn.quant_heads_int8(out)
+    dt = (time.perf_counter() - t0) / repeats
+    return n_seq / dt, dt
+
+
+def host_threads() -> int:
+    try:
+        import torch
+        return int(torch.get_num_threads())
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_seq = 16
+    for _ in range(args.warmup):
+        cpu_oracle_rate(0, 4)
+    t0 = time.perf_counter()
+    total = 0.0
+    for _ in range(args.steps):
+        _, dt = cpu_oracle_rate(0, n_seq)
+        total += dt
+    rate = n_seq * args.steps / total
+    sample = f"{n_seq} of the 64 sequences per step (all 32 heads), numpy oracle port, BLAS threads for the dot products"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": rate, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "int8 paged decode attention, batch 64, 32q/8kv heads, head_dim 128, page 16, "
+                               "ctx U[512,4096] (CPU sample)", **WORKLOAD},
+        "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": host_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- clocks sampler
+class ClockSampler:
+    FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.samples = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [s for (t, s) in self.samples if t0 <= t <= t1] or [s for (_, s) in self.samples]
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            parts = [p.strip() for p in r.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0])); mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# ----------------------------------------------------------------------------- GPU leg
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from mini_sgl_integer_b200 import _lib
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    w = WORKLOAD
+    B, Hq, Hkv, D, P = w["batch"], w["q_heads"], w["kv_heads"], w["head_dim"], w["pool_pages"]
+
+    # ---- seeded synthetic state and inputs (each rank its own draw)
+    lens_np = draw_lens(rank)
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    pool = Int8PagedKVCache(Hkv, 1, D, P, dev)
+    pool.k_cache(0).copy_(torch.randint(-127, 128, pool.k_cache(0).shape, dtype=torch.int8, device=dev, generator=g))
+    pool.v_cache(0).copy_(torch.randint(-127, 128, pool.v_cache(0).shape, dtype=torch.int8, device=dev, generator=g))
+    meta = pool.meta(0)
+    meta[:, :, 0:32] = torch.randint(2**30, 2**31, (P, Hkv, 32), dtype=torch.int64, device=dev, generator=g).to(torch.int32)
+    meta[:, :, 32:36] = torch.randint(35, 39, (P, Hkv, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
+    meta[:, :, 36:40] = torch.randint(33, 38, (P, Hkv, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
+    rng = np.random.default_rng(2000 + rank)
+    perm = rng.permutation(P)
+    n_pg = (lens_np + 15) // 16
+    pitch = int(((w["ctx_hi"] + 15) // 16))
+    table_np = np.zeros((B, pitch), dtype=np.int32)
+    off = 0
+    for b in range(B):
+        table_np[b, : n_pg[b]] = perm[off:off + n_pg[b]]; off += n_pg[b]
+    h_q = torch.from_numpy(rng.integers(-127, 128, (B, Hq, D), dtype=np.int8)).pin_memory()
+    h_qm = torch.from_numpy(rng.integers(2**30, 2**31, (B, Hq)).astype(np.int32)).pin_memory()
+    h_qs = torch.from_numpy(rng.integers(43, 46, (B, Hq)).astype(np.int32)).pin_memory()
+    h_table = torch.from_numpy(table_np).pin_memory()
+    h_lens = torch.from_numpy(lens_np.astype(np.int32)).pin_memory()
+    h_out = torch.empty((B, Hq, D), dtype=torch.int8).pin_memory()
+    h_absmax = torch.empty((B, Hq), dtype=torch.int32).pin_memory()
+    d_q, d_qm, d_qs, d_table, d_lens = (t.to(dev) for t in (h_q, h_qm, h_qs, h_table, h_lens))
+    d_out = torch.empty((B, Hq, D), dtype=torch.int8, device=dev)
+    d_absmax = torch.empty((B, Hq), dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream()
+    sp = _lib.c_void_p(stream.cuda_stream)
+    p = _lib.ptr
+
+    def launch():
+        _lib.call("b200_attn_decode", p(d_q), p(d_qm), p(d_qs), p(pool.k_cache(0)), p(pool.v_cache(0)), p(pool.meta(0)),
+                  p(d_table), pitch, p(d_lens), None, p(d_out), p(d_absmax), B, Hq, Hkv, P, w["ctx_hi"], args.cluster, sp)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        launch()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    t_wall0 = time.perf_counter()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for a, b in evs:
+        a.record(stream); launch(); b.record(stream)
+    e1.record(stream)
+    barrier()
+    t_wall1 = time.perf_counter()
+    total_ms = e0.elapsed_time(e1)
+    kern_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
+
+    # ---- end to end: host inputs -> device, launch, result -> host, every step
+    def e2e_step():
+        d_q.copy_(h_q, non_blocking=True); d_qm.copy_(h_qm, non_blocking=True); d_qs.copy_(h_qs, non_blocking=True)
+        d_table.copy_(h_table, non_blocking=True); d_lens.copy_(h_lens, non_blocking=True)
+        launch()
+        h_out.copy_(d_out, non_blocking=True); h_absmax.copy_(d_absmax, non_blocking=True)
+        stream.synchronize()
+
+    for _ in range(args.warmup):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record(stream)
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+    clocks = sampler.stop(t_wall0, time.perf_counter()) if sampler else None
+
+    t = torch.tensor([total_ms, e2e_ms, kern_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, kern_ms = (float(x) for x in t.tolist())
+    if rank == 0:
+        alg = algorithmic_bytes(lens_np)
+        peak, how = measured_peak()
+        achieved = alg / (kern_ms * 1e-3) / 1e9
+        h2d = sum(x.numel() * x.element_size() for x in (h_q, h_qm, h_qs, h_table, h_lens))
+        d2h = sum(x.numel() * x.element_size() for x in (h_out, h_absmax))
+        n_cpu = 8
+        cpu_rate, cpu_dt = cpu_oracle_rate(0, n_cpu)
+        line = {
+            "metric": METRIC, "value": world * B * args.steps / (total_ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "int8 paged decode attention, batch 64 per GPU, 32q/8kv heads, head_dim 128, page 16, "
+                                   "ctx U[512,4096], 200k-page pool", **w, "sum_ctx": int(lens_np.sum()),
+                       "l2": "inputs larger than L2 (about 314 MB of KV touched per launch vs 126 MB)",
+                       "cluster": args.cluster},
+            "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_BYTES, "peak_source": how, "algorithmic_bytes": alg,
+                         "kernel_ms": kern_ms, "kernel": "attn_decode_kernel<4>", "frac_of_8TBs": achieved / 8000.0},
+            "cpu_baseline": {"value": cpu_rate, "unit": "tokens/s", "cores": host_threads(), "kind": "port",
+                             "sample": f"{n_cpu} of the 64 sequences, one pass ({cpu_dt:.2f} s), numpy oracle port"},
+            "clocks": clocks, "wall_s": t_wall1 - t_wall0,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cluster", type=int, default=0, help="CTAs per (sequence, KV head); 0 = library default")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,157 @@
+/*
+ * b200int — C ABI of the B200 (sm_100a) kernels for the integer-only W8A8 forward path.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the given
+ * CUDA stream and returns immediately: 0 on success, a negative B200_E_* code when
+ * an argument is rejected (nothing is launched in that case).  No entry point
+ * allocates, frees or synchronises unless its comment says so.  All pointers are
+ * borrowed for the duration of the call; the caller owns every buffer.
+ * b200_last_error_string() returns the message of the calling thread's last failure.
+ *
+ * Citations name the reference interface each entry point stands in for, as
+ * file:line inside the mini-sgl-integer source tree (python/minisgl/...).
+ */
+#ifndef B200INT_H_
+#define B200INT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define B200_API __attribute__((visibility("default")))
+#else
+#define B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* b200_stream_t; /* a cudaStream_t; NULL is the legacy default stream */
+
+enum {
+  B200_OK = 0,
+  B200_E_NULL = -1,        /* a required pointer is NULL */
+  B200_E_SHAPE = -2,       /* a size is zero/negative or inconsistent */
+  B200_E_ALIGN = -3,       /* a pointer or row pitch is not 16-byte aligned */
+  B200_E_UNSUPPORTED = -4, /* a size outside what the kernels are built for */
+  B200_E_CUDA = -5         /* the CUDA runtime reported an error at launch */
+};
+
+B200_API int b200_version(void);
+B200_API const char* b200_last_error_string(void);
+
+/* Copies one compiled-in 1024-entry table to host memory.
+ * which: 0 = inverse-sqrt (kernel/fixed_point/rmsnorm_int_only_v2.py:31-43),
+ *        1 = exp2 for SiLU (kernel/fixed_point/silu_and_mul_int_only.py:35-46),
+ *        2 = exp2 for attention (kernel/triton/int8_attention_kernels.py:27-29). */
+B200_API int b200_get_lut(int which, int32_t* out_host_1024);
+
+/* ---- Q15.16 conversion: kernel/fixed_point/q15_tensor.py:17-28 (to_fixed / from_fixed).
+ * bf16 values travel as raw 16-bit patterns. */
+B200_API int b200_to_fixed_f32(const float* x, int32_t* out, int64_t n, b200_stream_t s);
+B200_API int b200_to_fixed_bf16(const uint16_t* x, int32_t* out, int64_t n, b200_stream_t s);
+B200_API int b200_from_fixed_f32(const int32_t* x, float* out, int64_t n, b200_stream_t s);
+B200_API int b200_from_fixed_bf16(const int32_t* x, uint16_t* out, int64_t n, b200_stream_t s);
+
+/* ---- Fixed-point RMSNorm, optional residual add, optional per-token int8 quant.
+ * Replaces rmsnorm_int_only_v2 (kernel/fixed_point/rmsnorm_int_only_v2.py:319-390),
+ * fused_add_rmsnorm_int_only_v2 (:393-475) and, when codes != NULL, the
+ * per_token_quant_int8_from_q15 that follows them inside apply_weights_q15
+ * (layers/quantization/w8a8_int8.py:104-131).
+ *   x, residual (nullable), residual_out (required iff residual), norm_out (nullable):
+ *       int32 [rows, hidden], dense rows; weight int32 [hidden].
+ *   codes int8 [rows, hidden], scale fp32 [rows], absmax int32 [rows]: all three or none.
+ * hidden must be a multiple of 4 and at most 32768. */
+B200_API int b200_rmsnorm_q15(const int32_t* x, const int32_t* residual, const int32_t* weight,
+                     int32_t* residual_out, int32_t* norm_out,
+                     int8_t* codes, float* scale, int32_t* absmax,
+                     int64_t rows, int hidden, b200_stream_t s);
+
+/* ---- SiLU(gate) * up, optional blocked Walsh-Hadamard rotation, optional per-token quant.
+ * Replaces silu_and_mul_int_only (kernel/fixed_point/silu_and_mul_int_only.py:233-275),
+ * apply_blockwise_fwht_q15 (models/utils_integer.py:46-60) and the per-token quant of the
+ * following down_proj (layers/quantization/w8a8_int8.py:104-131).
+ *   gate_up int32 [rows, 2*inter] laid out gate || up; q15_out int32 [rows, inter] (nullable);
+ *   codes/scale/absmax as above (all three or none).
+ * fwht_block: 0 = no rotation, or 128.  inter must be a multiple of 128 (of 4 when
+ * fwht_block == 0 and codes == NULL) and at most 32768. */
+B200_API int b200_silu_mul_q15(const int32_t* gate_up, int32_t* q15_out,
+                      int8_t* codes, float* scale, int32_t* absmax,
+                      int64_t rows, int inter, int fwht_block, b200_stream_t s);
+
+/* ---- Walsh-Hadamard transform of every n-wide row with per-stage int32 saturation.
+ * Replaces fwht_int_q15 (kernel/fixed_point/fwht_int.py:99-147). n: power of two, 2..1024. */
+B200_API int b200_fwht_q15(const int32_t* x, int32_t* out, int64_t rows, int n, int normalize,
+                  b200_stream_t s);
+
+/* ---- Integer RoPE (neox halves), optionally followed by the FWHT over every head.
+ * Replaces rope_int_q15 (kernel/fixed_point/rope_int.py:128-247) and rope_fwht_int_q15
+ * (kernel/fixed_point/rope_fwht_int.py:9-23).
+ *   positions int32 [tokens]; q int32 [tokens, q_heads, 128]; k int32 [tokens, kv_heads, 128];
+ *   cos_sin int32 [max_pos, 128] (cos || sin, Q1.15).  head_dim is fixed at 128.
+ *   q_norm_w / k_norm_w (nullable, int32 [128]): when given, each head row first goes
+ *   through the fixed-point RMSNorm (the q_norm / k_norm of models/utils_integer.py:214-218).
+ * Row pitches are in int32 elements so that q and k may be views into one qkv buffer. */
+B200_API int b200_qk_rope_q15(const int32_t* positions, const int32_t* q, int64_t q_pitch,
+                     const int32_t* k, int64_t k_pitch, const int32_t* cos_sin, int max_pos,
+                     const int32_t* q_norm_w, const int32_t* k_norm_w,
+                     int32_t* q_out, int32_t* k_out, int64_t tokens, int q_heads, int kv_heads,
+                     int with_fwht, b200_stream_t s);
+
+/* ---- Per-row int8 quantisation of Q15.16 values.
+ * Replaces per_token_quant_int8_from_q15 (layers/quantization/w8a8_int8.py:104-131).
+ * x int32 [rows, k] -> codes int8 [rows, k], scale fp32 [rows], absmax int32 [rows]. */
+B200_API int b200_per_token_quant_q15(const int32_t* x, int8_t* codes, float* scale, int32_t* absmax,
+                             int64_t rows, int k, b200_stream_t s);
+
+/* ---- Fixed-point form (multiplier in [2^30,2^31), shift) of the scale absmax/(127*65536).
+ * No counterpart in the reference (its requant is a float library epilogue). */
+B200_API int b200_absmax_to_mul_shift(const int32_t* absmax, int32_t* mul, int32_t* shift, int64_t n,
+                             b200_stream_t s);
+
+/* ---- int8 paged KV pool, one layer:
+ *   k_codes int8 [pages, kv_heads, 16, 128]; v_codes int8 [pages, kv_heads, 128, 16]
+ *   (transposed inside a page); meta int32 [pages, kv_heads, 40]: words 0-15 k multipliers,
+ *   16-31 v multipliers, 32-35 sixteen int8 k shifts, 36-39 sixteen int8 v shifts.
+ * A token location is page*16 + offset.
+ *
+ * b200_kv_store_q15 quantises Q15.16 K and V rows per token and KV head (codes as
+ * per_token_quant_int8_from_q15 on each 128-wide row; multiplier/shift as
+ * b200_absmax_to_mul_shift) and scatters them to out_loc.  It stands in for
+ * MHAKVCache.store_kv (kvcache/mha_pool.py:46-57) -> store_cache (kernel/store.py:30-42)
+ * -> store_kv_cache (kernel/csrc/jit/store.cu:27-56).  k, v: int32 rows of
+ * kv_heads*128 with the given pitch (elements); out_loc int32 [tokens]. */
+B200_API int b200_kv_store_q15(const int32_t* k, int64_t k_pitch, const int32_t* v, int64_t v_pitch,
+                      const int32_t* out_loc, int8_t* k_codes, int8_t* v_codes, int32_t* meta,
+                      int64_t tokens, int kv_heads, int64_t num_pages, b200_stream_t s);
+
+/* Scatter already-quantised tokens (codes int8 [tokens, kv_heads, 128]; mul/shift int32
+ * [tokens, kv_heads]) into the pool.  Used to preload pools with given codes. */
+B200_API int b200_kv_store_codes(const int8_t* k8, const int8_t* v8, const int32_t* k_mul,
+                        const int32_t* k_shift, const int32_t* v_mul, const int32_t* v_shift,
+                        const int32_t* out_loc, int8_t* k_codes, int8_t* v_codes, int32_t* meta,
+                        int64_t tokens, int kv_heads, int64_t num_pages, b200_stream_t s);
+
+/* ---- Decode attention over the int8 paged pool with an exact fixed-point softmax.
+ * Stands in for Int8Backend._forward_decode (attention/triton_int8.py:155-176), which in the
+ * reference runs a bf16 kernel; the integer arithmetic follows int8_context_attention_fwd
+ * (kernel/triton/int8_attention_kernels.py:278-383) generalised to per-key scales.
+ *   q int8 [batch, q_heads, 128]; q_mul, q_shift int32 [batch, q_heads];
+ *   page_table int32 [batch, table_pitch] of page ids; kv_lens int32 [batch];
+ *   out_q15 int32 [batch, q_heads, 128] (nullable); out_codes int8 same shape with
+ *   out_absmax int32 [batch, q_heads] (both or none): per (token, head) row quant.
+ * q_heads / kv_heads must be 1, 2, 4 or 8.  max_kv_len bounds every kv_lens[i] (it sizes
+ * shared memory); lengths above it are clamped.  cluster: CTAs that share one
+ * (sequence, KV head), 1, 2, 4 or 8; 0 lets the library choose. */
+B200_API int b200_attn_decode(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
+                     const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
+                     const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                     int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax,
+                     int batch, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
+                     int cluster, b200_stream_t s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200INT_H_ */

@@ -1,0 +1,44 @@
+"""Functional entry points of the int8 paged attention kernels."""
+from __future__ import annotations
+
+import torch
+
+from .._lib import call, ptr, require_cuda, stream
+from .kv_pool import HEAD_DIM, Int8PagedKVCache
+
+
+def decode_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: torch.Tensor,
+                                pool: Int8PagedKVCache, layer_id: int, page_table: torch.Tensor,
+                                kv_lens: torch.Tensor, max_kv_len: int, *, out_q15: bool = True,
+                                out_int8: bool = False, cluster: int = 0):
+    """One decode step of integer attention over the int8 paged pool.
+
+    q8 int8 [batch, q_heads, 128]; q_mul / q_shift int32 [batch, q_heads]; page_table int32
+    [batch, pitch] of page ids; kv_lens int32 [batch].  Returns the Q15.16 output int32
+    [batch, q_heads, 128] and/or (int8 codes, int32 absmax [batch, q_heads]) per the flags.
+
+    The arithmetic is int8_context_attention_fwd's (kernel/triton/int8_attention_kernels.py:278-383)
+    with one (multiplier, shift) per key; it stands in for Int8Backend._forward_decode
+    (attention/triton_int8.py:155-176).
+    """
+    if q8.dtype != torch.int8:
+        raise TypeError(f"q8 must be int8, got {q8.dtype}")
+    if q8.ndim != 3 or q8.shape[-1] != HEAD_DIM:
+        raise ValueError(f"q8 must be [batch, q_heads, {HEAD_DIM}], got shape {tuple(q8.shape)}")
+    require_cuda(q8, q_mul, q_shift, page_table, kv_lens)
+    batch, q_heads, _ = q8.shape
+    c = lambda t: t.to(torch.int32).contiguous()
+    q8 = q8.contiguous()
+    q_mul, q_shift, page_table, kv_lens = c(q_mul), c(q_shift), c(page_table), c(kv_lens)
+    if page_table.ndim != 2 or page_table.shape[0] != batch:
+        raise ValueError(f"page_table must be [batch, pitch], got shape {tuple(page_table.shape)}")
+    o32 = torch.empty((batch, q_heads, HEAD_DIM), dtype=torch.int32, device=q8.device) if out_q15 else None
+    o8 = torch.empty((batch, q_heads, HEAD_DIM), dtype=torch.int8, device=q8.device) if out_int8 else None
+    om = torch.empty((batch, q_heads), dtype=torch.int32, device=q8.device) if out_int8 else None
+    call("b200_attn_decode", ptr(q8), ptr(q_mul), ptr(q_shift), ptr(pool.k_cache(layer_id)),
+         ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(page_table), page_table.stride(0),
+         ptr(kv_lens), ptr(o32), ptr(o8), ptr(om), batch, q_heads, pool.kv_heads, pool.num_pages,
+         int(max_kv_len), int(cluster), stream())
+    if out_q15 and out_int8:
+        return o32, o8, om
+    return o32 if out_q15 else (o8, om)

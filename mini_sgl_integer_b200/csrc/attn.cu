@@ -1,0 +1,550 @@
+// int8 paged KV pool: store kernels and decode attention with an exact fixed-point softmax.
+//
+// Pool layout of one layer (page = 16 tokens, head_dim = 128):
+//   k_codes [pages][kv_heads][16 tok][128 d]      one (page, head) chunk = 2 KB, token rows
+//   v_codes [pages][kv_heads][128 d][16 tok]      transposed inside the page: the 16 tokens of
+//                                                 one d are contiguous (PV contracts over tokens)
+//   meta    [pages][kv_heads][40 words]           k_mul[16] v_mul[16] k_shift[16 x i8] v_shift[16 x i8]
+//
+// Decode: a thread-block cluster owns one (sequence, KV head); each CTA of the cluster takes a
+// contiguous run of pages.  The softmax is exact (LUT exp with truncation), so partial results
+// cannot be rescaled: the scores of a slice stay in shared memory and the row maximum, the sum of
+// exponentials and the partial outputs are exchanged between the CTAs over distributed shared
+// memory.  K and V are each read from HBM exactly once.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "luts.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace b200 {
+
+constexpr int kPage = 16;
+constexpr int kD = 128;
+constexpr int kMetaWords = 40;
+
+__device__ __forceinline__ void absmax_to_ms_dev(int m, int* mul, int* shift) {
+  m = max(m, 1);
+  const int p = 31 - __clz(m);
+  int k = 37 - p;
+  unsigned long long v = (((unsigned long long)m << k) + 63ull) / 127ull;
+  if (v >= (1ull << 31)) {
+    k -= 1;
+    v = (((unsigned long long)m << k) + 63ull) / 127ull;
+  }
+  *mul = (int)v;
+  *shift = k + 16;
+}
+
+// ============================================================================ store
+// One warp per (token, kv head).  QUANT: rows are Q15.16 int32 and are quantised here;
+// otherwise codes and scales are given.
+template <bool QUANT>
+__global__ void __launch_bounds__(256)
+kv_store_kernel(const void* __restrict__ k_in, int64_t k_pitch, const void* __restrict__ v_in,
+                int64_t v_pitch, const int32_t* __restrict__ k_mul_in, const int32_t* __restrict__ k_shift_in,
+                const int32_t* __restrict__ v_mul_in, const int32_t* __restrict__ v_shift_in,
+                const int32_t* __restrict__ out_loc, int8_t* __restrict__ k_codes,
+                int8_t* __restrict__ v_codes, int32_t* __restrict__ meta, int64_t tokens, int kv_heads,
+                int64_t num_pages) {
+  const int lane = threadIdx.x & 31;
+  const int64_t wid = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (wid >= tokens * kv_heads) return;
+  const int64_t t = wid / kv_heads;
+  const int h = (int)(wid - t * kv_heads);
+  const int64_t loc = out_loc[t];
+  const int64_t pid = loc >> 4;
+  const int tok = (int)(loc & 15);
+  if (loc < 0 || pid >= num_pages) return;  // out-of-pool locations are dropped, never written
+
+  unsigned kw, vw;
+  int kmul, kshift, vmul, vshift;
+  if (QUANT) {
+    const int32_t* kr = reinterpret_cast<const int32_t*>(k_in) + t * k_pitch + (int64_t)h * kD;
+    const int32_t* vr = reinterpret_cast<const int32_t*>(v_in) + t * v_pitch + (int64_t)h * kD;
+    const int4 a = *reinterpret_cast<const int4*>(kr + 4 * lane);
+    const int4 b = *reinterpret_cast<const int4*>(vr + 4 * lane);
+    int mk = max(max(0, abs_wrap(a.x)), max(abs_wrap(a.y), max(abs_wrap(a.z), abs_wrap(a.w))));
+    int mv = max(max(0, abs_wrap(b.x)), max(abs_wrap(b.y), max(abs_wrap(b.z), abs_wrap(b.w))));
+    mk = max(1, warp_max(mk));
+    mv = max(1, warp_max(mv));
+    const float fk = __int2float_rn(mk), fv = __int2float_rn(mv);
+    kw = pack4(quant_code(a.x, fk), quant_code(a.y, fk), quant_code(a.z, fk), quant_code(a.w, fk));
+    vw = pack4(quant_code(b.x, fv), quant_code(b.y, fv), quant_code(b.z, fv), quant_code(b.w, fv));
+    absmax_to_ms_dev(mk, &kmul, &kshift);
+    absmax_to_ms_dev(mv, &vmul, &vshift);
+  } else {
+    kw = reinterpret_cast<const unsigned*>(reinterpret_cast<const int8_t*>(k_in) + (t * kv_heads + h) * kD)[lane];
+    vw = reinterpret_cast<const unsigned*>(reinterpret_cast<const int8_t*>(v_in) + (t * kv_heads + h) * kD)[lane];
+    kmul = k_mul_in[t * kv_heads + h];
+    kshift = k_shift_in[t * kv_heads + h];
+    vmul = v_mul_in[t * kv_heads + h];
+    vshift = v_shift_in[t * kv_heads + h];
+  }
+  const int64_t chunk = pid * kv_heads + h;
+  reinterpret_cast<unsigned*>(k_codes + (chunk * kPage + tok) * kD)[lane] = kw;
+  int8_t* vdst = v_codes + chunk * (kD * kPage) + tok;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) vdst[(4 * lane + e) * kPage] = (int8_t)((vw >> (8 * e)) & 0xff);
+  if (lane == 0) {
+    int32_t* mt = meta + chunk * kMetaWords;
+    mt[tok] = kmul;
+    mt[16 + tok] = vmul;
+    reinterpret_cast<int8_t*>(mt + 32)[tok] = (int8_t)kshift;
+    reinterpret_cast<int8_t*>(mt + 36)[tok] = (int8_t)vshift;
+  }
+}
+
+// ============================================================================ decode
+struct DecodeParams {
+  const int8_t* q;
+  const int32_t* q_mul;
+  const int32_t* q_shift;
+  const int8_t* k_codes;
+  const int8_t* v_codes;
+  const int32_t* meta;
+  const int32_t* page_table;
+  int64_t table_pitch;
+  const int32_t* kv_lens;
+  int32_t* out_q15;
+  int8_t* out_codes;
+  int32_t* out_absmax;
+  int q_heads, kv_heads;
+  int64_t num_pages;
+  int max_kv_len;
+  int s_max;  // key capacity of one CTA's slice (multiple of 32)
+};
+
+__device__ __forceinline__ int dp4a_ss(unsigned a, unsigned b, int c) {
+  int d;
+  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_su(unsigned a, unsigned b, int c) {  // a signed bytes, b unsigned
+  int d;
+  asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+constexpr int kDecodeThreads = 256;
+constexpr int kDecodeWarps = kDecodeThreads / 32;
+
+template <int G>
+__global__ void __launch_bounds__(kDecodeThreads)
+attn_decode_kernel(const DecodeParams p) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int C = (int)cluster.num_blocks();
+  const int rank = (int)cluster.block_rank();
+  const int kh = blockIdx.y;
+  const int b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int S = p.s_max;
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int32_t* sc = reinterpret_cast<int32_t*>(smem_raw);                 // [G][S] scores, then exponentials
+  uint8_t* p_hi = reinterpret_cast<uint8_t*>(sc + G * S);             // [G][S]
+  uint8_t* p_lo = p_hi + G * S;                                       // [G][S]
+  uint16_t* rel = reinterpret_cast<uint16_t*>(p_lo + G * S);          // [S]
+  int32_t* pages = reinterpret_cast<int32_t*>(rel + S);               // [S / 16]
+
+  __shared__ __align__(16) int8_t q_s[G][kD];
+  __shared__ int q_mul_s[G], q_shift_s[G];
+  __shared__ int cta_max[G];
+  __shared__ unsigned long long cta_sum[G];
+  __shared__ unsigned long long cta_vref;
+  __shared__ int cta_acc[G][kD];
+  __shared__ int g_max[G];
+  __shared__ int g_inv[G];
+  __shared__ int out_absmax_s[G];
+
+  int L = p.kv_lens[b];
+  L = max(0, min(L, p.max_kv_len));
+  const int n_pages = (L + kPage - 1) / kPage;
+  const int ppc = (n_pages + C - 1) / C;                 // pages per CTA
+  const int pg0 = min(n_pages, rank * ppc);
+  const int pg1 = min(n_pages, pg0 + ppc);
+  const int my_pages = pg1 - pg0;
+  const int key0 = pg0 * kPage;                          // first key of the slice
+  const int my_keys = max(0, min(L, pg1 * kPage) - key0);  // valid keys in the slice
+
+  // ---- set-up
+  for (int i = tid; i < G * kD / 16; i += kDecodeThreads) {
+    const int g = i / (kD / 16), c = i % (kD / 16);
+    reinterpret_cast<int4*>(&q_s[g][0])[c] =
+        reinterpret_cast<const int4*>(p.q + ((int64_t)b * p.q_heads + kh * G + g) * kD)[c];
+  }
+  if (tid < G) {
+    q_mul_s[tid] = p.q_mul[(int64_t)b * p.q_heads + kh * G + tid];
+    q_shift_s[tid] = p.q_shift[(int64_t)b * p.q_heads + kh * G + tid];
+    cta_max[tid] = (int)(-2147483647 - 1);
+    cta_sum[tid] = 0ull;
+    out_absmax_s[tid] = 0;
+  }
+  if (tid == 0) cta_vref = ~0ull;
+  for (int i = tid; i < G * kD; i += kDecodeThreads) (&cta_acc[0][0])[i] = 0;
+  for (int i = tid; i < my_pages; i += kDecodeThreads) {
+    int64_t pid = p.page_table[(int64_t)b * p.table_pitch + pg0 + i];
+    pid = pid < 0 ? 0 : (pid >= p.num_pages ? p.num_pages - 1 : pid);
+    pages[i] = (int)pid;
+  }
+  __syncthreads();
+
+  // ---- phase 1: scores of the slice.  A warp takes 32 keys (two pages), one key per lane.
+  {
+    int lmax[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) lmax[g] = (int)(-2147483647 - 1);
+    unsigned long long lvref = ~0ull;
+    const int n_pairs = (my_pages + 1) >> 1;
+    for (int pair = warp; pair < n_pairs; pair += kDecodeWarps) {
+      const int kl = pair * 32 + lane;             // key index inside the slice
+      const bool valid = kl < my_keys;
+      const int pg = min(kl >> 4, max(my_pages - 1, 0));
+      const int tok = kl & 15;
+      const int64_t chunk = (int64_t)pages[pg] * p.kv_heads + kh;
+      int dot[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) dot[g] = 0;
+      if (valid) {
+        const int4* kr = reinterpret_cast<const int4*>(p.k_codes + (chunk * kPage + tok) * kD);
+        int4 kv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) kv[j] = __ldcs(kr + j);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const int4 qq = reinterpret_cast<const int4*>(&q_s[g][0])[j];
+            dot[g] = dp4a_ss(kv[j].x, qq.x, dot[g]);
+            dot[g] = dp4a_ss(kv[j].y, qq.y, dot[g]);
+            dot[g] = dp4a_ss(kv[j].z, qq.z, dot[g]);
+            dot[g] = dp4a_ss(kv[j].w, qq.w, dot[g]);
+          }
+        }
+        const int32_t* mt = p.meta + chunk * kMetaWords;
+        const int k_mul = __ldg(mt + tok);
+        const int k_shift = reinterpret_cast<const int8_t*>(mt + 32)[tok];
+        const int v_mul = __ldg(mt + 16 + tok);
+        const int v_shift = reinterpret_cast<const int8_t*>(mt + 36)[tok];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const int cm = __mulhi(q_mul_s[g], k_mul);   // (q_mul * k_mul) >> 32
+          const int s = q_shift_s[g] + k_shift - 48;
+          const int v = sat32(mul_shift64((long long)dot[g], (long long)cm, s));
+          sc[g * S + kl] = v;
+          lmax[g] = max(lmax[g], v);
+        }
+        const unsigned long long vkey =
+            ((unsigned long long)(unsigned)(v_shift + 128) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)v_mul);
+        lvref = vkey < lvref ? vkey : lvref;
+      } else {
+#pragma unroll
+        for (int g = 0; g < G; ++g) sc[g * S + kl] = (int)(-2147483647 - 1);
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int m = warp_max(lmax[g]);
+      if (lane == 0) atomicMax(&cta_max[g], m);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(FULL_MASK, lvref, o);
+      lvref = other < lvref ? other : lvref;
+    }
+    if (lane == 0) atomicMin(&cta_vref, lvref);
+  }
+  cluster.sync();
+
+  // ---- exchange 1: row maxima and the V reference scale over the cluster
+  if (tid < G) {
+    int m = (int)(-2147483647 - 1);
+    for (int r = 0; r < C; ++r) m = max(m, *cluster.map_shared_rank(&cta_max[tid], r));
+    g_max[tid] = m;
+  }
+  unsigned long long vref = ~0ull;
+  for (int r = 0; r < C; ++r) {
+    const unsigned long long o = *cluster.map_shared_rank(&cta_vref, r);
+    vref = o < vref ? o : vref;
+  }
+  const int v_shift_ref = (int)(vref >> 32) - 128;
+  const int v_mul_ref = (int)(0xFFFFFFFFu - (unsigned)(vref & 0xFFFFFFFFull));
+  __syncthreads();
+
+  // ---- phase 2: exponentials, their sum, and the relative V scale of every key
+  {
+    long long lsum[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) lsum[g] = 0;
+    const int n_slots = ((my_pages + 1) >> 1) * 32;
+    for (int kl = tid; kl < n_slots; kl += kDecodeThreads) {
+      const bool valid = kl < my_keys;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        int e = 0;
+        if (valid) {
+          int x = sub_sat(sc[g * S + kl], g_max[g]);
+          x = max(x, -(1 << 30));
+          const int y = (int)(((long long)x * 94548LL) >> 16);
+          const int yi = y >> 16;
+          const int idx = (y & 0xFFFF) >> 6;
+          const int sh = max(0, min(31, 13 - yi));
+          e = __ldg(&g_exp2_attn_lut[idx]) >> sh;
+        }
+        sc[g * S + kl] = e;
+        lsum[g] += e;
+      }
+      unsigned r = 0;
+      if (valid) {
+        const int pg = kl >> 4, tok = kl & 15;
+        const int32_t* mt = p.meta + ((int64_t)pages[pg] * p.kv_heads + kh) * kMetaWords;
+        const int v_mul = __ldg(mt + 16 + tok);
+        const int v_shift = reinterpret_cast<const int8_t*>(mt + 36)[tok];
+        const int d = v_shift - v_shift_ref;
+        if (v_mul_ref > 0 && d < 32) {
+          const unsigned long long ratio = ((unsigned long long)(unsigned)v_mul << 15) / (unsigned)v_mul_ref;
+          r = (unsigned)(ratio >> d);
+          r = min(r, 65535u);
+        }
+      }
+      rel[kl] = (uint16_t)r;
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const long long s = warp_sum64(lsum[g]);
+      if (lane == 0) atomicAdd(&cta_sum[g], (unsigned long long)s);
+    }
+  }
+  cluster.sync();
+
+  // ---- exchange 2: total of the exponentials -> inv = (2^31 - 1) / max(1, total)
+  if (tid < G) {
+    unsigned long long tot = 0;
+    for (int r = 0; r < C; ++r) tot += *cluster.map_shared_rank(&cta_sum[tid], r);
+    if (tot < 1ull) tot = 1ull;
+    g_inv[tid] = (int)(2147483647ull / tot);
+  }
+  __syncthreads();
+
+  // ---- phase 3a: probabilities (Q0.15), folded with the relative V scale, as two byte limbs
+  {
+    const int n_slots = ((my_pages + 1) >> 1) * 32;
+    for (int kl = tid; kl < n_slots; kl += kDecodeThreads) {
+      const unsigned r = rel[kl];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const long long pr = ((long long)sc[g * S + kl] * (long long)g_inv[g]) >> 16;
+        const unsigned w = (unsigned)((pr * (long long)r + 16384) >> 15);
+        p_hi[g * S + kl] = (uint8_t)(w >> 8);
+        p_lo[g * S + kl] = (uint8_t)(w & 0xff);
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 3b: PV.  A warp takes one page; lane = d within each 32-wide quarter.
+  {
+    int acc_hi[G][4], acc_lo[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc_hi[g][i] = acc_lo[g][i] = 0;
+    for (int pg = warp; pg < my_pages; pg += kDecodeWarps) {
+      const int64_t chunk = (int64_t)pages[pg] * p.kv_heads + kh;
+      const int4* vr = reinterpret_cast<const int4*>(p.v_codes + chunk * (kD * kPage));
+      int4 vv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) vv[i] = __ldcs(vr + i * 32 + lane);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const uint4 ph = *reinterpret_cast<const uint4*>(p_hi + g * S + pg * 16);
+        const uint4 pl = *reinterpret_cast<const uint4*>(p_lo + g * S + pg * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          int h = acc_hi[g][i], l = acc_lo[g][i];
+          h = dp4a_su(vv[i].x, ph.x, h); l = dp4a_su(vv[i].x, pl.x, l);
+          h = dp4a_su(vv[i].y, ph.y, h); l = dp4a_su(vv[i].y, pl.y, l);
+          h = dp4a_su(vv[i].z, ph.z, h); l = dp4a_su(vv[i].z, pl.z, l);
+          h = dp4a_su(vv[i].w, ph.w, h); l = dp4a_su(vv[i].w, pl.w, l);
+          acc_hi[g][i] = h; acc_lo[g][i] = l;
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int v = acc_hi[g][i] * 256 + acc_lo[g][i];
+        if (v != 0) atomicAdd(&cta_acc[g][i * 32 + lane], v);
+      }
+  }
+  cluster.sync();
+
+  // ---- exchange 3: rank 0 sums the partial outputs and requantises
+  if (rank == 0) {
+    int outv[(G * kD + kDecodeThreads - 1) / kDecodeThreads];
+#pragma unroll
+    for (int it = 0; it < (G * kD + kDecodeThreads - 1) / kDecodeThreads; ++it) {
+      const int i = tid + it * kDecodeThreads;
+      int o = 0;
+      if (i < G * kD) {
+        long long a = 0;
+        for (int r = 0; r < C; ++r) a += *cluster.map_shared_rank(&cta_acc[0][0] + i, r);
+        if (L > 0) o = sat32(mul_shift64(a, (long long)v_mul_ref, v_shift_ref - 1));
+        const int g = i / kD;
+        if (p.out_q15) p.out_q15[((int64_t)b * p.q_heads + kh * G + g) * kD + (i % kD)] = o;
+        if (p.out_codes) atomicMax(&out_absmax_s[g], abs_wrap(o));
+      }
+      outv[it] = o;
+    }
+    if (p.out_codes) {
+      __syncthreads();
+#pragma unroll
+      for (int it = 0; it < (G * kD + kDecodeThreads - 1) / kDecodeThreads; ++it) {
+        const int i = tid + it * kDecodeThreads;
+        if (i < G * kD) {
+          const int g = i / kD;
+          const int m = max(1, out_absmax_s[g]);
+          p.out_codes[((int64_t)b * p.q_heads + kh * G + g) * kD + (i % kD)] =
+              (int8_t)quant_code(outv[it], __int2float_rn(m));
+          if ((i % kD) == 0) p.out_absmax[(int64_t)b * p.q_heads + kh * G + g] = m;
+        }
+      }
+    }
+  }
+  cluster.sync();  // nobody leaves while rank 0 still reads its shared memory
+}
+
+static size_t decode_smem_bytes(int G, int s_max) {
+  return (size_t)G * s_max * 6 + (size_t)s_max * 2 + (size_t)(s_max / 16) * 4;
+}
+
+template <int G>
+static int launch_decode(const DecodeParams& p, int batch, int cluster, cudaStream_t st) {
+  const size_t smem = decode_smem_bytes(G, p.s_max);
+  if (smem > 200 * 1024) {
+    set_error("attn_decode: max_kv_len=%d needs %zu bytes of shared memory per CTA; raise cluster", p.max_kv_len, smem);
+    return B200_E_UNSUPPORTED;
+  }
+  cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_error("attn_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    return B200_E_CUDA;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cluster, p.kv_heads, batch);
+  cfg.blockDim = dim3(kDecodeThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<G>, p);
+  if (e != cudaSuccess) {
+    set_error("attn_decode: launch: %s", cudaGetErrorString(e));
+    return B200_E_CUDA;
+  }
+  return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+static int store_common(bool quant, const void* k, int64_t k_pitch, const void* v, int64_t v_pitch,
+                        const int32_t* k_mul, const int32_t* k_shift, const int32_t* v_mul,
+                        const int32_t* v_shift, const int32_t* out_loc, int8_t* k_codes, int8_t* v_codes,
+                        int32_t* meta, int64_t tokens, int kv_heads, int64_t num_pages, cudaStream_t st,
+                        const char* name) {
+  B200_REQUIRE(k && v && out_loc && k_codes && v_codes && meta, B200_E_NULL, "%s: null pointer", name);
+  B200_REQUIRE(tokens >= 0 && kv_heads > 0 && num_pages > 0, B200_E_SHAPE,
+               "%s: tokens=%lld kv_heads=%d num_pages=%lld", name, (long long)tokens, kv_heads, (long long)num_pages);
+  B200_REQUIRE(aligned16(k_codes) && aligned16(v_codes) && aligned16(meta), B200_E_ALIGN,
+               "%s: pool buffers must be 16-byte aligned", name);
+  if (quant) {
+    B200_REQUIRE(aligned16(k) && aligned16(v) && k_pitch % 4 == 0 && v_pitch % 4 == 0, B200_E_ALIGN,
+                 "%s: k/v rows must be 16-byte aligned", name);
+    B200_REQUIRE(k_pitch >= (int64_t)kv_heads * kD && v_pitch >= (int64_t)kv_heads * kD, B200_E_SHAPE,
+                 "%s: row pitch smaller than kv_heads*128", name);
+  } else {
+    B200_REQUIRE(k_mul && k_shift && v_mul && v_shift, B200_E_NULL, "%s: null scale pointer", name);
+    B200_REQUIRE(((uintptr_t)k & 3u) == 0 && ((uintptr_t)v & 3u) == 0, B200_E_ALIGN, "%s: codes must be 4-byte aligned", name);
+  }
+  if (tokens == 0) return B200_OK;
+  const int64_t blocks = (tokens * kv_heads + 7) / 8;
+  B200_REQUIRE(blocks < (1ll << 31), B200_E_SHAPE, "%s: too many rows", name);
+  if (quant)
+    kv_store_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(k, k_pitch, v, v_pitch, nullptr, nullptr, nullptr, nullptr,
+                                                           out_loc, k_codes, v_codes, meta, tokens, kv_heads, num_pages);
+  else
+    kv_store_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(k, 0, v, 0, k_mul, k_shift, v_mul, v_shift, out_loc,
+                                                            k_codes, v_codes, meta, tokens, kv_heads, num_pages);
+  return check_launch(name);
+}
+
+extern "C" int b200_kv_store_q15(const int32_t* k, int64_t k_pitch, const int32_t* v, int64_t v_pitch,
+                                 const int32_t* out_loc, int8_t* k_codes, int8_t* v_codes, int32_t* meta,
+                                 int64_t tokens, int kv_heads, int64_t num_pages, b200_stream_t s) {
+  return store_common(true, k, k_pitch, v, v_pitch, nullptr, nullptr, nullptr, nullptr, out_loc, k_codes, v_codes,
+                      meta, tokens, kv_heads, num_pages, (cudaStream_t)s, "kv_store_q15");
+}
+
+extern "C" int b200_kv_store_codes(const int8_t* k8, const int8_t* v8, const int32_t* k_mul,
+                                   const int32_t* k_shift, const int32_t* v_mul, const int32_t* v_shift,
+                                   const int32_t* out_loc, int8_t* k_codes, int8_t* v_codes, int32_t* meta,
+                                   int64_t tokens, int kv_heads, int64_t num_pages, b200_stream_t s) {
+  return store_common(false, k8, 0, v8, 0, k_mul, k_shift, v_mul, v_shift, out_loc, k_codes, v_codes, meta, tokens,
+                      kv_heads, num_pages, (cudaStream_t)s, "kv_store_codes");
+}
+
+extern "C" int b200_attn_decode(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
+                                const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
+                                const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                                int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax, int batch,
+                                int q_heads, int kv_heads, int64_t num_pages, int max_kv_len, int cluster,
+                                b200_stream_t s) {
+  B200_REQUIRE(q && q_mul && q_shift && k_codes && v_codes && meta && page_table && kv_lens, B200_E_NULL,
+               "attn_decode: null pointer");
+  B200_REQUIRE((out_codes == nullptr) == (out_absmax == nullptr), B200_E_NULL,
+               "attn_decode: out_codes and out_absmax must be given together");
+  B200_REQUIRE(out_q15 || out_codes, B200_E_NULL, "attn_decode: no output requested");
+  B200_REQUIRE(batch >= 0 && batch <= 65535 && q_heads > 0 && kv_heads > 0 && kv_heads <= 65535 && num_pages > 0 &&
+                   max_kv_len > 0,
+               B200_E_SHAPE, "attn_decode: batch=%d q_heads=%d kv_heads=%d num_pages=%lld max_kv_len=%d", batch,
+               q_heads, kv_heads, (long long)num_pages, max_kv_len);
+  B200_REQUIRE(q_heads % kv_heads == 0, B200_E_SHAPE, "attn_decode: q_heads=%d not a multiple of kv_heads=%d", q_heads, kv_heads);
+  const int G = q_heads / kv_heads;
+  B200_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8, B200_E_UNSUPPORTED, "attn_decode: group size %d (1, 2, 4 or 8)", G);
+  const int max_pages = (max_kv_len + kPage - 1) / kPage;
+  B200_REQUIRE(table_pitch >= max_pages, B200_E_SHAPE, "attn_decode: table_pitch=%lld < pages for max_kv_len (%d)",
+               (long long)table_pitch, max_pages);
+  B200_REQUIRE(aligned16(q) && aligned16(k_codes) && aligned16(v_codes) && aligned16(meta), B200_E_ALIGN,
+               "attn_decode: q and pool buffers must be 16-byte aligned");
+  if (cluster == 0) {
+    cluster = max_pages >= 128 ? 4 : (max_pages >= 32 ? 2 : 1);
+    while (cluster < 8 && decode_smem_bytes(G, ((((max_pages + cluster - 1) / cluster) * kPage + 31) / 32) * 32) > 96 * 1024)
+      cluster *= 2;
+  }
+  B200_REQUIRE(cluster == 1 || cluster == 2 || cluster == 4 || cluster == 8, B200_E_UNSUPPORTED,
+               "attn_decode: cluster=%d (1, 2, 4 or 8)", cluster);
+  if (batch == 0) return B200_OK;
+  DecodeParams p;
+  p.q = q; p.q_mul = q_mul; p.q_shift = q_shift; p.k_codes = k_codes; p.v_codes = v_codes; p.meta = meta;
+  p.page_table = page_table; p.table_pitch = table_pitch; p.kv_lens = kv_lens; p.out_q15 = out_q15;
+  p.out_codes = out_codes; p.out_absmax = out_absmax; p.q_heads = q_heads; p.kv_heads = kv_heads;
+  p.num_pages = num_pages; p.max_kv_len = max_kv_len;
+  const int ppc = (max_pages + cluster - 1) / cluster;
+  p.s_max = ((ppc * kPage + 31) / 32) * 32;
+  cudaStream_t st = (cudaStream_t)s;
+  switch (G) {
+    case 1: return launch_decode<1>(p, batch, cluster, st);
+    case 2: return launch_decode<2>(p, batch, cluster, st);
+    case 4: return launch_decode<4>(p, batch, cluster, st);
+    default: return launch_decode<8>(p, batch, cluster, st);
+  }
+}

@@ -1,0 +1,149 @@
+// Shared device/host helpers for the integer-path kernels (sm_100a).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200int.h"
+
+namespace b200 {
+
+// ----------------------------------------------------------------------------- host side
+void set_error(const char* fmt, ...);
+int check_launch(const char* what);
+
+#define B200_REQUIRE(cond, code, ...)   \
+  do {                                  \
+    if (!(cond)) {                      \
+      ::b200::set_error(__VA_ARGS__);   \
+      return (code);                    \
+    }                                   \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// The 1024-entry tables live in luts.cuh; a translation unit that needs them on the device
+// includes that header (each gets its own copy, so no relocatable device code is needed).
+
+// ----------------------------------------------------------------------------- device side
+#define FULL_MASK 0xffffffffu
+
+__device__ __forceinline__ int sat32(long long v) {
+  return v > 2147483647LL ? 2147483647 : (v < -2147483648LL ? (int)(-2147483647 - 1) : (int)v);
+}
+
+// |x| with two's-complement wrap (|-2^31| stays -2^31), as the reference's where(x<0,-x,x).
+__device__ __forceinline__ int abs_wrap(int x) { return x < 0 ? (int)(0u - (unsigned)x) : x; }
+
+__device__ __forceinline__ int add_sat(int a, int b) {
+  int r;
+  asm("add.sat.s32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ int sub_sat(int a, int b) {
+  int r;
+  asm("sub.sat.s32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// Sign-dependent rounding shift by 15 of a 64-bit value: v>=0 ? (v+2^14)>>15 : (v-2^14)>>15.
+__device__ __forceinline__ long long rsr15(long long v) {
+  return (v >= 0 ? v + 16384 : v - 16384) >> 15;
+}
+
+// mul-shift of the attention / requant convention:
+//   s >= 0: (x*m + (s>0 ? 2^(s-1) : 0)) >> s ;  s < 0: (x*m) << -s.   64-bit wrap-around.
+__device__ __forceinline__ long long mul_shift64(long long x, long long m, int s) {
+  unsigned long long prod = (unsigned long long)x * (unsigned long long)m;
+  if (s >= 0) {
+    if (s == 0) return (long long)prod;
+    if (s >= 63) {
+      long long t = (long long)(prod + (1ull << 62));
+      return t < 0 ? -1 : 0;
+    }
+    return (long long)(prod + (1ull << (s - 1))) >> s;
+  }
+  int l = -s;
+  return l >= 64 ? 0 : (long long)(prod << l);
+}
+
+__device__ __forceinline__ int warp_max(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(FULL_MASK, v, o));
+  return v;
+}
+__device__ __forceinline__ long long warp_sum64(long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL_MASK, v, o);
+  return v;
+}
+
+// Block-wide reductions; `scratch` holds >= 33 elements; every thread gets the result.
+// Safe to call back to back with the same scratch.
+__device__ __forceinline__ int block_max(int v, int* scratch) {
+  v = warp_max(v);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (nw == 1) return v;
+  __syncthreads();
+  if (lane == 0) scratch[wid] = v;
+  __syncthreads();
+  int r = (lane < nw) ? scratch[lane] : (int)(-2147483647 - 1);
+  return warp_max(r);
+}
+__device__ __forceinline__ long long block_sum64(long long v, long long* scratch) {
+  v = warp_sum64(v);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (nw == 1) return v;
+  __syncthreads();
+  if (lane == 0) scratch[wid] = v;
+  __syncthreads();
+  long long r = (lane < nw) ? scratch[lane] : 0;
+  return warp_sum64(r);
+}
+
+// per_token_quant_int8_from_q15's arithmetic for one element: IEEE fp32 multiply, divide,
+// round-half-even, clamp.  `mf` = float(absmax).
+__device__ __forceinline__ int quant_code(int x, float mf) {
+  float q = __fdiv_rn(__fmul_rn(__int2float_rn(x), 127.0f), mf);
+  int r = __float2int_rn(q);
+  return max(-128, min(127, r));
+}
+__device__ __forceinline__ float quant_scale(float mf) { return __fdiv_rn(mf, 8323072.0f); }
+
+__device__ __forceinline__ unsigned pack4(int a, int b, int c, int d) {
+  return (unsigned)(a & 0xff) | ((unsigned)(b & 0xff) << 8) | ((unsigned)(c & 0xff) << 16) |
+         ((unsigned)(d & 0xff) << 24);
+}
+
+// Fixed-point RMSNorm scalars of one row (rmsnorm_int_only_v2.py:144-218 steps 1, 4).
+struct NormRow {
+  int p;         // MSB index of the row's absmax (0 for a zero row)
+  int zero;      // row is all zeros
+};
+__device__ __forceinline__ NormRow norm_row_from_absmax(int m) {
+  NormRow r;
+  r.zero = (m == 0);
+  r.p = r.zero ? 0 : (31 - __clz(m));
+  return r;
+}
+__device__ __forceinline__ int norm_normalised_sq(int v, int p) {
+  int n = ((int)((unsigned)v << (30 - p))) >> 16;
+  return (int)((unsigned)n * (unsigned)n);
+}
+// inverse_sqrt_q0_31 (rmsnorm_int_only_v2.py:89-117) of ms = ((S / H) >> 1) + 1.
+__device__ __forceinline__ int norm_inv_sqrt(long long S, int H, const int32_t* lut) {
+  int ms = (int)((S / H) >> 1) + 1;
+  if (ms <= 0) return 0;
+  int pos = 31 - __clz(ms);
+  int even = ((pos + 1) >> 1) << 1;
+  int xn = ((int)((unsigned)ms << (30 - even))) >> 21;
+  xn = max(0, min(1023, xn));
+  return (int)((unsigned)lut[xn] << (16 - (even >> 1)));
+}
+__device__ __forceinline__ int norm_apply(int v, int inv, int w, int p) {
+  long long a = (long long)v * (long long)inv;
+  long long b = (long long)((unsigned long long)a * (unsigned long long)(long long)w);
+  return sat32(b >> (p + 18));
+}
+
+}  // namespace b200

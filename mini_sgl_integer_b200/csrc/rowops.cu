@@ -1,0 +1,693 @@
+// Memory-bound row kernels of the integer path: Q15.16 conversion, fixed-point RMSNorm
+// (+ residual add, + per-token int8 quant), SiLU*up (+ blocked FWHT, + quant), FWHT,
+// q/k norm + RoPE + FWHT, per-token quant.  One row stays resident in registers between
+// its reductions, so every input element is read from HBM once.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "luts.cuh"
+
+namespace b200 {
+
+// ============================================================================ conversions
+template <typename SRC>
+__device__ __forceinline__ float load_as_f32(const SRC* p, int64_t i);
+template <>
+__device__ __forceinline__ float load_as_f32<float>(const float* p, int64_t i) { return p[i]; }
+template <>
+__device__ __forceinline__ float load_as_f32<uint16_t>(const uint16_t* p, int64_t i) {
+  return __uint_as_float(((unsigned)p[i]) << 16);
+}
+
+// to_fixed (q15_tensor.py:17-22): round-half-even of x*65536 in fp32; the convert saturates.
+template <typename SRC>
+__global__ void to_fixed_kernel(const SRC* __restrict__ x, int32_t* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    out[i] = __float2int_rn(__fmul_rn(load_as_f32<SRC>(x, i), 65536.0f));
+  }
+}
+
+// from_fixed (q15_tensor.py:25-27): fp32(x) / 65536, then the output dtype.
+template <bool BF16>
+__global__ void from_fixed_kernel(const int32_t* __restrict__ x, void* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float f = __fdiv_rn(__int2float_rn(x[i]), 65536.0f);
+    if (BF16) {
+      reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(f);
+    } else {
+      reinterpret_cast<float*>(out)[i] = f;
+    }
+  }
+}
+
+static int elementwise_grid(int64_t n, int threads) {
+  int64_t b = (n + threads - 1) / threads;
+  const int64_t cap = 148 * 16;
+  return (int)(b < cap ? (b < 1 ? 1 : b) : cap);
+}
+
+// ============================================================================ RMSNorm rows
+// One CTA per row; thread t owns int4 vectors t, t+T, ... (VPT of them).
+template <int VPT>
+__global__ void __launch_bounds__(1024)
+rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ res,
+                    const int32_t* __restrict__ w, int32_t* __restrict__ res_out,
+                    int32_t* __restrict__ norm_out, int8_t* __restrict__ codes,
+                    float* __restrict__ scale, int32_t* __restrict__ absmax, int H) {
+  __shared__ long long red64[33];
+  __shared__ int red32[33];
+  const int64_t row = blockIdx.x;
+  const int nvec = H >> 2;
+  const int4* xr = reinterpret_cast<const int4*>(x + row * H);
+  const int4* rr = res ? reinterpret_cast<const int4*>(res + row * H) : nullptr;
+  int4* ro = res ? reinterpret_cast<int4*>(res_out + row * H) : nullptr;
+
+  int4 v[VPT];
+  int m = 0;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    int4 a = make_int4(0, 0, 0, 0);
+    if (idx < nvec) {
+      a = __ldcs(xr + idx);
+      if (rr) {
+        int4 b = __ldcs(rr + idx);
+        a.x = (int)((unsigned)a.x + (unsigned)b.x);
+        a.y = (int)((unsigned)a.y + (unsigned)b.y);
+        a.z = (int)((unsigned)a.z + (unsigned)b.z);
+        a.w = (int)((unsigned)a.w + (unsigned)b.w);
+        ro[idx] = a;
+      }
+    }
+    v[i] = a;
+    m = max(max(m, abs_wrap(a.x)), max(abs_wrap(a.y), max(abs_wrap(a.z), abs_wrap(a.w))));
+  }
+  m = block_max(m, red32);
+  const NormRow nr = norm_row_from_absmax(m);
+
+  long long S = 0;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    S += (long long)norm_normalised_sq(v[i].x, nr.p) + (long long)norm_normalised_sq(v[i].y, nr.p) +
+         (long long)norm_normalised_sq(v[i].z, nr.p) + (long long)norm_normalised_sq(v[i].w, nr.p);
+  }
+  S = block_sum64(S, red64);
+  const int inv = norm_inv_sqrt(S, H, g_inv_sqrt_lut);
+
+  const int4* wr = reinterpret_cast<const int4*>(w);
+  int4* no = norm_out ? reinterpret_cast<int4*>(norm_out + row * H) : nullptr;
+  int m2 = 0;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nvec) {
+      const int4 ww = __ldg(wr + idx);
+      int4 o;
+      o.x = nr.zero ? 0 : norm_apply(v[i].x, inv, ww.x, nr.p);
+      o.y = nr.zero ? 0 : norm_apply(v[i].y, inv, ww.y, nr.p);
+      o.z = nr.zero ? 0 : norm_apply(v[i].z, inv, ww.z, nr.p);
+      o.w = nr.zero ? 0 : norm_apply(v[i].w, inv, ww.w, nr.p);
+      v[i] = o;
+      if (no) no[idx] = o;
+      m2 = max(max(m2, abs_wrap(o.x)), max(abs_wrap(o.y), max(abs_wrap(o.z), abs_wrap(o.w))));
+    }
+  }
+  if (codes == nullptr) return;
+  m2 = max(1, block_max(m2, red32));
+  const float mf = __int2float_rn(m2);
+  unsigned* co = reinterpret_cast<unsigned*>(codes + row * H);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nvec) {
+      co[idx] = pack4(quant_code(v[i].x, mf), quant_code(v[i].y, mf), quant_code(v[i].z, mf),
+                      quant_code(v[i].w, mf));
+    }
+  }
+  if (threadIdx.x == 0) {
+    scale[row] = quant_scale(mf);
+    absmax[row] = m2;
+  }
+}
+
+// Per-row quant only (per_token_quant_int8_from_q15), same row residency.
+template <int VPT>
+__global__ void __launch_bounds__(1024)
+quant_rows_kernel(const int32_t* __restrict__ x, int8_t* __restrict__ codes,
+                  float* __restrict__ scale, int32_t* __restrict__ absmax, int K) {
+  __shared__ int red32[33];
+  const int64_t row = blockIdx.x;
+  const int nvec = K >> 2;
+  const int4* xr = reinterpret_cast<const int4*>(x + row * K);
+  int4 v[VPT];
+  int m = 0;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    int4 a = make_int4(0, 0, 0, 0);
+    if (idx < nvec) a = __ldcs(xr + idx);
+    v[i] = a;
+    m = max(max(m, abs_wrap(a.x)), max(abs_wrap(a.y), max(abs_wrap(a.z), abs_wrap(a.w))));
+  }
+  m = max(1, block_max(m, red32));
+  const float mf = __int2float_rn(m);
+  unsigned* co = reinterpret_cast<unsigned*>(codes + row * K);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nvec) {
+      co[idx] = pack4(quant_code(v[i].x, mf), quant_code(v[i].y, mf), quant_code(v[i].z, mf),
+                      quant_code(v[i].w, mf));
+    }
+  }
+  if (threadIdx.x == 0) {
+    scale[row] = quant_scale(mf);
+    absmax[row] = m;
+  }
+}
+
+struct RowPlan {
+  int threads, vpt;
+};
+static bool plan_rows(int width, RowPlan* p) {
+  const int nvec = width >> 2;
+  if (nvec <= 256) {
+    p->threads = ((nvec + 31) / 32) * 32;
+    p->vpt = 1;
+    return true;
+  }
+  int vpt = (nvec + 255) / 256;
+  if (vpt <= 8) {
+    p->threads = 256;
+    p->vpt = vpt;
+    return true;
+  }
+  vpt = (nvec + 1023) / 1024;
+  if (vpt <= 8) {
+    p->threads = 1024;
+    p->vpt = vpt;
+    return true;
+  }
+  return false;
+}
+
+#define DISPATCH_VPT(vpt, CALL)   \
+  switch (vpt) {                  \
+    case 1: { constexpr int V = 1; CALL; } break; \
+    case 2: { constexpr int V = 2; CALL; } break; \
+    case 3: { constexpr int V = 3; CALL; } break; \
+    case 4: { constexpr int V = 4; CALL; } break; \
+    case 5: { constexpr int V = 5; CALL; } break; \
+    case 6: { constexpr int V = 6; CALL; } break; \
+    case 7: { constexpr int V = 7; CALL; } break; \
+    default: { constexpr int V = 8; CALL; } break; \
+  }
+
+// ============================================================================ SiLU * up
+// silu_and_mul_int_only_kernel's arithmetic (silu_and_mul_int_only.py:156-226) for one element.
+__device__ __forceinline__ int silu_mul_elem(int g, int u, const int32_t* __restrict__ lut) {
+  const unsigned ua = g > 0 ? (unsigned)g : (0u - (unsigned)g);         // |g| in [0, 2^31]
+  const long long prod = -(long long)((unsigned long long)ua * 94549ull);  // -|g| * log2e, Q30.32
+  const int yi = (int)(prod >> 32);                                      // (y >> 16), y = prod >> 16
+  const unsigned idx = ((unsigned)prod) >> 22;                           // ((y & 0xFFFF) >> 6)
+  const int shift = 13 - yi;                                             // >= 13
+  const unsigned e2 = (unsigned)lut[idx];
+  unsigned E = shift >= 32 ? 0u : (e2 >> shift);
+  E = min(E, 65536u);
+  const unsigned sneg = (E == 65536u) ? 32768u : (E << 16) / (65536u + E);
+  const unsigned sig = g > 0 ? 65536u - sneg : sneg;
+  const long long t = ((long long)g * (long long)sig) >> 16;
+  return sat32((t * (long long)u) >> 16);
+}
+
+// FWHT-128 of a block spread over an 8-lane group: each lane holds 16 values, index
+// i = e + 4*lane8 + 32*k for val[4*k + e] (e = 0..3 inside an int4, k = 0..3).
+// Stage order is the reference's (step 1, 2, 4, ... 64), with saturation at every stage.
+__device__ __forceinline__ void fwht128_group(int (&val)[16], int lane8) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {  // steps 1 and 2: inside each int4
+    int a = val[4 * k], b = val[4 * k + 1], c = val[4 * k + 2], d = val[4 * k + 3];
+    int a1 = add_sat(a, b), b1 = sub_sat(a, b), c1 = add_sat(c, d), d1 = sub_sat(c, d);
+    val[4 * k] = add_sat(a1, c1);
+    val[4 * k + 2] = sub_sat(a1, c1);
+    val[4 * k + 1] = add_sat(b1, d1);
+    val[4 * k + 3] = sub_sat(b1, d1);
+  }
+#pragma unroll
+  for (int bit = 0; bit < 3; ++bit) {  // steps 4, 8, 16: across the 8 lanes
+    const bool lower = ((lane8 >> bit) & 1) == 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int partner = __shfl_xor_sync(FULL_MASK, val[j], 1 << bit);
+      val[j] = lower ? add_sat(val[j], partner) : sub_sat(partner, val[j]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {  // steps 32 and 64: across the four int4 of a lane
+    int a = val[e], b = val[4 + e], c = val[8 + e], d = val[12 + e];
+    int a1 = add_sat(a, b), b1 = sub_sat(a, b), c1 = add_sat(c, d), d1 = sub_sat(c, d);
+    val[e] = add_sat(a1, c1);
+    val[8 + e] = sub_sat(a1, c1);
+    val[4 + e] = add_sat(b1, d1);
+    val[12 + e] = sub_sat(b1, d1);
+  }
+}
+
+__device__ __forceinline__ int fwht_scale(int y, int kq15) {
+  return sat32(rsr15((long long)y * (long long)kq15));
+}
+
+// One CTA per row.  Every 8-lane group owns ITER blocks of 128 outputs (block = group + it*ngroups).
+template <int ITER, bool FWHT, bool QUANT>
+__global__ void __launch_bounds__(512)
+silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_out,
+                 int8_t* __restrict__ codes, float* __restrict__ scale,
+                 int32_t* __restrict__ absmax, int I) {
+  __shared__ int32_t lut[1024];
+  __shared__ int red32[33];
+  for (int i = threadIdx.x; i < 1024; i += blockDim.x) lut[i] = g_exp2_silu_lut[i];
+  __syncthreads();
+
+  const int64_t row = blockIdx.x;
+  const int lane8 = threadIdx.x & 7;
+  const int group = threadIdx.x >> 3;
+  const int ngroups = blockDim.x >> 3;
+  const int nblocks = I >> 7;
+  const int32_t* gate = gate_up + row * 2 * (int64_t)I;
+  const int32_t* up = gate + I;
+
+  int val[ITER][16];
+  int m = 0;
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    const int b = group + it * ngroups;
+    const bool live = b < nblocks;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      int4 g = make_int4(0, 0, 0, 0), u = make_int4(0, 0, 0, 0);
+      if (live) {
+        const int off = b * 128 + k * 32 + lane8 * 4;
+        g = __ldcs(reinterpret_cast<const int4*>(gate + off));
+        u = __ldcs(reinterpret_cast<const int4*>(up + off));
+      }
+      val[it][4 * k + 0] = silu_mul_elem(g.x, u.x, lut);
+      val[it][4 * k + 1] = silu_mul_elem(g.y, u.y, lut);
+      val[it][4 * k + 2] = silu_mul_elem(g.z, u.z, lut);
+      val[it][4 * k + 3] = silu_mul_elem(g.w, u.w, lut);
+    }
+    if (FWHT) {
+      fwht128_group(val[it], lane8);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) val[it][j] = fwht_scale(val[it][j], 2896);
+    }
+    if (q15_out != nullptr && live) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int off = b * 128 + k * 32 + lane8 * 4;
+        *reinterpret_cast<int4*>(q15_out + row * (int64_t)I + off) =
+            make_int4(val[it][4 * k], val[it][4 * k + 1], val[it][4 * k + 2], val[it][4 * k + 3]);
+      }
+    }
+    if (QUANT) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) m = max(m, abs_wrap(val[it][j]));
+    }
+  }
+  if (!QUANT) return;
+  m = max(1, block_max(m, red32));
+  const float mf = __int2float_rn(m);
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    const int b = group + it * ngroups;
+    if (b < nblocks) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int off = b * 128 + k * 32 + lane8 * 4;
+        *reinterpret_cast<unsigned*>(codes + row * (int64_t)I + off) =
+            pack4(quant_code(val[it][4 * k], mf), quant_code(val[it][4 * k + 1], mf),
+                  quant_code(val[it][4 * k + 2], mf), quant_code(val[it][4 * k + 3], mf));
+      }
+    }
+  }
+  if (threadIdx.x == 0) {
+    scale[row] = quant_scale(mf);
+    absmax[row] = m;
+  }
+}
+
+// SiLU*up only, any inter that is a multiple of 4 (no rotation, no quant).
+__global__ void silu_simple_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ out,
+                                   int64_t rows, int I) {
+  __shared__ int32_t lut[1024];
+  for (int i = threadIdx.x; i < 1024; i += blockDim.x) lut[i] = g_exp2_silu_lut[i];
+  __syncthreads();
+  const int nvec = I >> 2;
+  const int64_t total = rows * nvec;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / nvec;
+    const int c = (int)(i - r * nvec);
+    const int4 g = *reinterpret_cast<const int4*>(gate_up + r * 2 * (int64_t)I + 4 * c);
+    const int4 u = *reinterpret_cast<const int4*>(gate_up + r * 2 * (int64_t)I + I + 4 * c);
+    *reinterpret_cast<int4*>(out + r * (int64_t)I + 4 * c) =
+        make_int4(silu_mul_elem(g.x, u.x, lut), silu_mul_elem(g.y, u.y, lut),
+                  silu_mul_elem(g.z, u.z, lut), silu_mul_elem(g.w, u.w, lut));
+  }
+}
+
+// ============================================================================ FWHT (standalone)
+// n == 128: an 8-lane group per row, four rows per warp and iteration.
+__global__ void __launch_bounds__(256)
+fwht128_rows_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ out, int64_t rows,
+                    int normalize) {
+  const int lane8 = threadIdx.x & 7;
+  const int sub = (threadIdx.x & 31) >> 3;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t base = warp * 4; base < rows; base += nwarps * 4) {  // warp-uniform trip count
+    const int64_t r = base + sub;
+    const bool live = r < rows;
+    int val[16];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      int4 a = make_int4(0, 0, 0, 0);
+      if (live) a = *reinterpret_cast<const int4*>(x + r * 128 + k * 32 + lane8 * 4);
+      val[4 * k] = a.x; val[4 * k + 1] = a.y; val[4 * k + 2] = a.z; val[4 * k + 3] = a.w;
+    }
+    fwht128_group(val, lane8);
+    if (normalize) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) val[j] = fwht_scale(val[j], 2896);
+    }
+    if (live) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        *reinterpret_cast<int4*>(out + r * 128 + k * 32 + lane8 * 4) =
+            make_int4(val[4 * k], val[4 * k + 1], val[4 * k + 2], val[4 * k + 3]);
+    }
+  }
+}
+
+// Any power-of-two n <= 1024: one CTA of n threads per row, ping-pong in shared memory.
+__global__ void fwht_generic_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ out,
+                                    int n, int normalize, int kq15) {
+  extern __shared__ int32_t buf[];  // 2 * n
+  const int64_t row = blockIdx.x;
+  const int i = threadIdx.x;
+  int32_t* src = buf;
+  int32_t* dst = buf + n;
+  src[i] = x[row * n + i];
+  __syncthreads();
+  for (int step = 1; step < n; step <<= 1) {
+    const int a = src[i], p = src[i ^ step];
+    dst[i] = (i & step) == 0 ? add_sat(a, p) : sub_sat(p, a);
+    __syncthreads();
+    int32_t* t = src; src = dst; dst = t;
+  }
+  int y = src[i];
+  if (normalize) y = fwht_scale(y, kq15);
+  out[row * n + i] = y;
+}
+
+// ============================================================================ q/k norm + RoPE + FWHT
+// One warp per (token, head) row of 128.  Lane l holds elements 2l, 2l+1, 64+2l, 64+2l+1 so
+// that the rotate-half pairs (j, j+64) sit in one thread.
+__global__ void __launch_bounds__(256)
+qk_rope_kernel(const int32_t* __restrict__ positions, const int32_t* __restrict__ q, int64_t q_pitch,
+               const int32_t* __restrict__ k, int64_t k_pitch, const int32_t* __restrict__ cos_sin,
+               int max_pos, const int32_t* __restrict__ q_norm_w, const int32_t* __restrict__ k_norm_w,
+               int32_t* __restrict__ q_out, int32_t* __restrict__ k_out, int64_t tokens, int q_heads,
+               int kv_heads, int with_fwht) {
+  const int lane = threadIdx.x & 31;
+  const int heads = q_heads + kv_heads;
+  const int64_t wid = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (wid >= tokens * heads) return;  // whole warps leave together
+  const int64_t t = wid / heads;
+  const int h = (int)(wid - t * heads);
+  const bool is_q = h < q_heads;
+  const int32_t* src = is_q ? q + t * q_pitch + (int64_t)h * 128
+                            : k + t * k_pitch + (int64_t)(h - q_heads) * 128;
+  int32_t* dst = is_q ? q_out + (t * q_heads + h) * 128 : k_out + (t * kv_heads + (h - q_heads)) * 128;
+  const int32_t* nw = is_q ? q_norm_w : k_norm_w;
+
+  int2 lo = *reinterpret_cast<const int2*>(src + 2 * lane);
+  int2 hi = *reinterpret_cast<const int2*>(src + 64 + 2 * lane);
+
+  if (nw != nullptr) {  // per-head fixed-point RMSNorm over the 128 values
+    int m = max(max(0, abs_wrap(lo.x)), max(abs_wrap(lo.y), max(abs_wrap(hi.x), abs_wrap(hi.y))));
+    m = warp_max(m);
+    const NormRow nr = norm_row_from_absmax(m);
+    long long S = (long long)norm_normalised_sq(lo.x, nr.p) + (long long)norm_normalised_sq(lo.y, nr.p) +
+                  (long long)norm_normalised_sq(hi.x, nr.p) + (long long)norm_normalised_sq(hi.y, nr.p);
+    S = warp_sum64(S);
+    const int inv = norm_inv_sqrt(S, 128, g_inv_sqrt_lut);
+    const int2 wl = *reinterpret_cast<const int2*>(nw + 2 * lane);
+    const int2 wh = *reinterpret_cast<const int2*>(nw + 64 + 2 * lane);
+    lo.x = nr.zero ? 0 : norm_apply(lo.x, inv, wl.x, nr.p);
+    lo.y = nr.zero ? 0 : norm_apply(lo.y, inv, wl.y, nr.p);
+    hi.x = nr.zero ? 0 : norm_apply(hi.x, inv, wh.x, nr.p);
+    hi.y = nr.zero ? 0 : norm_apply(hi.y, inv, wh.y, nr.p);
+  }
+
+  int pos = positions[t];
+  pos = max(0, min(max_pos - 1, pos));
+  const int2 c = *reinterpret_cast<const int2*>(cos_sin + (int64_t)pos * 128 + 2 * lane);
+  const int2 s = *reinterpret_cast<const int2*>(cos_sin + (int64_t)pos * 128 + 64 + 2 * lane);
+  int a0 = sat32(rsr15((long long)lo.x * c.x - (long long)hi.x * s.x));
+  int b0 = sat32(rsr15((long long)lo.x * s.x + (long long)hi.x * c.x));
+  int a1 = sat32(rsr15((long long)lo.y * c.y - (long long)hi.y * s.y));
+  int b1 = sat32(rsr15((long long)lo.y * s.y + (long long)hi.y * c.y));
+
+  if (with_fwht) {
+    // step 1: (2l, 2l+1) pairs
+    int t0 = add_sat(a0, a1), t1 = sub_sat(a0, a1), u0 = add_sat(b0, b1), u1 = sub_sat(b0, b1);
+    a0 = t0; a1 = t1; b0 = u0; b1 = u1;
+#pragma unroll
+    for (int bit = 0; bit < 5; ++bit) {  // steps 2..32: lane bits
+      const bool lower = ((lane >> bit) & 1) == 0;
+      int p;
+      p = __shfl_xor_sync(FULL_MASK, a0, 1 << bit); a0 = lower ? add_sat(a0, p) : sub_sat(p, a0);
+      p = __shfl_xor_sync(FULL_MASK, a1, 1 << bit); a1 = lower ? add_sat(a1, p) : sub_sat(p, a1);
+      p = __shfl_xor_sync(FULL_MASK, b0, 1 << bit); b0 = lower ? add_sat(b0, p) : sub_sat(p, b0);
+      p = __shfl_xor_sync(FULL_MASK, b1, 1 << bit); b1 = lower ? add_sat(b1, p) : sub_sat(p, b1);
+    }
+    // step 64: (j, j+64)
+    t0 = add_sat(a0, b0); u0 = sub_sat(a0, b0); t1 = add_sat(a1, b1); u1 = sub_sat(a1, b1);
+    a0 = fwht_scale(t0, 2896); b0 = fwht_scale(u0, 2896);
+    a1 = fwht_scale(t1, 2896); b1 = fwht_scale(u1, 2896);
+  }
+  *reinterpret_cast<int2*>(dst + 2 * lane) = make_int2(a0, a1);
+  *reinterpret_cast<int2*>(dst + 64 + 2 * lane) = make_int2(b0, b1);
+}
+
+// ============================================================================ absmax -> (mul, shift)
+__device__ __forceinline__ void absmax_to_ms(int m, int* mul, int* shift) {
+  m = max(m, 1);
+  const int p = 31 - __clz(m);
+  int k = 37 - p;
+  unsigned long long v = (((unsigned long long)m << k) + 63ull) / 127ull;
+  if (v >= (1ull << 31)) {
+    k -= 1;
+    v = (((unsigned long long)m << k) + 63ull) / 127ull;
+  }
+  *mul = (int)v;
+  *shift = k + 16;
+}
+
+__global__ void absmax_to_ms_kernel(const int32_t* __restrict__ m, int32_t* __restrict__ mul,
+                                    int32_t* __restrict__ shift, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int a, b;
+    absmax_to_ms(m[i], &a, &b);
+    mul[i] = a;
+    shift[i] = b;
+  }
+}
+
+}  // namespace b200
+
+// ================================================================================ C ABI
+using namespace b200;
+
+extern "C" int b200_to_fixed_f32(const float* x, int32_t* out, int64_t n, b200_stream_t s) {
+  B200_REQUIRE(x && out, B200_E_NULL, "to_fixed_f32: null pointer");
+  B200_REQUIRE(n >= 0, B200_E_SHAPE, "to_fixed_f32: n=%lld", (long long)n);
+  if (n == 0) return B200_OK;
+  to_fixed_kernel<float><<<elementwise_grid(n, 256), 256, 0, (cudaStream_t)s>>>(x, out, n);
+  return check_launch("to_fixed_f32");
+}
+extern "C" int b200_to_fixed_bf16(const uint16_t* x, int32_t* out, int64_t n, b200_stream_t s) {
+  B200_REQUIRE(x && out, B200_E_NULL, "to_fixed_bf16: null pointer");
+  B200_REQUIRE(n >= 0, B200_E_SHAPE, "to_fixed_bf16: n=%lld", (long long)n);
+  if (n == 0) return B200_OK;
+  to_fixed_kernel<uint16_t><<<elementwise_grid(n, 256), 256, 0, (cudaStream_t)s>>>(x, out, n);
+  return check_launch("to_fixed_bf16");
+}
+extern "C" int b200_from_fixed_f32(const int32_t* x, float* out, int64_t n, b200_stream_t s) {
+  B200_REQUIRE(x && out, B200_E_NULL, "from_fixed_f32: null pointer");
+  B200_REQUIRE(n >= 0, B200_E_SHAPE, "from_fixed_f32: n=%lld", (long long)n);
+  if (n == 0) return B200_OK;
+  from_fixed_kernel<false><<<elementwise_grid(n, 256), 256, 0, (cudaStream_t)s>>>(x, out, n);
+  return check_launch("from_fixed_f32");
+}
+extern "C" int b200_from_fixed_bf16(const int32_t* x, uint16_t* out, int64_t n, b200_stream_t s) {
+  B200_REQUIRE(x && out, B200_E_NULL, "from_fixed_bf16: null pointer");
+  B200_REQUIRE(n >= 0, B200_E_SHAPE, "from_fixed_bf16: n=%lld", (long long)n);
+  if (n == 0) return B200_OK;
+  from_fixed_kernel<true><<<elementwise_grid(n, 256), 256, 0, (cudaStream_t)s>>>(x, out, n);
+  return check_launch("from_fixed_bf16");
+}
+
+extern "C" int b200_rmsnorm_q15(const int32_t* x, const int32_t* residual, const int32_t* weight,
+                                int32_t* residual_out, int32_t* norm_out, int8_t* codes,
+                                float* scale, int32_t* absmax, int64_t rows, int hidden,
+                                b200_stream_t s) {
+  B200_REQUIRE(x && weight, B200_E_NULL, "rmsnorm_q15: x or weight is null");
+  B200_REQUIRE((residual == nullptr) == (residual_out == nullptr), B200_E_NULL,
+               "rmsnorm_q15: residual and residual_out must be given together");
+  const bool q = codes != nullptr;
+  B200_REQUIRE(q == (scale != nullptr) && q == (absmax != nullptr), B200_E_NULL,
+               "rmsnorm_q15: codes, scale and absmax must be given together");
+  B200_REQUIRE(norm_out || q, B200_E_NULL, "rmsnorm_q15: no output requested");
+  B200_REQUIRE(rows >= 0 && rows < (1ll << 31) && hidden > 0, B200_E_SHAPE,
+               "rmsnorm_q15: rows=%lld hidden=%d", (long long)rows, hidden);
+  B200_REQUIRE(hidden % 4 == 0, B200_E_UNSUPPORTED, "rmsnorm_q15: hidden=%d is not a multiple of 4", hidden);
+  RowPlan p;
+  B200_REQUIRE(plan_rows(hidden, &p), B200_E_UNSUPPORTED, "rmsnorm_q15: hidden=%d exceeds 32768", hidden);
+  B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(residual) && aligned16(residual_out) &&
+                   aligned16(norm_out) && ((uintptr_t)codes & 3u) == 0,
+               B200_E_ALIGN, "rmsnorm_q15: int32 buffers must be 16-byte aligned (codes 4-byte)");
+  if (rows == 0) return B200_OK;
+  DISPATCH_VPT(p.vpt, (rmsnorm_rows_kernel<V><<<(unsigned)rows, p.threads, 0, (cudaStream_t)s>>>(
+                          x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
+  return check_launch("rmsnorm_q15");
+}
+
+extern "C" int b200_per_token_quant_q15(const int32_t* x, int8_t* codes, float* scale,
+                                        int32_t* absmax, int64_t rows, int k, b200_stream_t s) {
+  B200_REQUIRE(x && codes && scale && absmax, B200_E_NULL, "per_token_quant_q15: null pointer");
+  B200_REQUIRE(rows >= 0 && rows < (1ll << 31) && k > 0, B200_E_SHAPE,
+               "per_token_quant_q15: rows=%lld k=%d", (long long)rows, k);
+  B200_REQUIRE(k % 4 == 0, B200_E_UNSUPPORTED, "per_token_quant_q15: k=%d is not a multiple of 4", k);
+  RowPlan p;
+  B200_REQUIRE(plan_rows(k, &p), B200_E_UNSUPPORTED, "per_token_quant_q15: k=%d exceeds 32768", k);
+  B200_REQUIRE(aligned16(x) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN,
+               "per_token_quant_q15: x must be 16-byte aligned, codes 4-byte");
+  if (rows == 0) return B200_OK;
+  DISPATCH_VPT(p.vpt, (quant_rows_kernel<V><<<(unsigned)rows, p.threads, 0, (cudaStream_t)s>>>(
+                          x, codes, scale, absmax, k)));
+  return check_launch("per_token_quant_q15");
+}
+
+template <int ITER>
+static void launch_silu(const int32_t* gu, int32_t* q15, int8_t* codes, float* scale, int32_t* absmax,
+                        int64_t rows, int inter, bool fwht, int threads, cudaStream_t st) {
+  const bool quant = codes != nullptr;
+  if (fwht && quant)
+    silu_rows_kernel<ITER, true, true><<<(unsigned)rows, threads, 0, st>>>(gu, q15, codes, scale, absmax, inter);
+  else if (fwht)
+    silu_rows_kernel<ITER, true, false><<<(unsigned)rows, threads, 0, st>>>(gu, q15, codes, scale, absmax, inter);
+  else if (quant)
+    silu_rows_kernel<ITER, false, true><<<(unsigned)rows, threads, 0, st>>>(gu, q15, codes, scale, absmax, inter);
+  else
+    silu_rows_kernel<ITER, false, false><<<(unsigned)rows, threads, 0, st>>>(gu, q15, codes, scale, absmax, inter);
+}
+
+extern "C" int b200_silu_mul_q15(const int32_t* gate_up, int32_t* q15_out, int8_t* codes, float* scale,
+                                 int32_t* absmax, int64_t rows, int inter, int fwht_block,
+                                 b200_stream_t s) {
+  B200_REQUIRE(gate_up, B200_E_NULL, "silu_mul_q15: gate_up is null");
+  const bool q = codes != nullptr;
+  B200_REQUIRE(q == (scale != nullptr) && q == (absmax != nullptr), B200_E_NULL,
+               "silu_mul_q15: codes, scale and absmax must be given together");
+  B200_REQUIRE(q15_out || q, B200_E_NULL, "silu_mul_q15: no output requested");
+  B200_REQUIRE(rows >= 0 && rows < (1ll << 31) && inter > 0, B200_E_SHAPE,
+               "silu_mul_q15: rows=%lld inter=%d", (long long)rows, inter);
+  B200_REQUIRE(fwht_block == 0 || fwht_block == 128, B200_E_UNSUPPORTED,
+               "silu_mul_q15: fwht_block=%d (0 or 128 supported)", fwht_block);
+  B200_REQUIRE(inter % 4 == 0 && inter <= 32768, B200_E_UNSUPPORTED,
+               "silu_mul_q15: inter=%d must be a multiple of 4 and at most 32768", inter);
+  B200_REQUIRE(aligned16(gate_up) && aligned16(q15_out) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN,
+               "silu_mul_q15: int32 buffers must be 16-byte aligned (codes 4-byte)");
+  if (rows == 0) return B200_OK;
+  cudaStream_t st = (cudaStream_t)s;
+  if (inter % 128 != 0) {
+    B200_REQUIRE(fwht_block == 0 && !q, B200_E_UNSUPPORTED,
+                 "silu_mul_q15: inter=%d must be a multiple of 128 for the rotation or the quant", inter);
+    silu_simple_kernel<<<elementwise_grid(rows * (inter / 4), 256), 256, 0, st>>>(gate_up, q15_out, rows, inter);
+    return check_launch("silu_mul_q15");
+  }
+  const int nblocks = inter / 128;
+  int iter = 4;
+  for (int c = 1; c <= 4; c *= 2) {
+    if (((nblocks + c - 1) / c) * 8 <= 512) { iter = c; break; }
+  }
+  const int ngroups = (nblocks + iter - 1) / iter;
+  const int threads = ((ngroups * 8 + 31) / 32) * 32;
+  B200_REQUIRE(threads <= 512, B200_E_UNSUPPORTED, "silu_mul_q15: inter=%d too wide", inter);
+  const bool fw = fwht_block == 128;
+  if (iter == 1) launch_silu<1>(gate_up, q15_out, codes, scale, absmax, rows, inter, fw, threads, st);
+  else if (iter == 2) launch_silu<2>(gate_up, q15_out, codes, scale, absmax, rows, inter, fw, threads, st);
+  else launch_silu<4>(gate_up, q15_out, codes, scale, absmax, rows, inter, fw, threads, st);
+  return check_launch("silu_mul_q15");
+}
+
+extern "C" int b200_fwht_q15(const int32_t* x, int32_t* out, int64_t rows, int n, int normalize,
+                             b200_stream_t s) {
+  B200_REQUIRE(x && out, B200_E_NULL, "fwht_q15: null pointer");
+  B200_REQUIRE(rows >= 0 && rows < (1ll << 31), B200_E_SHAPE, "fwht_q15: rows=%lld", (long long)rows);
+  B200_REQUIRE(n >= 2 && (n & (n - 1)) == 0, B200_E_SHAPE, "fwht_q15: n=%d is not a power of two >= 2", n);
+  B200_REQUIRE(n <= 1024, B200_E_UNSUPPORTED, "fwht_q15: n=%d exceeds 1024", n);
+  if (rows == 0) return B200_OK;
+  cudaStream_t st = (cudaStream_t)s;
+  if (n == 128 && aligned16(x) && aligned16(out)) {
+    int64_t blocks = (rows + 31) / 32;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    fwht128_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, out, rows, normalize);
+  } else {
+    // round(2^15 / sqrt(n)), as the reference computes it in double precision
+    int log2n = 0;
+    while ((1 << log2n) < n) ++log2n;
+    const int kq15 = (log2n % 2 == 0) ? (32768 >> (log2n / 2))
+                                      : (int)(32768.0 / __builtin_sqrt((double)n) + 0.5);
+    fwht_generic_kernel<<<(unsigned)rows, n, 2 * n * sizeof(int32_t), st>>>(x, out, n, normalize, kq15);
+  }
+  return check_launch("fwht_q15");
+}
+
+extern "C" int b200_qk_rope_q15(const int32_t* positions, const int32_t* q, int64_t q_pitch,
+                                const int32_t* k, int64_t k_pitch, const int32_t* cos_sin, int max_pos,
+                                const int32_t* q_norm_w, const int32_t* k_norm_w, int32_t* q_out,
+                                int32_t* k_out, int64_t tokens, int q_heads, int kv_heads,
+                                int with_fwht, b200_stream_t s) {
+  B200_REQUIRE(positions && q && k && cos_sin && q_out && k_out, B200_E_NULL, "qk_rope_q15: null pointer");
+  B200_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && max_pos > 0, B200_E_SHAPE,
+               "qk_rope_q15: tokens=%lld q_heads=%d kv_heads=%d max_pos=%d", (long long)tokens, q_heads,
+               kv_heads, max_pos);
+  B200_REQUIRE(q_pitch >= (int64_t)q_heads * 128 && k_pitch >= (int64_t)kv_heads * 128, B200_E_SHAPE,
+               "qk_rope_q15: row pitch smaller than heads*128");
+  auto a8 = [](const void* p) { return ((uintptr_t)p & 7u) == 0; };
+  B200_REQUIRE(a8(q) && a8(k) && a8(cos_sin) && a8(q_out) && a8(k_out) && a8(q_norm_w) && a8(k_norm_w) &&
+                   q_pitch % 2 == 0 && k_pitch % 2 == 0,
+               B200_E_ALIGN, "qk_rope_q15: buffers must be 8-byte aligned and pitches even");
+  if (tokens == 0) return B200_OK;
+  const int64_t warps = tokens * (q_heads + kv_heads);
+  const int64_t blocks = (warps + 7) / 8;
+  B200_REQUIRE(blocks < (1ll << 31), B200_E_SHAPE, "qk_rope_q15: too many rows");
+  qk_rope_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)s>>>(positions, q, q_pitch, k, k_pitch, cos_sin,
+                                                               max_pos, q_norm_w, k_norm_w, q_out, k_out,
+                                                               tokens, q_heads, kv_heads, with_fwht);
+  return check_launch("qk_rope_q15");
+}
+
+extern "C" int b200_absmax_to_mul_shift(const int32_t* absmax, int32_t* mul, int32_t* shift, int64_t n,
+                                        b200_stream_t s) {
+  B200_REQUIRE(absmax && mul && shift, B200_E_NULL, "absmax_to_mul_shift: null pointer");
+  B200_REQUIRE(n >= 0, B200_E_SHAPE, "absmax_to_mul_shift: n=%lld", (long long)n);
+  if (n == 0) return B200_OK;
+  absmax_to_ms_kernel<<<elementwise_grid(n, 256), 256, 0, (cudaStream_t)s>>>(absmax, mul, shift, n);
+  return check_launch("absmax_to_mul_shift");
+}

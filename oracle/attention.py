@@ -25,7 +25,8 @@ queries (query i may see keys 0 .. L-n_q+i), query head h, KV head h // group:
   inv     = (2**31 - 1) // max(1, sum_j e_j) ;  p_j = (e_j * inv) >> 16   (Q0.15)
   V reference scale of the call = the (v_mul, v_shift) with the smallest shift,
   then the largest multiplier, over all L keys of the sequence and KV head
-  r_j     = ((v_mul_j << 15) // v_mul_ref) >> (v_shift_j - v_shift_ref)   (Q0.15, <= 32768)
+  r_j     = min(65535, ((v_mul_j << 15) // v_mul_ref) >> (v_shift_j - v_shift_ref))   (Q0.15; <= 32768
+            for multipliers normalised to [2**30, 2**31))
   w_j     = (p_j * r_j + 2**14) >> 15
   acc[d]  = sum_j w_j * v_j[d]
   out[d]  = sat32(mul_shift(acc[d], v_mul_ref, v_shift_ref - 1))   (Q15.16)
@@ -146,10 +147,10 @@ def absmax_to_mul_shift(m):
       p = msb(m); k = 37 - p; mul = ((m << k) + 63) // 127
       if mul >= 2**31: k -= 1 and recompute;  shift = k + 16
     """
-    m = np.asarray(m, dtype=np.int64)
     from .fixed_point import msb
 
-    p = msb(np.maximum(m, 1)).astype(np.int64)
+    m = np.maximum(np.asarray(m, dtype=np.int64), 1)
+    p = msb(m).astype(np.int64)
     k = 37 - p
     mul = ((m << k) + 63) // 127
     over = mul >= (1 << 31)
@@ -232,7 +233,7 @@ def v_relative_q15(v_mul, v_shift, m_ref: int, s_ref: int) -> np.ndarray:
     if m_ref <= 0:
         return np.zeros_like(d)
     ratio = (v_mul.astype(np.int64) << 15) // m_ref
-    return np.where(d >= 32, 0, ratio >> np.minimum(d, 31))
+    return np.minimum(np.where(d >= 32, 0, ratio >> np.minimum(d, 31)), 65535)
 
 
 def sequence_attention(q, q_mul, q_shift, k, v, k_mul, k_shift, v_mul, v_shift):

@@ -1,0 +1,163 @@
+"""int8 paged KV store + decode attention on CUDA vs the CPU oracle (bit-exact)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as oattn
+from oracle import fixed_point as ofp
+from tests.attn_util import device_pool, make_case
+
+pytestmark = pytest.mark.gpu
+
+
+def d(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def eq(a, b):
+    a, b = np.asarray(a), np.asarray(b)
+    assert a.shape == b.shape and a.dtype == b.dtype, (a.shape, b.shape, a.dtype, b.dtype)
+    if not np.array_equal(a, b):
+        bad = np.argwhere(a != b)
+        raise AssertionError(f"{len(bad)} mismatches of {a.size}, first at {bad[0]}: {a[tuple(bad[0])]} vs {b[tuple(bad[0])]}")
+
+
+def run_decode(case, pool, max_kv_len, cluster=0, **kw):
+    from mini_sgl_integer_b200.attention import decode_attention_int8_paged
+    return decode_attention_int8_paged(d(case["q8"]), d(case["qm"]), d(case["qs"]), pool, 0, d(case["table"]),
+                                       d(case["kv_lens"]), max_kv_len, cluster=cluster, **kw)
+
+
+def oracle_decode(case):
+    B = len(case["kv_lens"])
+    return oattn.paged_attention(case["q8"], case["qm"], case["qs"], case["pool"], case["tables"],
+                                 case["kv_lens"], [1] * B)
+
+
+def test_store_codes_layout_matches_oracle_pool():
+    case = make_case(1, [5, 16, 17, 40], 8, 2, 32)
+    pool = device_pool(case, 32, 2)
+    eq(pool.k_cache(0).cpu().numpy(), case["pool"].k_codes)
+    eq(pool.v_cache(0).cpu().numpy(), case["pool"].v_codes)
+    eq(pool.meta(0).cpu().numpy(), case["pool"].meta)
+
+
+def test_store_q15_quantises_like_oracle():
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    rng = np.random.default_rng(4)
+    T, H, P = 37, 4, 8
+    qkv = rng.integers(-(2**21), 2**21, (T, (8 + 2 * H) * 128)).astype(np.int32)
+    qkv[3, 8 * 128: 9 * 128] = 0                                   # an all-zero K head row
+    k, v = qkv[:, 8 * 128:(8 + H) * 128], qkv[:, (8 + H) * 128:]
+    loc = rng.permutation(P * 16)[:T].astype(np.int32)
+    ref = oattn.PagedKV(P, H, 128)
+    ref.store_q15(loc, k, v)
+    pool = Int8PagedKVCache(H, 2, 128, P, "cuda")
+    dq = d(qkv)
+    pool.store_kv(dq[:, 8 * 128:(8 + H) * 128], dq[:, (8 + H) * 128:], d(loc), 1)   # strided views, layer 1
+    eq(pool.k_cache(1).cpu().numpy(), ref.k_codes)
+    eq(pool.v_cache(1).cpu().numpy(), ref.v_codes)
+    eq(pool.meta(1).cpu().numpy(), ref.meta)
+    assert int(pool.k_cache(0).abs().max()) == 0                  # the other layer is untouched
+
+
+@pytest.mark.parametrize("q_heads,kv_heads", [(2, 2), (4, 2), (8, 2), (16, 2), (32, 8)])
+@pytest.mark.parametrize("cluster", [1, 2, 4, 8])
+def test_decode_vs_oracle(q_heads, kv_heads, cluster):
+    lens = [1, 15, 16, 17, 31, 33, 64, 100, 257, 640]
+    case = make_case(q_heads * 10 + cluster, lens, q_heads, kv_heads, 128)
+    pool = device_pool(case, 128, kv_heads)
+    want = oracle_decode(case)
+    got, codes, absmax = run_decode(case, pool, 640, cluster, out_q15=True, out_int8=True)
+    eq(got.cpu().numpy(), want)
+    wc, wm = oattn.quant_heads_int8(want)
+    eq(codes.cpu().numpy(), wc); eq(absmax.cpu().numpy(), wm)
+    assert np.abs(want).max() > 0
+
+
+def test_decode_auto_cluster_long_context_and_clamp():
+    lens = [4096, 3000, 2049, 512, 7]
+    case = make_case(77, lens, 8, 2, 640)
+    pool = device_pool(case, 640, 2)
+    want = oracle_decode(case)
+    eq(run_decode(case, pool, 4096).cpu().numpy(), want)
+    eq(run_decode(case, pool, 8192, cluster=8).cpu().numpy(), want)   # larger bound, same result
+    codes, absmax = run_decode(case, pool, 4096, out_q15=False, out_int8=True)
+    wc, wm = oattn.quant_heads_int8(want)
+    eq(codes.cpu().numpy(), wc); eq(absmax.cpu().numpy(), wm)
+
+
+def test_decode_zero_length_sequences_give_zero():
+    case = make_case(9, [0, 20, 0], 4, 2, 8)
+    pool = device_pool(case, 8, 2)
+    got = run_decode(case, pool, 32, cluster=2).cpu().numpy()
+    eq(got, oracle_decode(case))
+    assert not got[0].any() and not got[2].any() and got[1].any()
+
+
+def test_decode_wide_shift_spread_and_uniform_scales():
+    rng = np.random.default_rng(5)
+    case = make_case(21, [200, 90], 8, 2, 32)
+    # push a few V shifts far away from the reference scale (relative scale underflows to 0)
+    case["vs"][rng.integers(0, 290, 40)] += 20
+    case["pool"].store_codes(case["loc"], case["k8"], case["v8"], case["km"], case["ks"], case["vm"], case["vs"])
+    pool = device_pool(case, 32, 2)
+    eq(run_decode(case, pool, 256, cluster=2).cpu().numpy(), oracle_decode(case))
+    uni = make_case(22, [48, 200], 4, 2, 32, uniform=True)
+    pool = device_pool(uni, 32, 2)
+    eq(run_decode(uni, pool, 256, cluster=1).cpu().numpy(), oracle_decode(uni))
+
+
+def test_decode_reduces_to_reference_prefill_row(golden):
+    """Uniform scales: decode over L keys == row L-1 of int8_context_attention_fwd (reference golden)."""
+    ms = golden["attn_ms"]
+    q, k, v = golden["attn_q"], golden["attn_k"], golden["attn_v"]
+    ref = oattn.context_attention(q, k, v, ms[0], ms[1], ms[2], [0, 16], [16, 32], True)
+    assert np.array_equal(oattn.q15_to_bf16_bits(ref), golden["attn_out_bf16_bits"])
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache, decode_attention_int8_paged
+    pool = Int8PagedKVCache(2, 1, 128, 8, "cuda")
+    pages = {0: [5], 1: [7, 2]}
+    table = np.zeros((2, 2), dtype=np.int32)
+    for b, (st, L) in enumerate(((0, 16), (16, 32))):
+        table[b, : len(pages[b])] = pages[b]
+        loc = np.concatenate([np.arange(16) + 16 * p for p in pages[b]])[:L].astype(np.int32)
+        full = lambda val: torch.full((L, 2), int(val), dtype=torch.int32, device="cuda")
+        pool.store_codes(d(k[st:st + L]), d(v[st:st + L]), full(ms[1][0]), full(ms[1][1]), full(ms[2][0]),
+                         full(ms[2][1]), d(loc), 0)
+    q_last = np.stack([q[15], q[47]])
+    qm = np.full((2, 4), ms[0][0], dtype=np.int32); qs = np.full((2, 4), ms[0][1], dtype=np.int32)
+    got = decode_attention_int8_paged(d(q_last), d(qm), d(qs), pool, 0, d(table),
+                                      d(np.array([16, 32], dtype=np.int32)), 32, cluster=2).cpu().numpy()
+    eq(got.astype(np.int64), np.stack([ref[15], ref[47]]))
+    bits = oattn.q15_to_bf16_bits(got.astype(np.int64))
+    eq(bits, np.stack([golden["attn_out_bf16_bits"][15], golden["attn_out_bf16_bits"][47]]))
+
+
+def test_decode_headline_shape_sample_and_invariants():
+    """Batch 64, 32/8 heads, contexts U[512,4096], 200k-page pool: oracle on a sample of sequences,
+    and page-permutation invariance (a size-independent property) on all of them."""
+    rng = np.random.default_rng(0)
+    lens = rng.integers(512, 4097, 64).tolist()
+    P = 200_000
+    case = make_case(0, lens, 32, 8, P)
+    pool = device_pool(case, P, 8)
+    got = run_decode(case, pool, 4096).cpu().numpy()
+    sample = [0, 7, 13, 21, 34, 42, 55, 63]
+    sub = oattn.paged_attention(case["q8"][sample], case["qm"][sample], case["qs"][sample], case["pool"],
+                                [case["tables"][i] for i in sample], case["kv_lens"][sample], [1] * len(sample))
+    eq(got[sample], sub)
+    # same tokens placed on other pages of the pool: identical output
+    case2 = make_case(0, lens, 32, 8, P)
+    perm = np.random.default_rng(123).permutation(P)
+    t2 = [perm[t] for t in case2["tables"]]
+    loc2 = np.concatenate([(pg[:, None] * 16 + np.arange(16)[None, :]).reshape(-1)[:l] for pg, l in zip(t2, lens)])
+    case2["loc"] = loc2.astype(np.int32)
+    table2 = np.zeros_like(case2["table"])
+    for b, pg in enumerate(t2):
+        table2[b, : len(pg)] = pg
+    case2["table"] = table2
+    pool2 = device_pool(case2, P, 8)
+    got2 = run_decode(case2, pool2, 4096, cluster=8).cpu().numpy()
+    eq(got2, got)
