@@ -83,7 +83,9 @@ def test_decode_auto_cluster_long_context_and_clamp():
     pool = device_pool(case, 640, 2)
     want = oracle_decode(case)
     eq(run_decode(case, pool, 4096).cpu().numpy(), want)
-    eq(run_decode(case, pool, 8192, cluster=8).cpu().numpy(), want)   # larger bound, same result
+    wide = dict(case)
+    wide["table"] = np.pad(case["table"], ((0, 0), (0, 512 - case["table"].shape[1])))
+    eq(run_decode(wide, pool, 8192, cluster=8).cpu().numpy(), want)   # larger bound, same result
     codes, absmax = run_decode(case, pool, 4096, out_q15=False, out_int8=True)
     wc, wm = oattn.quant_heads_int8(want)
     eq(codes.cpu().numpy(), wc); eq(absmax.cpu().numpy(), wm)
