@@ -111,10 +111,13 @@ B200_API int b200_absmax_to_mul_shift(const int32_t* absmax, int32_t* mul, int32
                              b200_stream_t s);
 
 /* ---- int8 paged KV pool, one layer:
- *   k_codes int8 [pages, kv_heads, 16, 128]; v_codes int8 [pages, kv_heads, 128, 16]
- *   (transposed inside a page); meta int32 [pages, kv_heads, 40]: words 0-15 k multipliers,
- *   16-31 v multipliers, 32-35 sixteen int8 k shifts, 36-39 sixteen int8 v shifts.
- * A token location is page*16 + offset.
+ *   k_codes int8 [pages, kv_heads, 16, 128] (token rows);
+ *   v_codes int8 [pages, kv_heads, 2048]: the page's 16 x 128 bytes in tensor-core operand
+ *   order, byte (d, tok) at ((w>>2)<<9) + (l<<4) + ((w&3)<<2) + (tok&3) with
+ *   w = (d>>4)*2 + ((d>>3)&1), l = (d&7)*4 + (tok>>2);
+ *   meta int32 [pages, kv_heads, 40]: words 0-15 k multipliers, 16-31 v multipliers,
+ *   32-35 sixteen int8 k shifts, 36-39 sixteen int8 v shifts.
+ * A token location is page*16 + offset.  Pools are written by the two store entry points.
  *
  * b200_kv_store_q15 quantises Q15.16 K and V rows per token and KV head (codes as
  * per_token_quant_int8_from_q15 on each 128-wide row; multiplier/shift as

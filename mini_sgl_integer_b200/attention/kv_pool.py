@@ -6,7 +6,8 @@ Mirrors ``MHAKVCache`` (kvcache/mha_pool.py:11-72) behind the same methods
 (multiplier, shift) per token and KV head:
 
     k_codes int8  [layers, pages, kv_heads, 16, 128]
-    v_codes int8  [layers, pages, kv_heads, 128, 16]   (transposed inside a page)
+    v_codes int8  [layers, pages, kv_heads, 2048]      (the page's 16 x 128 bytes in the operand
+                                                        order of the integer MMA; see b200int.h)
     meta    int32 [layers, pages, kv_heads, 40]
 
 A token location is ``page * 16 + offset`` (the reference's page table holds token
@@ -38,7 +39,7 @@ class Int8PagedKVCache:
         self.kv_heads = num_kv_heads // tp_size
         shape = (num_layers, num_pages, self.kv_heads)
         self._k = torch.zeros(shape + (PAGE_SIZE, HEAD_DIM), dtype=torch.int8, device=self._device)
-        self._v = torch.zeros(shape + (HEAD_DIM, PAGE_SIZE), dtype=torch.int8, device=self._device)
+        self._v = torch.zeros(shape + (HEAD_DIM * PAGE_SIZE,), dtype=torch.int8, device=self._device)
         self._meta = torch.zeros(shape + (META_WORDS,), dtype=torch.int32, device=self._device)
 
     def k_cache(self, index: int) -> torch.Tensor:

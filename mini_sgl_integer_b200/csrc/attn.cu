@@ -2,8 +2,10 @@
 //
 // Pool layout of one layer (page = 16 tokens, head_dim = 128):
 //   k_codes [pages][kv_heads][16 tok][128 d]      one (page, head) chunk = 2 KB, token rows
-//   v_codes [pages][kv_heads][128 d][16 tok]      transposed inside the page: the 16 tokens of
-//                                                 one d are contiguous (PV contracts over tokens)
+//   v_codes [pages][kv_heads][2048 B]             the same 16 x 128 bytes in the operand order of
+//                                                 the integer MMA (see v_chunk_offset): PV
+//                                                 contracts over tokens, so 4 tokens of one d
+//                                                 share a 32-bit word
 //   meta    [pages][kv_heads][40 words]           k_mul[16] v_mul[16] k_shift[16 x i8] v_shift[16 x i8]
 //
 // Decode: a thread-block cluster owns one (sequence, KV head); each CTA of the cluster takes a
@@ -23,6 +25,17 @@ namespace b200 {
 constexpr int kPage = 16;
 constexpr int kD = 128;
 constexpr int kMetaWords = 40;
+
+// Byte offset of (d, tok) inside a 2 KB V chunk.  The chunk is stored in the operand order of
+// the m16n8k32 integer MMA (A = V^T, 16 d x 32 tokens): four 512-byte quarters, each holding one
+// 16-byte vector per lane; lane = (d % 8) * 4 + tok / 4 owns, as word (d / 16) * 2 + (d % 16) / 8,
+// the four tokens tok & ~3 .. of row d.  A lane's 128-bit load of quarter q therefore yields the
+// a0/a1 registers of the d-tiles 2q and 2q+1 for one page.
+__host__ __device__ __forceinline__ int v_chunk_offset(int d, int tok) {
+  const int wi = ((d >> 4) << 1) | ((d >> 3) & 1);
+  const int lane = ((d & 7) << 2) | (tok >> 2);
+  return ((wi >> 2) << 9) + (lane << 4) + ((wi & 3) << 2) + (tok & 3);
+}
 
 __device__ __forceinline__ void absmax_to_ms_dev(int m, int* mul, int* shift) {
   m = max(m, 1);
@@ -84,9 +97,9 @@ kv_store_kernel(const void* __restrict__ k_in, int64_t k_pitch, const void* __re
   }
   const int64_t chunk = pid * kv_heads + h;
   reinterpret_cast<unsigned*>(k_codes + (chunk * kPage + tok) * kD)[lane] = kw;
-  int8_t* vdst = v_codes + chunk * (kD * kPage) + tok;
+  int8_t* vdst = v_codes + chunk * (kD * kPage);
 #pragma unroll
-  for (int e = 0; e < 4; ++e) vdst[(4 * lane + e) * kPage] = (int8_t)((vw >> (8 * e)) & 0xff);
+  for (int e = 0; e < 4; ++e) vdst[v_chunk_offset(4 * lane + e, tok)] = (int8_t)((vw >> (8 * e)) & 0xff);
   if (lane == 0) {
     int32_t* mt = meta + chunk * kMetaWords;
     mt[tok] = kmul;
@@ -116,22 +129,36 @@ struct DecodeParams {
   int s_max;  // key capacity of one CTA's slice (multiple of 32)
 };
 
-__device__ __forceinline__ int dp4a_ss(unsigned a, unsigned b, int c) {
-  int d;
-  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
+__device__ __forceinline__ void mma_s8s8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ int dp4a_su(unsigned a, unsigned b, int c) {  // a signed bytes, b unsigned
-  int d;
-  asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
+__device__ __forceinline__ void mma_s8u8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned word_of(const uint4 (&v)[4], int wi) {
+  const uint4& q = v[wi >> 2];
+  return (wi & 3) == 0 ? q.x : (wi & 3) == 1 ? q.y : (wi & 3) == 2 ? q.z : q.w;
 }
 
-constexpr int kDecodeThreads = 256;
-constexpr int kDecodeWarps = kDecodeThreads / 32;
+constexpr int kDecodeWarps = 4;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
 
+// Both contractions run on the integer tensor-core MMA with the long dimension on M:
+//   scores^T [16 keys x 8 heads] = K page [16 x 128] . Q^T [128 x 8]      (4 k-steps of 32 d)
+//   out^T    [16 d    x 8 heads] = V^T [16 x 32 tokens] . W^T [32 x 8]    (two pages per k-step)
+// so a page is exactly one M tile and the (<= 8) query heads of the group are the N columns.
+// Operands go straight from global memory into MMA registers with 128-bit loads: K rows are read
+// 32 contiguous bytes per lane (the d axis is permuted identically in Q), V uses v_chunk_offset.
 template <int G>
-__global__ void __launch_bounds__(kDecodeThreads)
+__global__ void __launch_bounds__(kDecodeThreads, 4)
 attn_decode_kernel(const DecodeParams p) {
   cg::cluster_group cluster = cg::this_cluster();
   const int C = (int)cluster.num_blocks();
@@ -139,6 +166,7 @@ attn_decode_kernel(const DecodeParams p) {
   const int kh = blockIdx.y;
   const int b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int fr = lane >> 2, fc = lane & 3;   // fragment row / column-group of this lane
   const int S = p.s_max;
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -148,7 +176,6 @@ attn_decode_kernel(const DecodeParams p) {
   uint16_t* rel = reinterpret_cast<uint16_t*>(p_lo + G * S);          // [S]
   int32_t* pages = reinterpret_cast<int32_t*>(rel + S);               // [S / 16]
 
-  __shared__ __align__(16) int8_t q_s[G][kD];
   __shared__ int q_mul_s[G], q_shift_s[G];
   __shared__ int cta_max[G];
   __shared__ unsigned long long cta_sum[G];
@@ -167,13 +194,10 @@ attn_decode_kernel(const DecodeParams p) {
   const int my_pages = pg1 - pg0;
   const int key0 = pg0 * kPage;                          // first key of the slice
   const int my_keys = max(0, min(L, pg1 * kPage) - key0);  // valid keys in the slice
+  const int n_pairs = (my_pages + 1) >> 1;
+  const int n_slots = n_pairs * 32;
 
   // ---- set-up
-  for (int i = tid; i < G * kD / 16; i += kDecodeThreads) {
-    const int g = i / (kD / 16), c = i % (kD / 16);
-    reinterpret_cast<int4*>(&q_s[g][0])[c] =
-        reinterpret_cast<const int4*>(p.q + ((int64_t)b * p.q_heads + kh * G + g) * kD)[c];
-  }
   if (tid < G) {
     q_mul_s[tid] = p.q_mul[(int64_t)b * p.q_heads + kh * G + tid];
     q_shift_s[tid] = p.q_shift[(int64_t)b * p.q_heads + kh * G + tid];
@@ -188,65 +212,95 @@ attn_decode_kernel(const DecodeParams p) {
     pid = pid < 0 ? 0 : (pid >= p.num_pages ? p.num_pages - 1 : pid);
     pages[i] = (int)pid;
   }
+  // Q as the MMA's B operand: lane (fr, fc) holds bytes [32 fc, 32 fc + 32) of head fr
+  unsigned qw[8];
+  {
+    uint4 qa = make_uint4(0, 0, 0, 0), qb = make_uint4(0, 0, 0, 0);
+    if (fr < G) {
+      const uint4* qp = reinterpret_cast<const uint4*>(p.q + ((int64_t)b * p.q_heads + kh * G + fr) * kD + fc * 32);
+      qa = __ldg(qp);
+      qb = __ldg(qp + 1);
+    }
+    qw[0] = qa.x; qw[1] = qa.y; qw[2] = qa.z; qw[3] = qa.w;
+    qw[4] = qb.x; qw[5] = qb.y; qw[6] = qb.z; qw[7] = qb.w;
+  }
   __syncthreads();
 
-  // ---- phase 1: scores of the slice.  A warp takes 32 keys (two pages), one key per lane.
+  // ---- phase 1: scores of the slice, one page (16 keys) per MMA tile
   {
-    int lmax[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) lmax[g] = (int)(-2147483647 - 1);
+    int lmax0 = (int)(-2147483647 - 1), lmax1 = lmax0;   // heads 2 fc and 2 fc + 1
     unsigned long long lvref = ~0ull;
-    const int n_pairs = (my_pages + 1) >> 1;
-    for (int pair = warp; pair < n_pairs; pair += kDecodeWarps) {
-      const int kl = pair * 32 + lane;             // key index inside the slice
-      const bool valid = kl < my_keys;
-      const int pg = min(kl >> 4, max(my_pages - 1, 0));
-      const int tok = kl & 15;
-      const int64_t chunk = (int64_t)pages[pg] * p.kv_heads + kh;
-      int dot[G];
+    const bool h0 = 2 * fc < G, h1 = 2 * fc + 1 < G;
+    for (int pg = warp; pg < 2 * n_pairs; pg += kDecodeWarps) {
+      const int kl0 = pg * 16 + fr, kl1 = kl0 + 8;       // the two keys this lane sees in the C tile
+      if (pg < my_pages) {
+        const int64_t chunk = (int64_t)pages[pg] * p.kv_heads + kh;
+        const uint4* kp = reinterpret_cast<const uint4*>(p.k_codes + chunk * (kPage * kD));
+        const uint4 k00 = __ldcs(kp + fr * 8 + fc * 2), k01 = __ldcs(kp + fr * 8 + fc * 2 + 1);
+        const uint4 k10 = __ldcs(kp + (fr + 8) * 8 + fc * 2), k11 = __ldcs(kp + (fr + 8) * 8 + fc * 2 + 1);
+        const int32_t* mt = p.meta + chunk * kMetaWords;
+        int km0 = 0, km1 = 0, ks0 = 0, ks1 = 0;
+        if (h0) {
+          km0 = __ldg(mt + fr); km1 = __ldg(mt + fr + 8);
+          ks0 = reinterpret_cast<const int8_t*>(mt + 32)[fr]; ks1 = reinterpret_cast<const int8_t*>(mt + 32)[fr + 8];
+        }
+        if (fc == 3) {   // one lane per key row looks at the V scales for the reference scale
 #pragma unroll
-      for (int g = 0; g < G; ++g) dot[g] = 0;
-      if (valid) {
-        const int4* kr = reinterpret_cast<const int4*>(p.k_codes + (chunk * kPage + tok) * kD);
-        int4 kv[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) kv[j] = __ldcs(kr + j);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-#pragma unroll
-          for (int g = 0; g < G; ++g) {
-            const int4 qq = reinterpret_cast<const int4*>(&q_s[g][0])[j];
-            dot[g] = dp4a_ss(kv[j].x, qq.x, dot[g]);
-            dot[g] = dp4a_ss(kv[j].y, qq.y, dot[g]);
-            dot[g] = dp4a_ss(kv[j].z, qq.z, dot[g]);
-            dot[g] = dp4a_ss(kv[j].w, qq.w, dot[g]);
+          for (int hlf = 0; hlf < 2; ++hlf) {
+            const int tok = fr + 8 * hlf;
+            if (pg * 16 + tok < my_keys) {
+              const int v_mul = __ldg(mt + 16 + tok);
+              const int v_shift = reinterpret_cast<const int8_t*>(mt + 36)[tok];
+              const unsigned long long vkey = ((unsigned long long)(unsigned)(v_shift + 128) << 32) |
+                                              (unsigned long long)(0xFFFFFFFFu - (unsigned)v_mul);
+              lvref = vkey < lvref ? vkey : lvref;
+            }
           }
         }
-        const int32_t* mt = p.meta + chunk * kMetaWords;
-        const int k_mul = __ldg(mt + tok);
-        const int k_shift = reinterpret_cast<const int8_t*>(mt + 32)[tok];
-        const int v_mul = __ldg(mt + 16 + tok);
-        const int v_shift = reinterpret_cast<const int8_t*>(mt + 36)[tok];
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const int cm = __mulhi(q_mul_s[g], k_mul);   // (q_mul * k_mul) >> 32
-          const int s = q_shift_s[g] + k_shift - 48;
-          const int v = sat32(mul_shift64((long long)dot[g], (long long)cm, s));
-          sc[g * S + kl] = v;
-          lmax[g] = max(lmax[g], v);
+        int c[4] = {0, 0, 0, 0};
+        mma_s8s8(c, k00.x, k10.x, k00.y, k10.y, qw[0], qw[1]);
+        mma_s8s8(c, k00.z, k10.z, k00.w, k10.w, qw[2], qw[3]);
+        mma_s8s8(c, k01.x, k11.x, k01.y, k11.y, qw[4], qw[5]);
+        mma_s8s8(c, k01.z, k11.z, k01.w, k11.w, qw[6], qw[7]);
+        // c[0]: (key kl0, head 2fc)  c[1]: (kl0, 2fc+1)  c[2]: (kl1, 2fc)  c[3]: (kl1, 2fc+1)
+        if (h0) {
+          const int g0 = 2 * fc;
+          const int v0 = kl0 < my_keys
+                             ? sat32(mul_shift64(c[0], __mulhi(q_mul_s[g0], km0), q_shift_s[g0] + ks0 - 48))
+                             : (int)(-2147483647 - 1);
+          const int v2 = kl1 < my_keys
+                             ? sat32(mul_shift64(c[2], __mulhi(q_mul_s[g0], km1), q_shift_s[g0] + ks1 - 48))
+                             : (int)(-2147483647 - 1);
+          sc[g0 * S + kl0] = v0;
+          sc[g0 * S + kl1] = v2;
+          lmax0 = max(lmax0, max(v0, v2));
         }
-        const unsigned long long vkey =
-            ((unsigned long long)(unsigned)(v_shift + 128) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)v_mul);
-        lvref = vkey < lvref ? vkey : lvref;
-      } else {
-#pragma unroll
-        for (int g = 0; g < G; ++g) sc[g * S + kl] = (int)(-2147483647 - 1);
+        if (h1) {
+          const int g1 = 2 * fc + 1;
+          const int v1 = kl0 < my_keys
+                             ? sat32(mul_shift64(c[1], __mulhi(q_mul_s[g1], km0), q_shift_s[g1] + ks0 - 48))
+                             : (int)(-2147483647 - 1);
+          const int v3 = kl1 < my_keys
+                             ? sat32(mul_shift64(c[3], __mulhi(q_mul_s[g1], km1), q_shift_s[g1] + ks1 - 48))
+                             : (int)(-2147483647 - 1);
+          sc[g1 * S + kl0] = v1;
+          sc[g1 * S + kl1] = v3;
+          lmax1 = max(lmax1, max(v1, v3));
+        }
+      } else {   // the odd page of the last pair: empty slots
+        if (h0) { sc[2 * fc * S + kl0] = (int)(-2147483647 - 1); sc[2 * fc * S + kl1] = (int)(-2147483647 - 1); }
+        if (h1) { sc[(2 * fc + 1) * S + kl0] = (int)(-2147483647 - 1); sc[(2 * fc + 1) * S + kl1] = (int)(-2147483647 - 1); }
       }
     }
+    // lanes with equal fc hold the same pair of heads: reduce over fr (lane bits 2..4)
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const int m = warp_max(lmax[g]);
-      if (lane == 0) atomicMax(&cta_max[g], m);
+    for (int o = 4; o < 32; o <<= 1) {
+      lmax0 = max(lmax0, __shfl_xor_sync(FULL_MASK, lmax0, o));
+      lmax1 = max(lmax1, __shfl_xor_sync(FULL_MASK, lmax1, o));
+    }
+    if (fr == 0) {
+      if (h0) atomicMax(&cta_max[2 * fc], lmax0);
+      if (h1) atomicMax(&cta_max[2 * fc + 1], lmax1);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -254,6 +308,25 @@ attn_decode_kernel(const DecodeParams p) {
       lvref = other < lvref ? other : lvref;
     }
     if (lane == 0) atomicMin(&cta_vref, lvref);
+  }
+
+  // V operands of this warp's first page pair are requested now so that the loads fly during
+  // the cluster-wide exchanges below.
+  uint4 va[4], vb[4];
+  {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) va[i] = vb[i] = make_uint4(0, 0, 0, 0);
+    const int pp = warp;
+    if (pp < n_pairs) {
+      const uint4* vpa = reinterpret_cast<const uint4*>(p.v_codes + ((int64_t)pages[2 * pp] * p.kv_heads + kh) * (kD * kPage));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) va[i] = __ldcs(vpa + i * 32 + lane);
+      if (2 * pp + 1 < my_pages) {
+        const uint4* vpb = reinterpret_cast<const uint4*>(p.v_codes + ((int64_t)pages[2 * pp + 1] * p.kv_heads + kh) * (kD * kPage));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) vb[i] = __ldcs(vpb + i * 32 + lane);
+      }
+    }
   }
   cluster.sync();
 
@@ -277,7 +350,6 @@ attn_decode_kernel(const DecodeParams p) {
     long long lsum[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) lsum[g] = 0;
-    const int n_slots = ((my_pages + 1) >> 1) * 32;
     for (int kl = tid; kl < n_slots; kl += kDecodeThreads) {
       const bool valid = kl < my_keys;
 #pragma unroll
@@ -328,64 +400,73 @@ attn_decode_kernel(const DecodeParams p) {
   __syncthreads();
 
   // ---- phase 3a: probabilities (Q0.15), folded with the relative V scale, as two byte limbs
-  {
-    const int n_slots = ((my_pages + 1) >> 1) * 32;
-    for (int kl = tid; kl < n_slots; kl += kDecodeThreads) {
-      const unsigned r = rel[kl];
+  for (int kl = tid; kl < n_slots; kl += kDecodeThreads) {
+    const unsigned r = rel[kl];
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const long long pr = ((long long)sc[g * S + kl] * (long long)g_inv[g]) >> 16;
-        const unsigned w = (unsigned)((pr * (long long)r + 16384) >> 15);
-        p_hi[g * S + kl] = (uint8_t)(w >> 8);
-        p_lo[g * S + kl] = (uint8_t)(w & 0xff);
-      }
+    for (int g = 0; g < G; ++g) {
+      const long long pr = ((long long)sc[g * S + kl] * (long long)g_inv[g]) >> 16;
+      const unsigned w = (unsigned)((pr * (long long)r + 16384) >> 15);
+      p_hi[g * S + kl] = (uint8_t)(w >> 8);
+      p_lo[g * S + kl] = (uint8_t)(w & 0xff);
     }
   }
   __syncthreads();
 
-  // ---- phase 3b: PV.  A warp takes one page; lane = d within each 32-wide quarter.
+  // ---- phase 3b: PV, two pages (32 tokens) per k-step, 8 d-tiles of 16
   {
-    int acc_hi[G][4], acc_lo[G][4];
+    int acc_hi[8][4], acc_lo[8][4];
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+    for (int m = 0; m < 8; ++m)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc_hi[g][i] = acc_lo[g][i] = 0;
-    for (int pg = warp; pg < my_pages; pg += kDecodeWarps) {
-      const int64_t chunk = (int64_t)pages[pg] * p.kv_heads + kh;
-      const int4* vr = reinterpret_cast<const int4*>(p.v_codes + chunk * (kD * kPage));
-      int4 vv[4];
+      for (int j = 0; j < 4; ++j) acc_hi[m][j] = acc_lo[m][j] = 0;
+    for (int pp = warp; pp < n_pairs; pp += kDecodeWarps) {
+      if (pp != warp) {   // the first pair was requested before the exchanges
+        const uint4* vpa = reinterpret_cast<const uint4*>(p.v_codes + ((int64_t)pages[2 * pp] * p.kv_heads + kh) * (kD * kPage));
 #pragma unroll
-      for (int i = 0; i < 4; ++i) vv[i] = __ldcs(vr + i * 32 + lane);
+        for (int i = 0; i < 4; ++i) va[i] = __ldcs(vpa + i * 32 + lane);
+        if (2 * pp + 1 < my_pages) {
+          const uint4* vpb = reinterpret_cast<const uint4*>(p.v_codes + ((int64_t)pages[2 * pp + 1] * p.kv_heads + kh) * (kD * kPage));
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const uint4 ph = *reinterpret_cast<const uint4*>(p_hi + g * S + pg * 16);
-        const uint4 pl = *reinterpret_cast<const uint4*>(p_lo + g * S + pg * 16);
+          for (int i = 0; i < 4; ++i) vb[i] = __ldcs(vpb + i * 32 + lane);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          int h = acc_hi[g][i], l = acc_lo[g][i];
-          h = dp4a_su(vv[i].x, ph.x, h); l = dp4a_su(vv[i].x, pl.x, l);
-          h = dp4a_su(vv[i].y, ph.y, h); l = dp4a_su(vv[i].y, pl.y, l);
-          h = dp4a_su(vv[i].z, ph.z, h); l = dp4a_su(vv[i].z, pl.z, l);
-          h = dp4a_su(vv[i].w, ph.w, h); l = dp4a_su(vv[i].w, pl.w, l);
-          acc_hi[g][i] = h; acc_lo[g][i] = l;
+          for (int i = 0; i < 4; ++i) vb[i] = make_uint4(0, 0, 0, 0);
         }
       }
+      unsigned bh0 = 0, bh1 = 0, bl0 = 0, bl1 = 0;   // W^T: head fr, tokens 4 fc .. of page A / B
+      if (fr < G) {
+        bh0 = *reinterpret_cast<const unsigned*>(p_hi + fr * S + pp * 32 + fc * 4);
+        bh1 = *reinterpret_cast<const unsigned*>(p_hi + fr * S + pp * 32 + 16 + fc * 4);
+        bl0 = *reinterpret_cast<const unsigned*>(p_lo + fr * S + pp * 32 + fc * 4);
+        bl1 = *reinterpret_cast<const unsigned*>(p_lo + fr * S + pp * 32 + 16 + fc * 4);
+      }
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        const unsigned a0 = word_of(va, 2 * m), a1 = word_of(va, 2 * m + 1);
+        const unsigned a2 = word_of(vb, 2 * m), a3 = word_of(vb, 2 * m + 1);
+        mma_s8u8(acc_hi[m], a0, a1, a2, a3, bh0, bh1);
+        mma_s8u8(acc_lo[m], a0, a1, a2, a3, bl0, bl1);
+      }
     }
+    // C tile: [0] (d = 16m + fr, head 2fc)  [1] (.., 2fc+1)  [2] (d + 8, 2fc)  [3] (d + 8, 2fc+1)
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+    for (int m = 0; m < 8; ++m)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int v = acc_hi[g][i] * 256 + acc_lo[g][i];
-        if (v != 0) atomicAdd(&cta_acc[g][i * 32 + lane], v);
+      for (int j = 0; j < 4; ++j) {
+        const int head = 2 * fc + (j & 1);
+        const int d = 16 * m + fr + 8 * (j >> 1);
+        const int v = acc_hi[m][j] * 256 + acc_lo[m][j];
+        if (head < G && v != 0) atomicAdd(&cta_acc[head][d], v);
       }
   }
   cluster.sync();
 
   // ---- exchange 3: rank 0 sums the partial outputs and requantises
   if (rank == 0) {
-    int outv[(G * kD + kDecodeThreads - 1) / kDecodeThreads];
+    constexpr int kIt = (G * kD + kDecodeThreads - 1) / kDecodeThreads;
+    int outv[kIt];
 #pragma unroll
-    for (int it = 0; it < (G * kD + kDecodeThreads - 1) / kDecodeThreads; ++it) {
+    for (int it = 0; it < kIt; ++it) {
       const int i = tid + it * kDecodeThreads;
       int o = 0;
       if (i < G * kD) {
@@ -401,7 +482,7 @@ attn_decode_kernel(const DecodeParams p) {
     if (p.out_codes) {
       __syncthreads();
 #pragma unroll
-      for (int it = 0; it < (G * kD + kDecodeThreads - 1) / kDecodeThreads; ++it) {
+      for (int it = 0; it < kIt; ++it) {
         const int i = tid + it * kDecodeThreads;
         if (i < G * kD) {
           const int g = i / kD;

@@ -159,11 +159,27 @@ def absmax_to_mul_shift(m):
     return mul.astype(np.int32), (k + 16).astype(np.int32)
 
 
+def v_chunk_offset(d, tok):
+    """Byte offset of (d, tok) inside a page's 2 KB V chunk (build-defined layout).
+
+    Four 512-byte quarters, each one 16-byte vector per "lane"; lane = (d % 8) * 4 + tok // 4
+    owns, as word (d // 16) * 2 + (d % 16) // 8, the four tokens tok & ~3 .. of row d.
+    """
+    wi = ((d >> 4) << 1) | ((d >> 3) & 1)
+    lane = ((d & 7) << 2) | (tok >> 2)
+    return ((wi >> 2) << 9) + (lane << 4) + ((wi & 3) << 2) + (tok & 3)
+
+
+V_OFFSETS = np.array([[v_chunk_offset(d, t) for t in range(PAGE)] for d in range(128)], dtype=np.int64)
+assert sorted(V_OFFSETS.reshape(-1).tolist()) == list(range(2048))
+
+
 class PagedKV:
     """An int8 KV pool for ONE layer in the physical layout the CUDA kernels read.
 
       k_codes int8  [P, Hkv, 16, D]   token-major rows inside a page
-      v_codes int8  [P, Hkv, D, 16]   transposed inside a page (16 tokens of one d contiguous)
+      v_codes int8  [P, Hkv, 2048]    the 16 x 128 bytes of a page in tensor-core operand order:
+                                      byte (d, tok) sits at ``v_chunk_offset(d, tok)``
       meta    int32 [P, Hkv, 40]      words 0-15 k_mul, 16-31 v_mul,
                                       32-35 k_shift (16 int8), 36-39 v_shift (16 int8)
     A token location is ``page * 16 + offset``.
@@ -172,7 +188,7 @@ class PagedKV:
     def __init__(self, num_pages: int, num_kv_heads: int, head_dim: int = 128):
         self.P, self.H, self.D = num_pages, num_kv_heads, head_dim
         self.k_codes = np.zeros((num_pages, num_kv_heads, PAGE, head_dim), dtype=np.int8)
-        self.v_codes = np.zeros((num_pages, num_kv_heads, head_dim, PAGE), dtype=np.int8)
+        self.v_codes = np.zeros((num_pages, num_kv_heads, head_dim * PAGE), dtype=np.int8)
         self.meta = np.zeros((num_pages, num_kv_heads, 40), dtype=np.int32)
 
     def _shift_view(self, which: int) -> np.ndarray:
@@ -186,7 +202,7 @@ class PagedKV:
         ks, vs = self._shift_view(0), self._shift_view(1)
         for t in range(len(loc)):
             self.k_codes[pg[t], :, off[t], :] = k8[t]
-            self.v_codes[pg[t], :, :, off[t]] = v8[t]
+            self.v_codes[pg[t], :, V_OFFSETS[:, off[t]]] = np.asarray(v8[t]).T
             self.meta[pg[t], :, off[t]] = k_mul[t]
             self.meta[pg[t], :, 16 + off[t]] = v_mul[t]
             ks[pg[t], :, off[t]] = k_shift[t]
@@ -213,7 +229,8 @@ class PagedKV:
         n = (length + PAGE - 1) // PAGE
         pg = pages[:n]
         k = self.k_codes[pg].transpose(0, 2, 1, 3).reshape(n * PAGE, self.H, self.D)[:length]
-        v = self.v_codes[pg].transpose(0, 3, 1, 2).reshape(n * PAGE, self.H, self.D)[:length]
+        v = self.v_codes[pg][:, :, V_OFFSETS]  # [n, H, D, 16]
+        v = v.transpose(0, 3, 1, 2).reshape(n * PAGE, self.H, self.D)[:length]
         km = self.meta[pg, :, 0:16].transpose(0, 2, 1).reshape(n * PAGE, self.H)[:length]
         vm = self.meta[pg, :, 16:32].transpose(0, 2, 1).reshape(n * PAGE, self.H)[:length]
         ks = self._shift_view(0)[pg].transpose(0, 2, 1).reshape(n * PAGE, self.H)[:length]
