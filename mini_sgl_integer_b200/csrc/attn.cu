@@ -150,13 +150,55 @@ __device__ __forceinline__ unsigned word_of(const uint4 (&v)[4], int wi) {
 
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kStages = 2;                 // ring slots per warp
+constexpr int kSlotMeta = 4096;            // K slots: the two pages' scale blocks follow the codes
+constexpr int kSlotBytes = 4096 + 2 * 192; // one slot = a pair of pages (+ 2 x 160 B of scales, padded)
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// sat32 of the rounding multiply-shift for the common case 0 < s < 63 (general form otherwise).
+__device__ __forceinline__ int mul_shift_sat32(int x, int m, int s) {
+  if (s > 0 && s < 63) {
+    const long long prod = (long long)x * (long long)m + (1LL << (s - 1));   // |x*m| < 2^62
+    return sat32(prod >> s);
+  }
+  return sat32(mul_shift64((long long)x, (long long)m, s));
+}
+
+// min(65535, ((v_mul << 15) / m_ref) >> d): relative V scale in Q0.15.
+__device__ __forceinline__ unsigned rel_scale_q15(unsigned v_mul, unsigned m_ref, int d) {
+  if (m_ref == 0u || d >= 32) return 0u;
+  const unsigned long long num = (unsigned long long)v_mul << 15;
+  unsigned long long q;
+  if (m_ref >= (1u << 30)) {   // normalised reference: the quotient is below 2^17 and a float
+    unsigned est = (unsigned)(((float)v_mul * 32768.0f) / (float)m_ref);   // estimate is off by <= 1
+    long long r = (long long)(num - (unsigned long long)est * m_ref);
+    if (r < 0) { est -= 1; } else if (r >= (long long)m_ref) { est += 1; }
+    q = est;
+  } else {
+    q = num / m_ref;
+  }
+  q >>= (d < 0 ? 0 : d);
+  return q > 65535ull ? 65535u : (unsigned)q;
+}
 
 // Both contractions run on the integer tensor-core MMA with the long dimension on M:
 //   scores^T [16 keys x 8 heads] = K page [16 x 128] . Q^T [128 x 8]      (4 k-steps of 32 d)
 //   out^T    [16 d    x 8 heads] = V^T [16 x 32 tokens] . W^T [32 x 8]    (two pages per k-step)
 // so a page is exactly one M tile and the (<= 8) query heads of the group are the N columns.
-// Operands go straight from global memory into MMA registers with 128-bit loads: K rows are read
-// 32 contiguous bytes per lane (the d axis is permuted identically in Q), V uses v_chunk_offset.
+// Every warp streams its own page pairs (first the K pairs of its share of the slice, each with
+// the pages' scale blocks, then the V pairs) through a private ring of shared-memory slots filled
+// by 16-byte asynchronous copies, so the loads of the next pair - including the first V pairs -
+// are in flight while the warp computes and while the cluster exchanges the softmax statistics.
+// Each lane reads its MMA registers from the slot with 128-bit loads: K rows 32 contiguous bytes
+// per lane (the d axis is permuted identically in Q; 16-byte columns are XOR-swizzled by the row
+// parity on the way in), V in the operand order of v_chunk_offset.
 template <int G>
 __global__ void __launch_bounds__(kDecodeThreads, 4)
 attn_decode_kernel(const DecodeParams p) {
@@ -168,13 +210,17 @@ attn_decode_kernel(const DecodeParams p) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int fr = lane >> 2, fc = lane & 3;   // fragment row / column-group of this lane
   const int S = p.s_max;
+  constexpr int kNeg = (int)(-2147483647 - 1);
 
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  int32_t* sc = reinterpret_cast<int32_t*>(smem_raw);                 // [G][S] scores, then exponentials
-  uint8_t* p_hi = reinterpret_cast<uint8_t*>(sc + G * S);             // [G][S]
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* ring = smem_raw + warp * (kStages * kSlotBytes);      // this warp's slots
+  int32_t* sc = reinterpret_cast<int32_t*>(smem_raw + kDecodeWarps * kStages * kSlotBytes);  // [G][S]
+  int32_t* vm_s = sc + G * S;                                         // [S] V multipliers
+  uint8_t* p_hi = reinterpret_cast<uint8_t*>(vm_s + S);               // [G][S]
   uint8_t* p_lo = p_hi + G * S;                                       // [G][S]
   uint16_t* rel = reinterpret_cast<uint16_t*>(p_lo + G * S);          // [S]
-  int32_t* pages = reinterpret_cast<int32_t*>(rel + S);               // [S / 16]
+  int8_t* vs_s = reinterpret_cast<int8_t*>(rel + S);                  // [S] V shifts
+  int32_t* pages = reinterpret_cast<int32_t*>(vs_s + S);              // [S / 16]
 
   __shared__ int q_mul_s[G], q_shift_s[G];
   __shared__ int cta_max[G];
@@ -196,12 +242,13 @@ attn_decode_kernel(const DecodeParams p) {
   const int my_keys = max(0, min(L, pg1 * kPage) - key0);  // valid keys in the slice
   const int n_pairs = (my_pages + 1) >> 1;
   const int n_slots = n_pairs * 32;
+  const int n_items = warp < n_pairs ? (n_pairs - warp + kDecodeWarps - 1) / kDecodeWarps : 0;  // pairs of this warp
 
   // ---- set-up
   if (tid < G) {
     q_mul_s[tid] = p.q_mul[(int64_t)b * p.q_heads + kh * G + tid];
     q_shift_s[tid] = p.q_shift[(int64_t)b * p.q_heads + kh * G + tid];
-    cta_max[tid] = (int)(-2147483647 - 1);
+    cta_max[tid] = kNeg;
     cta_sum[tid] = 0ull;
     out_absmax_s[tid] = 0;
   }
@@ -226,71 +273,105 @@ attn_decode_kernel(const DecodeParams p) {
   }
   __syncthreads();
 
+  // Item j of this warp: j < n_items is the K copy of pair (warp + j * warps), otherwise the V
+  // copy of pair (warp + (j - n_items) * warps).  One commit group per item, also when empty.
+  // A lane moves the 16-byte columns lane, lane+32, lane+64, lane+96 of each 2 KB chunk.
+  int k_dst[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int ch = lane + 32 * i;
+    k_dst[i] = ((ch >> 3) << 7) | (((ch & 7) ^ ((ch >> 3) & 1)) << 4);
+  }
+  auto issue = [&](int j) {
+    if (j < 2 * n_items) {
+      const bool is_k = j < n_items;
+      const int pp = warp + (is_k ? j : j - n_items) * kDecodeWarps;
+      unsigned char* slot = ring + (j % kStages) * kSlotBytes;
+      const unsigned char* base = reinterpret_cast<const unsigned char*>(is_k ? p.k_codes : p.v_codes);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int pg = 2 * pp + h;
+        if (pg < my_pages) {
+          const int64_t chunk = (int64_t)pages[pg] * p.kv_heads + kh;
+          const unsigned char* src = base + chunk * (kPage * kD) + (lane << 4);
+          unsigned char* dst = slot + h * 2048;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) cp_async16(dst + (is_k ? k_dst[i] : ((lane + 32 * i) << 4)), src + i * 512);
+          if (is_k && (lane & 15) < 10 && (lane >> 4) == h)
+            cp_async16(slot + kSlotMeta + h * 192 + ((lane & 15) << 4),
+                       reinterpret_cast<const unsigned char*>(p.meta + chunk * kMetaWords) + ((lane & 15) << 4));
+        }
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int j = 0; j < kStages; ++j) issue(j);
+
   // ---- phase 1: scores of the slice, one page (16 keys) per MMA tile
   {
-    int lmax0 = (int)(-2147483647 - 1), lmax1 = lmax0;   // heads 2 fc and 2 fc + 1
+    int lmax0 = kNeg, lmax1 = kNeg;   // heads 2 fc and 2 fc + 1
     unsigned long long lvref = ~0ull;
     const bool h0 = 2 * fc < G, h1 = 2 * fc + 1 < G;
-    for (int pg = warp; pg < 2 * n_pairs; pg += kDecodeWarps) {
-      const int kl0 = pg * 16 + fr, kl1 = kl0 + 8;       // the two keys this lane sees in the C tile
-      if (pg < my_pages) {
-        const int64_t chunk = (int64_t)pages[pg] * p.kv_heads + kh;
-        const uint4* kp = reinterpret_cast<const uint4*>(p.k_codes + chunk * (kPage * kD));
-        const uint4 k00 = __ldcs(kp + fr * 8 + fc * 2), k01 = __ldcs(kp + fr * 8 + fc * 2 + 1);
-        const uint4 k10 = __ldcs(kp + (fr + 8) * 8 + fc * 2), k11 = __ldcs(kp + (fr + 8) * 8 + fc * 2 + 1);
-        const int32_t* mt = p.meta + chunk * kMetaWords;
-        int km0 = 0, km1 = 0, ks0 = 0, ks1 = 0;
-        if (h0) {
-          km0 = __ldg(mt + fr); km1 = __ldg(mt + fr + 8);
-          ks0 = reinterpret_cast<const int8_t*>(mt + 32)[fr]; ks1 = reinterpret_cast<const int8_t*>(mt + 32)[fr + 8];
-        }
-        if (fc == 3) {   // one lane per key row looks at the V scales for the reference scale
+    const int g0 = 2 * fc, g1 = 2 * fc + 1;
+    const int qm0 = h0 ? q_mul_s[g0] : 0, qs0 = h0 ? q_shift_s[g0] - 48 : 0;
+    const int qm1 = h1 ? q_mul_s[g1] : 0, qs1 = h1 ? q_shift_s[g1] - 48 : 0;
+    const int sw = fr & 1;
+    for (int it = 0; it < n_items; ++it) {
+      const int pp = warp + it * kDecodeWarps;
+      cp_async_wait<kStages - 1>();
+      __syncwarp();
+      const unsigned char* slot = ring + (it % kStages) * kSlotBytes;
 #pragma unroll
-          for (int hlf = 0; hlf < 2; ++hlf) {
-            const int tok = fr + 8 * hlf;
-            if (pg * 16 + tok < my_keys) {
-              const int v_mul = __ldg(mt + 16 + tok);
+      for (int h = 0; h < 2; ++h) {
+        const int pg = 2 * pp + h;
+        const int kl0 = pg * 16 + fr, kl1 = kl0 + 8;       // the two keys this lane sees in the C tile
+        int v0 = kNeg, v1 = kNeg, v2 = kNeg, v3 = kNeg;
+        if (pg < my_pages) {
+          const unsigned char* r0 = slot + h * 2048 + fr * 128;   // rows fr and fr + 8 share a parity
+          const uint4 k00 = *reinterpret_cast<const uint4*>(r0 + (((2 * fc) ^ sw) << 4));
+          const uint4 k01 = *reinterpret_cast<const uint4*>(r0 + (((2 * fc + 1) ^ sw) << 4));
+          const uint4 k10 = *reinterpret_cast<const uint4*>(r0 + 1024 + (((2 * fc) ^ sw) << 4));
+          const uint4 k11 = *reinterpret_cast<const uint4*>(r0 + 1024 + (((2 * fc + 1) ^ sw) << 4));
+          const int32_t* mt = reinterpret_cast<const int32_t*>(slot + kSlotMeta + h * 192);
+          const int km0 = mt[fr], km1 = mt[fr + 8];
+          const int ks0 = reinterpret_cast<const int8_t*>(mt + 32)[fr], ks1 = reinterpret_cast<const int8_t*>(mt + 32)[fr + 8];
+          if (fc == 3) {   // one lane per key row keeps the V scales and tracks the reference scale
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+              const int tok = fr + 8 * hlf;
+              const int kl = pg * 16 + tok;
+              const int v_mul = mt[16 + tok];
               const int v_shift = reinterpret_cast<const int8_t*>(mt + 36)[tok];
-              const unsigned long long vkey = ((unsigned long long)(unsigned)(v_shift + 128) << 32) |
-                                              (unsigned long long)(0xFFFFFFFFu - (unsigned)v_mul);
-              lvref = vkey < lvref ? vkey : lvref;
+              vm_s[kl] = v_mul;
+              vs_s[kl] = (int8_t)v_shift;
+              if (kl < my_keys) {
+                const unsigned long long vkey = ((unsigned long long)(unsigned)(v_shift + 128) << 32) |
+                                                (unsigned long long)(0xFFFFFFFFu - (unsigned)v_mul);
+                lvref = vkey < lvref ? vkey : lvref;
+              }
             }
           }
+          int c[4] = {0, 0, 0, 0};
+          mma_s8s8(c, k00.x, k10.x, k00.y, k10.y, qw[0], qw[1]);
+          mma_s8s8(c, k00.z, k10.z, k00.w, k10.w, qw[2], qw[3]);
+          mma_s8s8(c, k01.x, k11.x, k01.y, k11.y, qw[4], qw[5]);
+          mma_s8s8(c, k01.z, k11.z, k01.w, k11.w, qw[6], qw[7]);
+          // c[0]: (key kl0, head 2fc)  c[1]: (kl0, 2fc+1)  c[2]: (kl1, 2fc)  c[3]: (kl1, 2fc+1)
+          if (h0) {
+            if (kl0 < my_keys) v0 = mul_shift_sat32(c[0], __mulhi(qm0, km0), qs0 + ks0);
+            if (kl1 < my_keys) v2 = mul_shift_sat32(c[2], __mulhi(qm0, km1), qs0 + ks1);
+          }
+          if (h1) {
+            if (kl0 < my_keys) v1 = mul_shift_sat32(c[1], __mulhi(qm1, km0), qs1 + ks0);
+            if (kl1 < my_keys) v3 = mul_shift_sat32(c[3], __mulhi(qm1, km1), qs1 + ks1);
+          }
         }
-        int c[4] = {0, 0, 0, 0};
-        mma_s8s8(c, k00.x, k10.x, k00.y, k10.y, qw[0], qw[1]);
-        mma_s8s8(c, k00.z, k10.z, k00.w, k10.w, qw[2], qw[3]);
-        mma_s8s8(c, k01.x, k11.x, k01.y, k11.y, qw[4], qw[5]);
-        mma_s8s8(c, k01.z, k11.z, k01.w, k11.w, qw[6], qw[7]);
-        // c[0]: (key kl0, head 2fc)  c[1]: (kl0, 2fc+1)  c[2]: (kl1, 2fc)  c[3]: (kl1, 2fc+1)
-        if (h0) {
-          const int g0 = 2 * fc;
-          const int v0 = kl0 < my_keys
-                             ? sat32(mul_shift64(c[0], __mulhi(q_mul_s[g0], km0), q_shift_s[g0] + ks0 - 48))
-                             : (int)(-2147483647 - 1);
-          const int v2 = kl1 < my_keys
-                             ? sat32(mul_shift64(c[2], __mulhi(q_mul_s[g0], km1), q_shift_s[g0] + ks1 - 48))
-                             : (int)(-2147483647 - 1);
-          sc[g0 * S + kl0] = v0;
-          sc[g0 * S + kl1] = v2;
-          lmax0 = max(lmax0, max(v0, v2));
-        }
-        if (h1) {
-          const int g1 = 2 * fc + 1;
-          const int v1 = kl0 < my_keys
-                             ? sat32(mul_shift64(c[1], __mulhi(q_mul_s[g1], km0), q_shift_s[g1] + ks0 - 48))
-                             : (int)(-2147483647 - 1);
-          const int v3 = kl1 < my_keys
-                             ? sat32(mul_shift64(c[3], __mulhi(q_mul_s[g1], km1), q_shift_s[g1] + ks1 - 48))
-                             : (int)(-2147483647 - 1);
-          sc[g1 * S + kl0] = v1;
-          sc[g1 * S + kl1] = v3;
-          lmax1 = max(lmax1, max(v1, v3));
-        }
-      } else {   // the odd page of the last pair: empty slots
-        if (h0) { sc[2 * fc * S + kl0] = (int)(-2147483647 - 1); sc[2 * fc * S + kl1] = (int)(-2147483647 - 1); }
-        if (h1) { sc[(2 * fc + 1) * S + kl0] = (int)(-2147483647 - 1); sc[(2 * fc + 1) * S + kl1] = (int)(-2147483647 - 1); }
+        if (h0) { sc[g0 * S + kl0] = v0; sc[g0 * S + kl1] = v2; lmax0 = max(lmax0, max(v0, v2)); }
+        if (h1) { sc[g1 * S + kl0] = v1; sc[g1 * S + kl1] = v3; lmax1 = max(lmax1, max(v1, v3)); }
       }
+      __syncwarp();
+      issue(it + kStages);
     }
     // lanes with equal fc hold the same pair of heads: reduce over fr (lane bits 2..4)
 #pragma unroll
@@ -299,8 +380,8 @@ attn_decode_kernel(const DecodeParams p) {
       lmax1 = max(lmax1, __shfl_xor_sync(FULL_MASK, lmax1, o));
     }
     if (fr == 0) {
-      if (h0) atomicMax(&cta_max[2 * fc], lmax0);
-      if (h1) atomicMax(&cta_max[2 * fc + 1], lmax1);
+      if (h0) atomicMax(&cta_max[g0], lmax0);
+      if (h1) atomicMax(&cta_max[g1], lmax1);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -309,30 +390,11 @@ attn_decode_kernel(const DecodeParams p) {
     }
     if (lane == 0) atomicMin(&cta_vref, lvref);
   }
-
-  // V operands of this warp's first page pair are requested now so that the loads fly during
-  // the cluster-wide exchanges below.
-  uint4 va[4], vb[4];
-  {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) va[i] = vb[i] = make_uint4(0, 0, 0, 0);
-    const int pp = warp;
-    if (pp < n_pairs) {
-      const uint4* vpa = reinterpret_cast<const uint4*>(p.v_codes + ((int64_t)pages[2 * pp] * p.kv_heads + kh) * (kD * kPage));
-#pragma unroll
-      for (int i = 0; i < 4; ++i) va[i] = __ldcs(vpa + i * 32 + lane);
-      if (2 * pp + 1 < my_pages) {
-        const uint4* vpb = reinterpret_cast<const uint4*>(p.v_codes + ((int64_t)pages[2 * pp + 1] * p.kv_heads + kh) * (kD * kPage));
-#pragma unroll
-        for (int i = 0; i < 4; ++i) vb[i] = __ldcs(vpb + i * 32 + lane);
-      }
-    }
-  }
   cluster.sync();
 
   // ---- exchange 1: row maxima and the V reference scale over the cluster
   if (tid < G) {
-    int m = (int)(-2147483647 - 1);
+    int m = kNeg;
     for (int r = 0; r < C; ++r) m = max(m, *cluster.map_shared_rank(&cta_max[tid], r));
     g_max[tid] = m;
   }
@@ -347,44 +409,32 @@ attn_decode_kernel(const DecodeParams p) {
 
   // ---- phase 2: exponentials, their sum, and the relative V scale of every key
   {
-    long long lsum[G];
+    int lsum[G];   // a thread sees at most S / threads keys, each e <= 2^16: no overflow
+    int gm[G];
 #pragma unroll
-    for (int g = 0; g < G; ++g) lsum[g] = 0;
+    for (int g = 0; g < G; ++g) { lsum[g] = 0; gm[g] = g_max[g]; }
     for (int kl = tid; kl < n_slots; kl += kDecodeThreads) {
       const bool valid = kl < my_keys;
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         int e = 0;
         if (valid) {
-          int x = sub_sat(sc[g * S + kl], g_max[g]);
-          x = max(x, -(1 << 30));
-          const int y = (int)(((long long)x * 94548LL) >> 16);
-          const int yi = y >> 16;
-          const int idx = (y & 0xFFFF) >> 6;
-          const int sh = max(0, min(31, 13 - yi));
-          e = __ldg(&g_exp2_attn_lut[idx]) >> sh;
+          const int x = max(sub_sat(sc[g * S + kl], gm[g]), -(1 << 30));          // <= 0
+          const long long prod = (long long)x * 94548LL;                          // y = prod >> 16
+          const int yi = (int)(prod >> 32);                                       // y >> 16
+          const unsigned idx = ((unsigned)prod) >> 22;                            // (y & 0xFFFF) >> 6
+          e = __ldg(&g_exp2_attn_lut[idx]) >> min(31, 13 - yi);
         }
         sc[g * S + kl] = e;
         lsum[g] += e;
       }
       unsigned r = 0;
-      if (valid) {
-        const int pg = kl >> 4, tok = kl & 15;
-        const int32_t* mt = p.meta + ((int64_t)pages[pg] * p.kv_heads + kh) * kMetaWords;
-        const int v_mul = __ldg(mt + 16 + tok);
-        const int v_shift = reinterpret_cast<const int8_t*>(mt + 36)[tok];
-        const int d = v_shift - v_shift_ref;
-        if (v_mul_ref > 0 && d < 32) {
-          const unsigned long long ratio = ((unsigned long long)(unsigned)v_mul << 15) / (unsigned)v_mul_ref;
-          r = (unsigned)(ratio >> d);
-          r = min(r, 65535u);
-        }
-      }
+      if (valid) r = rel_scale_q15((unsigned)vm_s[kl], (unsigned)v_mul_ref, (int)vs_s[kl] - v_shift_ref);
       rel[kl] = (uint16_t)r;
     }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      const long long s = warp_sum64(lsum[g]);
+      const long long s = warp_sum64((long long)lsum[g]);
       if (lane == 0) atomicAdd(&cta_sum[g], (unsigned long long)s);
     }
   }
@@ -399,15 +449,22 @@ attn_decode_kernel(const DecodeParams p) {
   }
   __syncthreads();
 
-  // ---- phase 3a: probabilities (Q0.15), folded with the relative V scale, as two byte limbs
-  for (int kl = tid; kl < n_slots; kl += kDecodeThreads) {
-    const unsigned r = rel[kl];
+  // ---- phase 3a: probabilities (Q0.15), folded with the relative V scale, as two byte limbs.
+  // The key holding the row maximum contributes e = 2^16, so total >= 2^16 and inv <= 32767:
+  // e * inv < 2^31 and p * rel < 2^31, 32-bit arithmetic is exact here.
+  {
+    unsigned gi[G];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const long long pr = ((long long)sc[g * S + kl] * (long long)g_inv[g]) >> 16;
-      const unsigned w = (unsigned)((pr * (long long)r + 16384) >> 15);
-      p_hi[g * S + kl] = (uint8_t)(w >> 8);
-      p_lo[g * S + kl] = (uint8_t)(w & 0xff);
+    for (int g = 0; g < G; ++g) gi[g] = (unsigned)g_inv[g];
+    for (int kl = tid; kl < n_slots; kl += kDecodeThreads) {
+      const unsigned r = rel[kl];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const unsigned pr = ((unsigned)sc[g * S + kl] * gi[g]) >> 16;
+        const unsigned w = (pr * r + 16384u) >> 15;
+        p_hi[g * S + kl] = (uint8_t)(w >> 8);
+        p_lo[g * S + kl] = (uint8_t)(w & 0xff);
+      }
     }
   }
   __syncthreads();
@@ -419,19 +476,18 @@ attn_decode_kernel(const DecodeParams p) {
     for (int m = 0; m < 8; ++m)
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc_hi[m][j] = acc_lo[m][j] = 0;
-    for (int pp = warp; pp < n_pairs; pp += kDecodeWarps) {
-      if (pp != warp) {   // the first pair was requested before the exchanges
-        const uint4* vpa = reinterpret_cast<const uint4*>(p.v_codes + ((int64_t)pages[2 * pp] * p.kv_heads + kh) * (kD * kPage));
+    for (int it = 0; it < n_items; ++it) {
+      const int pp = warp + it * kDecodeWarps;
+      const int j = n_items + it;
+      cp_async_wait<kStages - 1>();
+      __syncwarp();
+      const unsigned char* slot = ring + (j % kStages) * kSlotBytes;
+      const bool has_b = 2 * pp + 1 < my_pages;
+      uint4 va[4], vb[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) va[i] = __ldcs(vpa + i * 32 + lane);
-        if (2 * pp + 1 < my_pages) {
-          const uint4* vpb = reinterpret_cast<const uint4*>(p.v_codes + ((int64_t)pages[2 * pp + 1] * p.kv_heads + kh) * (kD * kPage));
-#pragma unroll
-          for (int i = 0; i < 4; ++i) vb[i] = __ldcs(vpb + i * 32 + lane);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) vb[i] = make_uint4(0, 0, 0, 0);
-        }
+      for (int i = 0; i < 4; ++i) {
+        va[i] = *reinterpret_cast<const uint4*>(slot + i * 512 + lane * 16);
+        vb[i] = has_b ? *reinterpret_cast<const uint4*>(slot + 2048 + i * 512 + lane * 16) : make_uint4(0, 0, 0, 0);
       }
       unsigned bh0 = 0, bh1 = 0, bl0 = 0, bl1 = 0;   // W^T: head fr, tokens 4 fc .. of page A / B
       if (fr < G) {
@@ -447,7 +503,10 @@ attn_decode_kernel(const DecodeParams p) {
         mma_s8u8(acc_hi[m], a0, a1, a2, a3, bh0, bh1);
         mma_s8u8(acc_lo[m], a0, a1, a2, a3, bl0, bl1);
       }
+      __syncwarp();
+      issue(j + kStages);
     }
+    cp_async_wait<0>();
     // C tile: [0] (d = 16m + fr, head 2fc)  [1] (.., 2fc+1)  [2] (d + 8, 2fc)  [3] (d + 8, 2fc+1)
 #pragma unroll
     for (int m = 0; m < 8; ++m)
@@ -498,7 +557,8 @@ attn_decode_kernel(const DecodeParams p) {
 }
 
 static size_t decode_smem_bytes(int G, int s_max) {
-  return (size_t)G * s_max * 6 + (size_t)s_max * 2 + (size_t)(s_max / 16) * 4;
+  return (size_t)kDecodeWarps * kStages * kSlotBytes + (size_t)G * s_max * 6 + (size_t)s_max * 7 +
+         (size_t)(s_max / 16) * 4;
 }
 
 template <int G>

@@ -557,10 +557,10 @@ extern "C" int b200_rmsnorm_q15(const int32_t* x, const int32_t* residual, const
   B200_REQUIRE(hidden % 4 == 0, B200_E_UNSUPPORTED, "rmsnorm_q15: hidden=%d is not a multiple of 4", hidden);
   RowPlan p;
   B200_REQUIRE(plan_rows(hidden, &p), B200_E_UNSUPPORTED, "rmsnorm_q15: hidden=%d exceeds 32768", hidden);
+  if (rows == 0) return B200_OK;
   B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(residual) && aligned16(residual_out) &&
                    aligned16(norm_out) && ((uintptr_t)codes & 3u) == 0,
                B200_E_ALIGN, "rmsnorm_q15: int32 buffers must be 16-byte aligned (codes 4-byte)");
-  if (rows == 0) return B200_OK;
   DISPATCH_VPT(p.vpt, (rmsnorm_rows_kernel<V><<<(unsigned)rows, p.threads, 0, (cudaStream_t)s>>>(
                           x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
   return check_launch("rmsnorm_q15");
@@ -574,9 +574,9 @@ extern "C" int b200_per_token_quant_q15(const int32_t* x, int8_t* codes, float* 
   B200_REQUIRE(k % 4 == 0, B200_E_UNSUPPORTED, "per_token_quant_q15: k=%d is not a multiple of 4", k);
   RowPlan p;
   B200_REQUIRE(plan_rows(k, &p), B200_E_UNSUPPORTED, "per_token_quant_q15: k=%d exceeds 32768", k);
+  if (rows == 0) return B200_OK;
   B200_REQUIRE(aligned16(x) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN,
                "per_token_quant_q15: x must be 16-byte aligned, codes 4-byte");
-  if (rows == 0) return B200_OK;
   DISPATCH_VPT(p.vpt, (quant_rows_kernel<V><<<(unsigned)rows, p.threads, 0, (cudaStream_t)s>>>(
                           x, codes, scale, absmax, k)));
   return check_launch("per_token_quant_q15");
@@ -610,9 +610,9 @@ extern "C" int b200_silu_mul_q15(const int32_t* gate_up, int32_t* q15_out, int8_
                "silu_mul_q15: fwht_block=%d (0 or 128 supported)", fwht_block);
   B200_REQUIRE(inter % 4 == 0 && inter <= 32768, B200_E_UNSUPPORTED,
                "silu_mul_q15: inter=%d must be a multiple of 4 and at most 32768", inter);
+  if (rows == 0) return B200_OK;
   B200_REQUIRE(aligned16(gate_up) && aligned16(q15_out) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN,
                "silu_mul_q15: int32 buffers must be 16-byte aligned (codes 4-byte)");
-  if (rows == 0) return B200_OK;
   cudaStream_t st = (cudaStream_t)s;
   if (inter % 128 != 0) {
     B200_REQUIRE(fwht_block == 0 && !q, B200_E_UNSUPPORTED,
@@ -670,10 +670,10 @@ extern "C" int b200_qk_rope_q15(const int32_t* positions, const int32_t* q, int6
   B200_REQUIRE(q_pitch >= (int64_t)q_heads * 128 && k_pitch >= (int64_t)kv_heads * 128, B200_E_SHAPE,
                "qk_rope_q15: row pitch smaller than heads*128");
   auto a8 = [](const void* p) { return ((uintptr_t)p & 7u) == 0; };
+  if (tokens == 0) return B200_OK;
   B200_REQUIRE(a8(q) && a8(k) && a8(cos_sin) && a8(q_out) && a8(k_out) && a8(q_norm_w) && a8(k_norm_w) &&
                    q_pitch % 2 == 0 && k_pitch % 2 == 0,
                B200_E_ALIGN, "qk_rope_q15: buffers must be 8-byte aligned and pitches even");
-  if (tokens == 0) return B200_OK;
   const int64_t warps = tokens * (q_heads + kv_heads);
   const int64_t blocks = (warps + 7) / 8;
   B200_REQUIRE(blocks < (1ll << 31), B200_E_SHAPE, "qk_rope_q15: too many rows");

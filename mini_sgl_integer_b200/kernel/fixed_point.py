@@ -29,6 +29,8 @@ def to_fixed(x: torch.Tensor) -> torch.Tensor:
     require_cuda(x)
     x = x.contiguous()
     out = torch.empty(x.shape, dtype=torch.int32, device=x.device)
+    if x.numel() == 0:
+        return out
     if x.dtype == torch.bfloat16:
         call("b200_to_fixed_bf16", ptr(x), ptr(out), x.numel(), stream())
     else:
@@ -43,6 +45,8 @@ def from_fixed(x: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Te
     assert_q15(x, "x")
     require_cuda(x)
     x = x.contiguous()
+    if x.numel() == 0:
+        return torch.empty(x.shape, dtype=dtype, device=x.device)
     if dtype == torch.bfloat16:
         out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
         call("b200_from_fixed_bf16", ptr(x), ptr(out), x.numel(), stream())
@@ -104,6 +108,8 @@ def rmsnorm_int_only_v2(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6
     require_cuda(x, weight)
     xc = x.contiguous()
     out = torch.empty_like(xc)
+    if xc.numel() == 0:
+        return out
     call("b200_rmsnorm_q15", ptr(xc), None, ptr(weight.contiguous()), None, ptr(out), None, None, None,
          xc.numel() // hidden, hidden, stream())
     return out
@@ -125,6 +131,8 @@ def fused_add_rmsnorm_int_only_v2(residual: torch.Tensor, x: torch.Tensor, weigh
     require_cuda(residual, x, weight)
     xc, rc = x.contiguous(), residual.contiguous()
     out, res_out = torch.empty_like(xc), torch.empty_like(rc)
+    if xc.numel() == 0:
+        return out, res_out
     call("b200_rmsnorm_q15", ptr(xc), ptr(rc), ptr(weight.contiguous()), ptr(res_out), ptr(out), None, None,
          None, xc.numel() // hidden, hidden, stream())
     return out, res_out
@@ -139,6 +147,8 @@ def silu_and_mul_int_only(x: torch.Tensor) -> torch.Tensor:
     require_cuda(x)
     xc = x.contiguous()
     out = torch.empty((batch, hidden), dtype=torch.int32, device=x.device)
+    if out.numel() == 0:
+        return out
     call("b200_silu_mul_q15", ptr(xc), ptr(out), None, None, None, batch, hidden, 0, stream())
     return out
 
@@ -156,7 +166,7 @@ def fwht_int_q15(x_q15: torch.Tensor, *, normalize: bool = True) -> torch.Tensor
     require_cuda(x_q15)
     xc = x_q15.contiguous()
     out = torch.empty_like(xc)
-    if head_dim == 1:
+    if head_dim == 1 or xc.numel() == 0:
         out.copy_(xc)  # a 1-point transform is the identity (scale round(2**15) >> 15 == 1)
         return out
     call("b200_fwht_q15", ptr(xc), ptr(out), xc.numel() // head_dim, head_dim, int(bool(normalize)), stream())
@@ -279,7 +289,8 @@ def per_token_quant_int8_from_q15(x_q15: torch.Tensor, return_absmax: bool = Fal
     codes = torch.empty(xc.shape, dtype=torch.int8, device=xc.device)
     scale = torch.empty(xc.shape[:-1] + (1,), dtype=torch.float32, device=xc.device)
     absmax = torch.empty(xc.shape[:-1] + (1,), dtype=torch.int32, device=xc.device)
-    call("b200_per_token_quant_q15", ptr(xc), ptr(codes), ptr(scale), ptr(absmax), rows, k, stream())
+    if xc.numel() > 0:
+        call("b200_per_token_quant_q15", ptr(xc), ptr(codes), ptr(scale), ptr(absmax), rows, k, stream())
     return (codes, scale, absmax) if return_absmax else (codes, scale)
 
 

@@ -196,9 +196,13 @@ def test_rope_and_qk_norm_fused_vs_oracle(fp):
     q, k = qkv[:, : Hq * 128], qkv[:, Hq * 128 : (Hq + Hk) * 128]
     eq_, ek_ = ofp.rope_q15(pos, q.reshape(T, Hq, 128), k.reshape(T, Hk, 128), cache)
     dq = dev(qkv)
-    gq, gk = fp.rope_int_q15(dev(pos), dq[:, : Hq * 128], dq[:, Hq * 128 : (Hq + Hk) * 128], dev(cache))
-    assert gq.shape == (T, Hq * 128) and gk.shape == (T, Hk * 128)     # 2-D in -> 2-D out
-    eq(host(gq).reshape(T, Hq, 128), eq_); eq(host(gk).reshape(T, Hk, 128), ek_)
+    q3 = dq[:, : Hq * 128].view(T, Hq, 128)                              # strided views into the qkv buffer
+    k2 = dq[:, Hq * 128 : (Hq + Hk) * 128]
+    gq, gk = fp.rope_int_q15(dev(pos), q3, k2, dev(cache))
+    assert gq.shape == (T, Hq, 128) and gk.shape == (T, Hk * 128)      # 3-D in -> 3-D out, 2-D in -> 2-D out
+    eq(host(gq), eq_); eq(host(gk).reshape(T, Hk, 128), ek_)
+    with pytest.raises(ValueError, match="Ambiguous"):                  # as the reference: 2-D q and k of 1024 / 256
+        fp.rope_int_q15(dev(pos), dq[:, : Hq * 128], k2, dev(cache))
     fq, fk = ofp.rope_fwht_q15(pos, q.reshape(T, Hq, 128), k.reshape(T, Hk, 128), cache)
     gq, gk = fp.rope_fwht_int_q15(dev(pos), dev(q.reshape(T, Hq, 128)), dev(k.reshape(T, Hk, 128)), dev(cache))
     eq(host(gq), fq); eq(host(gk), fk)
@@ -207,9 +211,8 @@ def test_rope_and_qk_norm_fused_vs_oracle(fp):
     nq = ofp.rmsnorm_v2(np.ascontiguousarray(q), qw).reshape(T, Hq, 128)
     nk = ofp.rmsnorm_v2(np.ascontiguousarray(k), kw).reshape(T, Hk, 128)
     fq, fk = ofp.rope_fwht_q15(pos, nq, nk, cache)
-    gq, gk = fp.qk_norm_rope_fwht(dev(pos), dq[:, : Hq * 128], dq[:, Hq * 128 : (Hq + Hk) * 128], dev(cache),
-                                  dev(qw), dev(kw))
-    eq(host(gq).reshape(T, Hq, 128), fq); eq(host(gk).reshape(T, Hk, 128), fk)
+    gq, gk = fp.qk_norm_rope_fwht(dev(pos), q3, k2, dev(cache), dev(qw), dev(kw))
+    eq(host(gq), fq); eq(host(gk).reshape(T, Hk, 128), fk)
 
 
 @pytest.mark.parametrize("rows,k", [(1, 4), (5, 128), (3, 1000), (4, 5120), (2, 17408), (1, 32768)])
