@@ -151,22 +151,31 @@ __device__ __forceinline__ unsigned word_of(const uint4 (&v)[4], int wi) {
 constexpr int kDecodeWarps = 4;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kStages = 2;                 // ring slots per warp
-constexpr int kSlotMeta = 4096;            // K slots: the two pages' scale blocks follow the codes
-constexpr int kSlotBytes = 4096 + 2 * 192; // one slot = a pair of pages (+ 2 x 160 B of scales, padded)
+constexpr int kSlotBytes = 4096;           // one slot = a pair of pages (K rows, or V in operand order)
+constexpr int kMetaBytes = kMetaWords * 4; // 160
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+__device__ __forceinline__ void cp_async16(unsigned smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// sat32 of the rounding multiply-shift for the common case 0 < s < 63 (general form otherwise).
+// sat32((x*m + 2^(s-1)) >> s) for 0 < s < 63 without 64-bit variable shifts of the product
+// (general form otherwise).  x*m is exact in 64 bits.
 __device__ __forceinline__ int mul_shift_sat32(int x, int m, int s) {
   if (s > 0 && s < 63) {
-    const long long prod = (long long)x * (long long)m + (1LL << (s - 1));   // |x*m| < 2^62
-    return sat32(prod >> s);
+    long long prod = (long long)x * (long long)m;
+    if (s <= 32) {
+      prod += (long long)(1u << (s - 1));
+      const int hi = (int)(prod >> 32);
+      const unsigned lo = (unsigned)prod;
+      const int res = (int)__funnelshift_rc(lo, (unsigned)hi, s);  // low 32 bits of prod >> s (clamped: s == 32 gives hi)
+      const int top = s == 32 ? (hi >> 31) : (hi >> s);             // bits 32.. of prod >> s
+      return top == (res >> 31) ? res : (top < 0 ? (int)(-2147483647 - 1) : 2147483647);
+    }
+    prod += 1LL << (s - 1);
+    return (int)(prod >> 32) >> (s - 32);   // fits int32: |prod| < 2^63
   }
   return sat32(mul_shift64((long long)x, (long long)m, s));
 }
@@ -189,16 +198,17 @@ __device__ __forceinline__ unsigned rel_scale_q15(unsigned v_mul, unsigned m_ref
 }
 
 // Both contractions run on the integer tensor-core MMA with the long dimension on M:
-//   scores^T [16 keys x 8 heads] = K page [16 x 128] . Q^T [128 x 8]      (4 k-steps of 32 d)
-//   out^T    [16 d    x 8 heads] = V^T [16 x 32 tokens] . W^T [32 x 8]    (two pages per k-step)
+//   dots^T [16 keys x 8 heads] = K page [16 x 128] . Q^T [128 x 8]        (4 k-steps of 32 d)
+//   out^T  [16 d    x 8 heads] = V^T [16 x 32 tokens] . W^T [32 x 8]      (two pages per k-step)
 // so a page is exactly one M tile and the (<= 8) query heads of the group are the N columns.
-// Every warp streams its own page pairs (first the K pairs of its share of the slice, each with
-// the pages' scale blocks, then the V pairs) through a private ring of shared-memory slots filled
-// by 16-byte asynchronous copies, so the loads of the next pair - including the first V pairs -
-// are in flight while the warp computes and while the cluster exchanges the softmax statistics.
-// Each lane reads its MMA registers from the slot with 128-bit loads: K rows 32 contiguous bytes
-// per lane (the d axis is permuted identically in Q; 16-byte columns are XOR-swizzled by the row
-// parity on the way in), V in the operand order of v_chunk_offset.
+// Every warp streams its own page pairs (first the K pairs of its share of the slice, then the V
+// pairs) through a private ring of shared-memory slots filled by 16-byte asynchronous copies, so
+// the loads of the next pair - including the first V pairs - are in flight while the warp
+// computes and while the cluster exchanges the softmax statistics.  Each lane reads its MMA
+// registers from the slot with 128-bit loads: K rows 32 contiguous bytes per lane (the d axis is
+// permuted identically in Q; 16-byte columns are XOR-swizzled by the row parity on the way in),
+// V in the operand order of v_chunk_offset.  The per-key fixed-point work (scale, exp, relative V
+// scale, probability limbs) runs in flat one-thread-per-key loops between the two MMA phases.
 template <int G>
 __global__ void __launch_bounds__(kDecodeThreads, 4)
 attn_decode_kernel(const DecodeParams p) {
@@ -215,12 +225,11 @@ attn_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* ring = smem_raw + warp * (kStages * kSlotBytes);      // this warp's slots
   int32_t* sc = reinterpret_cast<int32_t*>(smem_raw + kDecodeWarps * kStages * kSlotBytes);  // [G][S]
-  int32_t* vm_s = sc + G * S;                                         // [S] V multipliers
-  uint8_t* p_hi = reinterpret_cast<uint8_t*>(vm_s + S);               // [G][S]
+  int32_t* meta_s = sc + G * S;                                       // [S/16][40] scale blocks
+  uint8_t* p_hi = reinterpret_cast<uint8_t*>(meta_s + (S / 16) * kMetaWords);   // [G][S]
   uint8_t* p_lo = p_hi + G * S;                                       // [G][S]
   uint16_t* rel = reinterpret_cast<uint16_t*>(p_lo + G * S);          // [S]
-  int8_t* vs_s = reinterpret_cast<int8_t*>(rel + S);                  // [S] V shifts
-  int32_t* pages = reinterpret_cast<int32_t*>(vs_s + S);              // [S / 16]
+  int32_t* pages = reinterpret_cast<int32_t*>(rel + S);               // [S / 16]
 
   __shared__ int q_mul_s[G], q_shift_s[G];
   __shared__ int cta_max[G];
@@ -273,116 +282,133 @@ attn_decode_kernel(const DecodeParams p) {
   }
   __syncthreads();
 
+  // The pages' scale blocks (160 B each) go to a part of shared memory that is kept: first
+  // commit group of every thread.
+  {
+    const unsigned meta_base = (unsigned)__cvta_generic_to_shared(meta_s);
+    for (int i = tid; i < my_pages * 10; i += kDecodeThreads) {
+      const int pg = i / 10, c16 = i - pg * 10;
+      cp_async16(meta_base + pg * kMetaBytes + c16 * 16,
+                 reinterpret_cast<const unsigned char*>(p.meta + ((int64_t)pages[pg] * p.kv_heads + kh) * kMetaWords) + c16 * 16);
+    }
+    cp_async_commit();
+  }
+
   // Item j of this warp: j < n_items is the K copy of pair (warp + j * warps), otherwise the V
   // copy of pair (warp + (j - n_items) * warps).  One commit group per item, also when empty.
   // A lane moves the 16-byte columns lane, lane+32, lane+64, lane+96 of each 2 KB chunk.
-  int k_dst[4];
+  const unsigned ring_base = (unsigned)__cvta_generic_to_shared(ring);
+  unsigned k_dst[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int ch = lane + 32 * i;
     k_dst[i] = ((ch >> 3) << 7) | (((ch & 7) ^ ((ch >> 3) & 1)) << 4);
   }
-  auto issue = [&](int j) {
-    if (j < 2 * n_items) {
-      const bool is_k = j < n_items;
-      const int pp = warp + (is_k ? j : j - n_items) * kDecodeWarps;
-      unsigned char* slot = ring + (j % kStages) * kSlotBytes;
-      const unsigned char* base = reinterpret_cast<const unsigned char*>(is_k ? p.k_codes : p.v_codes);
+  const int64_t head_off = (int64_t)kh * (kPage * kD) + (lane << 4);
+  const int64_t page_stride = (int64_t)p.kv_heads * (kPage * kD);
+  auto issue_k = [&](int it) {   // it-th K pair of this warp
+    if (it < n_items) {
+      const int pp = warp + it * kDecodeWarps;
+      const unsigned slot = ring_base + (it % kStages) * kSlotBytes;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int pg = 2 * pp + h;
-        if (pg < my_pages) {
-          const int64_t chunk = (int64_t)pages[pg] * p.kv_heads + kh;
-          const unsigned char* src = base + chunk * (kPage * kD) + (lane << 4);
-          unsigned char* dst = slot + h * 2048;
+        if (2 * pp + h < my_pages) {
+          const unsigned char* src = reinterpret_cast<const unsigned char*>(p.k_codes) + pages[2 * pp + h] * page_stride + head_off;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) cp_async16(dst + (is_k ? k_dst[i] : ((lane + 32 * i) << 4)), src + i * 512);
-          if (is_k && (lane & 15) < 10 && (lane >> 4) == h)
-            cp_async16(slot + kSlotMeta + h * 192 + ((lane & 15) << 4),
-                       reinterpret_cast<const unsigned char*>(p.meta + chunk * kMetaWords) + ((lane & 15) << 4));
+          for (int i = 0; i < 4; ++i) cp_async16(slot + h * 2048 + k_dst[i], src + i * 512);
         }
       }
     }
     cp_async_commit();
   };
+  auto issue_v = [&](int it) {   // it-th V pair of this warp; ring position continues after the K items
+    if (it < n_items) {
+      const int pp = warp + it * kDecodeWarps;
+      const unsigned slot = ring_base + ((n_items + it) % kStages) * kSlotBytes + (lane << 4);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (2 * pp + h < my_pages) {
+          const unsigned char* src = reinterpret_cast<const unsigned char*>(p.v_codes) + pages[2 * pp + h] * page_stride + head_off;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) cp_async16(slot + h * 2048 + i * 512, src + i * 512);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+  auto issue = [&](int j) { if (j < n_items) issue_k(j); else issue_v(j - n_items); };
 #pragma unroll
   for (int j = 0; j < kStages; ++j) issue(j);
 
-  // ---- phase 1: scores of the slice, one page (16 keys) per MMA tile
+  // ---- phase 1: raw int32 dots of the slice, one page (16 keys) per MMA tile
   {
-    int lmax0 = kNeg, lmax1 = kNeg;   // heads 2 fc and 2 fc + 1
-    unsigned long long lvref = ~0ull;
     const bool h0 = 2 * fc < G, h1 = 2 * fc + 1 < G;
-    const int g0 = 2 * fc, g1 = 2 * fc + 1;
-    const int qm0 = h0 ? q_mul_s[g0] : 0, qs0 = h0 ? q_shift_s[g0] - 48 : 0;
-    const int qm1 = h1 ? q_mul_s[g1] : 0, qs1 = h1 ? q_shift_s[g1] - 48 : 0;
-    const int sw = fr & 1;
+    int32_t* sc0 = sc + (2 * fc) * S + fr;
+    int32_t* sc1 = sc0 + S;
+    const int o0 = ((2 * fc) ^ (fr & 1)) << 4, o1 = ((2 * fc + 1) ^ (fr & 1)) << 4;
     for (int it = 0; it < n_items; ++it) {
       const int pp = warp + it * kDecodeWarps;
       cp_async_wait<kStages - 1>();
       __syncwarp();
-      const unsigned char* slot = ring + (it % kStages) * kSlotBytes;
+      const unsigned char* slot = ring + (it % kStages) * kSlotBytes + fr * 128;   // rows fr, fr + 8: same parity
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int pg = 2 * pp + h;
-        const int kl0 = pg * 16 + fr, kl1 = kl0 + 8;       // the two keys this lane sees in the C tile
-        int v0 = kNeg, v1 = kNeg, v2 = kNeg, v3 = kNeg;
-        if (pg < my_pages) {
-          const unsigned char* r0 = slot + h * 2048 + fr * 128;   // rows fr and fr + 8 share a parity
-          const uint4 k00 = *reinterpret_cast<const uint4*>(r0 + (((2 * fc) ^ sw) << 4));
-          const uint4 k01 = *reinterpret_cast<const uint4*>(r0 + (((2 * fc + 1) ^ sw) << 4));
-          const uint4 k10 = *reinterpret_cast<const uint4*>(r0 + 1024 + (((2 * fc) ^ sw) << 4));
-          const uint4 k11 = *reinterpret_cast<const uint4*>(r0 + 1024 + (((2 * fc + 1) ^ sw) << 4));
-          const int32_t* mt = reinterpret_cast<const int32_t*>(slot + kSlotMeta + h * 192);
-          const int km0 = mt[fr], km1 = mt[fr + 8];
-          const int ks0 = reinterpret_cast<const int8_t*>(mt + 32)[fr], ks1 = reinterpret_cast<const int8_t*>(mt + 32)[fr + 8];
-          if (fc == 3) {   // one lane per key row keeps the V scales and tracks the reference scale
-#pragma unroll
-            for (int hlf = 0; hlf < 2; ++hlf) {
-              const int tok = fr + 8 * hlf;
-              const int kl = pg * 16 + tok;
-              const int v_mul = mt[16 + tok];
-              const int v_shift = reinterpret_cast<const int8_t*>(mt + 36)[tok];
-              vm_s[kl] = v_mul;
-              vs_s[kl] = (int8_t)v_shift;
-              if (kl < my_keys) {
-                const unsigned long long vkey = ((unsigned long long)(unsigned)(v_shift + 128) << 32) |
-                                                (unsigned long long)(0xFFFFFFFFu - (unsigned)v_mul);
-                lvref = vkey < lvref ? vkey : lvref;
-              }
-            }
-          }
-          int c[4] = {0, 0, 0, 0};
+        int c[4] = {0, 0, 0, 0};
+        if (2 * pp + h < my_pages) {
+          const unsigned char* r0 = slot + h * 2048;
+          const uint4 k00 = *reinterpret_cast<const uint4*>(r0 + o0);
+          const uint4 k01 = *reinterpret_cast<const uint4*>(r0 + o1);
+          const uint4 k10 = *reinterpret_cast<const uint4*>(r0 + 1024 + o0);
+          const uint4 k11 = *reinterpret_cast<const uint4*>(r0 + 1024 + o1);
           mma_s8s8(c, k00.x, k10.x, k00.y, k10.y, qw[0], qw[1]);
           mma_s8s8(c, k00.z, k10.z, k00.w, k10.w, qw[2], qw[3]);
           mma_s8s8(c, k01.x, k11.x, k01.y, k11.y, qw[4], qw[5]);
           mma_s8s8(c, k01.z, k11.z, k01.w, k11.w, qw[6], qw[7]);
-          // c[0]: (key kl0, head 2fc)  c[1]: (kl0, 2fc+1)  c[2]: (kl1, 2fc)  c[3]: (kl1, 2fc+1)
-          if (h0) {
-            if (kl0 < my_keys) v0 = mul_shift_sat32(c[0], __mulhi(qm0, km0), qs0 + ks0);
-            if (kl1 < my_keys) v2 = mul_shift_sat32(c[2], __mulhi(qm0, km1), qs0 + ks1);
-          }
-          if (h1) {
-            if (kl0 < my_keys) v1 = mul_shift_sat32(c[1], __mulhi(qm1, km0), qs1 + ks0);
-            if (kl1 < my_keys) v3 = mul_shift_sat32(c[3], __mulhi(qm1, km1), qs1 + ks1);
-          }
         }
-        if (h0) { sc[g0 * S + kl0] = v0; sc[g0 * S + kl1] = v2; lmax0 = max(lmax0, max(v0, v2)); }
-        if (h1) { sc[g1 * S + kl0] = v1; sc[g1 * S + kl1] = v3; lmax1 = max(lmax1, max(v1, v3)); }
+        // c[0]: (key fr, head 2fc)  c[1]: (fr, 2fc+1)  c[2]: (fr + 8, 2fc)  c[3]: (fr + 8, 2fc+1)
+        const int kl = (2 * pp + h) * 16;
+        if (h0) { sc0[kl] = c[0]; sc0[kl + 8] = c[2]; }
+        if (h1) { sc1[kl] = c[1]; sc1[kl + 8] = c[3]; }
       }
       __syncwarp();
       issue(it + kStages);
     }
-    // lanes with equal fc hold the same pair of heads: reduce over fr (lane bits 2..4)
+  }
+  cp_async_wait<kStages>();   // the scale blocks (oldest group) have landed
+  __syncthreads();
+
+  // ---- phase 1b: Q15.16 scores, their maximum, and the reference V scale; one thread per key
+  {
+    int lmax[G], qm[G], qs[G];
 #pragma unroll
-    for (int o = 4; o < 32; o <<= 1) {
-      lmax0 = max(lmax0, __shfl_xor_sync(FULL_MASK, lmax0, o));
-      lmax1 = max(lmax1, __shfl_xor_sync(FULL_MASK, lmax1, o));
+    for (int g = 0; g < G; ++g) { lmax[g] = kNeg; qm[g] = q_mul_s[g]; qs[g] = q_shift_s[g] - 48; }
+    int best_s = 0x7fffffff;
+    unsigned best_m = 0;
+    for (int kl = tid; kl < n_slots; kl += kDecodeThreads) {
+      if (kl < my_keys) {
+        const int32_t* mt = meta_s + (kl >> 4) * kMetaWords;
+        const int tok = kl & 15;
+        const int km = mt[tok];
+        const int ks = reinterpret_cast<const int8_t*>(mt + 32)[tok];
+        const unsigned vm = (unsigned)mt[16 + tok];
+        const int vs = reinterpret_cast<const int8_t*>(mt + 36)[tok];
+        if (vs < best_s || (vs == best_s && vm > best_m)) { best_s = vs; best_m = vm; }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const int v = mul_shift_sat32(sc[g * S + kl], __mulhi(qm[g], km), qs[g] + ks);
+          sc[g * S + kl] = v;
+          lmax[g] = max(lmax[g], v);
+        }
+      }
     }
-    if (fr == 0) {
-      if (h0) atomicMax(&cta_max[g0], lmax0);
-      if (h1) atomicMax(&cta_max[g1], lmax1);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int m = warp_max(lmax[g]);
+      if (lane == 0) atomicMax(&cta_max[g], m);
     }
+    unsigned long long lvref = best_s == 0x7fffffff
+                                   ? ~0ull
+                                   : (((unsigned long long)(unsigned)(best_s + 128) << 32) | (unsigned long long)(0xFFFFFFFFu - best_m));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const unsigned long long other = __shfl_xor_sync(FULL_MASK, lvref, o);
@@ -429,7 +455,12 @@ attn_decode_kernel(const DecodeParams p) {
         lsum[g] += e;
       }
       unsigned r = 0;
-      if (valid) r = rel_scale_q15((unsigned)vm_s[kl], (unsigned)v_mul_ref, (int)vs_s[kl] - v_shift_ref);
+      if (valid) {
+        const int32_t* mt = meta_s + (kl >> 4) * kMetaWords;
+        const int tok = kl & 15;
+        r = rel_scale_q15((unsigned)mt[16 + tok], (unsigned)v_mul_ref,
+                          (int)reinterpret_cast<const int8_t*>(mt + 36)[tok] - v_shift_ref);
+      }
       rel[kl] = (uint16_t)r;
     }
 #pragma unroll
@@ -476,25 +507,27 @@ attn_decode_kernel(const DecodeParams p) {
     for (int m = 0; m < 8; ++m)
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc_hi[m][j] = acc_lo[m][j] = 0;
+    const uint8_t* ph = p_hi + fr * S + fc * 4;
+    const uint8_t* pl = p_lo + fr * S + fc * 4;
     for (int it = 0; it < n_items; ++it) {
       const int pp = warp + it * kDecodeWarps;
       const int j = n_items + it;
       cp_async_wait<kStages - 1>();
       __syncwarp();
-      const unsigned char* slot = ring + (j % kStages) * kSlotBytes;
+      const unsigned char* slot = ring + (j % kStages) * kSlotBytes + lane * 16;
       const bool has_b = 2 * pp + 1 < my_pages;
       uint4 va[4], vb[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        va[i] = *reinterpret_cast<const uint4*>(slot + i * 512 + lane * 16);
-        vb[i] = has_b ? *reinterpret_cast<const uint4*>(slot + 2048 + i * 512 + lane * 16) : make_uint4(0, 0, 0, 0);
+        va[i] = *reinterpret_cast<const uint4*>(slot + i * 512);
+        vb[i] = has_b ? *reinterpret_cast<const uint4*>(slot + 2048 + i * 512) : make_uint4(0, 0, 0, 0);
       }
       unsigned bh0 = 0, bh1 = 0, bl0 = 0, bl1 = 0;   // W^T: head fr, tokens 4 fc .. of page A / B
       if (fr < G) {
-        bh0 = *reinterpret_cast<const unsigned*>(p_hi + fr * S + pp * 32 + fc * 4);
-        bh1 = *reinterpret_cast<const unsigned*>(p_hi + fr * S + pp * 32 + 16 + fc * 4);
-        bl0 = *reinterpret_cast<const unsigned*>(p_lo + fr * S + pp * 32 + fc * 4);
-        bl1 = *reinterpret_cast<const unsigned*>(p_lo + fr * S + pp * 32 + 16 + fc * 4);
+        bh0 = *reinterpret_cast<const unsigned*>(ph + pp * 32);
+        bh1 = *reinterpret_cast<const unsigned*>(ph + pp * 32 + 16);
+        bl0 = *reinterpret_cast<const unsigned*>(pl + pp * 32);
+        bl1 = *reinterpret_cast<const unsigned*>(pl + pp * 32 + 16);
       }
 #pragma unroll
       for (int m = 0; m < 8; ++m) {
@@ -504,7 +537,7 @@ attn_decode_kernel(const DecodeParams p) {
         mma_s8u8(acc_lo[m], a0, a1, a2, a3, bl0, bl1);
       }
       __syncwarp();
-      issue(j + kStages);
+      issue_v(it + kStages);
     }
     cp_async_wait<0>();
     // C tile: [0] (d = 16m + fr, head 2fc)  [1] (.., 2fc+1)  [2] (d + 8, 2fc)  [3] (d + 8, 2fc+1)
@@ -557,8 +590,8 @@ attn_decode_kernel(const DecodeParams p) {
 }
 
 static size_t decode_smem_bytes(int G, int s_max) {
-  return (size_t)kDecodeWarps * kStages * kSlotBytes + (size_t)G * s_max * 6 + (size_t)s_max * 7 +
-         (size_t)(s_max / 16) * 4;
+  return (size_t)kDecodeWarps * kStages * kSlotBytes + (size_t)G * s_max * 6 + (size_t)s_max * 2 +
+         (size_t)(s_max / 16) * (kMetaBytes + 4);
 }
 
 template <int G>
