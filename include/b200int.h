@@ -154,6 +154,27 @@ B200_API int b200_attn_decode(const int8_t* q, const int32_t* q_mul, const int32
                      int batch, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
                      int cluster, b200_stream_t s);
 
+/* ---- W8A8 linear: int8 x int8 -> int32 on the tcgen05 tensor cores, fixed-point requant.
+ * Stands in for the GEMM + epilogue inside W8A8Int8LinearMethod.apply_weights_q15
+ * (layers/quantization/w8a8_int8.py:242-286), i.e. the sgl_kernel.int8_scaled_mm call at :272-279
+ * and the conversions around it; the per-token quant that precedes it is b200_per_token_quant_q15
+ * or one of the fused row kernels.
+ *   x8 int8 [m, k] (token rows), w8 int8 [n, k] (the checkpoint's [out, in] layout, untransposed);
+ *   x_mul, x_shift int32 [m]: fixed-point per-token scale (b200_absmax_to_mul_shift);
+ *   w_mul int32 [n], w_shift int32 [n] (nullable = 31 everywhere): per-output-channel scale;
+ *   out_q15 int32 [m, n] (nullable): sat32(mul_shift(acc, (x_mul*w_mul)>>32, x_shift+w_shift-48));
+ *   acc_out int32 [m, n] (nullable): the exact int32 accumulators.
+ * k must be a multiple of 16.  Builds two TMA descriptors on the host per call. */
+B200_API int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t* x_mul,
+                            const int32_t* x_shift, const int32_t* w_mul, const int32_t* w_shift,
+                            int32_t* out_q15, int32_t* acc_out, int64_t m, int64_t n, int64_t k,
+                            b200_stream_t s);
+
+/* Reads (and optionally clears) the device-side status word of the GEMM kernels: 0 = fine,
+ * non-zero = a bounded wait inside a kernel expired (1 producer, 2 MMA issuer, 3 epilogue).
+ * Synchronises with the device.  No counterpart in the reference. */
+B200_API int b200_gemm_status(int* out_host, int reset);
+
 #ifdef __cplusplus
 }
 #endif

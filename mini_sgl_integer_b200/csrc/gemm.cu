@@ -1,0 +1,323 @@
+// W8A8 linear on the 5th-generation tensor cores: int8 x int8 -> int32 accumulators in tensor
+// memory (tcgen05.mma kind::i8), operands staged by TMA into 128-byte-swizzled shared memory,
+// fixed-point requant epilogue read back with tcgen05.ld.
+//
+//   acc[t, n]  = sum_k x8[t, k] * w8[n, k]                      exact int32
+//   out[t, n]  = sat32(mul_shift(acc, (x_mul[t] * w_mul[n]) >> 32, x_shift[t] + w_shift[n] - 48))
+//
+// Both operands are K-major (x8 [M, K] and w8 [N, K] row-major), which is what the UMMA wants.
+// One CTA computes one 128 x BN output tile:
+//   warp 0        TMA producer (one lane): A tile 128 x 128 B and B tile BN x 128 B per k-block
+//   warp 1        allocates tensor memory; one lane issues the MMAs (4 per k-block, K = 32 each)
+//   warps 2..5    epilogue: each reads its 32-lane quarter of the accumulator tile
+// Stages are handed over with mbarriers (TMA -> MMA by transaction bytes, MMA -> TMA and
+// MMA -> epilogue by tcgen05.commit).  Every wait is bounded: on expiry the waiter raises an
+// error flag that the host can read, and the CTA still runs to its end and frees its tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kBM = 128;            // rows of x per tile (UMMA M)
+constexpr int kBK = 128;            // bytes of K per stage = one 128-byte swizzle row
+constexpr int kUmmaK = 32;          // K per tcgen05.mma for 8-bit operands
+constexpr int kGemmThreads = 192;
+constexpr unsigned kSpinLimit = 1u << 22;
+
+__device__ int g_gemm_status = 0;   // 0 = fine; otherwise the code of the first wait that gave up
+
+// ----------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false (and the status flag) on expiry.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int code) {
+  for (unsigned it = 0; it < kSpinLimit; ++it) {
+    unsigned ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  atomicCAS(&g_gemm_status, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_i8(unsigned tmem_d, uint64_t desc_a, uint64_t desc_b, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(unsigned taddr, int (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory operand descriptor: K-major tile whose rows are 128 bytes, 128-byte swizzle.
+// Eight rows form one 1024-byte swizzle atom, so the stride between 8-row groups is 1024 bytes;
+// the leading-dimension offset is unused in this mode.  Bits: [0,14) address >> 4,
+// [32,46) stride >> 4, [46,48) descriptor version 1, [61,64) layout 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t make_smem_desc(unsigned addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::i8: D = s32 (2 << 4), A = B = signed 8-bit (1 << 7, 1 << 10),
+// both K-major (bits 15, 16 clear), N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr unsigned make_idesc(int m, int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+
+struct GemmParams {
+  const int32_t* x_mul;
+  const int32_t* x_shift;
+  const int32_t* w_mul;
+  const int32_t* w_shift;   // nullable: every channel uses shift 31
+  int32_t* out_q15;         // nullable
+  int32_t* acc_out;         // nullable
+  int M, N, K;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmParams p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  constexpr int kABytes = kBM * kBK;
+  constexpr int kBBytes = BN * kBK;
+  constexpr int kStageBytes = kABytes + kBBytes;
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * kStageBytes);   // full[S], empty[S], tmem_full
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_blk = blockIdx.x, m_blk = blockIdx.y;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), tfull = smem_u32(bars + 2 * STAGES);
+
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(tfull, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // the whole warp allocates BN columns (a power of two >= 32) of tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const unsigned ph = (kb / STAGES) & 1;
+        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, 1)) break;
+        mbar_expect_tx(full0 + 8 * s, kStageBytes);
+        const unsigned a_dst = smem_u32(tiles + s * kStageBytes);
+        tma_load_2d(a_dst, &map_a, kb * kBK, m_blk * kBM, full0 + 8 * s);
+        tma_load_2d(a_dst + kABytes, &map_b, kb * kBK, n_blk * BN, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr unsigned idesc = make_idesc(kBM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const unsigned ph = (kb / STAGES) & 1;
+        ok = mbar_wait(full0 + 8 * s, ph, 2);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const unsigned a_addr = smem_u32(tiles + s * kStageBytes);
+        const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + kABytes);
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          // the next 32 bytes of K inside the swizzle row: start address + 32 (encoded >> 4)
+          umma_i8(tmem_base, da + (uint64_t)(k * kUmmaK >> 4), db + (uint64_t)(k * kUmmaK >> 4), idesc,
+                  (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        tcgen05_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
+      }
+      tcgen05_commit(tfull);              // accumulators complete (or abandoned): release the epilogue
+    }
+  } else {
+    // epilogue warps 2..5: TMEM lane quarter = warp % 4, one accumulator row per thread
+    const int q = warp & 3;
+    const int row = m_blk * kBM + q * 32 + lane;
+    const bool ok = mbar_wait(tfull, 0, 3);
+    tcgen05_fence_after();
+    int xm = 0, xs = 0;
+    if (row < p.M && p.out_q15) { xm = p.x_mul[row]; xs = p.x_shift[row] - 48; }
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      int v[32];
+      tmem_ld_32x32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+      const int col0 = n_blk * BN + c0;
+      if (ok && row < p.M && num_kb > 0) {
+        if (p.acc_out) {
+          int32_t* dst = p.acc_out + (int64_t)row * p.N + col0;
+          if (col0 + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4*>(dst + j) = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
+          }
+        }
+        if (p.out_q15) {
+          int32_t* dst = p.out_q15 + (int64_t)row * p.N + col0;
+          const bool full = col0 + 32 <= p.N && (p.N & 3) == 0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            int o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int col = min(col0 + j + e, p.N - 1);
+              const int wm = __ldg(p.w_mul + col);
+              const int ws = p.w_shift ? __ldg(p.w_shift + col) : 31;
+              const int s = xs + ws;
+              const int cm = __mulhi(xm, wm);
+              long long r;
+              if (s > 0 && s < 63) {
+                r = ((long long)v[j + e] * (long long)cm + (1LL << (s - 1))) >> s;
+              } else {
+                r = mul_shift64((long long)v[j + e], (long long)cm, s);
+              }
+              o[e] = sat32(r);
+            }
+            if (full) {
+              *reinterpret_cast<int4*>(dst + j) = make_int4(o[0], o[1], o[2], o[3]);
+            } else {
+              for (int e = 0; e < 4; ++e)
+                if (col0 + j + e < p.N) dst[j + e] = o[e];
+            }
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+  }
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// int8 matrix [rows, K] row-major; box = 128 bytes of K x box_rows rows, 128-byte swizzle, zero fill.
+static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
+  constexpr size_t smem = (size_t)STAGES * (kBM * kBK + BN * kBK) + 1024 + (2 * STAGES + 1) * 8 + 16;
+  cudaError_t e = cudaFuncSetAttribute(gemm_w8a8_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_error("gemm_w8a8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    return B200_E_CUDA;
+  }
+  dim3 grid((p.N + BN - 1) / BN, (p.M + kBM - 1) / kBM);
+  gemm_w8a8_kernel<BN, STAGES><<<grid, kGemmThreads, smem, st>>>(ma, mb, p);
+  return check_launch("gemm_w8a8");
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t* x_mul, const int32_t* x_shift,
+                              const int32_t* w_mul, const int32_t* w_shift, int32_t* out_q15, int32_t* acc_out,
+                              int64_t m, int64_t n, int64_t k, b200_stream_t s) {
+  B200_REQUIRE(x8 && w8, B200_E_NULL, "gemm_w8a8: x8 or w8 is null");
+  B200_REQUIRE(out_q15 || acc_out, B200_E_NULL, "gemm_w8a8: no output requested");
+  B200_REQUIRE(!out_q15 || (x_mul && x_shift && w_mul), B200_E_NULL,
+               "gemm_w8a8: the Q15.16 output needs x_mul, x_shift and w_mul");
+  B200_REQUIRE(m >= 0 && n > 0 && k > 0 && m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), B200_E_SHAPE,
+               "gemm_w8a8: m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
+  B200_REQUIRE(k % 16 == 0, B200_E_UNSUPPORTED, "gemm_w8a8: k=%lld must be a multiple of 16 (TMA row pitch)", (long long)k);
+  if (m == 0) return B200_OK;
+  B200_REQUIRE(aligned16(x8) && aligned16(w8) && aligned16(out_q15) && aligned16(acc_out), B200_E_ALIGN,
+               "gemm_w8a8: buffers must be 16-byte aligned");
+  CUtensorMap ma, mb;
+  B200_REQUIRE(make_map(&ma, x8, m, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");
+  GemmParams p;
+  p.x_mul = x_mul; p.x_shift = x_shift; p.w_mul = w_mul; p.w_shift = w_shift;
+  p.out_q15 = out_q15; p.acc_out = acc_out; p.M = (int)m; p.N = (int)n; p.K = (int)k;
+  B200_REQUIRE(make_map(&mb, w8, n, k, 128), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for w8");
+  return launch_gemm<128, 6>(ma, mb, p, (cudaStream_t)s);
+}
+
+extern "C" int b200_gemm_status(int* out_host, int reset) {
+  B200_REQUIRE(out_host, B200_E_NULL, "gemm_status: null pointer");
+  cudaError_t e = cudaMemcpyFromSymbol(out_host, g_gemm_status, sizeof(int));
+  if (e == cudaSuccess && reset) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+  }
+  if (e != cudaSuccess) {
+    set_error("gemm_status: %s", cudaGetErrorString(e));
+    return B200_E_CUDA;
+  }
+  return B200_OK;
+}
