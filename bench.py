@@ -306,6 +306,93 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+
+# ----------------------------------------------------------------------------- secondary workloads
+def _time_cuda(fn, steps, warmup):
+    import torch
+    for _ in range(max(warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_rowops(args) -> None:
+    """Configuration 3: add+RMSNorm+quant (A) on [rows, 5120] and SiLU*up+FWHT128+quant (B) on [rows, 2*17408]."""
+    import torch
+    from mini_sgl_integer_b200.kernel import fixed_point as fp
+    from oracle import fixed_point as ofp
+    torch.cuda.set_device(0)
+    T, H, I = args.rows, 5120, 17408
+    g = torch.Generator(device="cuda").manual_seed(0)
+    clip = lambda t: t.round().clamp(-(2**23), 2**23).to(torch.int32)
+    x = clip(torch.randn(T, H, device="cuda", generator=g) * 4096.0)
+    r = clip(torch.randn(T, H, device="cuda", generator=g) * 4096.0)
+    w = torch.randint(2**13, 2**15 + 1, (H,), device="cuda", dtype=torch.int32, generator=g)
+    gu = (torch.randn(T, 2 * I, device="cuda", generator=g) * 2.0**17).round().to(torch.int32)
+    ms_a = _time_cuda(lambda: fp.fused_add_rmsnorm_quant(x, r, w), args.steps, args.warmup)
+    ms_b = _time_cuda(lambda: fp.silu_mul_fwht_quant(gu, 128), args.steps, args.warmup)
+    bytes_a, bytes_b = T * (13 * H + 8), T * (9 * I + 8)
+    peak, how = measured_peak()
+    n_cpu = 64
+    t0 = time.perf_counter()
+    xo, ro, wo, go = (t[:n_cpu].cpu().numpy() if t.ndim == 2 else t.cpu().numpy() for t in (x, r, w, gu))
+    eo, _ = ofp.fused_add_rmsnorm_v2(ro, xo, wo); ofp.per_token_quant_from_q15(eo)
+    ofp.per_token_quant_from_q15(ofp.blockwise_fwht_q15(ofp.silu_and_mul(go), 128))
+    cpu_dt = time.perf_counter() - t0
+    kern = {"A_add_rmsnorm_quant": {"ms": ms_a, "GBs": bytes_a / ms_a / 1e6, "frac": bytes_a / ms_a / 1e6 / peak, "bytes": bytes_a},
+            "B_silu_fwht_quant": {"ms": ms_b, "GBs": bytes_b / ms_b / 1e6, "frac": bytes_b / ms_b / 1e6 / peak, "bytes": bytes_b}}
+    tot = ms_a + ms_b
+    print(json.dumps({
+        "metric": "fused fixed-point row kernels A+B (tokens/s; HBM GB/s in roofline)", "value": T / (tot * 1e-3),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": tot,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
+        "config": {"workload": f"add+RMSNorm+quant on [{T},5120] and SiLU*up+FWHT128+quant on [{T},2*17408]",
+                   "rows": T, "hidden": H, "inter": I, "l2": "inputs larger than L2"},
+        "gpu_launches": 2 * args.steps, "kernels": kern,
+        "roofline": {"bound": "hbm", "achieved": (bytes_a + bytes_b) / tot / 1e6, "peak": peak, "unit": "GB/s",
+                     "frac": (bytes_a + bytes_b) / tot / 1e6 / peak, "traffic": None, "peak_source": how},
+        "cpu_baseline": {"value": n_cpu / cpu_dt, "unit": "tokens/s", "cores": host_threads(), "kind": "port",
+                         "sample": f"{n_cpu} of the {T} rows through the vectorised numpy oracle ({cpu_dt:.2f} s)"},
+    }))
+
+
+def run_gemm(args) -> None:
+    """W8A8 GEMM micro-benchmark: the (N, K) pairs of the 8B-shaped model at the given M."""
+    import torch
+    from mini_sgl_integer_b200.layers import int8_gemm_q15
+    torch.cuda.set_device(0)
+    M = args.m
+    out = {}
+    for name, (N, K) in {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (24576, 4096), "down": (4096, 12288)}.items():
+        x8 = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda")
+        w8 = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda")
+        xm = torch.randint(2**30, 2**31 - 1, (M,), dtype=torch.int64, device="cuda").to(torch.int32)
+        xs = torch.full((M,), 40, dtype=torch.int32, device="cuda")
+        wm = torch.randint(2**29, 2**30, (N,), dtype=torch.int32, device="cuda")
+        ms = _time_cuda(lambda: int8_gemm_q15(x8, xm, xs, w8, wm), args.steps, args.warmup)
+        lib = _time_cuda(lambda: torch._int_mm(x8, w8.t()), args.steps, args.warmup) if M > 16 else float("nan")
+        out[name] = {"N": N, "K": K, "ms": ms, "TOPS": 2 * M * N * K / ms / 1e9,
+                     "GBs": (M * K + N * K + 4 * M * N) / ms / 1e6, "library_int_mm_TOPS": 2 * M * N * K / lib / 1e9}
+    tot_ops = sum(2 * M * v["N"] * v["K"] for v in out.values())
+    tot_ms = sum(v["ms"] for v in out.values())
+    print(json.dumps({
+        "metric": "W8A8 GEMM with fixed-point epilogue (int8 TOPS)", "value": tot_ops / tot_ms / 1e9, "unit": "TOPS",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": tot_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": f"four linears of the 8B-shaped layer at M={M}", "M": M}, "gpu_launches": 4 * args.steps,
+        "kernels": out,
+        "roofline": {"bound": "tensor", "achieved": tot_ops / tot_ms / 1e9, "peak": 4500.0, "unit": "TOPS",
+                     "frac": tot_ops / tot_ms / 1e9 / 4500.0, "traffic": None,
+                     "peak_source": "nominal dense int8 (no measured int8 figure in MEASURED_PEAKS.json)"},
+    }))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -317,10 +404,18 @@ def main() -> None:
                     help="pages in the KV pool (smaller pools are for profiler captures only)")
     ap.add_argument("--sustain-s", type=float, default=1.0,
                     help="seconds of untimed back-to-back launches before the timed region (clock sampling)")
+    ap.add_argument("--workload", default="attn", choices=["attn", "rowops", "gemm"],
+                    help="attn = the headline decode attention (default); rowops / gemm = the other kernels of the path")
+    ap.add_argument("--rows", type=int, default=16384, help="rows for --workload rowops")
+    ap.add_argument("--m", type=int, default=4096, help="M for --workload gemm")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "rowops":
+        run_rowops(args)
+    elif args.workload == "gemm":
+        run_gemm(args)
     else:
         run_ours(args)
 

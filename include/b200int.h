@@ -75,7 +75,7 @@ B200_API int b200_rmsnorm_q15(const int32_t* x, const int32_t* residual, const i
  *   gate_up int32 [rows, 2*inter] laid out gate || up; q15_out int32 [rows, inter] (nullable);
  *   codes/scale/absmax as above (all three or none).
  * fwht_block: 0 = no rotation, or 128.  inter must be a multiple of 128 (of 4 when
- * fwht_block == 0 and codes == NULL) and at most 32768. */
+ * fwht_block == 0 and codes == NULL) and at most 49152. */
 B200_API int b200_silu_mul_q15(const int32_t* gate_up, int32_t* q15_out,
                       int8_t* codes, float* scale, int32_t* absmax,
                       int64_t rows, int inter, int fwht_block, b200_stream_t s);

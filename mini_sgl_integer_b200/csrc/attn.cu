@@ -84,8 +84,11 @@ kv_store_kernel(const void* __restrict__ k_in, int64_t k_pitch, const void* __re
     mk = max(1, warp_max(mk));
     mv = max(1, warp_max(mv));
     const float fk = __int2float_rn(mk), fv = __int2float_rn(mv);
-    kw = pack4(quant_code(a.x, fk), quant_code(a.y, fk), quant_code(a.z, fk), quant_code(a.w, fk));
-    vw = pack4(quant_code(b.x, fv), quant_code(b.y, fv), quant_code(b.z, fv), quant_code(b.w, fv));
+    const float yk = __frcp_rn(fk), yv = __frcp_rn(fv);
+    kw = pack4(quant_code_fast(a.x, fk, yk), quant_code_fast(a.y, fk, yk), quant_code_fast(a.z, fk, yk),
+               quant_code_fast(a.w, fk, yk));
+    vw = pack4(quant_code_fast(b.x, fv, yv), quant_code_fast(b.y, fv, yv), quant_code_fast(b.z, fv, yv),
+               quant_code_fast(b.w, fv, yv));
     absmax_to_ms_dev(mk, &kmul, &kshift);
     absmax_to_ms_dev(mv, &vmul, &vshift);
   } else {

@@ -108,6 +108,20 @@ __device__ __forceinline__ int quant_code(int x, float mf) {
   int r = __float2int_rn(q);
   return max(-128, min(127, r));
 }
+// The same code with the division replaced by a multiply and two fused multiply-adds on the
+// row's correctly rounded reciprocal (y = __frcp_rn(mf)): q1 = fma(fma(-mf, a*y, a), y, a*y) is
+// the correctly rounded quotient up to, at worst, a few units in the last place, so it can only
+// disagree with the division after rounding to an integer when it lies within a hair of a
+// half-integer; in that band (2^-10 wide, far above any such error) the true division is used.
+__device__ __forceinline__ int quant_code_fast(int x, float mf, float y) {
+  const float a = __fmul_rn(__int2float_rn(x), 127.0f);
+  const float q0 = __fmul_rn(a, y);
+  float q1 = __fmaf_rn(__fmaf_rn(-mf, q0, a), y, q0);
+  const float fr = q1 - floorf(q1);
+  if (fabsf(fr - 0.5f) < 0.0009765625f) q1 = __fdiv_rn(a, mf);
+  const int r = __float2int_rn(q1);
+  return max(-128, min(127, r));
+}
 __device__ __forceinline__ float quant_scale(float mf) { return __fdiv_rn(mf, 8323072.0f); }
 
 __device__ __forceinline__ unsigned pack4(int a, int b, int c, int d) {

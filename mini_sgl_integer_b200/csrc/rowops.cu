@@ -117,13 +117,14 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
   if (codes == nullptr) return;
   m2 = max(1, block_max(m2, red32));
   const float mf = __int2float_rn(m2);
+  const float my = __frcp_rn(mf);
   unsigned* co = reinterpret_cast<unsigned*>(codes + row * H);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < nvec) {
-      co[idx] = pack4(quant_code(v[i].x, mf), quant_code(v[i].y, mf), quant_code(v[i].z, mf),
-                      quant_code(v[i].w, mf));
+      co[idx] = pack4(quant_code_fast(v[i].x, mf, my), quant_code_fast(v[i].y, mf, my),
+                      quant_code_fast(v[i].z, mf, my), quant_code_fast(v[i].w, mf, my));
     }
   }
   if (threadIdx.x == 0) {
@@ -153,13 +154,14 @@ quant_rows_kernel(const int32_t* __restrict__ x, int8_t* __restrict__ codes,
   }
   m = max(1, block_max(m, red32));
   const float mf = __int2float_rn(m);
+  const float my = __frcp_rn(mf);
   unsigned* co = reinterpret_cast<unsigned*>(codes + row * K);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < nvec) {
-      co[idx] = pack4(quant_code(v[i].x, mf), quant_code(v[i].y, mf), quant_code(v[i].z, mf),
-                      quant_code(v[i].w, mf));
+      co[idx] = pack4(quant_code_fast(v[i].x, mf, my), quant_code_fast(v[i].y, mf, my),
+                      quant_code_fast(v[i].z, mf, my), quant_code_fast(v[i].w, mf, my));
     }
   }
   if (threadIdx.x == 0) {
@@ -208,18 +210,23 @@ static bool plan_rows(int width, RowPlan* p) {
 // ============================================================================ SiLU * up
 // silu_and_mul_int_only_kernel's arithmetic (silu_and_mul_int_only.py:156-226) for one element.
 __device__ __forceinline__ int silu_mul_elem(int g, int u, const int32_t* __restrict__ lut) {
-  const unsigned ua = g > 0 ? (unsigned)g : (0u - (unsigned)g);         // |g| in [0, 2^31]
-  const long long prod = -(long long)((unsigned long long)ua * 94549ull);  // -|g| * log2e, Q30.32
-  const int yi = (int)(prod >> 32);                                      // (y >> 16), y = prod >> 16
-  const unsigned idx = ((unsigned)prod) >> 22;                           // ((y & 0xFFFF) >> 6)
-  const int shift = 13 - yi;                                             // >= 13
-  const unsigned e2 = (unsigned)lut[idx];
-  unsigned E = shift >= 32 ? 0u : (e2 >> shift);
+  const int a = g > 0 ? -g : g;                                  // -|g|, fits int32 for every g
+  const long long prod = (long long)a * 94549LL;                 // -|g| * log2e, Q30.32; y = prod >> 16
+  const int yi = (int)(prod >> 32);                              // y >> 16  (<= 0)
+  const unsigned idx = ((unsigned)prod) >> 22;                   // (y & 0xFFFF) >> 6
+  unsigned E;
+  asm("shr.u32 %0, %1, %2;" : "=r"(E) : "r"((unsigned)lut[idx]), "r"((unsigned)(13 - yi)));  // >= 32 gives 0
   E = min(E, 65536u);
-  const unsigned sneg = (E == 65536u) ? 32768u : (E << 16) / (65536u + E);
+  // sneg = floor(E * 2^16 / (2^16 + E)): float estimate (off by at most 1), exact correction
+  const unsigned den = 65536u + E;
+  const unsigned num = E << 16;                                  // wraps only for E == 2^16 (handled below)
+  unsigned sneg = (unsigned)__fdividef((float)E * 65536.0f, (float)den);
+  const int rem = (int)(num - sneg * den);
+  sneg += rem < 0 ? -1 : (rem >= (int)den ? 1 : 0);
+  sneg = (E == 65536u) ? 32768u : sneg;
   const unsigned sig = g > 0 ? 65536u - sneg : sneg;
-  const long long t = ((long long)g * (long long)sig) >> 16;
-  return sat32((t * (long long)u) >> 16);
+  const int t = (int)(((long long)g * (long long)sig) >> 16);   // |t| <= |g|
+  return sat32(((long long)t * (long long)u) >> 16);
 }
 
 // FWHT-128 of a block spread over an 8-lane group: each lane holds 16 values, index
@@ -259,14 +266,43 @@ __device__ __forceinline__ int fwht_scale(int y, int kq15) {
   return sat32(rsr15((long long)y * (long long)kq15));
 }
 
-// One CTA per row.  Every 8-lane group owns ITER blocks of 128 outputs (block = group + it*ngroups).
-template <int ITER, bool FWHT, bool QUANT>
-__global__ void __launch_bounds__(512)
+// FWHT-128 butterflies without saturation: valid when every input satisfies |v| < 2^24, so that
+// no partial sum can leave int32 (seven stages add seven bits).
+__device__ __forceinline__ void fwht128_group_nosat(int (&val)[16], int lane8) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int a = val[4 * k], b = val[4 * k + 1], c = val[4 * k + 2], d = val[4 * k + 3];
+    const int a1 = a + b, b1 = a - b, c1 = c + d, d1 = c - d;
+    val[4 * k] = a1 + c1; val[4 * k + 2] = a1 - c1; val[4 * k + 1] = b1 + d1; val[4 * k + 3] = b1 - d1;
+  }
+#pragma unroll
+  for (int bit = 0; bit < 3; ++bit) {
+    const bool lower = ((lane8 >> bit) & 1) == 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int partner = __shfl_xor_sync(FULL_MASK, val[j], 1 << bit);
+      val[j] = lower ? val[j] + partner : partner - val[j];
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int a = val[e], b = val[4 + e], c = val[8 + e], d = val[12 + e];
+    const int a1 = a + b, b1 = a - b, c1 = c + d, d1 = c - d;
+    val[e] = a1 + c1; val[8 + e] = a1 - c1; val[4 + e] = b1 + d1; val[12 + e] = b1 - d1;
+  }
+}
+
+// One CTA per row.  An 8-lane group takes the 128-blocks group, group + ngroups, ...; the
+// SiLU*up (+ rotation) results of the whole row are parked in shared memory until the row's
+// absmax is known, then quantised from there: gate and up are read from HBM once.
+template <bool FWHT, bool QUANT>
+__global__ void __launch_bounds__(512, 2)
 silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_out,
                  int8_t* __restrict__ codes, float* __restrict__ scale,
                  int32_t* __restrict__ absmax, int I) {
-  __shared__ int32_t lut[1024];
+  extern __shared__ __align__(16) int32_t rowbuf[];   // QUANT: [I] results of the row; then the LUT
   __shared__ int red32[33];
+  int32_t* lut = rowbuf + (QUANT ? I : 0);
   for (int i = threadIdx.x; i < 1024; i += blockDim.x) lut[i] = g_exp2_silu_lut[i];
   __syncthreads();
 
@@ -275,15 +311,16 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   const int group = threadIdx.x >> 3;
   const int ngroups = blockDim.x >> 3;
   const int nblocks = I >> 7;
+  const int niter = (nblocks + ngroups - 1) / ngroups;
   const int32_t* gate = gate_up + row * 2 * (int64_t)I;
   const int32_t* up = gate + I;
 
-  int val[ITER][16];
   int m = 0;
-#pragma unroll
-  for (int it = 0; it < ITER; ++it) {
+  for (int it = 0; it < niter; ++it) {           // uniform trip count: the shuffles need whole warps
     const int b = group + it * ngroups;
     const bool live = b < nblocks;
+    int val[16];
+    int big = 0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       int4 g = make_int4(0, 0, 0, 0), u = make_int4(0, 0, 0, 0);
@@ -292,44 +329,45 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
         g = __ldcs(reinterpret_cast<const int4*>(gate + off));
         u = __ldcs(reinterpret_cast<const int4*>(up + off));
       }
-      val[it][4 * k + 0] = silu_mul_elem(g.x, u.x, lut);
-      val[it][4 * k + 1] = silu_mul_elem(g.y, u.y, lut);
-      val[it][4 * k + 2] = silu_mul_elem(g.z, u.z, lut);
-      val[it][4 * k + 3] = silu_mul_elem(g.w, u.w, lut);
+      val[4 * k + 0] = silu_mul_elem(g.x, u.x, lut);
+      val[4 * k + 1] = silu_mul_elem(g.y, u.y, lut);
+      val[4 * k + 2] = silu_mul_elem(g.z, u.z, lut);
+      val[4 * k + 3] = silu_mul_elem(g.w, u.w, lut);
     }
     if (FWHT) {
-      fwht128_group(val[it], lane8);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) val[it][j] = fwht_scale(val[it][j], 2896);
+      for (int j = 0; j < 16; ++j) big |= (int)((unsigned)(val[j] + (1 << 24)) >> 25);   // != 0 iff |v| >= 2^24
+      if (__any_sync(FULL_MASK, big != 0)) {
+        fwht128_group(val, lane8);                // saturating butterflies, the reference's stage order
+      } else {
+        fwht128_group_nosat(val, lane8);
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) val[j] = fwht_scale(val[j], 2896);
     }
-    if (q15_out != nullptr && live) {
+    if (live) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const int off = b * 128 + k * 32 + lane8 * 4;
-        *reinterpret_cast<int4*>(q15_out + row * (int64_t)I + off) =
-            make_int4(val[it][4 * k], val[it][4 * k + 1], val[it][4 * k + 2], val[it][4 * k + 3]);
+        const int4 o = make_int4(val[4 * k], val[4 * k + 1], val[4 * k + 2], val[4 * k + 3]);
+        if (q15_out != nullptr) *reinterpret_cast<int4*>(q15_out + row * (int64_t)I + off) = o;
+        if (QUANT) *reinterpret_cast<int4*>(rowbuf + off) = o;
       }
     }
     if (QUANT) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) m = max(m, abs_wrap(val[it][j]));
+      for (int j = 0; j < 16; ++j) m = max(m, abs_wrap(val[j]));
     }
   }
   if (!QUANT) return;
-  m = max(1, block_max(m, red32));
+  m = max(1, block_max(m, red32));     // its barriers also order the rowbuf writes before the reads
   const float mf = __int2float_rn(m);
-#pragma unroll
-  for (int it = 0; it < ITER; ++it) {
-    const int b = group + it * ngroups;
-    if (b < nblocks) {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int off = b * 128 + k * 32 + lane8 * 4;
-        *reinterpret_cast<unsigned*>(codes + row * (int64_t)I + off) =
-            pack4(quant_code(val[it][4 * k], mf), quant_code(val[it][4 * k + 1], mf),
-                  quant_code(val[it][4 * k + 2], mf), quant_code(val[it][4 * k + 3], mf));
-      }
-    }
+  const float my = __frcp_rn(mf);
+  unsigned* co = reinterpret_cast<unsigned*>(codes + row * (int64_t)I);
+  for (int i = threadIdx.x; i < (I >> 2); i += blockDim.x) {
+    const int4 v = reinterpret_cast<const int4*>(rowbuf)[i];
+    co[i] = pack4(quant_code_fast(v.x, mf, my), quant_code_fast(v.y, mf, my), quant_code_fast(v.z, mf, my),
+                  quant_code_fast(v.w, mf, my));
   }
   if (threadIdx.x == 0) {
     scale[row] = quant_scale(mf);
@@ -582,18 +620,29 @@ extern "C" int b200_per_token_quant_q15(const int32_t* x, int8_t* codes, float* 
   return check_launch("per_token_quant_q15");
 }
 
-template <int ITER>
-static void launch_silu(const int32_t* gu, int32_t* q15, int8_t* codes, float* scale, int32_t* absmax,
-                        int64_t rows, int inter, bool fwht, int threads, cudaStream_t st) {
+static int launch_silu(const int32_t* gu, int32_t* q15, int8_t* codes, float* scale, int32_t* absmax,
+                       int64_t rows, int inter, bool fwht, cudaStream_t st) {
   const bool quant = codes != nullptr;
-  if (fwht && quant)
-    silu_rows_kernel<ITER, true, true><<<(unsigned)rows, threads, 0, st>>>(gu, q15, codes, scale, absmax, inter);
-  else if (fwht)
-    silu_rows_kernel<ITER, true, false><<<(unsigned)rows, threads, 0, st>>>(gu, q15, codes, scale, absmax, inter);
-  else if (quant)
-    silu_rows_kernel<ITER, false, true><<<(unsigned)rows, threads, 0, st>>>(gu, q15, codes, scale, absmax, inter);
-  else
-    silu_rows_kernel<ITER, false, false><<<(unsigned)rows, threads, 0, st>>>(gu, q15, codes, scale, absmax, inter);
+  const int nblocks = inter / 128;
+  int threads = ((nblocks * 8 + 31) / 32) * 32;
+  if (threads > 512) threads = 512;
+  const size_t smem = (size_t)((quant ? inter : 0) + 1024) * sizeof(int32_t);
+#define B200_SILU_LAUNCH(F, Q)                                                                          \
+  do {                                                                                                  \
+    cudaError_t e = cudaFuncSetAttribute(silu_rows_kernel<F, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                    \
+    if (e != cudaSuccess) {                                                                             \
+      set_error("silu_mul_q15: cudaFuncSetAttribute: %s", cudaGetErrorString(e));                       \
+      return B200_E_CUDA;                                                                               \
+    }                                                                                                   \
+    silu_rows_kernel<F, Q><<<(unsigned)rows, threads, smem, st>>>(gu, q15, codes, scale, absmax, inter); \
+  } while (0)
+  if (fwht && quant) B200_SILU_LAUNCH(true, true);
+  else if (fwht) B200_SILU_LAUNCH(true, false);
+  else if (quant) B200_SILU_LAUNCH(false, true);
+  else B200_SILU_LAUNCH(false, false);
+#undef B200_SILU_LAUNCH
+  return check_launch("silu_mul_q15");
 }
 
 extern "C" int b200_silu_mul_q15(const int32_t* gate_up, int32_t* q15_out, int8_t* codes, float* scale,
@@ -608,8 +657,8 @@ extern "C" int b200_silu_mul_q15(const int32_t* gate_up, int32_t* q15_out, int8_
                "silu_mul_q15: rows=%lld inter=%d", (long long)rows, inter);
   B200_REQUIRE(fwht_block == 0 || fwht_block == 128, B200_E_UNSUPPORTED,
                "silu_mul_q15: fwht_block=%d (0 or 128 supported)", fwht_block);
-  B200_REQUIRE(inter % 4 == 0 && inter <= 32768, B200_E_UNSUPPORTED,
-               "silu_mul_q15: inter=%d must be a multiple of 4 and at most 32768", inter);
+  B200_REQUIRE(inter % 4 == 0 && inter <= 49152, B200_E_UNSUPPORTED,
+               "silu_mul_q15: inter=%d must be a multiple of 4 and at most 49152", inter);
   if (rows == 0) return B200_OK;
   B200_REQUIRE(aligned16(gate_up) && aligned16(q15_out) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN,
                "silu_mul_q15: int32 buffers must be 16-byte aligned (codes 4-byte)");
@@ -620,19 +669,7 @@ extern "C" int b200_silu_mul_q15(const int32_t* gate_up, int32_t* q15_out, int8_
     silu_simple_kernel<<<elementwise_grid(rows * (inter / 4), 256), 256, 0, st>>>(gate_up, q15_out, rows, inter);
     return check_launch("silu_mul_q15");
   }
-  const int nblocks = inter / 128;
-  int iter = 4;
-  for (int c = 1; c <= 4; c *= 2) {
-    if (((nblocks + c - 1) / c) * 8 <= 512) { iter = c; break; }
-  }
-  const int ngroups = (nblocks + iter - 1) / iter;
-  const int threads = ((ngroups * 8 + 31) / 32) * 32;
-  B200_REQUIRE(threads <= 512, B200_E_UNSUPPORTED, "silu_mul_q15: inter=%d too wide", inter);
-  const bool fw = fwht_block == 128;
-  if (iter == 1) launch_silu<1>(gate_up, q15_out, codes, scale, absmax, rows, inter, fw, threads, st);
-  else if (iter == 2) launch_silu<2>(gate_up, q15_out, codes, scale, absmax, rows, inter, fw, threads, st);
-  else launch_silu<4>(gate_up, q15_out, codes, scale, absmax, rows, inter, fw, threads, st);
-  return check_launch("silu_mul_q15");
+  return launch_silu(gate_up, q15_out, codes, scale, absmax, rows, inter, fwht_block == 128, st);
 }
 
 extern "C" int b200_fwht_q15(const int32_t* x, int32_t* out, int64_t rows, int n, int normalize,
