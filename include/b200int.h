@@ -154,6 +154,23 @@ B200_API int b200_attn_decode(const int8_t* q, const int32_t* q_mul, const int32
                      int batch, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
                      int cluster, b200_stream_t s);
 
+/* ---- Extend (prefill over a cached prefix) attention on the same pool and arithmetic.
+ * Stands in for Int8Backend._forward_prefill (attention/triton_int8.py:178-212) ->
+ * int8_context_attention_fwd (kernel/triton/int8_attention_kernels.py:229-383), and unlike the
+ * reference it attends the cached prefix as well as the new tokens.  The new tokens must already be
+ * in the pool.  One query row per new token: q int8 [rows, q_heads, 128]; row_seq int32 [rows] is the
+ * row's sequence (index into page_table / kv_lens); row_limit int32 [rows] the number of keys the row
+ * may see (for the i-th of n new tokens of a sequence with L keys: L - n + i + 1).  The reference V
+ * scale of a row is taken over all kv_lens[seq] keys.  rows <= 65535.  Every row re-reads its keys:
+ * meant for short extends (chunked prefill tails, speculative/verify steps), not for long prompts. */
+B200_API int b200_attn_extend(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
+                              const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
+                              const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                              const int32_t* row_seq, const int32_t* row_limit,
+                              int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax,
+                              int rows, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
+                              int cluster, b200_stream_t s);
+
 /* ---- W8A8 linear: int8 x int8 -> int32 on the tcgen05 tensor cores, fixed-point requant.
  * Stands in for the GEMM + epilogue inside W8A8Int8LinearMethod.apply_weights_q15
  * (layers/quantization/w8a8_int8.py:242-286), i.e. the sgl_kernel.int8_scaled_mm call at :272-279

@@ -33,6 +33,7 @@ SIGNATURES: dict[str, list] = {
     "b200_absmax_to_mul_shift": [P, P, P, L, P],
     "b200_kv_store_q15": [P, L, P, L, P, P, P, P, L, I, L, P],
     "b200_kv_store_codes": [P, P, P, P, P, P, P, P, P, P, L, I, L, P],
+    "b200_attn_extend": [P, P, P, P, P, P, P, L, P, P, P, P, P, P, I, I, I, L, I, I, P],
     "b200_gemm_w8a8": [P, P, P, P, P, P, P, P, L, L, L, P],
     "b200_gemm_status": [P, I],
     "b200_attn_decode": [P, P, P, P, P, P, P, L, P, P, P, P, I, I, I, L, I, I, P],

@@ -42,3 +42,46 @@ def decode_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
     if out_q15 and out_int8:
         return o32, o8, om
     return o32 if out_q15 else (o8, om)
+
+
+def extend_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: torch.Tensor,
+                                pool: Int8PagedKVCache, layer_id: int, page_table: torch.Tensor,
+                                kv_lens: torch.Tensor, q_lens: torch.Tensor, max_kv_len: int, *,
+                                out_q15: bool = True, out_int8: bool = False, cluster: int = 0):
+    """Causal attention of newly appended tokens over the cached prefix plus themselves.
+
+    q8 int8 [sum(q_lens), q_heads, 128] with the sequences back to back; kv_lens int32 [batch] count the
+    new tokens too (they must already be stored in the pool); q_lens int32 [batch].  The i-th of the n new
+    tokens of a sequence with L keys sees keys 0 .. L-n+i.  Stands in for Int8Backend._forward_prefill
+    (attention/triton_int8.py:178-212) -> int8_context_attention_fwd
+    (kernel/triton/int8_attention_kernels.py:229-383); unlike the reference it attends the cached prefix.
+    """
+    if q8.dtype != torch.int8:
+        raise TypeError(f"q8 must be int8, got {q8.dtype}")
+    if q8.ndim != 3 or q8.shape[-1] != HEAD_DIM:
+        raise ValueError(f"q8 must be [tokens, q_heads, {HEAD_DIM}], got shape {tuple(q8.shape)}")
+    require_cuda(q8, q_mul, q_shift, page_table, kv_lens, q_lens)
+    rows, q_heads, _ = q8.shape
+    c = lambda t: t.to(torch.int32).contiguous()
+    q8 = q8.contiguous()
+    q_mul, q_shift, page_table, kv_lens, q_lens = c(q_mul), c(q_shift), c(page_table), c(kv_lens), c(q_lens)
+    if int(q_lens.sum()) != rows:
+        raise ValueError(f"sum(q_lens)={int(q_lens.sum())} does not match the {rows} query rows")
+    batch = kv_lens.shape[0]
+    seq_ids = torch.arange(batch, device=q8.device, dtype=torch.int32)
+    row_seq = torch.repeat_interleave(seq_ids, q_lens.to(torch.int64)).to(torch.int32).contiguous()
+    starts = torch.cumsum(q_lens, 0, dtype=torch.int32) - q_lens
+    rs = row_seq.to(torch.int64)
+    within = torch.arange(rows, device=q8.device, dtype=torch.int32) - starts[rs]
+    row_limit = (kv_lens[rs] - q_lens[rs] + within + 1).to(torch.int32).contiguous()
+    o32 = torch.empty((rows, q_heads, HEAD_DIM), dtype=torch.int32, device=q8.device) if out_q15 else None
+    o8 = torch.empty((rows, q_heads, HEAD_DIM), dtype=torch.int8, device=q8.device) if out_int8 else None
+    om = torch.empty((rows, q_heads), dtype=torch.int32, device=q8.device) if out_int8 else None
+    if rows > 0:
+        call("b200_attn_extend", ptr(q8), ptr(q_mul), ptr(q_shift), ptr(pool.k_cache(layer_id)),
+             ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(page_table), page_table.stride(0),
+             ptr(kv_lens), ptr(row_seq), ptr(row_limit), ptr(o32), ptr(o8), ptr(om), rows, q_heads,
+             pool.kv_heads, pool.num_pages, int(max_kv_len), int(cluster), stream())
+    if out_q15 and out_int8:
+        return o32, o8, om
+    return o32 if out_q15 else (o8, om)

@@ -124,6 +124,8 @@ struct DecodeParams {
   const int32_t* page_table;
   int64_t table_pitch;
   const int32_t* kv_lens;
+  const int32_t* row_seq;    // nullable: query row -> sequence (extend); null = one row per sequence
+  const int32_t* row_limit;  // nullable: keys visible to the row (causal limit); null = all of the sequence
   int32_t* out_q15;
   int8_t* out_codes;
   int32_t* out_absmax;
@@ -248,8 +250,11 @@ attn_decode_kernel(const DecodeParams p) {
   __shared__ int g_inv[G];
   __shared__ int red_s[33];
 
-  int L = p.kv_lens[b];
-  L = max(0, min(L, p.max_kv_len));
+  // b is the query row; its keys come from sequence `seq`.  In an extend batch a row sees only the
+  // first `row_limit` keys, but the reference V scale is taken over all L_all keys of the sequence.
+  const int seq = p.row_seq ? p.row_seq[b] : b;
+  const int L_all = max(0, min(p.kv_lens[seq], p.max_kv_len));
+  const int L = p.row_limit ? max(0, min(p.row_limit[b], L_all)) : L_all;
   const int n_pages = (L + kPage - 1) / kPage;
   const int ppc = (n_pages + C - 1) / C;                 // pages per CTA
   const int pg0 = min(n_pages, rank * ppc);
@@ -271,7 +276,7 @@ attn_decode_kernel(const DecodeParams p) {
   if (tid == 0) cta_vref = ~0ull;
   for (int i = tid; i < G * kD; i += kDecodeThreads) (&cta_acc[0][0])[i] = 0;
   for (int i = tid; i < my_pages; i += kDecodeThreads) {
-    int64_t pid = p.page_table[(int64_t)b * p.table_pitch + pg0 + i];
+    int64_t pid = p.page_table[(int64_t)seq * p.table_pitch + pg0 + i];
     pid = pid < 0 ? 0 : (pid >= p.num_pages ? p.num_pages - 1 : pid);
     pages[i] = (int)pid;
   }
@@ -419,6 +424,24 @@ attn_decode_kernel(const DecodeParams p) {
       lvref = other < lvref ? other : lvref;
     }
     if (lane == 0) atomicMin(&cta_vref, lvref);
+  }
+  if (rank == 0 && L_all > L) {   // extend rows: keys behind the causal limit still count for the V reference scale
+    unsigned long long lv = ~0ull;
+    for (int key = L + tid; key < L_all; key += kDecodeThreads) {
+      int64_t pid = p.page_table[(int64_t)seq * p.table_pitch + (key >> 4)];
+      pid = pid < 0 ? 0 : (pid >= p.num_pages ? p.num_pages - 1 : pid);
+      const int32_t* mt = p.meta + (pid * p.kv_heads + kh) * kMetaWords;
+      const unsigned vm = (unsigned)__ldg(mt + 16 + (key & 15));
+      const int vs = reinterpret_cast<const int8_t*>(mt + 36)[key & 15];
+      const unsigned long long vkey = ((unsigned long long)(unsigned)(vs + 128) << 32) | (unsigned long long)(0xFFFFFFFFu - vm);
+      lv = vkey < lv ? vkey : lv;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(FULL_MASK, lv, o);
+      lv = other < lv ? other : lv;
+    }
+    if (lane == 0) atomicMin(&cta_vref, lv);
   }
   cluster.sync();
 
@@ -687,12 +710,13 @@ extern "C" int b200_kv_store_codes(const int8_t* k8, const int8_t* v8, const int
                       kv_heads, num_pages, (cudaStream_t)s, "kv_store_codes");
 }
 
-extern "C" int b200_attn_decode(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
-                                const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
-                                const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
-                                int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax, int batch,
-                                int q_heads, int kv_heads, int64_t num_pages, int max_kv_len, int cluster,
-                                b200_stream_t s) {
+static int attn_common(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
+                       const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
+                       const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                       const int32_t* row_seq, const int32_t* row_limit,
+                       int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax, int batch,
+                       int q_heads, int kv_heads, int64_t num_pages, int max_kv_len, int cluster,
+                       b200_stream_t s) {
   B200_REQUIRE(q && q_mul && q_shift && k_codes && v_codes && meta && page_table && kv_lens, B200_E_NULL,
                "attn_decode: null pointer");
   B200_REQUIRE((out_codes == nullptr) == (out_absmax == nullptr), B200_E_NULL,
@@ -722,7 +746,7 @@ extern "C" int b200_attn_decode(const int8_t* q, const int32_t* q_mul, const int
   p.q = q; p.q_mul = q_mul; p.q_shift = q_shift; p.k_codes = k_codes; p.v_codes = v_codes; p.meta = meta;
   p.page_table = page_table; p.table_pitch = table_pitch; p.kv_lens = kv_lens; p.out_q15 = out_q15;
   p.out_codes = out_codes; p.out_absmax = out_absmax; p.q_heads = q_heads; p.kv_heads = kv_heads;
-  p.num_pages = num_pages; p.max_kv_len = max_kv_len;
+  p.num_pages = num_pages; p.max_kv_len = max_kv_len; p.row_seq = row_seq; p.row_limit = row_limit;
   { const char* e = getenv("B200_DECODE_SKIP"); p.dbg_skip = e ? atoi(e) : 0; }
   const int ppc = (max_pages + cluster - 1) / cluster;
   p.s_max = ((ppc * kPage + 31) / 32) * 32;
@@ -733,4 +757,26 @@ extern "C" int b200_attn_decode(const int8_t* q, const int32_t* q_mul, const int
     case 4: return launch_decode<4>(p, batch, cluster, st);
     default: return launch_decode<8>(p, batch, cluster, st);
   }
+}
+
+extern "C" int b200_attn_decode(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
+                                const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
+                                const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                                int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax, int batch,
+                                int q_heads, int kv_heads, int64_t num_pages, int max_kv_len, int cluster,
+                                b200_stream_t s) {
+  return attn_common(q, q_mul, q_shift, k_codes, v_codes, meta, page_table, table_pitch, kv_lens, nullptr, nullptr,
+                     out_q15, out_codes, out_absmax, batch, q_heads, kv_heads, num_pages, max_kv_len, cluster, s);
+}
+
+extern "C" int b200_attn_extend(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
+                                const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
+                                const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                                const int32_t* row_seq, const int32_t* row_limit,
+                                int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax, int rows,
+                                int q_heads, int kv_heads, int64_t num_pages, int max_kv_len, int cluster,
+                                b200_stream_t s) {
+  B200_REQUIRE(row_seq && row_limit, B200_E_NULL, "attn_extend: row_seq or row_limit is null");
+  return attn_common(q, q_mul, q_shift, k_codes, v_codes, meta, page_table, table_pitch, kv_lens, row_seq, row_limit,
+                     out_q15, out_codes, out_absmax, rows, q_heads, kv_heads, num_pages, max_kv_len, cluster, s);
 }

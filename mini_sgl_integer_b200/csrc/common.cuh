@@ -113,20 +113,23 @@ __device__ __forceinline__ int quant_code(int x, float mf) {
 // the correctly rounded quotient up to, at worst, a few units in the last place, so it can only
 // disagree with the division after rounding to an integer when it lies within a hair of a
 // half-integer; in that band (2^-10 wide, far above any such error) the true division is used.
+// Rounding to the nearest-even integer is done by adding 1.5 * 2^23 (|q| <= 127, no clamp needed).
 __device__ __forceinline__ int quant_code_fast(int x, float mf, float y) {
   const float a = __fmul_rn(__int2float_rn(x), 127.0f);
   const float q0 = __fmul_rn(a, y);
   float q1 = __fmaf_rn(__fmaf_rn(-mf, q0, a), y, q0);
-  const float fr = q1 - floorf(q1);
-  if (fabsf(fr - 0.5f) < 0.0009765625f) q1 = __fdiv_rn(a, mf);
-  const int r = __float2int_rn(q1);
-  return max(-128, min(127, r));
+  float t = __fadd_rn(q1, 12582912.0f);                       // integer part now sits in the mantissa
+  if (fabsf(__fsub_rn(q1, __fsub_rn(t, 12582912.0f))) > 0.4990234375f)   // within 2^-10 of a half-integer
+    t = __fadd_rn(__fdiv_rn(a, mf), 12582912.0f);
+  return __float_as_int(t) - 0x4B400000;
 }
 __device__ __forceinline__ float quant_scale(float mf) { return __fdiv_rn(mf, 8323072.0f); }
 
 __device__ __forceinline__ unsigned pack4(int a, int b, int c, int d) {
-  return (unsigned)(a & 0xff) | ((unsigned)(b & 0xff) << 8) | ((unsigned)(c & 0xff) << 16) |
-         ((unsigned)(d & 0xff) << 24);
+  // two byte permutes: (a,b) -> low half, (c,d) -> high half, then merge
+  const unsigned ab = __byte_perm((unsigned)a, (unsigned)b, 0x0040);
+  const unsigned cd = __byte_perm((unsigned)c, (unsigned)d, 0x0040);
+  return __byte_perm(ab, cd, 0x5410);
 }
 
 // Fixed-point RMSNorm scalars of one row (rmsnorm_int_only_v2.py:144-218 steps 1, 4).

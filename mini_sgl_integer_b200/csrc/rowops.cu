@@ -224,9 +224,14 @@ __device__ __forceinline__ int silu_mul_elem(int g, int u, const int32_t* __rest
   const int rem = (int)(num - sneg * den);
   sneg += rem < 0 ? -1 : (rem >= (int)den ? 1 : 0);
   sneg = (E == 65536u) ? 32768u : sneg;
-  const unsigned sig = g > 0 ? 65536u - sneg : sneg;
-  const int t = (int)(((long long)g * (long long)sig) >> 16);   // |t| <= |g|
-  return sat32(((long long)t * (long long)u) >> 16);
+  const int sig = (int)(g > 0 ? 65536u - sneg : sneg);           // <= 2^16: 32 x 32 -> 64 bit products below
+  const long long gs = (long long)g * (long long)sig;
+  const int t = (int)__funnelshift_r((unsigned)gs, (unsigned)(gs >> 32), 16);   // (g * sig) >> 16, |t| <= |g|
+  const long long tu = (long long)t * (long long)u;
+  const int hi = (int)(tu >> 32);
+  const int res = (int)__funnelshift_r((unsigned)tu, (unsigned)hi, 16);        // low 32 bits of tu >> 16
+  // tu >> 16 fits int32 iff bits 47..63 of tu all equal the sign bit of the result
+  return (hi >> 15) == (res >> 31) ? res : (hi < 0 ? (int)(-2147483647 - 1) : 2147483647);
 }
 
 // FWHT-128 of a block spread over an 8-lane group: each lane holds 16 values, index
@@ -265,6 +270,14 @@ __device__ __forceinline__ void fwht128_group(int (&val)[16], int lane8) {
 __device__ __forceinline__ int fwht_scale(int y, int kq15) {
   return sat32(rsr15((long long)y * (long long)kq15));
 }
+// The n = 128 scale rsr15(y * 2896) in 32-bit arithmetic.  2896 = 16 * 181, so
+// (16a +- 2^14) >> 15 == (a +- 2^10) >> 11 with a = y * 181; splitting y = yh * 2^11 + yl
+// (yl in [0, 2048)) gives yh * 181 + ((yl * 181 +- 2^10) >> 11), all below 2^31.  |result| < |y|.
+__device__ __forceinline__ int fwht_scale128(int y) {
+  const int yh = y >> 11, yl = y & 2047;
+  const int bias = 1024 - ((y >> 31) & 2048);          // +1024 for y >= 0, -1024 for y < 0
+  return yh * 181 + ((yl * 181 + bias) >> 11);
+}
 
 // FWHT-128 butterflies without saturation: valid when every input satisfies |v| < 2^24, so that
 // no partial sum can leave int32 (seven stages add seven bits).
@@ -281,7 +294,7 @@ __device__ __forceinline__ void fwht128_group_nosat(int (&val)[16], int lane8) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const int partner = __shfl_xor_sync(FULL_MASK, val[j], 1 << bit);
-      val[j] = lower ? val[j] + partner : partner - val[j];
+      val[j] = partner + (lower ? 1 : -1) * val[j];
     }
   }
 #pragma unroll
@@ -336,14 +349,14 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
     }
     if (FWHT) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) big |= (int)((unsigned)(val[j] + (1 << 24)) >> 25);   // != 0 iff |v| >= 2^24
-      if (__any_sync(FULL_MASK, big != 0)) {
+      for (int j = 0; j < 16; ++j) big |= val[j] ^ (val[j] >> 31);   // >= 2^24 iff some |v| >= 2^24 (-2^24 also passes)
+      if (__any_sync(FULL_MASK, big >= (1 << 24))) {
         fwht128_group(val, lane8);                // saturating butterflies, the reference's stage order
       } else {
         fwht128_group_nosat(val, lane8);
       }
 #pragma unroll
-      for (int j = 0; j < 16; ++j) val[j] = fwht_scale(val[j], 2896);
+      for (int j = 0; j < 16; ++j) val[j] = fwht_scale128(val[j]);
     }
     if (live) {
 #pragma unroll
@@ -417,7 +430,7 @@ fwht128_rows_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ out, in
     fwht128_group(val, lane8);
     if (normalize) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) val[j] = fwht_scale(val[j], 2896);
+      for (int j = 0; j < 16; ++j) val[j] = fwht_scale128(val[j]);
     }
     if (live) {
 #pragma unroll

@@ -165,3 +165,67 @@ def test_decode_headline_shape_sample_and_invariants():
     pool2 = device_pool(case2, P, 8)
     got2 = run_decode(case2, pool2, 4096, cluster=8).cpu().numpy()
     eq(got2, got)
+
+
+def _extend_case(seed, kv_lens, q_lens, q_heads, kv_heads, num_pages, uniform=False):
+    case = make_case(seed, kv_lens, q_heads, kv_heads, num_pages, uniform=uniform)
+    rng = np.random.default_rng(seed + 99)
+    T = int(sum(q_lens))
+    case["q8"] = rng.integers(-127, 128, (T, q_heads, 128), dtype=np.int8)
+    case["qm"] = rng.integers(2**30, 2**31, (T, q_heads)).astype(np.int32)
+    case["qs"] = rng.integers(43, 46, (T, q_heads)).astype(np.int32)
+    case["q_lens"] = np.asarray(q_lens, dtype=np.int32)
+    return case
+
+
+def run_extend(case, pool, max_kv_len, cluster=0, **kw):
+    from mini_sgl_integer_b200.attention import extend_attention_int8_paged
+    need = (max_kv_len + 15) // 16
+    table = case["table"]
+    if table.shape[1] < need:
+        table = np.pad(table, ((0, 0), (0, need - table.shape[1])))
+    return extend_attention_int8_paged(d(case["q8"]), d(case["qm"]), d(case["qs"]), pool, 0, d(table),
+                                       d(case["kv_lens"]), d(case["q_lens"]), max_kv_len, cluster=cluster, **kw)
+
+
+@pytest.mark.parametrize("cluster", [1, 2, 4])
+def test_extend_over_prefix_vs_oracle(cluster):
+    """New tokens attend the cached prefix and, causally, themselves (the layer case: 16 new tokens over
+    prefixes 0, 16, 48, 112, plus ragged ones)."""
+    kv_lens = [16, 32, 64, 128, 37, 5, 200]
+    q_lens = [16, 16, 16, 16, 9, 5, 1]
+    case = _extend_case(40 + cluster, kv_lens, q_lens, 16, 8, 64)
+    pool = device_pool(case, 64, 8)
+    want = oattn.paged_attention(case["q8"], case["qm"], case["qs"], case["pool"], case["tables"], kv_lens, q_lens)
+    got, codes, absmax = run_extend(case, pool, 256, cluster, out_q15=True, out_int8=True)
+    eq(got.cpu().numpy(), want)
+    wc, wm = oattn.quant_heads_int8(want)
+    eq(codes.cpu().numpy(), wc); eq(absmax.cpu().numpy(), wm)
+
+
+def test_extend_without_prefix_reduces_to_reference(golden):
+    """Uniform scales, no prefix: the extend kernel reproduces int8_context_attention_fwd bit for bit."""
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache, extend_attention_int8_paged
+    ms = golden["attn_ms"]
+    q, k, v = golden["attn_q"], golden["attn_k"], golden["attn_v"]
+    pool = Int8PagedKVCache(2, 1, 128, 8, "cuda")
+    pages = {0: [5], 1: [7, 2]}
+    table = np.zeros((2, 2), dtype=np.int32)
+    for b, (st, L) in enumerate(((0, 16), (16, 32))):
+        table[b, : len(pages[b])] = pages[b]
+        loc = np.concatenate([np.arange(16) + 16 * p for p in pages[b]])[:L].astype(np.int32)
+        full = lambda val: torch.full((L, 2), int(val), dtype=torch.int32, device="cuda")
+        pool.store_codes(d(k[st:st + L]), d(v[st:st + L]), full(ms[1][0]), full(ms[1][1]), full(ms[2][0]),
+                         full(ms[2][1]), d(loc), 0)
+    qm = np.full((48, 4), ms[0][0], dtype=np.int32); qs = np.full((48, 4), ms[0][1], dtype=np.int32)
+    lens = d(np.array([16, 32], dtype=np.int32))
+    got = extend_attention_int8_paged(d(q), d(qm), d(qs), pool, 0, d(table), lens, lens, 32, cluster=2).cpu().numpy()
+    eq(oattn.q15_to_bf16_bits(got.astype(np.int64)), golden["attn_out_bf16_bits"])
+
+
+def test_extend_empty_batch():
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache, extend_attention_int8_paged
+    pool = Int8PagedKVCache(2, 1, 128, 4, "cuda")
+    z = lambda *s, dt=torch.int32: torch.zeros(s, dtype=dt, device="cuda")
+    out = extend_attention_int8_paged(z(0, 4, 128, dt=torch.int8), z(0, 4), z(0, 4), pool, 0, z(1, 2), z(1), z(1), 32)
+    assert out.shape == (0, 4, 128)
