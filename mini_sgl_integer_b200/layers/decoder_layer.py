@@ -1,0 +1,99 @@
+"""One integer-only decoder layer on the sm_100a kernels.
+
+Follows the data flow of ``Qwen3DecoderLayerInteger.forward_q15`` (models/integer/qwen3_integer.py:62-80),
+``RopeAttnInteger.forward_q15`` / ``AttentionLayerInteger.forward_q15`` (models/utils_integer.py:192-301) and
+``GatedMLPInteger.forward_q15`` (models/utils_integer.py:99-121), with two differences that the integer
+path makes possible: activations travel between a norm / activation and the following linear as int8 codes
+(never as Q15.16 through HBM), and attention runs on int8 q/k/v against the int8 paged pool instead of the
+reference's bf16 bridge (models/utils_integer.py:222-227).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..attention import Int8PagedKVCache, decode_attention_int8_paged, extend_attention_int8_paged
+from ..kernel import fixed_point as fp
+from .w8a8_int8 import W8A8Int8LinearMethod
+
+
+@dataclass
+class AttnBatch:
+    """What the reference keeps in ``Batch`` + attention metadata (core.py:72-97, attention/triton_int8.py:50-64)."""
+
+    positions: torch.Tensor      # int32 [tokens]
+    out_loc: torch.Tensor        # int32 [tokens]  token locations (page*16 + offset) of the new tokens
+    page_table: torch.Tensor     # int32 [batch, pitch] page ids
+    kv_lens: torch.Tensor        # int32 [batch]  keys per sequence including the new tokens
+    q_lens: Optional[torch.Tensor]  # int32 [batch] new tokens per sequence; None = decode (one each)
+    max_kv_len: int
+
+
+class _Linear(torch.nn.Module):
+    """Holder of ``weight`` int8 [out, in] and ``weight_scale`` fp32 [out, 1] (or fixed-point scales directly)."""
+
+    def __init__(self, weight: torch.Tensor, weight_scale: Optional[torch.Tensor] = None,
+                 weight_mul: Optional[torch.Tensor] = None, weight_shift: Optional[torch.Tensor] = None):
+        super().__init__()
+        self.weight = weight
+        if weight_scale is not None:
+            self.weight_scale = weight_scale
+        self.weight_mul, self.weight_shift = weight_mul, weight_shift
+
+
+class Qwen3DecoderLayerInteger:
+    def __init__(self, layer_id: int, num_qo_heads: int, num_kv_heads: int, hidden: int, inter: int,
+                 weights: dict, cos_sin_cache_q15: torch.Tensor, pool: Int8PagedKVCache,
+                 hadamard_block: int = 128):
+        """``weights``: qkv/o/gate_up/down -> _Linear; input_norm/post_norm int32 [hidden];
+        q_norm/k_norm int32 [128] or None (Q15.16; q_norm already carries head_dim**-0.5)."""
+        self.layer_id, self.hq, self.hk, self.hidden, self.inter = layer_id, num_qo_heads, num_kv_heads, hidden, inter
+        self.w = weights
+        self.cache = cos_sin_cache_q15
+        self.pool = pool
+        self.hadamard_block = hadamard_block
+        self.method = W8A8Int8LinearMethod()
+
+    def forward_q15(self, x_q15: torch.Tensor, residual_q15: Optional[torch.Tensor], batch: AttnBatch,
+                    trace: Optional[dict] = None):
+        """Returns (x_out, residual_out), both Q15.16 int32 [tokens, hidden]."""
+        fp.assert_q15(x_q15, "x_q15")
+        t = trace if trace is not None else {}
+        w, m = self.w, self.method
+        T = x_q15.shape[0]
+        # input_layernorm (+ residual add) -> int8 codes for qkv_proj
+        codes, _, absmax, res, _ = fp.fused_add_rmsnorm_quant(x_q15, residual_q15, w["input_norm"])
+        residual = res if residual_q15 is not None else x_q15
+        t["ln1_codes"], t["ln1_absmax"] = codes, absmax
+        qkv = m.apply_quantised(w["qkv"], codes, absmax)
+        t["qkv"] = qkv
+        qd, kd = self.hq * 128, self.hk * 128
+        q, k, v = qkv[:, :qd].view(T, self.hq, 128), qkv[:, qd:qd + kd], qkv[:, qd + kd:]
+        q, k = fp.qk_norm_rope_fwht(batch.positions, q, k, self.cache, w.get("q_norm"), w.get("k_norm"))
+        t["q_rot"], t["k_rot"] = q, k
+        self.pool.store_kv(k, v, batch.out_loc, self.layer_id)
+        q8, _, q_absmax = fp.per_token_quant_int8_from_q15(q.reshape(T * self.hq, 128), return_absmax=True)
+        q_mul, q_shift = fp.absmax_to_mul_shift(q_absmax)
+        q8, q_mul, q_shift = q8.view(T, self.hq, 128), q_mul.view(T, self.hq), q_shift.view(T, self.hq)
+        t["q8"] = q8
+        if batch.q_lens is None:
+            attn = decode_attention_int8_paged(q8, q_mul, q_shift, self.pool, self.layer_id, batch.page_table,
+                                               batch.kv_lens, batch.max_kv_len)
+        else:
+            attn = extend_attention_int8_paged(q8, q_mul, q_shift, self.pool, self.layer_id, batch.page_table,
+                                               batch.kv_lens, batch.q_lens, batch.max_kv_len)
+        t["attn"] = attn
+        o = m.apply_weights_q15(w["o"], attn.view(T, qd))
+        t["o"] = o
+        # post_attention_layernorm (+ residual add) -> codes for gate_up_proj
+        codes, _, absmax, residual, _ = fp.fused_add_rmsnorm_quant(o, residual, w["post_norm"])
+        t["ln2_codes"], t["res2"] = codes, residual
+        gate_up = m.apply_quantised(w["gate_up"], codes, absmax)
+        t["gate_up"] = gate_up
+        codes, _, absmax, _ = fp.silu_mul_fwht_quant(gate_up, self.hadamard_block)
+        t["act_codes"], t["act_absmax"] = codes, absmax
+        down = m.apply_quantised(w["down"], codes, absmax)
+        t["down"] = down
+        return down, residual
