@@ -6,10 +6,12 @@
 //   out[t, n]  = sat32(mul_shift(acc, (x_mul[t] * w_mul[n]) >> 32, x_shift[t] + w_shift[n] - 48))
 //
 // Both operands are K-major (x8 [M, K] and w8 [N, K] row-major), which is what the UMMA wants.
-// One CTA computes one 128 x BN output tile:
+// A tile is 128 x BN outputs (BN = 256 at large M, down to 32 at decode sizes):
 //   warp 0        TMA producer (one lane): A tile 128 x 128 B and B tile BN x 128 B per k-block
 //   warp 1        allocates tensor memory; one lane issues the MMAs (4 per k-block, K = 32 each)
-//   warps 2..5    epilogue: each reads its 32-lane quarter of the accumulator tile
+//   warps 2..9    epilogue: two per 32-lane quarter of the accumulator tile, half the columns each
+// The kernel is persistent (one CTA per SM walks a strided list of tiles) and keeps two accumulator
+// copies in tensor memory, so the epilogue of one tile overlaps the MMAs of the next.
 // Stages are handed over with mbarriers (TMA -> MMA by transaction bytes, MMA -> TMA and
 // MMA -> epilogue by tcgen05.commit).  Every wait is bounded: on expiry the waiter raises an
 // error flag that the host can read, and the CTA still runs to its end and frees its tensor memory.
@@ -22,7 +24,8 @@ namespace b200 {
 constexpr int kBM = 128;            // rows of x per tile (UMMA M)
 constexpr int kBK = 128;            // bytes of K per stage = one 128-byte swizzle row
 constexpr int kUmmaK = 32;          // K per tcgen05.mma for 8-bit operands
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;         // two per 32-lane quarter of tensor memory, each half of the columns
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr unsigned kSpinLimit = 1u << 22;
 
 __device__ int g_gemm_status = 0;   // 0 = fine; otherwise the code of the first wait that gave up
@@ -108,6 +111,58 @@ struct GemmParams {
   int M, N, K;
 };
 
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void epilogue_bar_sync() {   // the epilogue threads only
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+}
+
+__device__ __forceinline__ int requant_one(int acc, int cm, int s) {
+  if (s > 0 && s < 63) return sat32(((long long)acc * (long long)cm + (1LL << (s - 1))) >> s);
+  return sat32(mul_shift64((long long)acc, (long long)cm, s));
+}
+
+constexpr int kStagePitch = 20;   // ints per staged row of 16: 16-byte aligned, conflict-free for int4 both ways
+
+// Warp-private 32 x 16 int32 tile, used twice per 32-column chunk: lane = row on the way in, eight
+// rows x four int4 (64 contiguous bytes per row) per instruction on the way out (rows r_base..,
+// columns col0.. of a row-major [M, N] matrix).
+__device__ __forceinline__ void store_chunk(int32_t* stage, int lane, const int (&v)[32], int32_t* out,
+                                            int r_base, int col0, int M, int N, bool vec) {
+  const int rr = lane >> 2, cc = (lane & 3) * 4;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 16; j += 4)
+      *reinterpret_cast<int4*>(stage + lane * kStagePitch + j) =
+          make_int4(v[16 * h + j], v[16 * h + j + 1], v[16 * h + j + 2], v[16 * h + j + 3]);
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int r = it * 8 + rr;
+      const int row = r_base + r, col = col0 + 16 * h + cc;
+      if (row < M && col < N) {
+        const int4 o = *reinterpret_cast<const int4*>(stage + r * kStagePitch + cc);
+        int32_t* dst = out + (int64_t)row * N + col;
+        if (vec) {   // N % 4 == 0 and col % 4 == 0: the whole int4 is inside the row
+          *reinterpret_cast<int4*>(dst) = o;
+        } else {
+          dst[0] = o.x;
+          if (col + 1 < N) dst[1] = o.y;
+          if (col + 2 < N) dst[2] = o.z;
+          if (col + 3 < N) dst[3] = o.w;
+        }
+      }
+    }
+  }
+}
+
+// Persistent kernel: CTA c computes tiles c, c + gridDim.x, ...  (tile -> n block outer, m block inner,
+// so the CTAs running at the same time share one block of weight rows in L2).  The accumulator
+// lives in tensor memory twice (2 x BN columns): while the epilogue warps drain one copy, the MMA
+// warp already fills the other with the next tile.
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -117,24 +172,32 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   constexpr int kBBytes = BN * kBK;
   constexpr int kStageBytes = kABytes + kBBytes;
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * kStageBytes);   // full[S], empty[S], tmem_full
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 1);
+  // barriers: full[S], empty[S], tmem_full[2], tmem_empty[2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * kStageBytes);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 4);
+  int32_t* col_scale = reinterpret_cast<int32_t*>(tmem_slot + 4);   // [2 slots][mul BN | shift BN]
+  int32_t* stage_all = col_scale + 4 * BN;                          // [epilogue warps][32][kStagePitch]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_blk = blockIdx.x, m_blk = blockIdx.y;
   const int num_kb = (p.K + kBK - 1) / kBK;
-  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), tfull = smem_u32(bars + 2 * STAGES);
+  const int m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const unsigned tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
 
   if (warp == 0 && lane == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(tfull, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull0 + 8 * s, 1);
+      mbar_init(tempty0 + 8 * s, kEpiWarps);   // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {   // the whole warp allocates BN columns (a power of two >= 32) of tensor memory
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+  if (warp == 1) {   // the whole warp allocates 2 x BN columns (a power of two >= 32) of tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tcgen05_fence_before();
@@ -144,98 +207,115 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const unsigned ph = (kb / STAGES) & 1;
-        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, 1)) break;
-        mbar_expect_tx(full0 + 8 * s, kStageBytes);
-        const unsigned a_dst = smem_u32(tiles + s * kStageBytes);
-        tma_load_2d(a_dst, &map_a, kb * kBK, m_blk * kBM, full0 + 8 * s);
-        tma_load_2d(a_dst + kABytes, &map_b, kb * kBK, n_blk * BN, full0 + 8 * s);
+      unsigned it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int n_blk = tile / m_tiles, m_blk = tile - n_blk * m_tiles;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
+          ok = mbar_wait(empty0 + 8 * s, ph ^ 1, 1);
+          if (!ok) break;
+          mbar_expect_tx(full0 + 8 * s, kStageBytes);
+          const unsigned a_dst = smem_u32(tiles + s * kStageBytes);
+          tma_load_2d(a_dst, &map_a, kb * kBK, m_blk * kBM, full0 + 8 * s);
+          tma_load_2d(a_dst + kABytes, &map_b, kb * kBK, n_blk * BN, full0 + 8 * s);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr unsigned idesc = make_idesc(kBM, BN);
+      unsigned it = 0, lt = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const unsigned ph = (kb / STAGES) & 1;
-        ok = mbar_wait(full0 + 8 * s, ph, 2);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+        const unsigned slot = lt & 1, aph = (lt >> 1) & 1;
+        ok = mbar_wait(tempty0 + 8 * slot, aph ^ 1, 4);   // the epilogue has drained this accumulator copy
         if (!ok) break;
         tcgen05_fence_after();
-        const unsigned a_addr = smem_u32(tiles + s * kStageBytes);
-        const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + kABytes);
+        const unsigned tmem_d = tmem_base + slot * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
+          ok = mbar_wait(full0 + 8 * s, ph, 2);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const unsigned a_addr = smem_u32(tiles + s * kStageBytes);
+          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + kABytes);
 #pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k) {
-          // the next 32 bytes of K inside the swizzle row: start address + 32 (encoded >> 4)
-          umma_i8(tmem_base, da + (uint64_t)(k * kUmmaK >> 4), db + (uint64_t)(k * kUmmaK >> 4), idesc,
-                  (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // the next 32 bytes of K inside the swizzle row: start address + 32 (encoded >> 4)
+            umma_i8(tmem_d, da + (uint64_t)(k * kUmmaK >> 4), db + (uint64_t)(k * kUmmaK >> 4), idesc,
+                    (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
         }
-        tcgen05_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
+        tcgen05_commit(tfull0 + 8 * slot);  // accumulators complete (or abandoned): release the epilogue
       }
-      tcgen05_commit(tfull);              // accumulators complete (or abandoned): release the epilogue
     }
   } else {
-    // epilogue warps 2..5: TMEM lane quarter = warp % 4, one accumulator row per thread
+    // epilogue warps 2..9: TMEM lane quarter = warp % 4 (one accumulator row per thread); the two
+    // warps of a quarter take alternate 32-column chunks of the tile
     const int q = warp & 3;
-    const int row = m_blk * kBM + q * 32 + lane;
-    const bool ok = mbar_wait(tfull, 0, 3);
-    tcgen05_fence_after();
-    int xm = 0, xs = 0;
-    if (row < p.M && p.out_q15) { xm = p.x_mul[row]; xs = p.x_shift[row] - 48; }
-#pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
-      int v[32];
-      tmem_ld_32x32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
-      const int col0 = n_blk * BN + c0;
-      if (ok && row < p.M && num_kb > 0) {
-        if (p.acc_out) {
-          int32_t* dst = p.acc_out + (int64_t)row * p.N + col0;
-          if (col0 + 32 <= p.N && (p.N & 3) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4*>(dst + j) = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
-          }
-        }
-        if (p.out_q15) {
-          int32_t* dst = p.out_q15 + (int64_t)row * p.N + col0;
-          const bool full = col0 + 32 <= p.N && (p.N & 3) == 0;
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            int o[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int col = min(col0 + j + e, p.N - 1);
-              const int wm = __ldg(p.w_mul + col);
-              const int ws = p.w_shift ? __ldg(p.w_shift + col) : 31;
-              const int s = xs + ws;
-              const int cm = __mulhi(xm, wm);
-              long long r;
-              if (s > 0 && s < 63) {
-                r = ((long long)v[j + e] * (long long)cm + (1LL << (s - 1))) >> s;
-              } else {
-                r = mul_shift64((long long)v[j + e], (long long)cm, s);
-              }
-              o[e] = sat32(r);
-            }
-            if (full) {
-              *reinterpret_cast<int4*>(dst + j) = make_int4(o[0], o[1], o[2], o[3]);
-            } else {
-              for (int e = 0; e < 4; ++e)
-                if (col0 + j + e < p.N) dst[j + e] = o[e];
-            }
-          }
+    const int half = (warp - 2) >> 2;
+    const int et = threadIdx.x - 64;   // 0 .. 32 * kEpiWarps - 1
+    int32_t* stage = stage_all + (warp - 2) * (32 * kStagePitch);
+    unsigned lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
+      const int n_blk = tile / m_tiles, m_blk = tile - n_blk * m_tiles;
+      const unsigned slot = lt & 1, aph = (lt >> 1) & 1;
+      const int row = m_blk * kBM + q * 32 + lane;
+      // the tile's per-column scales go to shared memory once (double-buffered by accumulator slot)
+      int32_t* cs = col_scale + slot * 2 * BN;
+      if (p.out_q15) {
+        for (int c = et; c < BN; c += 32 * kEpiWarps) {
+          const int col = min(n_blk * BN + c, p.N - 1);
+          cs[c] = __ldg(p.w_mul + col);
+          cs[BN + c] = (p.w_shift ? __ldg(p.w_shift + col) : 31) - 48;   // x_shift + w_shift - 48 later
         }
       }
+      int xm = 0, xs = 0;
+      if (row < p.M && p.out_q15) { xm = __ldg(p.x_mul + row); xs = __ldg(p.x_shift + row); }
+      epilogue_bar_sync();
+      if (ok) ok = mbar_wait(tfull0 + 8 * slot, aph, 3);
+      tcgen05_fence_after();
+#pragma unroll 1
+      for (int c0 = half * 32; c0 < BN; c0 += 64) {   // the quarter's two warps take alternate 32-column chunks
+        int v[32];
+        tmem_ld_32x32(tmem_base + ((unsigned)(q * 32) << 16) + slot * BN + (unsigned)c0, v);
+        const int col0 = n_blk * BN + c0;
+        if (!ok || col0 >= p.N) continue;   // warp-uniform
+        // A thread holds 32 columns of ONE row; storing that directly would touch 32 rows per
+        // instruction.  The chunk goes through a padded shared-memory tile so that each store
+        // instruction writes four rows of 128 contiguous bytes.
+        const int r_base = m_blk * kBM + q * 32;
+        const bool vec = (p.N & 3) == 0;
+        if (p.acc_out) {
+          store_chunk(stage, lane, v, p.acc_out, r_base, col0, p.M, p.N, vec);
+        }
+        if (p.out_q15) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const int4 wm = *reinterpret_cast<const int4*>(cs + c0 + j);
+            const int4 ws = *reinterpret_cast<const int4*>(cs + BN + c0 + j);
+            v[j + 0] = requant_one(v[j + 0], __mulhi(xm, wm.x), xs + ws.x);
+            v[j + 1] = requant_one(v[j + 1], __mulhi(xm, wm.y), xs + ws.y);
+            v[j + 2] = requant_one(v[j + 2], __mulhi(xm, wm.z), xs + ws.z);
+            v[j + 3] = requant_one(v[j + 3], __mulhi(xm, wm.w), xs + ws.w);
+          }
+          store_chunk(stage, lane, v, p.out_q15, r_base, col0, p.M, p.N, vec);
+        }
+      }
+      // this warp has read its quarter of the accumulator copy: hand it back to the MMA warp
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * slot);
     }
   }
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
 }
 
@@ -269,15 +349,27 @@ static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
-  constexpr size_t smem = (size_t)STAGES * (kBM * kBK + BN * kBK) + 1024 + (2 * STAGES + 1) * 8 + 16;
+  constexpr size_t smem = (size_t)STAGES * (kBM * kBK + BN * kBK) + 1024 + (2 * STAGES + 4) * 8 + 16 + 4 * BN * 4 + kEpiWarps * 32 * kStagePitch * 4;
+  static_assert(smem <= 227 * 1024, "shared memory budget");
   cudaError_t e = cudaFuncSetAttribute(gemm_w8a8_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("gemm_w8a8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return B200_E_CUDA;
   }
-  dim3 grid((p.N + BN - 1) / BN, (p.M + kBM - 1) / kBM);
+  const int tiles = ((p.N + BN - 1) / BN) * ((p.M + kBM - 1) / kBM);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
   gemm_w8a8_kernel<BN, STAGES><<<grid, kGemmThreads, smem, st>>>(ma, mb, p);
   return check_launch("gemm_w8a8");
 }
@@ -304,8 +396,19 @@ extern "C" int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t*
   GemmParams p;
   p.x_mul = x_mul; p.x_shift = x_shift; p.w_mul = w_mul; p.w_shift = w_shift;
   p.out_q15 = out_q15; p.acc_out = acc_out; p.M = (int)m; p.N = (int)n; p.K = (int)k;
-  B200_REQUIRE(make_map(&mb, w8, n, k, 128), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for w8");
-  return launch_gemm<128, 6>(ma, mb, p, (cudaStream_t)s);
+  // tile width: wide tiles for throughput at large M; narrow ones at decode sizes so that enough CTAs
+  // stream the weights (one m block there, so the tile count is n / BN)
+  const int64_t m_tiles = (m + kBM - 1) / kBM;
+  int bn = 256;
+  while (bn > 32 && m_tiles * ((n + bn - 1) / bn) < sm_count()) bn >>= 1;
+  B200_REQUIRE(make_map(&mb, w8, n, k, bn), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for w8");
+  cudaStream_t st = (cudaStream_t)s;
+  switch (bn) {
+    case 256: return launch_gemm<256, 4>(ma, mb, p, st);
+    case 128: return launch_gemm<128, 6>(ma, mb, p, st);
+    case 64: return launch_gemm<64, 8>(ma, mb, p, st);
+    default: return launch_gemm<32, 10>(ma, mb, p, st);
+  }
 }
 
 extern "C" int b200_gemm_status(int* out_host, int reset) {
