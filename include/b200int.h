@@ -187,6 +187,20 @@ B200_API int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t* x
                             int32_t* out_q15, int32_t* acc_out, int64_t m, int64_t n, int64_t k,
                             b200_stream_t s);
 
+/* ---- Pieces of the W8A8 linear for tensor-parallel row-split layers, where the int32 partial
+ * sums of the ranks are added (all-reduce) between the GEMM and its epilogue.  They stand in for
+ * the per-rank quant + GEMM + all-reduce of LinearOProj / LinearRowParallel
+ * (layers/linear.py:108-160) in a way that gives the same bits as one GPU: quantise every shard
+ * with the maximum of the ranks' absmax, add the exact int32 accumulators, requantise once.
+ *   b200_quant_given_absmax_q15: x int32 [rows, k], absmax int32 [rows] -> codes int8 [rows, k]
+ *   b200_requant_q15: acc int32 [m, n] -> out int32 [m, n] with the epilogue formula of b200_gemm_w8a8
+ *                     (w_shift nullable = 31). */
+B200_API int b200_quant_given_absmax_q15(const int32_t* x, const int32_t* absmax, int8_t* codes,
+                                         int64_t rows, int k, b200_stream_t s);
+B200_API int b200_requant_q15(const int32_t* acc, const int32_t* x_mul, const int32_t* x_shift,
+                              const int32_t* w_mul, const int32_t* w_shift, int32_t* out,
+                              int64_t m, int64_t n, b200_stream_t s);
+
 /* Reads (and optionally clears) the device-side status word of the GEMM kernels: 0 = fine,
  * non-zero = a bounded wait inside a kernel expired (1 producer, 2 MMA issuer, 3 epilogue).
  * Synchronises with the device.  No counterpart in the reference. */

@@ -14,7 +14,6 @@
 // exponentials and the partial outputs are exchanged between the CTAs over distributed shared
 // memory.  K and V are each read from HBM exactly once.
 #include <cooperative_groups.h>
-#include <cstdlib>
 
 #include "common.cuh"
 #include "luts.cuh"
@@ -133,7 +132,6 @@ struct DecodeParams {
   int64_t num_pages;
   int max_kv_len;
   int s_max;  // key capacity of one CTA's slice (multiple of 32)
-  int dbg_skip;
 };
 
 __device__ __forceinline__ void mma_s8s8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -357,7 +355,7 @@ attn_decode_kernel(const DecodeParams p) {
 
   // ---- phase 1: one page (16 keys) per MMA tile gives raw int32 dots; then, one key per lane,
   // the Q15.16 scores of the pair, their running maximum and the reference V scale
-  if (!(p.dbg_skip & 1)) {
+  {
     const bool h0 = 2 * fc < G, h1 = 2 * fc + 1 < G;
     int32_t* sc0 = sc + (2 * fc) * S + fr;
     int32_t* sc1 = sc0 + S;
@@ -461,7 +459,7 @@ attn_decode_kernel(const DecodeParams p) {
   __syncthreads();
 
   // ---- phase 2: exponentials, their sum, and the relative V scale of every key
-  if (!(p.dbg_skip & 4)) {
+  {
     int lsum[G];   // a thread sees at most S / threads keys, each e <= 2^16: no overflow
     int gm[G];
 #pragma unroll
@@ -537,7 +535,7 @@ attn_decode_kernel(const DecodeParams p) {
   // folded with the relative V scale, as two byte limbs; then PV, two pages (32 tokens) per
   // k-step, 8 d-tiles of 16.  The key holding the row maximum contributes e = 2^16, so the
   // total is >= 2^16 and inv <= 32767: e * inv < 2^31 and p * rel < 2^31, 32-bit arithmetic is exact.
-  if (!(p.dbg_skip & 16)) {
+  {
     unsigned gi[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) gi[g] = (unsigned)g_inv[g];
@@ -605,7 +603,7 @@ attn_decode_kernel(const DecodeParams p) {
 
   // ---- exchange 3: head g is finished by rank g % C: sum the partial outputs of all CTAs over
   // distributed shared memory, requantise, and (for the int8 output) quantise the 128-wide row
-  if (!(p.dbg_skip & 32)) {
+  {
     for (int g = rank; g < G; g += C) {   // uniform per CTA
       const int d = tid;                   // kDecodeThreads == kD
       long long a = 0;
@@ -747,7 +745,6 @@ static int attn_common(const int8_t* q, const int32_t* q_mul, const int32_t* q_s
   p.page_table = page_table; p.table_pitch = table_pitch; p.kv_lens = kv_lens; p.out_q15 = out_q15;
   p.out_codes = out_codes; p.out_absmax = out_absmax; p.q_heads = q_heads; p.kv_heads = kv_heads;
   p.num_pages = num_pages; p.max_kv_len = max_kv_len; p.row_seq = row_seq; p.row_limit = row_limit;
-  { const char* e = getenv("B200_DECODE_SKIP"); p.dbg_skip = e ? atoi(e) : 0; }
   const int ppc = (max_pages + cluster - 1) / cluster;
   p.s_max = ((ppc * kPage + 31) / 32) * 32;
   cudaStream_t st = (cudaStream_t)s;

@@ -170,6 +170,36 @@ quant_rows_kernel(const int32_t* __restrict__ x, int8_t* __restrict__ codes,
   }
 }
 
+// Quantise rows with a GIVEN absmax (tensor-parallel row-split linears: the absmax is the maximum
+// over all ranks' shards so that every rank uses the same per-token scale).
+__global__ void quant_given_absmax_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ absmax,
+                                          int8_t* __restrict__ codes, int64_t rows, int K) {
+  const int nvec = K >> 2;
+  const int64_t total = rows * nvec;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / nvec;
+    const float mf = __int2float_rn(max(1, absmax[r]));
+    const float my = __frcp_rn(mf);
+    const int4 v = reinterpret_cast<const int4*>(x)[i];
+    reinterpret_cast<unsigned*>(codes)[i] = pack4(quant_code_fast(v.x, mf, my), quant_code_fast(v.y, mf, my),
+                                                  quant_code_fast(v.z, mf, my), quant_code_fast(v.w, mf, my));
+  }
+}
+
+// The GEMM's fixed-point epilogue on its own: out = sat32(mul_shift(acc, (x_mul*w_mul)>>32, x_shift+w_shift-48)).
+__global__ void requant_kernel(const int32_t* __restrict__ acc, const int32_t* __restrict__ x_mul,
+                               const int32_t* __restrict__ x_shift, const int32_t* __restrict__ w_mul,
+                               const int32_t* __restrict__ w_shift, int32_t* __restrict__ out, int64_t m, int n) {
+  const int64_t total = m * n;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / n;
+    const int c = (int)(i - r * n);
+    const int cm = __mulhi(x_mul[r], w_mul[c]);
+    const int s = x_shift[r] + (w_shift ? w_shift[c] : 31) - 48;
+    out[i] = sat32(mul_shift64((long long)acc[i], (long long)cm, s));
+  }
+}
+
 struct RowPlan {
   int threads, vpt;
 };
@@ -740,4 +770,26 @@ extern "C" int b200_absmax_to_mul_shift(const int32_t* absmax, int32_t* mul, int
   if (n == 0) return B200_OK;
   absmax_to_ms_kernel<<<elementwise_grid(n, 256), 256, 0, (cudaStream_t)s>>>(absmax, mul, shift, n);
   return check_launch("absmax_to_mul_shift");
+}
+
+extern "C" int b200_quant_given_absmax_q15(const int32_t* x, const int32_t* absmax, int8_t* codes, int64_t rows,
+                                           int k, b200_stream_t s) {
+  B200_REQUIRE(x && absmax && codes, B200_E_NULL, "quant_given_absmax_q15: null pointer");
+  B200_REQUIRE(rows >= 0 && k > 0, B200_E_SHAPE, "quant_given_absmax_q15: rows=%lld k=%d", (long long)rows, k);
+  B200_REQUIRE(k % 4 == 0, B200_E_UNSUPPORTED, "quant_given_absmax_q15: k=%d is not a multiple of 4", k);
+  if (rows == 0) return B200_OK;
+  B200_REQUIRE(aligned16(x) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN,
+               "quant_given_absmax_q15: x must be 16-byte aligned, codes 4-byte");
+  quant_given_absmax_kernel<<<elementwise_grid(rows * (k / 4), 256), 256, 0, (cudaStream_t)s>>>(x, absmax, codes, rows, k);
+  return check_launch("quant_given_absmax_q15");
+}
+
+extern "C" int b200_requant_q15(const int32_t* acc, const int32_t* x_mul, const int32_t* x_shift,
+                                const int32_t* w_mul, const int32_t* w_shift, int32_t* out, int64_t m, int64_t n,
+                                b200_stream_t s) {
+  B200_REQUIRE(acc && x_mul && x_shift && w_mul && out, B200_E_NULL, "requant_q15: null pointer");
+  B200_REQUIRE(m >= 0 && n > 0 && n < (1ll << 31), B200_E_SHAPE, "requant_q15: m=%lld n=%lld", (long long)m, (long long)n);
+  if (m == 0) return B200_OK;
+  requant_kernel<<<elementwise_grid(m * n, 256), 256, 0, (cudaStream_t)s>>>(acc, x_mul, x_shift, w_mul, w_shift, out, m, (int)n);
+  return check_launch("requant_q15");
 }

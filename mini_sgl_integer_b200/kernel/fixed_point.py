@@ -359,6 +359,20 @@ def silu_mul_fwht_quant(gate_up: torch.Tensor, fwht_block: int = 128, want_q15: 
     return codes, scale, absmax, q15
 
 
+def silu_mul_fwht_q15(gate_up: torch.Tensor, fwht_block: int = 128) -> torch.Tensor:
+    """SiLU(gate) * up -> blocked FWHT, Q15.16 out (no quant): silu_and_mul_int_only + apply_blockwise_fwht_q15."""
+    assert_q15(gate_up, "gate_up")
+    if gate_up.ndim != 2:
+        raise ValueError(f"gate_up must be 2D [tokens, 2*inter], got shape {tuple(gate_up.shape)}")
+    require_cuda(gate_up)
+    g = gate_up.contiguous()
+    rows, inter = g.shape[0], g.shape[1] // 2
+    out = torch.empty((rows, inter), dtype=torch.int32, device=g.device)
+    if out.numel():
+        call("b200_silu_mul_q15", ptr(g), ptr(out), None, None, None, rows, inter, int(fwht_block), stream())
+    return out
+
+
 def qk_norm_rope_fwht(positions, query_q15, key_q15, cos_sin_cache_q15, q_norm_weight, k_norm_weight):
     """Per-head RMSNorm of q and k, RoPE and FWHT in one kernel.
 
@@ -379,5 +393,5 @@ __all__ = [
     "rope_int_q15", "fwht_int_q15", "rope_fwht_int_q15", "rmsnorm_int_only_v2",
     "fused_add_rmsnorm_int_only_v2", "silu_and_mul_int_only", "apply_blockwise_fwht_q15",
     "per_token_quant_int8_from_q15", "absmax_to_mul_shift", "fused_add_rmsnorm_quant",
-    "silu_mul_fwht_quant", "qk_norm_rope_fwht",
+    "silu_mul_fwht_quant", "silu_mul_fwht_q15", "qk_norm_rope_fwht",
 ]

@@ -16,6 +16,8 @@ import torch
 
 from ..attention import Int8PagedKVCache, decode_attention_int8_paged, extend_attention_int8_paged
 from ..kernel import fixed_point as fp
+from ..distributed import DistributedCommunicator
+from .tp_linear import row_parallel_q15
 from .w8a8_int8 import W8A8Int8LinearMethod
 
 
@@ -46,9 +48,15 @@ class _Linear(torch.nn.Module):
 class Qwen3DecoderLayerInteger:
     def __init__(self, layer_id: int, num_qo_heads: int, num_kv_heads: int, hidden: int, inter: int,
                  weights: dict, cos_sin_cache_q15: torch.Tensor, pool: Int8PagedKVCache,
-                 hadamard_block: int = 128):
+                 hadamard_block: int = 128, comm: Optional[DistributedCommunicator] = None):
         """``weights``: qkv/o/gate_up/down -> _Linear; input_norm/post_norm int32 [hidden];
-        q_norm/k_norm int32 [128] or None (Q15.16; q_norm already carries head_dim**-0.5)."""
+        q_norm/k_norm int32 [128] or None (Q15.16; q_norm already carries head_dim**-0.5).
+
+        Under tensor parallelism (``comm`` with more than one rank) ``num_qo_heads``, ``num_kv_heads`` and
+        ``inter`` are this rank's share, qkv / gate_up hold this rank's output channels (q | k | v and
+        gate | up blocks of the local heads / columns), o / down this rank's input features, as the
+        reference shards them (models/weight.py:12-52, layers/linear.py:73-160)."""
+        self.comm = comm if comm is not None else DistributedCommunicator()
         self.layer_id, self.hq, self.hk, self.hidden, self.inter = layer_id, num_qo_heads, num_kv_heads, hidden, inter
         self.w = weights
         self.cache = cos_sin_cache_q15
@@ -85,15 +93,19 @@ class Qwen3DecoderLayerInteger:
             attn = extend_attention_int8_paged(q8, q_mul, q_shift, self.pool, self.layer_id, batch.page_table,
                                                batch.kv_lens, batch.q_lens, batch.max_kv_len)
         t["attn"] = attn
-        o = m.apply_weights_q15(w["o"], attn.view(T, qd))
+        tp = self.comm.size > 1
+        o = row_parallel_q15(m, w["o"], attn.view(T, qd), self.comm) if tp else m.apply_weights_q15(w["o"], attn.view(T, qd))
         t["o"] = o
         # post_attention_layernorm (+ residual add) -> codes for gate_up_proj
         codes, _, absmax, residual, _ = fp.fused_add_rmsnorm_quant(o, residual, w["post_norm"])
         t["ln2_codes"], t["res2"] = codes, residual
         gate_up = m.apply_quantised(w["gate_up"], codes, absmax)
         t["gate_up"] = gate_up
-        codes, _, absmax, _ = fp.silu_mul_fwht_quant(gate_up, self.hadamard_block)
-        t["act_codes"], t["act_absmax"] = codes, absmax
-        down = m.apply_quantised(w["down"], codes, absmax)
+        if tp:   # the token's absmax spans all ranks' columns: rotate locally, agree on the scale, then quantise
+            down = row_parallel_q15(m, w["down"], fp.silu_mul_fwht_q15(gate_up, self.hadamard_block), self.comm)
+        else:
+            codes, _, absmax, _ = fp.silu_mul_fwht_quant(gate_up, self.hadamard_block)
+            t["act_codes"], t["act_absmax"] = codes, absmax
+            down = m.apply_quantised(w["down"], codes, absmax)
         t["down"] = down
         return down, residual
