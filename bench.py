@@ -393,6 +393,94 @@ def run_gemm(args) -> None:
     }))
 
 
+def run_tp_layer(args) -> None:
+    """Configuration 5 proxy: ONE Qwen3-32B-shaped integer decoder layer, decode step of batch 256 with contexts
+    U[1024, 8192], tensor-parallel over the launched ranks (attention by KV head, column/row-split GEMMs, two
+    int32 all-reduces per layer over NCCL).  tokens/s are quoted for the 64-layer model (64 x this layer)."""
+    import torch
+    import torch.distributed as dist
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    from mini_sgl_integer_b200.distributed import DistributedCommunicator
+    from mini_sgl_integer_b200.layers.decoder_layer import AttnBatch, Qwen3DecoderLayerInteger, _Linear
+
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    HID, HQ, HK, INTER, LAYERS, B = 5120, 64, 8, 25600, 64, args.tp_batch
+    hq, hk, inter = HQ // world, HK // world, INTER // world
+    g = torch.Generator(device=dev).manual_seed(7)            # same seed on every rank: replicated tensors agree
+    ri8 = lambda *shape: torch.randint(-127, 128, shape, dtype=torch.int8, device=dev, generator=g)
+    def lin(n, k):
+        l = _Linear(ri8(n, k), weight_mul=torch.randint(2**29, 2**30, (n,), dtype=torch.int32, device=dev, generator=g),
+                    weight_shift=torch.full((n,), 38, dtype=torch.int32, device=dev))
+        return l
+    weights = {"qkv": lin((hq + 2 * hk) * 128, HID), "o": lin(HID, hq * 128), "gate_up": lin(2 * inter, HID), "down": lin(HID, inter),
+               "input_norm": torch.randint(2**13, 2**15, (HID,), dtype=torch.int32, device=dev, generator=g),
+               "post_norm": torch.randint(2**13, 2**15, (HID,), dtype=torch.int32, device=dev, generator=g),
+               "q_norm": torch.randint(2**11, 2**13, (128,), dtype=torch.int32, device=dev, generator=g),
+               "k_norm": torch.randint(2**12, 2**14, (128,), dtype=torch.int32, device=dev, generator=g)}
+    rng = np.random.default_rng(11)
+    lens = rng.integers(1024, 8193, B)
+    n_pg = (lens + 15) // 16
+    P = int(n_pg.sum()) + 8
+    pool = Int8PagedKVCache(hk, 1, 128, P, dev)
+    pool.k_cache(0).copy_(ri8(*pool.k_cache(0).shape)); pool.v_cache(0).copy_(ri8(*pool.v_cache(0).shape))
+    meta = pool.meta(0)
+    meta[:, :, 0:32] = torch.randint(2**30, 2**31, (P, hk, 32), dtype=torch.int64, device=dev, generator=g).to(torch.int32)
+    meta[:, :, 32:36] = torch.randint(35, 39, (P, hk, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
+    meta[:, :, 36:40] = torch.randint(36, 40, (P, hk, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
+    perm = rng.permutation(P)
+    pitch = 512
+    table = np.zeros((B, pitch), dtype=np.int32)
+    off = 0
+    for b in range(B):
+        table[b, : n_pg[b]] = perm[off:off + n_pg[b]]; off += n_pg[b]
+    out_loc = np.array([table[b, (lens[b] - 1) // 16] * 16 + (lens[b] - 1) % 16 for b in range(B)], dtype=np.int32)
+    inv = 1.0 / (1000000.0 ** (torch.arange(0, 128, 2, dtype=torch.float) / 128))
+    fr = torch.einsum("i,j -> ij", torch.arange(8192, dtype=torch.float), inv)
+    cache = torch.clamp(torch.round(torch.cat((fr.cos(), fr.sin()), -1) * 32768), -32768, 32767).to(torch.int32).to(dev)
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    comm = DistributedCommunicator()
+    layer = Qwen3DecoderLayerInteger(0, hq, hk, HID, inter, weights, cache, pool, comm=comm)
+    batch = AttnBatch(d((lens - 1).astype(np.int32)), d(out_loc), d(table), d(lens.astype(np.int32)), None, 8192)
+    x = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
+    res = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
+    step = lambda: layer.forward_q15(x, res, batch)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms)
+    if rank == 0:
+        w_bytes = ((HQ + 2 * HK) * 128 * HID + HID * HQ * 128 + 2 * INTER * HID + HID * INTER) / world
+        kv_bytes = float(lens.sum()) * hk * 266
+        peak, how = measured_peak()
+        ach = (w_bytes + kv_bytes) / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "decode tok/s of a 64-layer 32B-shaped integer model, from one tensor-parallel layer step", "value": B / (LAYERS * ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "one Qwen3-32B-shaped decoder layer, decode batch %d, ctx U[1024,8192], TP=%d" % (B, world),
+                       "per_gpu_tok_s": B / (LAYERS * ms * 1e-3) / world, "eager_launches": True},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "peak_source": how, "bytes_per_rank": w_bytes + kv_bytes},
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -404,10 +492,11 @@ def main() -> None:
                     help="pages in the KV pool (smaller pools are for profiler captures only)")
     ap.add_argument("--sustain-s", type=float, default=1.0,
                     help="seconds of untimed back-to-back launches before the timed region (clock sampling)")
-    ap.add_argument("--workload", default="attn", choices=["attn", "rowops", "gemm"],
+    ap.add_argument("--workload", default="attn", choices=["attn", "rowops", "gemm", "tp_layer"],
                     help="attn = the headline decode attention (default); rowops / gemm = the other kernels of the path")
     ap.add_argument("--rows", type=int, default=16384, help="rows for --workload rowops")
     ap.add_argument("--m", type=int, default=4096, help="M for --workload gemm")
+    ap.add_argument("--tp-batch", type=int, default=256, help="decode batch for --workload tp_layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -416,6 +505,8 @@ def main() -> None:
         run_rowops(args)
     elif args.workload == "gemm":
         run_gemm(args)
+    elif args.workload == "tp_layer":
+        run_tp_layer(args)
     else:
         run_ours(args)
 
