@@ -153,10 +153,10 @@ __device__ __forceinline__ unsigned word_of(const uint4 (&v)[4], int wi) {
   return (wi & 3) == 0 ? q.x : (wi & 3) == 1 ? q.y : (wi & 3) == 2 ? q.z : q.w;
 }
 
-constexpr int kDecodeWarps = 4;
+constexpr int kDecodeWarps = 8;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
-static_assert(kDecodeThreads == kD, "the output stage maps one thread to one d");
-constexpr int kStages = 2;                 // ring slots per warp
+static_assert(kDecodeThreads >= kD, "the output stage maps one thread to one d");
+constexpr int kStages = 1;                 // ring slots per warp
 constexpr int kSlotBytes = 4096;           // one slot = a pair of pages (K rows, or V in operand order)
 constexpr int kMetaBytes = kMetaWords * 4; // 160
 
@@ -215,7 +215,7 @@ __device__ __forceinline__ unsigned rel_scale_q15(unsigned v_mul, unsigned m_ref
 // V in the operand order of v_chunk_offset.  The per-key fixed-point work (scale, exp, relative V
 // scale, probability limbs) runs in flat one-thread-per-key loops between the two MMA phases.
 template <int G>
-__global__ void __launch_bounds__(kDecodeThreads, 4)
+__global__ void __launch_bounds__(kDecodeThreads, 2)
 attn_decode_kernel(const DecodeParams p) {
   cg::cluster_group cluster = cg::this_cluster();
   const int C = (int)cluster.num_blocks();
@@ -605,16 +605,17 @@ attn_decode_kernel(const DecodeParams p) {
   // distributed shared memory, requantise, and (for the int8 output) quantise the 128-wide row
   {
     for (int g = rank; g < G; g += C) {   // uniform per CTA
-      const int d = tid;                   // kDecodeThreads == kD
+      const int d = tid & (kD - 1);        // threads beyond kD repeat a d and keep quiet
+      const bool act = tid < kD;
       long long a = 0;
       for (int r = 0; r < C; ++r) a += *cluster.map_shared_rank(&cta_acc[g][d], r);
       const int o = L > 0 ? mul_shift_sat32_wide(a, v_mul_ref, v_shift_ref - 1) : 0;
       const int64_t row = ((int64_t)b * p.q_heads + kh * G + g) * kD;
-      if (p.out_q15) p.out_q15[row + d] = o;
+      if (p.out_q15 && act) p.out_q15[row + d] = o;
       if (p.out_codes) {
         const int m = max(1, block_max(abs_wrap(o), red_s));
-        p.out_codes[row + d] = (int8_t)quant_code(o, __int2float_rn(m));
-        if (d == 0) p.out_absmax[(int64_t)b * p.q_heads + kh * G + g] = m;
+        if (act) p.out_codes[row + d] = (int8_t)quant_code(o, __int2float_rn(m));
+        if (tid == 0) p.out_absmax[(int64_t)b * p.q_heads + kh * G + g] = m;
       }
     }
   }
@@ -733,8 +734,10 @@ static int attn_common(const int8_t* q, const int32_t* q_mul, const int32_t* q_s
   B200_REQUIRE(aligned16(q) && aligned16(k_codes) && aligned16(v_codes) && aligned16(meta), B200_E_ALIGN,
                "attn_decode: q and pool buffers must be 16-byte aligned");
   if (cluster == 0) {
-    cluster = max_pages >= 128 ? 4 : (max_pages >= 32 ? 2 : 1);
-    while (cluster < 8 && decode_smem_bytes(G, ((((max_pages + cluster - 1) / cluster) * kPage + 31) / 32) * 32) > 96 * 1024)
+    // fewest CTAs per (sequence, KV head) whose slice state still lets two CTAs share an SM
+    cluster = 1;
+    while (cluster < 8 &&
+           decode_smem_bytes(G, ((((max_pages + cluster - 1) / cluster) * kPage + 31) / 32) * 32) > 100 * 1024)
       cluster *= 2;
   }
   B200_REQUIRE(cluster == 1 || cluster == 2 || cluster == 4 || cluster == 8, B200_E_UNSUPPORTED,
