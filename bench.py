@@ -219,9 +219,17 @@ def run_ours(args) -> None:
     sp = _lib.c_void_p(stream.cuda_stream)
     p = _lib.ptr
 
+    ws_bytes = int(_lib.load().b200_attn_workspace_bytes(B, Hq, Hkv, w["ctx_hi"]))
+    d_ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)      # caller-owned scratch of the workspace variant
+
     def launch():
-        _lib.call("b200_attn_decode", p(d_q), p(d_qm), p(d_qs), p(pool.k_cache(0)), p(pool.v_cache(0)), p(pool.meta(0)),
-                  p(d_table), pitch, p(d_lens), None, p(d_out), p(d_absmax), B, Hq, Hkv, P, w["ctx_hi"], args.cluster, sp)
+        if args.attn_impl == "split":
+            _lib.call("b200_attn_paged_ws", p(d_q), p(d_qm), p(d_qs), p(pool.k_cache(0)), p(pool.v_cache(0)), p(pool.meta(0)),
+                      p(d_table), pitch, p(d_lens), None, None, None, p(d_out), p(d_absmax), B, Hq, Hkv, P, w["ctx_hi"],
+                      p(d_ws), ws_bytes, sp)
+        else:
+            _lib.call("b200_attn_decode", p(d_q), p(d_qm), p(d_qs), p(pool.k_cache(0)), p(pool.v_cache(0)), p(pool.meta(0)),
+                      p(d_table), pitch, p(d_lens), None, p(d_out), p(d_absmax), B, Hq, Hkv, P, w["ctx_hi"], args.cluster, sp)
 
     def barrier():
         if world > 1:
@@ -290,13 +298,14 @@ def run_ours(args) -> None:
             "config": {"workload": "int8 paged decode attention, batch 64 per GPU, 32q/8kv heads, head_dim 128, page 16, "
                                    "ctx U[512,4096], 200k-page pool", **w, "sum_ctx": int(lens_np.sum()),
                        "l2": "inputs larger than L2 (about 314 MB of KV touched per launch vs 126 MB)",
-                       "cluster": args.cluster},
+                       "cluster": args.cluster, "attn_impl": args.attn_impl},
             "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * (5 if args.attn_impl == "split" else 1),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES, "peak_source": how, "algorithmic_bytes": alg,
-                         "kernel_ms": kern_ms, "kernel": "attn_decode_kernel<4>", "frac_of_8TBs": achieved / 8000.0},
+                         "kernel_ms": kern_ms, "kernel": "split_scores + split_expsum + split_pv (+ init, final)" if args.attn_impl == "split" else "attn_decode_kernel<4>",
+                         "workspace_bytes": ws_bytes if args.attn_impl == "split" else 0, "frac_of_8TBs": achieved / 8000.0},
             "cpu_baseline": {"value": cpu_rate, "unit": "tokens/s", "cores": host_threads(), "kind": "port",
                              "sample": f"{n_cpu} of the 64 sequences, one pass ({cpu_dt:.2f} s), numpy oracle port"},
             "clocks": clocks, "wall_s": t_wall1 - t_wall0,
@@ -488,6 +497,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cluster", type=int, default=0, help="CTAs per (sequence, KV head); 0 = library default")
+    ap.add_argument("--attn-impl", default="cluster", choices=["split", "cluster"],
+                    help="split = grid-wide passes over a workspace (5 launches per step); cluster = one kernel per step")
     ap.add_argument("--pool-pages", type=int, default=WORKLOAD["pool_pages"],
                     help="pages in the KV pool (smaller pools are for profiler captures only)")
     ap.add_argument("--sustain-s", type=float, default=1.0,

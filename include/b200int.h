@@ -171,6 +171,21 @@ B200_API int b200_attn_extend(const int8_t* q, const int32_t* q_mul, const int32
                               int rows, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
                               int cluster, b200_stream_t s);
 
+/* ---- The same decode / extend attention as a chain of grid-wide passes that meet in a caller-provided
+ * workspace (scores, row maxima and sums, reference V scales, int32 output accumulators) instead of
+ * inside thread-block clusters: better balanced, any context length.  Same arguments and results as
+ * b200_attn_decode (row_seq == row_limit == NULL, rows = batch) and b200_attn_extend.
+ * workspace: device memory, 256-byte aligned, at least b200_attn_workspace_bytes(...) bytes; its
+ * contents need not survive the call.  Calls that share a workspace must not overlap on the GPU. */
+B200_API size_t b200_attn_workspace_bytes(int rows, int q_heads, int kv_heads, int max_kv_len);
+B200_API int b200_attn_paged_ws(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
+                                const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
+                                const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                                const int32_t* row_seq, const int32_t* row_limit,
+                                int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax,
+                                int rows, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
+                                void* workspace, size_t workspace_bytes, b200_stream_t s);
+
 /* ---- W8A8 linear: int8 x int8 -> int32 on the tcgen05 tensor cores, fixed-point requant.
  * Stands in for the GEMM + epilogue inside W8A8Int8LinearMethod.apply_weights_q15
  * (layers/quantization/w8a8_int8.py:242-286), i.e. the sgl_kernel.int8_scaled_mm call at :272-279

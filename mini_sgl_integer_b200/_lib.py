@@ -34,13 +34,15 @@ SIGNATURES: dict[str, list] = {
     "b200_kv_store_q15": [P, L, P, L, P, P, P, P, L, I, L, P],
     "b200_kv_store_codes": [P, P, P, P, P, P, P, P, P, P, L, I, L, P],
     "b200_attn_extend": [P, P, P, P, P, P, P, L, P, P, P, P, P, P, I, I, I, L, I, I, P],
+    "b200_attn_workspace_bytes": [I, I, I, I],
+    "b200_attn_paged_ws": [P, P, P, P, P, P, P, L, P, P, P, P, P, P, I, I, I, L, I, P, ctypes.c_size_t, P],
     "b200_gemm_w8a8": [P, P, P, P, P, P, P, P, L, L, L, P],
     "b200_gemm_status": [P, I],
     "b200_quant_given_absmax_q15": [P, P, P, L, I, P],
     "b200_requant_q15": [P, P, P, P, P, P, L, L, P],
     "b200_attn_decode": [P, P, P, P, P, P, P, L, P, P, P, P, I, I, I, L, I, I, P],
 }
-_RESTYPES = {"b200_last_error_string": c_char_p}
+_RESTYPES = {"b200_last_error_string": c_char_p, "b200_attn_workspace_bytes": ctypes.c_size_t}
 
 _lib = None
 

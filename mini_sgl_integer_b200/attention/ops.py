@@ -3,15 +3,52 @@ from __future__ import annotations
 
 import torch
 
+from .. import _lib
 from .._lib import call, ptr, require_cuda, stream
 from .kv_pool import HEAD_DIM, Int8PagedKVCache
+
+_WORKSPACES: dict = {}
+
+
+def attention_workspace(rows: int, q_heads: int, kv_heads: int, max_kv_len: int, device) -> torch.Tensor:
+    """A cached uint8 workspace for the workspace-based attention passes (one per device and stream)."""
+    need = int(_lib.load().b200_attn_workspace_bytes(rows, q_heads, kv_heads, int(max_kv_len)))
+    key = (torch.device(device).index, torch.cuda.current_stream().cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def _cluster_fits(group: int, max_kv_len: int) -> bool:
+    """Shared memory of the cluster kernel with eight CTAs per (sequence, KV head): ring + per-key state."""
+    pages = (int(max_kv_len) + 15) // 16
+    s_max = (((pages + 7) // 8) * 16 + 31) // 32 * 32
+    smem = 8 * 4096 + group * s_max * 4 + s_max * 2 + (s_max // 16) * 164 + 8 * 2 * group * 32
+    return smem <= 200 * 1024
+
+
+def _paged_ws(q8, q_mul, q_shift, pool, layer_id, page_table, kv_lens, row_seq, row_limit, o32, o8, om, rows, q_heads,
+              max_kv_len, workspace):
+    ws = workspace if workspace is not None else attention_workspace(rows, q_heads, pool.kv_heads, max_kv_len, q8.device)
+    call("b200_attn_paged_ws", ptr(q8), ptr(q_mul), ptr(q_shift), ptr(pool.k_cache(layer_id)),
+         ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(page_table), page_table.stride(0),
+         ptr(kv_lens), ptr(row_seq), ptr(row_limit), ptr(o32), ptr(o8), ptr(om), rows, q_heads, pool.kv_heads,
+         pool.num_pages, int(max_kv_len), ptr(ws), ws.numel(), stream())
 
 
 def decode_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: torch.Tensor,
                                 pool: Int8PagedKVCache, layer_id: int, page_table: torch.Tensor,
                                 kv_lens: torch.Tensor, max_kv_len: int, *, out_q15: bool = True,
-                                out_int8: bool = False, cluster: int = 0):
+                                out_int8: bool = False, cluster: int = 0, impl: str = "auto",
+                                workspace: torch.Tensor | None = None):
     """One decode step of integer attention over the int8 paged pool.
+
+    ``impl``: "cluster" = one kernel whose CTAs exchange the softmax statistics inside thread-block clusters
+    (fastest; a slice's scores must fit in shared memory, which bounds the context at roughly 50k keys for
+    four query heads per KV head); "split" = grid-wide passes over a workspace (any context length; the
+    workspace is cached per device and stream unless given); "auto" = cluster when it fits, else split.
 
     q8 int8 [batch, q_heads, 128]; q_mul / q_shift int32 [batch, q_heads]; page_table int32
     [batch, pitch] of page ids; kv_lens int32 [batch].  Returns the Q15.16 output int32
@@ -35,10 +72,18 @@ def decode_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
     o32 = torch.empty((batch, q_heads, HEAD_DIM), dtype=torch.int32, device=q8.device) if out_q15 else None
     o8 = torch.empty((batch, q_heads, HEAD_DIM), dtype=torch.int8, device=q8.device) if out_int8 else None
     om = torch.empty((batch, q_heads), dtype=torch.int32, device=q8.device) if out_int8 else None
-    call("b200_attn_decode", ptr(q8), ptr(q_mul), ptr(q_shift), ptr(pool.k_cache(layer_id)),
-         ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(page_table), page_table.stride(0),
-         ptr(kv_lens), ptr(o32), ptr(o8), ptr(om), batch, q_heads, pool.kv_heads, pool.num_pages,
-         int(max_kv_len), int(cluster), stream())
+    if impl == "auto":
+        impl = "cluster" if _cluster_fits(q_heads // pool.kv_heads, max_kv_len) else "split"
+    if batch == 0:
+        pass
+    elif impl == "split":
+        _paged_ws(q8, q_mul, q_shift, pool, layer_id, page_table, kv_lens, None, None, o32, o8, om, batch, q_heads,
+                  max_kv_len, workspace)
+    else:
+        call("b200_attn_decode", ptr(q8), ptr(q_mul), ptr(q_shift), ptr(pool.k_cache(layer_id)),
+             ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(page_table), page_table.stride(0),
+             ptr(kv_lens), ptr(o32), ptr(o8), ptr(om), batch, q_heads, pool.kv_heads, pool.num_pages,
+             int(max_kv_len), int(cluster), stream())
     if out_q15 and out_int8:
         return o32, o8, om
     return o32 if out_q15 else (o8, om)
@@ -47,7 +92,8 @@ def decode_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
 def extend_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: torch.Tensor,
                                 pool: Int8PagedKVCache, layer_id: int, page_table: torch.Tensor,
                                 kv_lens: torch.Tensor, q_lens: torch.Tensor, max_kv_len: int, *,
-                                out_q15: bool = True, out_int8: bool = False, cluster: int = 0):
+                                out_q15: bool = True, out_int8: bool = False, cluster: int = 0,
+                                impl: str = "auto", workspace: torch.Tensor | None = None):
     """Causal attention of newly appended tokens over the cached prefix plus themselves.
 
     q8 int8 [sum(q_lens), q_heads, 128] with the sequences back to back; kv_lens int32 [batch] count the
@@ -77,7 +123,12 @@ def extend_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
     o32 = torch.empty((rows, q_heads, HEAD_DIM), dtype=torch.int32, device=q8.device) if out_q15 else None
     o8 = torch.empty((rows, q_heads, HEAD_DIM), dtype=torch.int8, device=q8.device) if out_int8 else None
     om = torch.empty((rows, q_heads), dtype=torch.int32, device=q8.device) if out_int8 else None
-    if rows > 0:
+    if impl == "auto":
+        impl = "cluster" if _cluster_fits(q_heads // pool.kv_heads, max_kv_len) else "split"
+    if rows > 0 and impl == "split":
+        _paged_ws(q8, q_mul, q_shift, pool, layer_id, page_table, kv_lens, row_seq, row_limit, o32, o8, om, rows, q_heads,
+                  max_kv_len, workspace)
+    elif rows > 0:
         call("b200_attn_extend", ptr(q8), ptr(q_mul), ptr(q_shift), ptr(pool.k_cache(layer_id)),
              ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(page_table), page_table.stride(0),
              ptr(kv_lens), ptr(row_seq), ptr(row_limit), ptr(o32), ptr(o8), ptr(om), rows, q_heads,

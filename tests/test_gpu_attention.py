@@ -24,6 +24,9 @@ def eq(a, b):
         raise AssertionError(f"{len(bad)} mismatches of {a.size}, first at {bad[0]}: {a[tuple(bad[0])]} vs {b[tuple(bad[0])]}")
 
 
+IMPLS = ["split", "cluster"]
+
+
 def run_decode(case, pool, max_kv_len, cluster=0, **kw):
     from mini_sgl_integer_b200.attention import decode_attention_int8_paged
     need = (max_kv_len + 15) // 16
@@ -68,13 +71,27 @@ def test_store_q15_quantises_like_oracle():
 
 
 @pytest.mark.parametrize("q_heads,kv_heads", [(2, 2), (4, 2), (8, 2), (16, 2), (32, 8)])
+def test_decode_split_vs_oracle(q_heads, kv_heads):
+    lens = [1, 15, 16, 17, 31, 33, 64, 100, 255, 256, 257, 640, 1000]
+    case = make_case(q_heads * 10 + 3, lens, q_heads, kv_heads, 256)
+    pool = device_pool(case, 256, kv_heads)
+    want = oracle_decode(case)
+    got, codes, absmax = run_decode(case, pool, 1000, impl="split", out_q15=True, out_int8=True)
+    eq(got.cpu().numpy(), want)
+    wc, wm = oattn.quant_heads_int8(want)
+    eq(codes.cpu().numpy(), wc); eq(absmax.cpu().numpy(), wm)
+    got2 = run_decode(case, pool, 1000, impl="split")            # the workspace is reused: results must not depend on its contents
+    eq(got2.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("q_heads,kv_heads", [(2, 2), (4, 2), (8, 2), (16, 2), (32, 8)])
 @pytest.mark.parametrize("cluster", [1, 2, 4, 8])
 def test_decode_vs_oracle(q_heads, kv_heads, cluster):
     lens = [1, 15, 16, 17, 31, 33, 64, 100, 257, 640]
     case = make_case(q_heads * 10 + cluster, lens, q_heads, kv_heads, 128)
     pool = device_pool(case, 128, kv_heads)
     want = oracle_decode(case)
-    got, codes, absmax = run_decode(case, pool, 640, cluster, out_q15=True, out_int8=True)
+    got, codes, absmax = run_decode(case, pool, 640, cluster, impl="cluster", out_q15=True, out_int8=True)
     eq(got.cpu().numpy(), want)
     wc, wm = oattn.quant_heads_int8(want)
     eq(codes.cpu().numpy(), wc); eq(absmax.cpu().numpy(), wm)
@@ -86,8 +103,10 @@ def test_decode_auto_cluster_long_context_and_clamp():
     case = make_case(77, lens, 8, 2, 640)
     pool = device_pool(case, 640, 2)
     want = oracle_decode(case)
-    eq(run_decode(case, pool, 4096).cpu().numpy(), want)
-    eq(run_decode(case, pool, 8192, cluster=8).cpu().numpy(), want)   # larger bound, same result
+    eq(run_decode(case, pool, 4096, impl="cluster").cpu().numpy(), want)
+    eq(run_decode(case, pool, 8192, cluster=8, impl="cluster").cpu().numpy(), want)   # larger bound, same result
+    eq(run_decode(case, pool, 4096, impl="split").cpu().numpy(), want)
+    eq(run_decode(case, pool, 8192, impl="split").cpu().numpy(), want)
     codes, absmax = run_decode(case, pool, 4096, out_q15=False, out_int8=True)
     wc, wm = oattn.quant_heads_int8(want)
     eq(codes.cpu().numpy(), wc); eq(absmax.cpu().numpy(), wm)
@@ -96,8 +115,9 @@ def test_decode_auto_cluster_long_context_and_clamp():
 def test_decode_zero_length_sequences_give_zero():
     case = make_case(9, [0, 20, 0], 4, 2, 8)
     pool = device_pool(case, 8, 2)
-    got = run_decode(case, pool, 32, cluster=2).cpu().numpy()
+    got = run_decode(case, pool, 32, cluster=2, impl="cluster").cpu().numpy()
     eq(got, oracle_decode(case))
+    eq(run_decode(case, pool, 32, impl="split").cpu().numpy(), got)
     assert not got[0].any() and not got[2].any() and got[1].any()
 
 
@@ -108,10 +128,12 @@ def test_decode_wide_shift_spread_and_uniform_scales():
     case["vs"][rng.integers(0, 290, 40)] += 20
     case["pool"].store_codes(case["loc"], case["k8"], case["v8"], case["km"], case["ks"], case["vm"], case["vs"])
     pool = device_pool(case, 32, 2)
-    eq(run_decode(case, pool, 256, cluster=2).cpu().numpy(), oracle_decode(case))
+    eq(run_decode(case, pool, 256, cluster=2, impl="cluster").cpu().numpy(), oracle_decode(case))
+    eq(run_decode(case, pool, 256, impl="split").cpu().numpy(), oracle_decode(case))
     uni = make_case(22, [48, 200], 4, 2, 32, uniform=True)
     pool = device_pool(uni, 32, 2)
-    eq(run_decode(uni, pool, 256, cluster=1).cpu().numpy(), oracle_decode(uni))
+    eq(run_decode(uni, pool, 256, cluster=1, impl="cluster").cpu().numpy(), oracle_decode(uni))
+    eq(run_decode(uni, pool, 256, impl="split").cpu().numpy(), oracle_decode(uni))
 
 
 def test_decode_reduces_to_reference_prefill_row(golden):
@@ -163,7 +185,7 @@ def test_decode_headline_shape_sample_and_invariants():
         table2[b, : len(pg)] = pg
     case2["table"] = table2
     pool2 = device_pool(case2, P, 8)
-    got2 = run_decode(case2, pool2, 4096, cluster=8).cpu().numpy()
+    got2 = run_decode(case2, pool2, 4096, cluster=8, impl="cluster").cpu().numpy()
     eq(got2, got)
 
 
@@ -188,7 +210,7 @@ def run_extend(case, pool, max_kv_len, cluster=0, **kw):
                                        d(case["kv_lens"]), d(case["q_lens"]), max_kv_len, cluster=cluster, **kw)
 
 
-@pytest.mark.parametrize("cluster", [1, 2, 4])
+@pytest.mark.parametrize("cluster", [0, 1, 2, 4])
 def test_extend_over_prefix_vs_oracle(cluster):
     """New tokens attend the cached prefix and, causally, themselves (the layer case: 16 new tokens over
     prefixes 0, 16, 48, 112, plus ragged ones)."""
@@ -197,7 +219,8 @@ def test_extend_over_prefix_vs_oracle(cluster):
     case = _extend_case(40 + cluster, kv_lens, q_lens, 16, 8, 64)
     pool = device_pool(case, 64, 8)
     want = oattn.paged_attention(case["q8"], case["qm"], case["qs"], case["pool"], case["tables"], kv_lens, q_lens)
-    got, codes, absmax = run_extend(case, pool, 256, cluster, out_q15=True, out_int8=True)
+    got, codes, absmax = run_extend(case, pool, 256, cluster, impl="split" if cluster == 0 else "cluster",
+                                    out_q15=True, out_int8=True)
     eq(got.cpu().numpy(), want)
     wc, wm = oattn.quant_heads_int8(want)
     eq(codes.cpu().numpy(), wc); eq(absmax.cpu().numpy(), wm)
@@ -221,6 +244,17 @@ def test_extend_without_prefix_reduces_to_reference(golden):
     lens = d(np.array([16, 32], dtype=np.int32))
     got = extend_attention_int8_paged(d(q), d(qm), d(qs), pool, 0, d(table), lens, lens, 32, cluster=2).cpu().numpy()
     eq(oattn.q15_to_bf16_bits(got.astype(np.int64)), golden["attn_out_bf16_bits"])
+
+
+def test_auto_falls_back_to_workspace_passes_for_long_contexts():
+    """A context too long for the cluster kernel's shared memory (eight query heads per KV head, 40k keys)."""
+    from mini_sgl_integer_b200.attention.ops import _cluster_fits
+    assert _cluster_fits(4, 4096) and not _cluster_fits(8, 40000)
+    lens = [40000, 33]
+    case = make_case(5, lens, 8, 1, 2600)
+    pool = device_pool(case, 2600, 1)
+    got = run_decode(case, pool, 40000).cpu().numpy()          # impl="auto"
+    eq(got, oracle_decode(case))
 
 
 def test_extend_empty_batch():
