@@ -186,6 +186,31 @@ B200_API int b200_attn_paged_ws(const int8_t* q, const int32_t* q_mul, const int
                                 int rows, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
                                 void* workspace, size_t workspace_bytes, b200_stream_t s);
 
+/* ---- b200_attn_paged_ws without a workspace argument: the scratch is a fixed area of
+ * B200_ATTN_STATIC_SCRATCH_BYTES that is part of the library's device image.  This entry point has no
+ * counterpart in the reference; it is for callers that cannot allocate device memory: a binding that only
+ * forwards the model's tensors (a plain C host, a tvm-ffi wrapper) and so has no allocator, or an engine that
+ * has already handed all free device memory to the KV pool and cannot rely on a later allocation.  The call
+ * allocates and frees nothing.
+ *  - Limit: b200_attn_workspace_bytes(rows, q_heads, kv_heads, max_kv_len) must not exceed
+ *    B200_ATTN_STATIC_SCRATCH_BYTES, otherwise B200_E_UNSUPPORTED with the two sizes in the message
+ *    (16 MiB holds e.g. 16 rows x 32 query heads x 7680 keys); use b200_attn_paged_ws beyond that.
+ *  - The first call on each device looks up the area's device address (the device must be current, as for
+ *    every call here); make that first call during set-up, before any stream capture begins.
+ *  - There is one area per device and every call uses it: calls on the same device must not overlap on the
+ *    GPU (issue them on one stream, or order them with events), else they corrupt each other's results.
+ *    Nothing in the area has to be cleared by the caller: the first kernel of each call resets what the
+ *    later ones accumulate into.
+ * Arguments and results are those of b200_attn_paged_ws. */
+#define B200_ATTN_STATIC_SCRATCH_BYTES (16u << 20)
+B200_API int b200_attn_paged_static(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
+                                    const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
+                                    const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                                    const int32_t* row_seq, const int32_t* row_limit,
+                                    int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax,
+                                    int rows, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
+                                    b200_stream_t s);
+
 /* ---- W8A8 linear: int8 x int8 -> int32 on the tcgen05 tensor cores, fixed-point requant.
  * Stands in for the GEMM + epilogue inside W8A8Int8LinearMethod.apply_weights_q15
  * (layers/quantization/w8a8_int8.py:242-286), i.e. the sgl_kernel.int8_scaled_mm call at :272-279

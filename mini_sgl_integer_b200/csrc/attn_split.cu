@@ -16,6 +16,8 @@
 // K and V are read once; the scores cost 4 B written and 8 B read per (key, head) on top, about 18 %
 // of the KV bytes for four query heads per KV head.  All CTAs are small and alike, so the grid
 // balances itself and many CTAs share an SM.
+#include <mutex>
+
 #include "attn_common.cuh"
 #include "luts.cuh"
 
@@ -479,4 +481,68 @@ extern "C" int b200_attn_paged_ws(const int8_t* q, const int32_t* q_mul, const i
     case 4: return launch_split<4>(p, st);
     default: return launch_split<8>(p, st);
   }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// The workspace passes over a scratch area that lives inside the library.
+//
+// Some callers cannot hand over a workspace: a binding that only forwards the tensors of the model (a plain
+// C host, a tvm-ffi wrapper) has no allocator of its own, and a serving engine that has already given all
+// free device memory to the KV pool cannot count on a later allocation to succeed.  For them the scratch is
+// a fixed array in device memory that comes with the library image; nothing is allocated or freed, here or
+// in any library this file calls.
+// ---------------------------------------------------------------------------------------------------
+namespace b200 {
+
+constexpr size_t kStaticScratchBytes = size_t(B200_ATTN_STATIC_SCRATCH_BYTES);
+static __device__ __align__(256) unsigned char g_attn_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_attn_scratch_ptr[kMaxDevices];   // device address of g_attn_scratch, per device ordinal
+static std::mutex g_attn_scratch_mutex;
+
+// Device address of the scratch array on the current device; looked up once per device, with that device
+// current (each device holds its own copy of the array at its own address).
+static int static_scratch_address(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  B200_REQUIRE(e == cudaSuccess, B200_E_CUDA, "attn_paged_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  B200_REQUIRE(dev >= 0 && dev < kMaxDevices, B200_E_UNSUPPORTED, "attn_paged_static: device ordinal %d (at most %d devices)", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_attn_scratch_mutex);
+  if (g_attn_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_attn_scratch);
+    B200_REQUIRE(e == cudaSuccess && ptr != nullptr, B200_E_CUDA, "attn_paged_static: cudaGetSymbolAddress: %s",
+                 cudaGetErrorString(e));
+    g_attn_scratch_ptr[dev] = ptr;
+  }
+  *out = g_attn_scratch_ptr[dev];
+  return B200_OK;
+}
+
+}  // namespace b200
+
+extern "C" int b200_attn_paged_static(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
+                                      const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
+                                      const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                                      const int32_t* row_seq, const int32_t* row_limit,
+                                      int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax, int rows,
+                                      int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
+                                      b200_stream_t s) {
+  // The size check comes first so that an oversized call is refused before anything else happens.
+  if (rows > 0 && q_heads > 0 && kv_heads > 0 && max_kv_len > 0) {
+    const size_t need = split_ws_bytes(rows, q_heads, kv_heads, max_kv_len, nullptr, nullptr);
+    B200_REQUIRE(need <= kStaticScratchBytes, B200_E_UNSUPPORTED,
+                 "attn_paged_static: rows=%d q_heads=%d max_kv_len=%d need %zu bytes of scratch, the built-in "
+                 "area holds %zu; use b200_attn_paged_ws with a workspace of your own",
+                 rows, q_heads, max_kv_len, need, kStaticScratchBytes);
+  }
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != B200_OK) return rc;
+  // Every pass of the chain (re)initialises what it accumulates into (row maxima, sums, reference V scales,
+  // output accumulators) in its first kernel, so nothing in the area has to be zero on entry.
+  return b200_attn_paged_ws(q, q_mul, q_shift, k_codes, v_codes, meta, page_table, table_pitch, kv_lens, row_seq,
+                            row_limit, out_q15, out_codes, out_absmax, rows, q_heads, kv_heads, num_pages,
+                            max_kv_len, scratch, kStaticScratchBytes, s);
 }
