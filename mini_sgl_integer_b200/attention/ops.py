@@ -25,7 +25,7 @@ def _cluster_fits(group: int, max_kv_len: int) -> bool:
     """Shared memory of the cluster kernel with eight CTAs per (sequence, KV head): ring + per-key state."""
     pages = (int(max_kv_len) + 15) // 16
     s_max = (((pages + 7) // 8) * 16 + 31) // 32 * 32
-    smem = 8 * 4096 + group * s_max * 4 + s_max * 2 + (s_max // 16) * 164 + 8 * 2 * group * 32
+    smem = 8 * 2 * 4480 + group * s_max * 4 + (s_max // 16) * 4 + 8 * 2 * group * 32
     return smem <= 200 * 1024
 
 

@@ -106,10 +106,17 @@ struct DecodeParams {
   int s_max;  // key capacity of one CTA's slice (multiple of 32)
 };
 
-constexpr int kDecodeWarps = 8;
+#ifndef B200_DW
+#define B200_DW 8
+#endif
+#ifndef B200_ST
+#define B200_ST 2
+#endif
+constexpr int kDecodeWarps = B200_DW;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 static_assert(kDecodeThreads >= kD, "the output stage maps one thread to one d");
-constexpr int kStages = 1;                 // ring slots per warp
+constexpr int kStages = B200_ST;            // ring slots per warp
+constexpr int kRingSlot = kSlotBytes + 384; // a pair of pages plus their two scale blocks (2 x 160 B), 128-byte granular
 // Both contractions run on the integer tensor-core MMA with the long dimension on M:
 //   dots^T [16 keys x 8 heads] = K page [16 x 128] . Q^T [128 x 8]        (4 k-steps of 32 d)
 //   out^T  [16 d    x 8 heads] = V^T [16 x 32 tokens] . W^T [32 x 8]      (two pages per k-step)
@@ -138,14 +145,11 @@ attn_decode_kernel(const DecodeParams p) {
   constexpr int kNeg = (int)(-2147483647 - 1);
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  unsigned char* ring = smem_raw + warp * (kStages * kSlotBytes);      // this warp's slots
-  int32_t* sc = reinterpret_cast<int32_t*>(smem_raw + kDecodeWarps * kStages * kSlotBytes);  // [G][S]
-  int32_t* meta_s = sc + G * S;                                       // [S/16][40] scale blocks
-  uint8_t* w_hi = reinterpret_cast<uint8_t*>(meta_s + (S / 16) * kMetaWords) + warp * (2 * G * 32);  // [G][32]
+  unsigned char* ring = smem_raw + warp * (kStages * kRingSlot);       // this warp's slots
+  int32_t* sc = reinterpret_cast<int32_t*>(smem_raw + kDecodeWarps * kStages * kRingSlot);  // [G][S]
+  uint8_t* w_hi = reinterpret_cast<uint8_t*>(sc + G * S) + warp * (2 * G * 32);  // [G][32]
   uint8_t* w_lo = w_hi + G * 32;                                      // [G][32] (this warp's pair)
-  uint16_t* rel = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(meta_s + (S / 16) * kMetaWords) +
-                                              kDecodeWarps * 2 * G * 32);   // [S]
-  int32_t* pages = reinterpret_cast<int32_t*>(rel + S);               // [S / 16]
+  int32_t* pages = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(sc + G * S) + kDecodeWarps * 2 * G * 32);  // [S / 16]
 
   __shared__ int q_mul_s[G], q_shift_s[G];
   __shared__ int cta_max[G];
@@ -200,21 +204,11 @@ attn_decode_kernel(const DecodeParams p) {
   }
   __syncthreads();
 
-  // The pages' scale blocks (160 B each) go to a part of shared memory that is kept: first
-  // commit group of every thread.
-  {
-    const unsigned meta_base = (unsigned)__cvta_generic_to_shared(meta_s);
-    for (int i = tid; i < my_pages * 10; i += kDecodeThreads) {
-      const int pg = i / 10, c16 = i - pg * 10;
-      cp_async16(meta_base + pg * kMetaBytes + c16 * 16,
-                 reinterpret_cast<const unsigned char*>(p.meta + ((int64_t)pages[pg] * p.kv_heads + kh) * kMetaWords) + c16 * 16);
-    }
-    cp_async_commit();
-  }
-
   // Item j of this warp: j < n_items is the K copy of pair (warp + j * warps), otherwise the V
   // copy of pair (warp + (j - n_items) * warps).  One commit group per item, also when empty.
-  // A lane moves the 16-byte columns lane, lane+32, lane+64, lane+96 of each 2 KB chunk.
+  // A lane moves the 16-byte columns lane, lane+32, lane+64, lane+96 of each 2 KB chunk; the
+  // pages' scale blocks (160 B each) travel behind the codes: whole with K (the K scales for the
+  // scores, the V scales for the reference V scale), words 16..39 with V.
   const unsigned ring_base = (unsigned)__cvta_generic_to_shared(ring);
   unsigned k_dst[4];
 #pragma unroll
@@ -227,7 +221,7 @@ attn_decode_kernel(const DecodeParams p) {
   auto issue_k = [&](int it) {   // it-th K pair of this warp
     if (it < n_items) {
       const int pp = warp + it * kDecodeWarps;
-      const unsigned slot = ring_base + (it % kStages) * kSlotBytes;
+      const unsigned slot = ring_base + (it % kStages) * kRingSlot;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         if (2 * pp + h < my_pages) {
@@ -236,13 +230,20 @@ attn_decode_kernel(const DecodeParams p) {
           for (int i = 0; i < 4; ++i) cp_async16(slot + h * 2048 + k_dst[i], src + i * 512);
         }
       }
+      if (lane < 20) {
+        const int h = lane >= 10, c16 = lane - 10 * h;
+        if (2 * pp + h < my_pages)
+          cp_async16(slot + kSlotBytes + h * kMetaBytes + c16 * 16,
+                     reinterpret_cast<const unsigned char*>(p.meta + ((int64_t)pages[2 * pp + h] * p.kv_heads + kh) * kMetaWords) + c16 * 16);
+      }
     }
     cp_async_commit();
   };
   auto issue_v = [&](int it) {   // it-th V pair of this warp; ring position continues after the K items
     if (it < n_items) {
       const int pp = warp + it * kDecodeWarps;
-      const unsigned slot = ring_base + ((n_items + it) % kStages) * kSlotBytes + (lane << 4);
+      const unsigned slot0 = ring_base + ((n_items + it) % kStages) * kRingSlot;
+      const unsigned slot = slot0 + (lane << 4);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         if (2 * pp + h < my_pages) {
@@ -251,15 +252,18 @@ attn_decode_kernel(const DecodeParams p) {
           for (int i = 0; i < 4; ++i) cp_async16(slot + h * 2048 + i * 512, src + i * 512);
         }
       }
+      if (lane < 12) {
+        const int h = lane >= 6, c16 = 4 + lane - 6 * h;     // words 16..39: V multipliers and shifts
+        if (2 * pp + h < my_pages)
+          cp_async16(slot0 + kSlotBytes + h * kMetaBytes + c16 * 16,
+                     reinterpret_cast<const unsigned char*>(p.meta + ((int64_t)pages[2 * pp + h] * p.kv_heads + kh) * kMetaWords) + c16 * 16);
+      }
     }
     cp_async_commit();
   };
   auto issue = [&](int j) { if (j < n_items) issue_k(j); else issue_v(j - n_items); };
 #pragma unroll
   for (int j = 0; j < kStages; ++j) issue(j);
-
-  cp_async_wait<kStages>();   // this thread's share of the scale blocks (oldest group) has landed
-  __syncthreads();
 
   // ---- phase 1: one page (16 keys) per MMA tile gives raw int32 dots; then, one key per lane,
   // the Q15.16 scores of the pair, their running maximum and the reference V scale
@@ -277,7 +281,8 @@ attn_decode_kernel(const DecodeParams p) {
       const int pp = warp + it * kDecodeWarps;
       cp_async_wait<kStages - 1>();
       __syncwarp();
-      const unsigned char* slot = ring + (it % kStages) * kSlotBytes + fr * 128;   // rows fr, fr + 8: same parity
+      const unsigned char* slot0 = ring + (it % kStages) * kRingSlot;
+      const unsigned char* slot = slot0 + fr * 128;   // rows fr, fr + 8: same parity
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         int c[4] = {0, 0, 0, 0};
@@ -297,16 +302,20 @@ attn_decode_kernel(const DecodeParams p) {
         if (h0) { sc0[kl] = c[0]; sc0[kl + 8] = c[2]; }
         if (h1) { sc1[kl] = c[1]; sc1[kl + 8] = c[3]; }
       }
+      const int kl = pp * 32 + lane;
+      int km = 0, ks = 0, vs = 0;
+      unsigned vm = 0;
+      if (kl < my_keys) {   // this lane's key: its scales, read before the slot is handed back
+        const int32_t* mt = reinterpret_cast<const int32_t*>(slot0 + kSlotBytes + (lane >> 4) * kMetaBytes);
+        const int tok = lane & 15;
+        km = mt[tok];
+        ks = reinterpret_cast<const int8_t*>(mt + 32)[tok];
+        vm = (unsigned)mt[16 + tok];
+        vs = reinterpret_cast<const int8_t*>(mt + 36)[tok];
+      }
       __syncwarp();
       issue(it + kStages);       // the slot is free again: refill it before the scalar work
-      const int kl = pp * 32 + lane;
       if (kl < my_keys) {
-        const int32_t* mt = meta_s + (kl >> 4) * kMetaWords;
-        const int tok = kl & 15;
-        const int km = mt[tok];
-        const int ks = reinterpret_cast<const int8_t*>(mt + 32)[tok];
-        const unsigned vm = (unsigned)mt[16 + tok];
-        const int vs = reinterpret_cast<const int8_t*>(mt + 36)[tok];
         if (vs < best_s || (vs == best_s && vm > best_m)) { best_s = vs; best_m = vm; }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
@@ -366,7 +375,7 @@ attn_decode_kernel(const DecodeParams p) {
   const int v_mul_ref = (int)(0xFFFFFFFFu - (unsigned)(vref & 0xFFFFFFFFull));
   __syncthreads();
 
-  // ---- phase 2: exponentials, their sum, and the relative V scale of every key
+  // ---- phase 2: exponentials and their sum
   {
     int lsum[G];   // a thread sees at most S / threads keys, each e <= 2^16: no overflow
     int gm[G];
@@ -384,18 +393,6 @@ attn_decode_kernel(const DecodeParams p) {
         s1[g] = valid1 ? sc[g * S + kl] : 0;
         s2[g] = valid2 ? sc[g * S + kl2] : 0;
       }
-      unsigned vm1 = 0, vm2 = 0;
-      int vs1 = 0, vs2 = 0;
-      if (valid1) {
-        const int32_t* mt = meta_s + (kl >> 4) * kMetaWords;
-        vm1 = (unsigned)mt[16 + (kl & 15)];
-        vs1 = reinterpret_cast<const int8_t*>(mt + 36)[kl & 15];
-      }
-      if (valid2) {
-        const int32_t* mt = meta_s + (kl2 >> 4) * kMetaWords;
-        vm2 = (unsigned)mt[16 + (kl2 & 15)];
-        vs2 = reinterpret_cast<const int8_t*>(mt + 36)[kl2 & 15];
-      }
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         int e1 = 0, e2 = 0;
@@ -412,15 +409,11 @@ attn_decode_kernel(const DecodeParams p) {
         s1[g] = e1; s2[g] = e2;
         lsum[g] += e1 + e2;
       }
-      const unsigned r1 = valid1 ? rel_scale_q15(vm1, (unsigned)v_mul_ref, vs1 - v_shift_ref) : 0u;
-      const unsigned r2 = valid2 ? rel_scale_q15(vm2, (unsigned)v_mul_ref, vs2 - v_shift_ref) : 0u;
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         sc[g * S + kl] = s1[g];
         if (in2) sc[g * S + kl2] = s2[g];
       }
-      rel[kl] = (uint16_t)r1;
-      if (in2) rel[kl2] = (uint16_t)r2;
     }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -457,20 +450,29 @@ attn_decode_kernel(const DecodeParams p) {
     for (int it = 0; it < n_items; ++it) {
       const int pp = warp + it * kDecodeWarps;
       const int j = n_items + it;
+      const int kl = pp * 32 + lane;
+      unsigned pr[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) pr[g] = ((unsigned)sc[g * S + kl] * gi[g]) >> 16;   // 0 for keys past the end
+      cp_async_wait<kStages - 1>();
+      __syncwarp();
+      const unsigned char* slot0 = ring + (j % kStages) * kRingSlot;
       {
-        const int kl = pp * 32 + lane;
-        const unsigned r = rel[kl];
+        // this lane's key: relative V scale from the scale block that came with the codes
+        // (stale bytes for a key past the end: its probability is 0, so is its weight)
+        const int32_t* mt = reinterpret_cast<const int32_t*>(slot0 + kSlotBytes + (lane >> 4) * kMetaBytes);
+        const unsigned vm = (unsigned)mt[16 + (lane & 15)];
+        const int vs = reinterpret_cast<const int8_t*>(mt + 36)[lane & 15];
+        const unsigned r = kl < my_keys ? rel_scale_q15(vm, (unsigned)v_mul_ref, vs - v_shift_ref) : 0u;
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-          const unsigned pr = ((unsigned)sc[g * S + kl] * gi[g]) >> 16;
-          const unsigned w = (pr * r + 16384u) >> 15;
+          const unsigned w = (pr[g] * r + 16384u) >> 15;
           w_hi[g * 32 + lane] = (uint8_t)(w >> 8);
           w_lo[g * 32 + lane] = (uint8_t)(w & 0xff);
         }
       }
-      cp_async_wait<kStages - 1>();
       __syncwarp();
-      const unsigned char* slot = ring + (j % kStages) * kSlotBytes + lane * 16;
+      const unsigned char* slot = slot0 + lane * 16;
       const bool has_b = 2 * pp + 1 < my_pages;
       uint4 va[4], vb[4];
 #pragma unroll
@@ -531,8 +533,8 @@ attn_decode_kernel(const DecodeParams p) {
 }
 
 static size_t decode_smem_bytes(int G, int s_max) {
-  return (size_t)kDecodeWarps * kStages * kSlotBytes + (size_t)G * s_max * 4 + (size_t)s_max * 2 +
-         (size_t)(s_max / 16) * (kMetaBytes + 4) + (size_t)kDecodeWarps * 2 * G * 32;
+  return (size_t)kDecodeWarps * kStages * kRingSlot + (size_t)G * s_max * 4 + (size_t)(s_max / 16) * 4 +
+         (size_t)kDecodeWarps * 2 * G * 32;
 }
 
 template <int G>
@@ -645,7 +647,7 @@ static int attn_common(const int8_t* q, const int32_t* q_mul, const int32_t* q_s
     // fewest CTAs per (sequence, KV head) whose slice state still lets two CTAs share an SM
     cluster = 1;
     while (cluster < 8 &&
-           decode_smem_bytes(G, ((((max_pages + cluster - 1) / cluster) * kPage + 31) / 32) * 32) > 100 * 1024)
+           decode_smem_bytes(G, ((((max_pages + cluster - 1) / cluster) * kPage + 31) / 32) * 32) > 110 * 1024)
       cluster *= 2;
   }
   B200_REQUIRE(cluster == 1 || cluster == 2 || cluster == 4 || cluster == 8, B200_E_UNSUPPORTED,
