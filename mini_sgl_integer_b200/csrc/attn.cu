@@ -112,6 +112,9 @@ struct DecodeParams {
 #ifndef B200_ST
 #define B200_ST 2
 #endif
+#ifndef B200_MB
+#define B200_MB 2
+#endif
 constexpr int kDecodeWarps = B200_DW;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 static_assert(kDecodeThreads >= kD, "the output stage maps one thread to one d");
@@ -130,7 +133,7 @@ constexpr int kRingSlot = kSlotBytes + 384; // a pair of pages plus their two sc
 // V in the operand order of v_chunk_offset.  The per-key fixed-point work (scale, exp, relative V
 // scale, probability limbs) runs in flat one-thread-per-key loops between the two MMA phases.
 template <int G>
-__global__ void __launch_bounds__(kDecodeThreads, 2)
+__global__ void __launch_bounds__(kDecodeThreads, B200_MB)
 attn_decode_kernel(const DecodeParams p) {
   cg::cluster_group cluster = cg::this_cluster();
   const int C = (int)cluster.num_blocks();
@@ -239,10 +242,10 @@ attn_decode_kernel(const DecodeParams p) {
     }
     cp_async_commit();
   };
-  auto issue_v = [&](int it) {   // it-th V pair of this warp; ring position continues after the K items
+  auto issue_v = [&](int it) {   // it-th V pair of this warp
     if (it < n_items) {
       const int pp = warp + it * kDecodeWarps;
-      const unsigned slot0 = ring_base + ((n_items + it) % kStages) * kRingSlot;
+      const unsigned slot0 = ring_base + (it % kStages) * kRingSlot;
       const unsigned slot = slot0 + (lane << 4);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -261,9 +264,8 @@ attn_decode_kernel(const DecodeParams p) {
     }
     cp_async_commit();
   };
-  auto issue = [&](int j) { if (j < n_items) issue_k(j); else issue_v(j - n_items); };
 #pragma unroll
-  for (int j = 0; j < kStages; ++j) issue(j);
+  for (int j = 0; j < kStages; ++j) issue_k(j);
 
   // ---- phase 1: one page (16 keys) per MMA tile gives raw int32 dots; then, one key per lane,
   // the Q15.16 scores of the pair, their running maximum and the reference V scale
@@ -314,7 +316,7 @@ attn_decode_kernel(const DecodeParams p) {
         vs = reinterpret_cast<const int8_t*>(mt + 36)[tok];
       }
       __syncwarp();
-      issue(it + kStages);       // the slot is free again: refill it before the scalar work
+      issue_k(it + kStages);     // the slot is free again: refill it before the scalar work
       if (kl < my_keys) {
         if (vs < best_s || (vs == best_s && vm > best_m)) { best_s = vs; best_m = vm; }
 #pragma unroll
@@ -358,7 +360,12 @@ attn_decode_kernel(const DecodeParams p) {
     }
     if (lane == 0) atomicMin(&cta_vref, lv);
   }
-  cluster.sync();
+  // The first V pairs are requested between the two halves of the cluster barrier: the release fence
+  // of the arrival would otherwise wait for copies that are still in flight.
+  cluster.barrier_arrive();
+#pragma unroll
+  for (int j = 0; j < kStages; ++j) issue_v(j);
+  cluster.barrier_wait();
 
   // ---- exchange 1: row maxima and the V reference scale over the cluster
   if (tid < G) {
@@ -449,14 +456,13 @@ attn_decode_kernel(const DecodeParams p) {
     const uint8_t* pl = w_lo + fr * 32 + fc * 4;
     for (int it = 0; it < n_items; ++it) {
       const int pp = warp + it * kDecodeWarps;
-      const int j = n_items + it;
       const int kl = pp * 32 + lane;
       unsigned pr[G];
 #pragma unroll
       for (int g = 0; g < G; ++g) pr[g] = ((unsigned)sc[g * S + kl] * gi[g]) >> 16;   // 0 for keys past the end
       cp_async_wait<kStages - 1>();
       __syncwarp();
-      const unsigned char* slot0 = ring + (j % kStages) * kRingSlot;
+      const unsigned char* slot0 = ring + (it % kStages) * kRingSlot;
       {
         // this lane's key: relative V scale from the scale block that came with the codes
         // (stale bytes for a key past the end: its probability is 0, so is its weight)
