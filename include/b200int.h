@@ -211,6 +211,27 @@ B200_API int b200_attn_paged_static(const int8_t* q, const int32_t* q_mul, const
                                     int rows, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
                                     b200_stream_t s);
 
+/* ---- The two ends of the model and the bookkeeping of a decode step.
+ * b200_embedding_bf16_q15: out[t, :] = to_fixed(table[ids[t] - vocab_start, :]) for a bf16 table of
+ *   vocab_rows rows; ids outside the shard give zero rows (a vocabulary-parallel shard, summed over ranks).
+ *   Stands in for VocabParallelEmbedding.forward (layers/embedding.py:33-42, csrc/jit/index.cu) followed by
+ *   to_fixed at the model entry (models/integer/qwen3_integer.py:115-124).  hidden % 8 == 0.
+ * b200_argmax_i32: out_idx[r] = index_offset + argmax_j logits[r, j], the lowest index among equal maxima;
+ *   out_val[r] (nullable) the maximum.  Stands in for the greedy branch of the sampler (engine/sample.py:74)
+ *   on integer logits.  Rows 16-byte aligned (pitch % 4 == 0).
+ * b200_decode_prepare: for a decode batch whose lengths live on the device: positions[b] = seq_lens[b],
+ *   out_loc[b] = page_table[b][pos / 16] * 16 + pos % 16, kv_lens[b] = pos + 1, then seq_lens[b] = pos + 1
+ *   (pos is held at max_len - 1 once a sequence is full).  Replaces the per-request host loops of
+ *   Int8Backend.prepare_metadata (attention/triton_int8.py:214-253) for decode, so a step can be replayed
+ *   from a CUDA graph. */
+B200_API int b200_embedding_bf16_q15(const uint16_t* table, const int32_t* ids, int32_t* out, int64_t rows,
+                                     int hidden, int64_t vocab_start, int64_t vocab_rows, b200_stream_t s);
+B200_API int b200_argmax_i32(const int32_t* logits, int64_t rows, int64_t n, int64_t pitch, int32_t index_offset,
+                             int32_t* out_idx, int32_t* out_val, b200_stream_t s);
+B200_API int b200_decode_prepare(const int32_t* page_table, int64_t table_pitch, int32_t* seq_lens,
+                                 int32_t* positions, int32_t* out_loc, int32_t* kv_lens, int batch, int max_len,
+                                 b200_stream_t s);
+
 /* ---- W8A8 linear: int8 x int8 -> int32 on the tcgen05 tensor cores, fixed-point requant.
  * Stands in for the GEMM + epilogue inside W8A8Int8LinearMethod.apply_weights_q15
  * (layers/quantization/w8a8_int8.py:242-286), i.e. the sgl_kernel.int8_scaled_mm call at :272-279

@@ -37,6 +37,9 @@ SIGNATURES: dict[str, list] = {
     "b200_attn_workspace_bytes": [I, I, I, I],
     "b200_attn_paged_ws": [P, P, P, P, P, P, P, L, P, P, P, P, P, P, I, I, I, L, I, P, ctypes.c_size_t, P],
     "b200_attn_paged_static": [P, P, P, P, P, P, P, L, P, P, P, P, P, P, I, I, I, L, I, P],
+    "b200_embedding_bf16_q15": [P, P, P, L, I, L, L, P],
+    "b200_argmax_i32": [P, L, L, L, I, P, P, P],
+    "b200_decode_prepare": [P, L, P, P, P, P, I, I, P],
     "b200_gemm_w8a8": [P, P, P, P, P, P, P, P, L, L, L, P],
     "b200_gemm_status": [P, I],
     "b200_quant_given_absmax_q15": [P, P, P, L, I, P],

@@ -1,0 +1,158 @@
+// The two ends of the integer model and the per-step bookkeeping of a decode batch:
+//   * embedding rows (bf16 table) gathered by token id and converted to Q15.16,
+//   * arg-max over int32 logits rows (lowest index wins ties),
+//   * advancing a decode batch by one token on the device (positions, KV locations, lengths).
+// All three are memory-bound row kernels: 16-byte loads and stores, one CTA (or warp) per row.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------------------------------
+// Embedding gather + to_fixed.  One warp per token row; a lane converts 8 bf16 values per trip.
+// Ids outside [vocab_start, vocab_start + vocab_rows) give a zero row (a vocabulary shard adds its
+// rows to the other shards' zeros).
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ int bf16_bits_to_q15(unsigned short b) {
+  // same conversion as to_fixed: fp32 product, round half to even, saturating (NaN gives 0)
+  return __float2int_rn(__fmul_rn(__uint_as_float((unsigned)b << 16), 65536.0f));
+}
+
+__global__ void __launch_bounds__(256)
+embedding_q15_kernel(const uint16_t* __restrict__ table, const int32_t* __restrict__ ids, int32_t* __restrict__ out,
+                     int64_t rows, int hidden, int64_t vocab_start, int64_t vocab_rows) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int64_t id = (int64_t)ids[row] - vocab_start;
+  int4* o = reinterpret_cast<int4*>(out + row * hidden);
+  if (id < 0 || id >= vocab_rows) {
+    for (int c = lane; c < hidden / 4; c += 32) o[c] = make_int4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(table + id * hidden);
+  for (int c = lane; c < hidden / 8; c += 32) {
+    const uint4 v = __ldg(src + c);
+    int4 a, b;
+    a.x = bf16_bits_to_q15((unsigned short)(v.x & 0xffff)); a.y = bf16_bits_to_q15((unsigned short)(v.x >> 16));
+    a.z = bf16_bits_to_q15((unsigned short)(v.y & 0xffff)); a.w = bf16_bits_to_q15((unsigned short)(v.y >> 16));
+    b.x = bf16_bits_to_q15((unsigned short)(v.z & 0xffff)); b.y = bf16_bits_to_q15((unsigned short)(v.z >> 16));
+    b.z = bf16_bits_to_q15((unsigned short)(v.w & 0xffff)); b.w = bf16_bits_to_q15((unsigned short)(v.w >> 16));
+    o[2 * c] = a;
+    o[2 * c + 1] = b;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Arg-max of int32 rows.  (value, index) is packed into one 64-bit key whose unsigned order is
+// "larger value first, then smaller index", so the reduction is a plain max.
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long argmax_key(int v, unsigned idx) {
+  return ((unsigned long long)((unsigned)v ^ 0x80000000u) << 32) | (unsigned long long)(0xFFFFFFFFu - idx);
+}
+
+constexpr int kArgmaxThreads = 512;
+
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_rows_kernel(const int32_t* __restrict__ logits, int64_t pitch, int64_t n, int32_t index_offset,
+                   int32_t* __restrict__ out_idx, int32_t* __restrict__ out_val) {
+  __shared__ unsigned long long red[kArgmaxThreads / 32];
+  const int32_t* row = logits + (int64_t)blockIdx.x * pitch;
+  unsigned long long best = 0ull;      // below every real key: an index < 2^31 makes the low word >= 2^31
+  const int64_t n4 = n / 4;
+  const int4* row4 = reinterpret_cast<const int4*>(row);
+  for (int64_t c = threadIdx.x; c < n4; c += kArgmaxThreads) {
+    const int4 v = __ldg(row4 + c);
+    const unsigned i0 = (unsigned)(c * 4);
+    unsigned long long k0 = argmax_key(v.x, i0), k1 = argmax_key(v.y, i0 + 1), k2 = argmax_key(v.z, i0 + 2), k3 = argmax_key(v.w, i0 + 3);
+    k0 = k0 > k1 ? k0 : k1;
+    k2 = k2 > k3 ? k2 : k3;
+    k0 = k0 > k2 ? k0 : k2;
+    best = k0 > best ? k0 : best;
+  }
+  for (int64_t c = n4 * 4 + threadIdx.x; c < n; c += kArgmaxThreads) {
+    const unsigned long long k = argmax_key(__ldg(row + c), (unsigned)c);
+    best = k > best ? k : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(FULL_MASK, best, o);
+    best = other > best ? other : best;
+  }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    unsigned long long b = threadIdx.x < kArgmaxThreads / 32 ? red[threadIdx.x] : 0ull;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(FULL_MASK, b, o);
+      b = other > b ? other : b;
+    }
+    if (threadIdx.x == 0) {
+      const unsigned idx = 0xFFFFFFFFu - (unsigned)(b & 0xFFFFFFFFull);
+      out_idx[blockIdx.x] = (int32_t)idx + index_offset;
+      if (out_val) out_val[blockIdx.x] = (int32_t)((unsigned)(b >> 32) ^ 0x80000000u);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// One decode step of bookkeeping for `batch` sequences, all on the device so that the step can be
+// replayed from a CUDA graph: the new token of sequence b sits at position seq_lens[b]; its KV slot
+// is page_table[b][pos / 16] * 16 + pos % 16; the sequence then has pos + 1 keys.
+// ---------------------------------------------------------------------------------------------------
+__global__ void decode_prepare_kernel(const int32_t* __restrict__ page_table, int64_t pitch, int32_t* __restrict__ seq_lens,
+                                      int32_t* __restrict__ positions, int32_t* __restrict__ out_loc,
+                                      int32_t* __restrict__ kv_lens, int batch, int max_len) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  int pos = seq_lens[b];
+  pos = pos < 0 ? 0 : (pos > max_len - 1 ? max_len - 1 : pos);      // a full sequence rewrites its last slot
+  const int page = page_table[(int64_t)b * pitch + (pos >> 4)];
+  positions[b] = pos;
+  out_loc[b] = page * 16 + (pos & 15);
+  kv_lens[b] = pos + 1;
+  seq_lens[b] = pos + 1;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_embedding_bf16_q15(const uint16_t* table, const int32_t* ids, int32_t* out, int64_t rows,
+                                       int hidden, int64_t vocab_start, int64_t vocab_rows, b200_stream_t s) {
+  B200_REQUIRE(rows >= 0 && hidden > 0 && vocab_rows > 0, B200_E_SHAPE, "embedding: rows=%lld hidden=%d vocab_rows=%lld",
+               (long long)rows, hidden, (long long)vocab_rows);
+  B200_REQUIRE(hidden % 8 == 0, B200_E_UNSUPPORTED, "embedding: hidden=%d must be a multiple of 8", hidden);
+  if (rows == 0) return B200_OK;
+  B200_REQUIRE(table && ids && out, B200_E_NULL, "embedding: null pointer");
+  B200_REQUIRE(aligned16(table) && aligned16(out), B200_E_ALIGN, "embedding: table and out must be 16-byte aligned");
+  const int64_t blocks = (rows + 7) / 8;
+  B200_REQUIRE(blocks < (1ll << 31), B200_E_SHAPE, "embedding: too many rows");
+  embedding_q15_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)s>>>(table, ids, out, rows, hidden, vocab_start, vocab_rows);
+  return check_launch("embedding_bf16_q15");
+}
+
+extern "C" int b200_argmax_i32(const int32_t* logits, int64_t rows, int64_t n, int64_t pitch, int32_t index_offset,
+                               int32_t* out_idx, int32_t* out_val, b200_stream_t s) {
+  B200_REQUIRE(rows >= 0 && n > 0 && pitch >= n && n < (1ll << 31), B200_E_SHAPE, "argmax: rows=%lld n=%lld pitch=%lld",
+               (long long)rows, (long long)n, (long long)pitch);
+  if (rows == 0) return B200_OK;
+  B200_REQUIRE(logits && out_idx, B200_E_NULL, "argmax: null pointer");
+  B200_REQUIRE(aligned16(logits) && pitch % 4 == 0, B200_E_ALIGN, "argmax: rows must be 16-byte aligned (pitch a multiple of 4)");
+  B200_REQUIRE(rows < (1ll << 31), B200_E_SHAPE, "argmax: too many rows");
+  argmax_rows_kernel<<<(unsigned)rows, kArgmaxThreads, 0, (cudaStream_t)s>>>(logits, pitch, n, index_offset, out_idx, out_val);
+  return check_launch("argmax_i32");
+}
+
+extern "C" int b200_decode_prepare(const int32_t* page_table, int64_t table_pitch, int32_t* seq_lens, int32_t* positions,
+                                   int32_t* out_loc, int32_t* kv_lens, int batch, int max_len, b200_stream_t s) {
+  B200_REQUIRE(batch >= 0 && max_len > 0 && table_pitch >= (max_len + 15) / 16, B200_E_SHAPE,
+               "decode_prepare: batch=%d max_len=%d table_pitch=%lld", batch, max_len, (long long)table_pitch);
+  if (batch == 0) return B200_OK;
+  B200_REQUIRE(page_table && seq_lens && positions && out_loc && kv_lens, B200_E_NULL, "decode_prepare: null pointer");
+  decode_prepare_kernel<<<(batch + 127) / 128, 128, 0, (cudaStream_t)s>>>(page_table, table_pitch, seq_lens, positions, out_loc,
+                                                                        kv_lens, batch, max_len);
+  return check_launch("decode_prepare");
+}
