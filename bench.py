@@ -490,6 +490,102 @@ def run_tp_layer(args) -> None:
         dist.destroy_process_group()
 
 
+def run_model(args) -> None:
+    """Configuration 4's model on one GPU: a full Qwen3-8B-shaped integer model (36 layers, hidden 4096, 32/8 heads,
+    intermediate 12288, vocab 151936; random-init int8 weights), greedy decode of a batch of 256 sequences whose
+    contexts are drawn from U[100, 2048] (the spread of prompt + generated lengths of the offline run).  One step =
+    bookkeeping on the device, embedding, 36 layers, final norm, integer lm_head, arg-max, token fed back; the step
+    is captured once in a CUDA graph and replayed.  KV pages hold seeded random codes instead of a real prefill."""
+    import torch
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    from mini_sgl_integer_b200.models import DecodeBatch, Qwen3ForCausalLMInteger, Qwen3IntegerConfig, random_weights
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    cfg = Qwen3IntegerConfig(args.model_layers, 4096, 32, 8, 12288, 151936, max_pos=4096)
+    B = args.tp_batch
+    rng = np.random.default_rng(21)
+    lens = rng.integers(100, 2049, B)
+    total_steps = args.warmup + args.steps + 4
+    max_len = int(-(-(int(lens.max()) + total_steps + 1) // 16) * 16)
+    n_pg = (lens + total_steps + 16) // 16
+    P = int(n_pg.sum()) + 8
+    w = random_weights(cfg, seed=4, device=dev, generate_on_device=True)
+    pool = Int8PagedKVCache(cfg.num_kv_heads, cfg.num_layers, 128, P, dev)
+    g = torch.Generator(device=dev).manual_seed(5)
+    for i in range(cfg.num_layers):
+        pool.k_cache(i).copy_(torch.randint(-127, 128, pool.k_cache(i).shape, dtype=torch.int8, device=dev, generator=g))
+        pool.v_cache(i).copy_(torch.randint(-127, 128, pool.v_cache(i).shape, dtype=torch.int8, device=dev, generator=g))
+        meta = pool.meta(i)
+        meta[:, :, 0:32] = torch.randint(2**30, 2**31, (P, 8, 32), dtype=torch.int64, device=dev, generator=g).to(torch.int32)
+        meta[:, :, 32:36] = torch.randint(35, 39, (P, 8, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
+        meta[:, :, 36:40] = torch.randint(36, 40, (P, 8, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
+    perm = rng.permutation(P)
+    pitch = max_len // 16
+    table = np.zeros((B, pitch), dtype=np.int32)
+    off = 0
+    for b in range(B):
+        table[b, : n_pg[b]] = perm[off:off + n_pg[b]]; off += n_pg[b]
+    state = DecodeBatch(torch.from_numpy(table).to(dev), torch.from_numpy(lens.astype(np.int32)).to(dev), max_len)
+    lm = Qwen3ForCausalLMInteger(cfg, w, pool)
+    h_in = torch.from_numpy(rng.integers(0, cfg.vocab, B).astype(np.int32)).pin_memory()
+    h_out = torch.empty(B, dtype=torch.int32).pin_memory()
+    cur = h_in.to(dev)
+
+    def step():
+        cur.copy_(lm.greedy(cur, state.advance()))
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()                                              # loads modules, sizes attributes (outside the capture)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(args.warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    t_wall0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t_wall1 = time.perf_counter()
+    ms = e0.elapsed_time(e1) / args.steps
+    # end to end: the scheduler's view of a step - tokens in from pinned host memory, tokens out to it
+    lens_after = state.seq_lens.cpu().numpy()
+    t0 = time.perf_counter()
+    e2e_steps = min(args.steps, 4)
+    for _ in range(e2e_steps):
+        cur.copy_(h_in, non_blocking=True)
+        graph.replay()
+        h_out.copy_(cur, non_blocking=True)
+        torch.cuda.synchronize()
+        h_in.copy_(h_out)
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    clocks = sampler.stop(t_wall0, t_wall1)
+    per_layer_w = (32 + 16) * 128 * 4096 + 4096 * 32 * 128 + 2 * 12288 * 4096 + 4096 * 12288
+    w_bytes = cfg.num_layers * per_layer_w + cfg.vocab * cfg.hidden
+    kv_bytes = float(lens_after.mean()) * B * 8 * 266 * cfg.num_layers
+    peak, how = measured_peak()
+    ach = (w_bytes + kv_bytes) / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "decode tokens/s per GPU, full integer model", "value": B / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "Qwen3-8B-shaped integer model (%d layers), greedy decode, batch %d, ctx U[100,2048] (mean %.0f), page 16, CUDA graph"
+                               % (cfg.num_layers, B, float(lens_after.mean())), "l2": "weights + KV per step (%.1f GB) exceed L2" % ((w_bytes + kv_bytes) / 1e9)},
+        "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                     "peak_source": how, "weight_bytes": w_bytes, "kv_bytes": kv_bytes},
+        "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+        "clocks": clocks,
+    }))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -503,11 +599,12 @@ def main() -> None:
                     help="pages in the KV pool (smaller pools are for profiler captures only)")
     ap.add_argument("--sustain-s", type=float, default=1.0,
                     help="seconds of untimed back-to-back launches before the timed region (clock sampling)")
-    ap.add_argument("--workload", default="attn", choices=["attn", "rowops", "gemm", "tp_layer"],
+    ap.add_argument("--workload", default="attn", choices=["attn", "rowops", "gemm", "tp_layer", "model"],
                     help="attn = the headline decode attention (default); rowops / gemm = the other kernels of the path")
     ap.add_argument("--rows", type=int, default=16384, help="rows for --workload rowops")
     ap.add_argument("--m", type=int, default=4096, help="M for --workload gemm")
-    ap.add_argument("--tp-batch", type=int, default=256, help="decode batch for --workload tp_layer")
+    ap.add_argument("--tp-batch", type=int, default=256, help="decode batch for --workload tp_layer / model")
+    ap.add_argument("--model-layers", type=int, default=36, help="layers for --workload model")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -518,6 +615,8 @@ def main() -> None:
         run_gemm(args)
     elif args.workload == "tp_layer":
         run_tp_layer(args)
+    elif args.workload == "model":
+        run_model(args)
     else:
         run_ours(args)
 

@@ -12,6 +12,14 @@
 //   warps 2..9    epilogue: two per 32-lane quarter of the accumulator tile, half the columns each
 // The kernel is persistent (one CTA per SM walks a strided list of tiles) and keeps two accumulator
 // copies in tensor memory, so the epilogue of one tile overlaps the MMAs of the next.
+//
+// Decode sizes (M <= 256 tokens) run "weights-stationary" (template flag WS): the operands swap
+// roles - 128 weight rows are the UMMA's M side, all the tokens its N side - so every weight byte
+// crosses HBM once and a tile's accumulators are out^T.  A thread then holds one weight channel and 32
+// tokens, and the store of a token's 32 channels by a warp is one contiguous 128 bytes.  When the
+// weight matrix has too few 128-row blocks to occupy the GPU, K is split across CTAs whose int32
+// partial sums are added with red.global (integer addition: any order gives the same bits) and a
+// second small kernel applies the epilogue.
 // Stages are handed over with mbarriers (TMA -> MMA by transaction bytes, MMA -> TMA and
 // MMA -> epilogue by tcgen05.commit).  Every wait is bounded: on expiry the waiter raises an
 // error flag that the host can read, and the CTA still runs to its end and frees its tensor memory.
@@ -109,6 +117,8 @@ struct GemmParams {
   int32_t* out_q15;         // nullable
   int32_t* acc_out;         // nullable
   int M, N, K;
+  int splits;               // weights-stationary mode: parts of K per block of weight rows (1 = none)
+  int32_t* partial;         // splits > 1: int32 [M, N] that the parts are added into (zeroed before the launch)
 };
 
 __device__ __forceinline__ void mbar_arrive(unsigned bar) {
@@ -163,7 +173,7 @@ __device__ __forceinline__ void store_chunk(int32_t* stage, int lane, const int 
 // so the CTAs running at the same time share one block of weight rows in L2).  The accumulator
 // lives in tensor memory twice (2 x BN columns): while the epilogue warps drain one copy, the MMA
 // warp already fills the other with the next tile.
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool WS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const GemmParams p) {
@@ -180,8 +190,11 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (p.K + kBK - 1) / kBK;
-  const int m_tiles = (p.M + kBM - 1) / kBM, n_tiles = (p.N + BN - 1) / BN;
+  // WS: a tile is (block of 128 weight rows, part of K); otherwise (block of BN weight rows, block of 128 tokens)
+  const int m_tiles = WS ? p.splits : (p.M + kBM - 1) / kBM;
+  const int n_tiles = WS ? (p.N + kBM - 1) / kBM : (p.N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
+  const int kb_per = WS ? (num_kb + p.splits - 1) / p.splits : num_kb;
   const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
   const unsigned tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
 
@@ -211,14 +224,16 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int n_blk = tile / m_tiles, m_blk = tile - n_blk * m_tiles;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = WS ? m_blk * kb_per : 0, kb1 = WS ? min(num_kb, kb0 + kb_per) : num_kb;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
           ok = mbar_wait(empty0 + 8 * s, ph ^ 1, 1);
           if (!ok) break;
           mbar_expect_tx(full0 + 8 * s, kStageBytes);
           const unsigned a_dst = smem_u32(tiles + s * kStageBytes);
-          tma_load_2d(a_dst, &map_a, kb * kBK, m_blk * kBM, full0 + 8 * s);
-          tma_load_2d(a_dst + kABytes, &map_b, kb * kBK, n_blk * BN, full0 + 8 * s);
+          // map_a always feeds the 128-row operand: token rows, or weight rows in WS mode (map_b: all tokens)
+          tma_load_2d(a_dst, &map_a, kb * kBK, (WS ? n_blk : m_blk) * kBM, full0 + 8 * s);
+          tma_load_2d(a_dst + kABytes, &map_b, kb * kBK, WS ? 0 : n_blk * BN, full0 + 8 * s);
         }
       }
     }
@@ -233,7 +248,9 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!ok) break;
         tcgen05_fence_after();
         const unsigned tmem_d = tmem_base + slot * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int m_blk = tile % m_tiles;
+        const int kb0 = WS ? m_blk * kb_per : 0, kb1 = WS ? min(num_kb, kb0 + kb_per) : num_kb;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
           ok = mbar_wait(full0 + 8 * s, ph, 2);
           if (!ok) break;
@@ -244,7 +261,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             // the next 32 bytes of K inside the swizzle row: start address + 32 (encoded >> 4)
             umma_i8(tmem_d, da + (uint64_t)(k * kUmmaK >> 4), db + (uint64_t)(k * kUmmaK >> 4), idesc,
-                    (kb > 0 || k > 0) ? 1u : 0u);
+                    (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tcgen05_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
         }
@@ -263,9 +280,51 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
       const int n_blk = tile / m_tiles, m_blk = tile - n_blk * m_tiles;
       const unsigned slot = lt & 1, aph = (lt >> 1) & 1;
+      int32_t* cs = col_scale + slot * 2 * BN;
+      if (WS) {
+        // rows of the accumulator tile are weight channels, columns are tokens
+        const int ch = n_blk * kBM + q * 32 + lane;
+        const bool direct = p.splits == 1;
+        const bool empty_part = m_blk * kb_per >= num_kb;      // a part of K with no k-blocks: nothing was accumulated
+        if (direct && p.out_q15) {
+          for (int c = et; c < BN; c += 32 * kEpiWarps) {
+            const int t = min(c, p.M - 1);
+            cs[c] = __ldg(p.x_mul + t);
+            cs[BN + c] = __ldg(p.x_shift + t) - 48;
+          }
+        }
+        int wm = 0, ws = 0;
+        if (ch < p.N && direct && p.out_q15) { wm = __ldg(p.w_mul + ch); ws = p.w_shift ? __ldg(p.w_shift + ch) : 31; }
+        epilogue_bar_sync();
+        if (ok) ok = mbar_wait(tfull0 + 8 * slot, aph, 3);
+        tcgen05_fence_after();
+#pragma unroll 1
+        for (int c0 = half * 32; c0 < BN; c0 += 64) {
+          int v[32];
+          tmem_ld_32x32(tmem_base + ((unsigned)(q * 32) << 16) + slot * BN + (unsigned)c0, v);
+          if (!ok || c0 >= p.M || ch >= p.N || empty_part) continue;
+          if (!direct) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j < p.M) atomicAdd(p.partial + (int64_t)(c0 + j) * p.N + ch, v[j]);   // result unused: a reduction
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (c0 + j < p.M) {
+                const int64_t o = (int64_t)(c0 + j) * p.N + ch;
+                if (p.acc_out) p.acc_out[o] = v[j];
+                if (p.out_q15) p.out_q15[o] = requant_one(v[j], __mulhi(cs[c0 + j], wm), cs[BN + c0 + j] + ws);
+              }
+            }
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty0 + 8 * slot);
+        continue;
+      }
       const int row = m_blk * kBM + q * 32 + lane;
       // the tile's per-column scales go to shared memory once (double-buffered by accumulator slot)
-      int32_t* cs = col_scale + slot * 2 * BN;
       if (p.out_q15) {
         for (int c = et; c < BN; c += 32 * kEpiWarps) {
           const int col = min(n_blk * BN + c, p.N - 1);
@@ -359,18 +418,18 @@ static int sm_count() {
   return n;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool WS = false>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
   constexpr size_t smem = (size_t)STAGES * (kBM * kBK + BN * kBK) + 1024 + (2 * STAGES + 4) * 8 + 16 + 4 * BN * 4 + kEpiWarps * 32 * kStagePitch * 4;
   static_assert(smem <= 227 * 1024, "shared memory budget");
-  cudaError_t e = cudaFuncSetAttribute(gemm_w8a8_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(gemm_w8a8_kernel<BN, STAGES, WS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("gemm_w8a8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return B200_E_CUDA;
   }
-  const int tiles = ((p.N + BN - 1) / BN) * ((p.M + kBM - 1) / kBM);
+  const int tiles = WS ? ((p.N + kBM - 1) / kBM) * p.splits : ((p.N + BN - 1) / BN) * ((p.M + kBM - 1) / kBM);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_w8a8_kernel<BN, STAGES><<<grid, kGemmThreads, smem, st>>>(ma, mb, p);
+  gemm_w8a8_kernel<BN, STAGES, WS><<<grid, kGemmThreads, smem, st>>>(ma, mb, p);
   return check_launch("gemm_w8a8");
 }
 
@@ -392,17 +451,46 @@ extern "C" int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t*
   B200_REQUIRE(aligned16(x8) && aligned16(w8) && aligned16(out_q15) && aligned16(acc_out), B200_E_ALIGN,
                "gemm_w8a8: buffers must be 16-byte aligned");
   CUtensorMap ma, mb;
-  B200_REQUIRE(make_map(&ma, x8, m, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");
   GemmParams p;
   p.x_mul = x_mul; p.x_shift = x_shift; p.w_mul = w_mul; p.w_shift = w_shift;
   p.out_q15 = out_q15; p.acc_out = acc_out; p.M = (int)m; p.N = (int)n; p.K = (int)k;
+  p.splits = 1; p.partial = nullptr;
+  cudaStream_t st = (cudaStream_t)s;
+  if (m <= 256) {
+    // decode sizes: weights-stationary, K split so that about one CTA per SM streams the weights
+    const int w_blocks = (int)((n + kBM - 1) / kBM), num_kb = (int)((k + kBK - 1) / kBK);
+    int splits = sm_count() / w_blocks;
+    splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
+    while (splits > 1 && num_kb / splits < 4) --splits;
+    while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;   // no empty part
+    p.splits = splits;
+    if (splits > 1) {
+      // the parts are added into the exact-accumulator output if the caller wants it, else into the
+      // Q15.16 output buffer itself, which the epilogue kernel then rewrites in place
+      p.partial = acc_out ? acc_out : out_q15;
+      cudaError_t e = cudaMemsetAsync(p.partial, 0, (size_t)m * n * sizeof(int32_t), st);
+      B200_REQUIRE(e == cudaSuccess, B200_E_CUDA, "gemm_w8a8: cudaMemsetAsync: %s", cudaGetErrorString(e));
+    }
+    const int bn = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
+    B200_REQUIRE(make_map(&ma, w8, n, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for w8");
+    B200_REQUIRE(make_map(&mb, x8, m, k, bn), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");
+    int rc;
+    switch (bn) {
+      case 256: rc = launch_gemm<256, 4, true>(ma, mb, p, st); break;
+      case 128: rc = launch_gemm<128, 6, true>(ma, mb, p, st); break;
+      case 64: rc = launch_gemm<64, 8, true>(ma, mb, p, st); break;
+      default: rc = launch_gemm<32, 10, true>(ma, mb, p, st); break;
+    }
+    if (rc != B200_OK || splits == 1 || !out_q15) return rc;
+    return b200_requant_q15(p.partial, x_mul, x_shift, w_mul, w_shift, out_q15, m, n, s);
+  }
+  B200_REQUIRE(make_map(&ma, x8, m, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");
   // tile width: wide tiles for throughput at large M; narrow ones at decode sizes so that enough CTAs
   // stream the weights (one m block there, so the tile count is n / BN)
   const int64_t m_tiles = (m + kBM - 1) / kBM;
   int bn = 256;
   while (bn > 32 && m_tiles * ((n + bn - 1) / bn) < sm_count()) bn >>= 1;
   B200_REQUIRE(make_map(&mb, w8, n, k, bn), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for w8");
-  cudaStream_t st = (cudaStream_t)s;
   switch (bn) {
     case 256: return launch_gemm<256, 4>(ma, mb, p, st);
     case 128: return launch_gemm<128, 6>(ma, mb, p, st);

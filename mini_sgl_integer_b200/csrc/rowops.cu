@@ -187,9 +187,10 @@ __global__ void quant_given_absmax_kernel(const int32_t* __restrict__ x, const i
 }
 
 // The GEMM's fixed-point epilogue on its own: out = sat32(mul_shift(acc, (x_mul*w_mul)>>32, x_shift+w_shift-48)).
-__global__ void requant_kernel(const int32_t* __restrict__ acc, const int32_t* __restrict__ x_mul,
+// acc and out may be the same buffer (each element is read, then written, by one thread).
+__global__ void requant_kernel(const int32_t* acc, const int32_t* __restrict__ x_mul,
                                const int32_t* __restrict__ x_shift, const int32_t* __restrict__ w_mul,
-                               const int32_t* __restrict__ w_shift, int32_t* __restrict__ out, int64_t m, int n) {
+                               const int32_t* __restrict__ w_shift, int32_t* out, int64_t m, int n) {
   const int64_t total = m * n;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / n;

@@ -53,6 +53,26 @@ def test_gemm_vs_oracle(M, N, K):
     run_case(M, N, K, M + N + K)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 4096, 12288), (33, 1024, 3072), (129, 6144, 4096), (7, 200, 2064), (256, 24576, 1024)])
+def test_decode_sizes_without_accumulator_output(M, N, K):
+    """M <= 256 runs weights-stationary with K split over CTAs; with only the Q15.16 output requested the
+    partial sums are gathered in that buffer and requantised in place."""
+    from mini_sgl_integer_b200.layers import int8_gemm_q15
+    rng = np.random.default_rng(M * 7 + N + K)
+    x8 = rng.integers(-127, 128, (M, K), dtype=np.int8)
+    w8 = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    x_mul = rng.integers(2**30, 2**31, M).astype(np.int32)
+    x_shift = rng.integers(36, 44, M).astype(np.int32)
+    w_mul = rng.integers(2**29, 2**30, N).astype(np.int32)
+    w_shift = rng.integers(31, 39, N).astype(np.int32)
+    want = olin.requant_q15(olin.int32_accumulate(x8, w8), x_mul, x_shift, w_mul, w_shift)
+    for _ in range(2):                                     # the second call finds the buffer dirty
+        out = int8_gemm_q15(d(x8), d(x_mul), d(x_shift), d(w8), d(w_mul), d(w_shift))
+        torch.cuda.synchronize()
+        assert gemm_status() == 0
+        np.testing.assert_array_equal(out.cpu().numpy(), want)
+
+
 def test_gemm_per_channel_shifts_and_deep_k():
     run_case(96, 256, 12288, 7, per_channel_shift=True)
 
