@@ -242,11 +242,19 @@ B200_API int b200_decode_prepare(const int32_t* page_table, int64_t table_pitch,
  *   w_mul int32 [n], w_shift int32 [n] (nullable = 31 everywhere): per-output-channel scale;
  *   out_q15 int32 [m, n] (nullable): sat32(mul_shift(acc, (x_mul*w_mul)>>32, x_shift+w_shift-48));
  *   acc_out int32 [m, n] (nullable): the exact int32 accumulators.
- * k must be a multiple of 16.  Builds two TMA descriptors on the host per call. */
+ * k must be a multiple of 16.  Builds two TMA descriptors on the host per call.  For m <= 256 the
+ * weights are streamed once by CTAs that each take a part of K; the parts are added into acc_out (or
+ * out_q15 itself) with integer reductions after a memset on the stream, and a second small kernel
+ * applies the epilogue - still no allocation and no synchronisation. */
 B200_API int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t* x_mul,
                             const int32_t* x_shift, const int32_t* w_mul, const int32_t* w_shift,
                             int32_t* out_q15, int32_t* acc_out, int64_t m, int64_t n, int64_t k,
                             b200_stream_t s);
+/* The same with the per-token scale given as the integer absmax that the row kernels emit
+ * (x_absmax int32 [m]); (x_mul, x_shift) = b200_absmax_to_mul_shift(x_absmax) are derived inside. */
+B200_API int b200_gemm_w8a8_absmax(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax,
+                                   const int32_t* w_mul, const int32_t* w_shift, int32_t* out_q15,
+                                   int32_t* acc_out, int64_t m, int64_t n, int64_t k, b200_stream_t s);
 
 /* ---- Pieces of the W8A8 linear for tensor-parallel row-split layers, where the int32 partial
  * sums of the ranks are added (all-reduce) between the GEMM and its epilogue.  They stand in for

@@ -41,6 +41,7 @@ SIGNATURES: dict[str, list] = {
     "b200_argmax_i32": [P, L, L, L, I, P, P, P],
     "b200_decode_prepare": [P, L, P, P, P, P, I, I, P],
     "b200_gemm_w8a8": [P, P, P, P, P, P, P, P, L, L, L, P],
+    "b200_gemm_w8a8_absmax": [P, P, P, P, P, P, P, L, L, L, P],
     "b200_gemm_status": [P, I],
     "b200_quant_given_absmax_q15": [P, P, P, L, I, P],
     "b200_requant_q15": [P, P, P, P, P, P, L, L, P],

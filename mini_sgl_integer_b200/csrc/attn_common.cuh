@@ -22,18 +22,6 @@ __host__ __device__ __forceinline__ int v_chunk_offset(int d, int tok) {
   return ((wi >> 2) << 9) + (lane << 4) + ((wi & 3) << 2) + (tok & 3);
 }
 
-__device__ __forceinline__ void absmax_to_ms_dev(int m, int* mul, int* shift) {
-  m = max(m, 1);
-  const int p = 31 - __clz(m);
-  int k = 37 - p;
-  unsigned long long v = (((unsigned long long)m << k) + 63ull) / 127ull;
-  if (v >= (1ull << 31)) {
-    k -= 1;
-    v = (((unsigned long long)m << k) + 63ull) / 127ull;
-  }
-  *mul = (int)v;
-  *shift = k + 16;
-}
 
 
 __device__ __forceinline__ void mma_s8s8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,

@@ -163,4 +163,19 @@ __device__ __forceinline__ int norm_apply(int v, int inv, int w, int p) {
   return sat32(b >> (p + 18));
 }
 
+// A per-row integer absmax as a fixed-point scale: value = code * mul / 2^shift with mul in [2^30, 2^31),
+// i.e. mul / 2^shift = absmax / (127 * 2^16) rounded up in the last place.
+__device__ __forceinline__ void absmax_to_ms_dev(int m, int* mul, int* shift) {
+  m = max(m, 1);
+  const int p = 31 - __clz(m);
+  int k = 37 - p;
+  unsigned long long v = (((unsigned long long)m << k) + 63ull) / 127ull;
+  if (v >= (1ull << 31)) {
+    k -= 1;
+    v = (((unsigned long long)m << k) + 63ull) / 127ull;
+  }
+  *mul = (int)v;
+  *shift = k + 16;
+}
+
 }  // namespace b200

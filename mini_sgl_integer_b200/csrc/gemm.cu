@@ -110,6 +110,7 @@ __host__ __device__ constexpr unsigned make_idesc(int m, int n) {
 }
 
 struct GemmParams {
+  const int32_t* x_absmax;  // nullable: per-token absmax from which (x_mul, x_shift) are derived on the fly
   const int32_t* x_mul;
   const int32_t* x_shift;
   const int32_t* w_mul;
@@ -289,8 +290,11 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (direct && p.out_q15) {
           for (int c = et; c < BN; c += 32 * kEpiWarps) {
             const int t = min(c, p.M - 1);
-            cs[c] = __ldg(p.x_mul + t);
-            cs[BN + c] = __ldg(p.x_shift + t) - 48;
+            int tm, ts;
+            if (p.x_absmax) absmax_to_ms_dev(__ldg(p.x_absmax + t), &tm, &ts);
+            else { tm = __ldg(p.x_mul + t); ts = __ldg(p.x_shift + t); }
+            cs[c] = tm;
+            cs[BN + c] = ts - 48;
           }
         }
         int wm = 0, ws = 0;
@@ -333,7 +337,10 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
       }
       int xm = 0, xs = 0;
-      if (row < p.M && p.out_q15) { xm = __ldg(p.x_mul + row); xs = __ldg(p.x_shift + row); }
+      if (row < p.M && p.out_q15) {
+        if (p.x_absmax) absmax_to_ms_dev(__ldg(p.x_absmax + row), &xm, &xs);
+        else { xm = __ldg(p.x_mul + row); xs = __ldg(p.x_shift + row); }
+      }
       epilogue_bar_sync();
       if (ok) ok = mbar_wait(tfull0 + 8 * slot, aph, 3);
       tcgen05_fence_after();
@@ -375,6 +382,36 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+  }
+}
+
+// The epilogue on its own, for the split-K parts gathered in `partial` ([M, N] int32; may be `out` itself):
+// four consecutive channels of one token per thread.
+__global__ void __launch_bounds__(256)
+splitk_epilogue_kernel(const int32_t* partial, const GemmParams p) {
+  const int t = blockIdx.y;
+  const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
+  if (c >= p.N) return;
+  int xm, xs;
+  if (p.x_absmax) absmax_to_ms_dev(__ldg(p.x_absmax + t), &xm, &xs);
+  else { xm = __ldg(p.x_mul + t); xs = __ldg(p.x_shift + t); }
+  xs -= 48;
+  const int64_t o = (int64_t)t * p.N + c;
+  if (c + 3 < p.N && (p.N & 3) == 0) {
+    const int4 a = *reinterpret_cast<const int4*>(partial + o);
+    const int4 wm = __ldg(reinterpret_cast<const int4*>(p.w_mul + c));
+    int4 ws = make_int4(31, 31, 31, 31);
+    if (p.w_shift) ws = __ldg(reinterpret_cast<const int4*>(p.w_shift + c));
+    int4 r;
+    r.x = requant_one(a.x, __mulhi(xm, wm.x), xs + ws.x);
+    r.y = requant_one(a.y, __mulhi(xm, wm.y), xs + ws.y);
+    r.z = requant_one(a.z, __mulhi(xm, wm.z), xs + ws.z);
+    r.w = requant_one(a.w, __mulhi(xm, wm.w), xs + ws.w);
+    *reinterpret_cast<int4*>(p.out_q15 + o) = r;
+  } else {
+    for (int j = 0; j < 4 && c + j < p.N; ++j)
+      p.out_q15[o + j] = requant_one(partial[o + j], __mulhi(xm, __ldg(p.w_mul + c + j)),
+                                     xs + (p.w_shift ? __ldg(p.w_shift + c + j) : 31));
   }
 }
 
@@ -437,13 +474,13 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
 
 using namespace b200;
 
-extern "C" int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t* x_mul, const int32_t* x_shift,
-                              const int32_t* w_mul, const int32_t* w_shift, int32_t* out_q15, int32_t* acc_out,
-                              int64_t m, int64_t n, int64_t k, b200_stream_t s) {
+static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax, const int32_t* x_mul,
+                     const int32_t* x_shift, const int32_t* w_mul, const int32_t* w_shift, int32_t* out_q15,
+                     int32_t* acc_out, int64_t m, int64_t n, int64_t k, b200_stream_t s) {
   B200_REQUIRE(x8 && w8, B200_E_NULL, "gemm_w8a8: x8 or w8 is null");
   B200_REQUIRE(out_q15 || acc_out, B200_E_NULL, "gemm_w8a8: no output requested");
-  B200_REQUIRE(!out_q15 || (x_mul && x_shift && w_mul), B200_E_NULL,
-               "gemm_w8a8: the Q15.16 output needs x_mul, x_shift and w_mul");
+  B200_REQUIRE(!out_q15 || (((x_mul && x_shift) || x_absmax) && w_mul), B200_E_NULL,
+               "gemm_w8a8: the Q15.16 output needs the token scales (x_mul and x_shift, or x_absmax) and w_mul");
   B200_REQUIRE(m >= 0 && n > 0 && k > 0 && m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), B200_E_SHAPE,
                "gemm_w8a8: m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
   B200_REQUIRE(k % 16 == 0, B200_E_UNSUPPORTED, "gemm_w8a8: k=%lld must be a multiple of 16 (TMA row pitch)", (long long)k);
@@ -452,13 +489,14 @@ extern "C" int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t*
                "gemm_w8a8: buffers must be 16-byte aligned");
   CUtensorMap ma, mb;
   GemmParams p;
-  p.x_mul = x_mul; p.x_shift = x_shift; p.w_mul = w_mul; p.w_shift = w_shift;
+  p.x_absmax = x_absmax; p.x_mul = x_mul; p.x_shift = x_shift; p.w_mul = w_mul; p.w_shift = w_shift;
   p.out_q15 = out_q15; p.acc_out = acc_out; p.M = (int)m; p.N = (int)n; p.K = (int)k;
   p.splits = 1; p.partial = nullptr;
   cudaStream_t st = (cudaStream_t)s;
-  if (m <= 256) {
+  const int w_blocks = (int)((n + kBM - 1) / kBM), num_kb = (int)((k + kBK - 1) / kBK);
+  if (m <= 128 || (m <= 256 && w_blocks < sm_count())) {
     // decode sizes: weights-stationary, K split so that about one CTA per SM streams the weights
-    const int w_blocks = (int)((n + kBM - 1) / kBM), num_kb = (int)((k + kBK - 1) / kBK);
+    // (256 tokens against a weight matrix with at least one 128-row block per SM do as well on the other path)
     int splits = sm_count() / w_blocks;
     splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
     while (splits > 1 && num_kb / splits < 4) --splits;
@@ -482,7 +520,8 @@ extern "C" int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t*
       default: rc = launch_gemm<32, 10, true>(ma, mb, p, st); break;
     }
     if (rc != B200_OK || splits == 1 || !out_q15) return rc;
-    return b200_requant_q15(p.partial, x_mul, x_shift, w_mul, w_shift, out_q15, m, n, s);
+    splitk_epilogue_kernel<<<dim3((unsigned)((n + 1023) / 1024), (unsigned)m), 256, 0, st>>>(p.partial, p);
+    return check_launch("gemm_w8a8 (split-K epilogue)");
   }
   B200_REQUIRE(make_map(&ma, x8, m, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");
   // tile width: wide tiles for throughput at large M; narrow ones at decode sizes so that enough CTAs
@@ -497,6 +536,19 @@ extern "C" int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t*
     case 64: return launch_gemm<64, 8>(ma, mb, p, st);
     default: return launch_gemm<32, 10>(ma, mb, p, st);
   }
+}
+
+extern "C" int b200_gemm_w8a8(const int8_t* x8, const int8_t* w8, const int32_t* x_mul, const int32_t* x_shift,
+                              const int32_t* w_mul, const int32_t* w_shift, int32_t* out_q15, int32_t* acc_out,
+                              int64_t m, int64_t n, int64_t k, b200_stream_t s) {
+  return gemm_impl(x8, w8, nullptr, x_mul, x_shift, w_mul, w_shift, out_q15, acc_out, m, n, k, s);
+}
+
+extern "C" int b200_gemm_w8a8_absmax(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax, const int32_t* w_mul,
+                                     const int32_t* w_shift, int32_t* out_q15, int32_t* acc_out, int64_t m, int64_t n,
+                                     int64_t k, b200_stream_t s) {
+  B200_REQUIRE(x_absmax || !out_q15, B200_E_NULL, "gemm_w8a8_absmax: x_absmax is null");
+  return gemm_impl(x8, w8, x_absmax, nullptr, nullptr, w_mul, w_shift, out_q15, acc_out, m, n, k, s);
 }
 
 extern "C" int b200_gemm_status(int* out_host, int reset) {

@@ -44,18 +44,20 @@ def weight_scale_to_mul_shift(weight_scale: torch.Tensor) -> tuple[torch.Tensor,
     return (torch.tensor(mul, dtype=torch.int32, device=dev), torch.tensor(sh, dtype=torch.int32, device=dev))
 
 
-def int8_gemm_q15(x8: torch.Tensor, x_mul: torch.Tensor, x_shift: torch.Tensor, w8: torch.Tensor,
+def int8_gemm_q15(x8: torch.Tensor, x_mul: Optional[torch.Tensor], x_shift: Optional[torch.Tensor], w8: torch.Tensor,
                   w_mul: torch.Tensor, w_shift: Optional[torch.Tensor] = None, *, want_q15: bool = True,
-                  want_acc: bool = False):
+                  want_acc: bool = False, x_absmax: Optional[torch.Tensor] = None):
     """x8 int8 [M, K] @ w8 int8 [N, K]^T with the fixed-point epilogue.
 
-    Returns the Q15.16 result int32 [M, N], the exact int32 accumulators, or both (q15, acc).
+    The per-token scale is (x_mul, x_shift), or ``x_absmax`` int32 [M] from which the kernel derives them
+    (same values as absmax_to_mul_shift).  Returns the Q15.16 result int32 [M, N], the exact int32
+    accumulators, or both (q15, acc).
     """
     if x8.dtype != torch.int8 or w8.dtype != torch.int8:
         raise TypeError(f"x8 and w8 must be int8, got {x8.dtype} and {w8.dtype}")
     if x8.ndim != 2 or w8.ndim != 2 or x8.shape[1] != w8.shape[1]:
         raise ValueError(f"shape mismatch: x8 {tuple(x8.shape)} vs w8 {tuple(w8.shape)}")
-    require_cuda(x8, w8, x_mul, x_shift, w_mul, w_shift)
+    require_cuda(x8, w8, x_mul, x_shift, w_mul, w_shift, x_absmax)
     m, k = x8.shape
     n = w8.shape[0]
     x8, w8 = x8.contiguous(), w8.contiguous()
@@ -63,7 +65,10 @@ def int8_gemm_q15(x8: torch.Tensor, x_mul: torch.Tensor, x_shift: torch.Tensor, 
     x_mul, x_shift, w_mul, w_shift = c(x_mul), c(x_shift), c(w_mul), c(w_shift)
     out = torch.empty((m, n), dtype=torch.int32, device=x8.device) if want_q15 else None
     acc = torch.empty((m, n), dtype=torch.int32, device=x8.device) if want_acc else None
-    if m > 0:
+    if m > 0 and x_absmax is not None:
+        call("b200_gemm_w8a8_absmax", ptr(x8), ptr(w8), ptr(c(x_absmax)), ptr(w_mul), ptr(w_shift), ptr(out), ptr(acc),
+             m, n, k, stream())
+    elif m > 0:
         call("b200_gemm_w8a8", ptr(x8), ptr(w8), ptr(x_mul), ptr(x_shift), ptr(w_mul), ptr(w_shift), ptr(out),
              ptr(acc), m, n, k, stream())
     if want_q15 and want_acc:
@@ -105,9 +110,8 @@ class W8A8Int8LinearMethod:
         """The GEMM half of apply_weights_q15 for activations already quantised by a fused row kernel."""
         if getattr(layer, "weight_mul", None) is None:
             self.process_weights_after_loading(layer)
-        x_mul, x_shift = absmax_to_mul_shift(absmax.reshape(-1))
-        out = int8_gemm_q15(codes.reshape(-1, codes.shape[-1]), x_mul, x_shift, layer.weight, layer.weight_mul,
-                            layer.weight_shift)
+        out = int8_gemm_q15(codes.reshape(-1, codes.shape[-1]), None, None, layer.weight, layer.weight_mul,
+                            layer.weight_shift, x_absmax=absmax.reshape(-1))
         if bias is not None:
             b = bias if bias.dtype == torch.int32 else torch.clamp(
                 torch.round(bias.to(torch.float32) * 65536.0), -(2 ** 31), 2 ** 31 - 1).to(torch.int32)

@@ -73,6 +73,25 @@ def test_decode_sizes_without_accumulator_output(M, N, K):
         np.testing.assert_array_equal(out.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 512, 1024), (64, 1024, 2048), (256, 20000, 256)])
+def test_token_scale_from_absmax(M, N, K):
+    """The entry point that takes the row kernels' integer absmax derives the same (multiplier, shift)."""
+    from mini_sgl_integer_b200.layers import int8_gemm_q15
+    rng = np.random.default_rng(M + N + K)
+    x8 = rng.integers(-127, 128, (M, K), dtype=np.int8)
+    w8 = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    absmax = rng.integers(1, 2**24, M).astype(np.int32)
+    absmax[0], absmax[1] = 1, 2**31 - 1
+    w_mul = rng.integers(2**29, 2**30, N).astype(np.int32)
+    w_shift = rng.integers(31, 39, N).astype(np.int32)
+    x_mul, x_shift = oattn.absmax_to_mul_shift(absmax)
+    want = olin.requant_q15(olin.int32_accumulate(x8, w8), x_mul, x_shift, w_mul, w_shift)
+    out = int8_gemm_q15(d(x8), None, None, d(w8), d(w_mul), d(w_shift), x_absmax=d(absmax))
+    torch.cuda.synchronize()
+    assert gemm_status() == 0
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+
+
 def test_gemm_per_channel_shifts_and_deep_k():
     run_case(96, 256, 12288, 7, per_channel_shift=True)
 
