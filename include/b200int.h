@@ -146,10 +146,15 @@ B200_API int b200_kv_store_codes(const int8_t* k8, const int8_t* v8, const int32
  *   out_absmax int32 [batch, q_heads] (both or none): per (token, head) row quant.
  * q_heads / kv_heads must be 1, 2, 4 or 8.  max_kv_len bounds every kv_lens[i] (it sizes
  * shared memory); lengths above it are clamped.  cluster: CTAs that share one
- * (sequence, KV head), 1, 2, 4 or 8; 0 lets the library choose. */
+ * (sequence, KV head), 1, 2, 4 or 8; 0 lets the library choose.
+ * row_order int32 [batch] (nullable): a permutation of the batch rows, longest sequence first; the
+ * CTAs take the rows in this order, which shortens the tail of the launch (the result does not depend
+ * on it).  Whoever schedules the batch knows the lengths; without it, batches of up to 64 rows are
+ * ranked inside the kernel and larger ones run in the given order. */
 B200_API int b200_attn_decode(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
                      const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
                      const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                     const int32_t* row_order,
                      int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax,
                      int batch, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
                      int cluster, b200_stream_t s);

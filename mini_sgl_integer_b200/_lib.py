@@ -45,7 +45,7 @@ SIGNATURES: dict[str, list] = {
     "b200_gemm_status": [P, I],
     "b200_quant_given_absmax_q15": [P, P, P, L, I, P],
     "b200_requant_q15": [P, P, P, P, P, P, L, L, P],
-    "b200_attn_decode": [P, P, P, P, P, P, P, L, P, P, P, P, I, I, I, L, I, I, P],
+    "b200_attn_decode": [P, P, P, P, P, P, P, L, P, P, P, P, P, I, I, I, L, I, I, P],
 }
 _RESTYPES = {"b200_last_error_string": c_char_p, "b200_attn_workspace_bytes": ctypes.c_size_t}
 

@@ -25,7 +25,7 @@ def _cluster_fits(group: int, max_kv_len: int) -> bool:
     """Shared memory of the cluster kernel with eight CTAs per (sequence, KV head): ring + per-key state."""
     pages = (int(max_kv_len) + 15) // 16
     s_max = (((pages + 7) // 8) * 16 + 31) // 32 * 32
-    smem = 8 * 2 * 4480 + group * s_max * 4 + (s_max // 16) * 4 + 8 * 2 * group * 32
+    smem = 8 * 4480 + group * s_max * 4 + (s_max // 16) * 4 + 8 * 2 * group * 32
     return smem <= 200 * 1024
 
 
@@ -42,8 +42,12 @@ def decode_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
                                 pool: Int8PagedKVCache, layer_id: int, page_table: torch.Tensor,
                                 kv_lens: torch.Tensor, max_kv_len: int, *, out_q15: bool = True,
                                 out_int8: bool = False, cluster: int = 0, impl: str = "auto",
-                                workspace: torch.Tensor | None = None):
+                                workspace: torch.Tensor | None = None, row_order: torch.Tensor | None = None):
     """One decode step of integer attention over the int8 paged pool.
+
+    ``row_order`` (optional int32 [batch]): the batch rows sorted by descending length, e.g.
+    ``torch.argsort(kv_lens, descending=True)``, computed once per step by whoever schedules the batch; the
+    kernel takes the rows in that order (the result does not depend on it, the run time does).
 
     ``impl``: "cluster" = one kernel whose CTAs exchange the softmax statistics inside thread-block clusters
     (fastest; a slice's scores must fit in shared memory, which bounds the context at roughly 50k keys for
@@ -82,8 +86,8 @@ def decode_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
     else:
         call("b200_attn_decode", ptr(q8), ptr(q_mul), ptr(q_shift), ptr(pool.k_cache(layer_id)),
              ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(page_table), page_table.stride(0),
-             ptr(kv_lens), ptr(o32), ptr(o8), ptr(om), batch, q_heads, pool.kv_heads, pool.num_pages,
-             int(max_kv_len), int(cluster), stream())
+             ptr(kv_lens), ptr(None if row_order is None else row_order.to(torch.int32).contiguous()), ptr(o32), ptr(o8),
+             ptr(om), batch, q_heads, pool.kv_heads, pool.num_pages, int(max_kv_len), int(cluster), stream())
     if out_q15 and out_int8:
         return o32, o8, om
     return o32 if out_q15 else (o8, om)

@@ -97,6 +97,7 @@ struct DecodeParams {
   const int32_t* kv_lens;
   const int32_t* row_seq;    // nullable: query row -> sequence (extend); null = one row per sequence
   const int32_t* row_limit;  // nullable: keys visible to the row (causal limit); null = all of the sequence
+  const int32_t* row_order;  // nullable: the rows in the order in which CTAs should take them (longest first)
   int32_t* out_q15;
   int8_t* out_codes;
   int32_t* out_absmax;
@@ -106,19 +107,9 @@ struct DecodeParams {
   int s_max;  // key capacity of one CTA's slice (multiple of 32)
 };
 
-#ifndef B200_DW
-#define B200_DW 8
-#endif
-#ifndef B200_ST
-#define B200_ST 2
-#endif
-#ifndef B200_MB
-#define B200_MB 2
-#endif
-constexpr int kDecodeWarps = B200_DW;
+constexpr int kDecodeWarps = 8;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 static_assert(kDecodeThreads >= kD, "the output stage maps one thread to one d");
-constexpr int kStages = B200_ST;            // ring slots per warp
 constexpr int kRingSlot = kSlotBytes + 384; // a pair of pages plus their two scale blocks (2 x 160 B), 128-byte granular
 // Both contractions run on the integer tensor-core MMA with the long dimension on M:
 //   dots^T [16 keys x 8 heads] = K page [16 x 128] . Q^T [128 x 8]        (4 k-steps of 32 d)
@@ -132,17 +123,48 @@ constexpr int kRingSlot = kSlotBytes + 384; // a pair of pages plus their two sc
 // permuted identically in Q; 16-byte columns are XOR-swizzled by the row parity on the way in),
 // V in the operand order of v_chunk_offset.  The per-key fixed-point work (scale, exp, relative V
 // scale, probability limbs) runs in flat one-thread-per-key loops between the two MMA phases.
-template <int G>
-__global__ void __launch_bounds__(kDecodeThreads, B200_MB)
+// kStages = ring slots per warp (1 or 2).
+template <int G, int kStages>
+__global__ void __launch_bounds__(kDecodeThreads, 2)
 attn_decode_kernel(const DecodeParams p) {
   cg::cluster_group cluster = cg::this_cluster();
   const int C = (int)cluster.num_blocks();
   const int rank = (int)cluster.block_rank();
-  // consecutive clusters take different sequences (different lengths), so the CTAs that share an
-  // SM drift out of phase and one CTA's scalar phases overlap another's loads
-  const int b = blockIdx.y;
-  const int kh = blockIdx.z;
+  const int kh = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // Rows are best taken longest first: the hardware hands out CTAs in grid order (the KV heads of a row
+  // together, then the next row), so the long rows start first and the short ones fill the tail of the
+  // launch, and CTAs that share an SM are half a wave apart in that order, so their lengths differ and
+  // their load and scalar phases interleave.  blockIdx.z is the position in that order: given by the
+  // caller (row_order), ranked here for small batches, else as is.
+  int b = blockIdx.z;
+  if (p.row_order) {
+    b = min(max(p.row_order[blockIdx.z], 0), (int)gridDim.z - 1);
+  } else {
+    const int rows = (int)gridDim.z;
+    if (rows > 1 && rows <= 64) {
+      __shared__ int len_s[kDecodeThreads];
+      __shared__ int order_s;
+      if (tid < rows) {
+        const int sq = p.row_seq ? p.row_seq[tid] : tid;
+        int len = min(p.kv_lens[sq], p.max_kv_len);
+        if (p.row_limit) len = min(len, p.row_limit[tid]);
+        len_s[tid] = len;
+      }
+      __syncthreads();
+      if (tid < rows) {
+        const int mine = len_s[tid];
+        int before = 0;
+        for (int j = 0; j < rows; ++j) {
+          const int v = len_s[j];
+          before += (v > mine) || (v == mine && j < tid);
+        }
+        if (before == (int)blockIdx.z) order_s = tid;
+      }
+      __syncthreads();
+      b = order_s;
+    }
+  }
   const int fr = lane >> 2, fc = lane & 3;   // fragment row / column-group of this lane
   const int S = p.s_max;
   constexpr int kNeg = (int)(-2147483647 - 1);
@@ -538,25 +560,25 @@ attn_decode_kernel(const DecodeParams p) {
   cluster.sync();  // nobody leaves while a peer still reads its shared memory
 }
 
-static size_t decode_smem_bytes(int G, int s_max) {
-  return (size_t)kDecodeWarps * kStages * kRingSlot + (size_t)G * s_max * 4 + (size_t)(s_max / 16) * 4 +
+static size_t decode_smem_bytes(int G, int s_max, int stages) {
+  return (size_t)kDecodeWarps * stages * kRingSlot + (size_t)G * s_max * 4 + (size_t)(s_max / 16) * 4 +
          (size_t)kDecodeWarps * 2 * G * 32;
 }
 
-template <int G>
+template <int G, int kStages>
 static int launch_decode(const DecodeParams& p, int batch, int cluster, cudaStream_t st) {
-  const size_t smem = decode_smem_bytes(G, p.s_max);
+  const size_t smem = decode_smem_bytes(G, p.s_max, kStages);
   if (smem > 200 * 1024) {
     set_error("attn_decode: max_kv_len=%d needs %zu bytes of shared memory per CTA; raise cluster", p.max_kv_len, smem);
     return B200_E_UNSUPPORTED;
   }
-  cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<G, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("attn_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return B200_E_CUDA;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(cluster, batch, p.kv_heads);
+  cfg.gridDim = dim3(cluster, p.kv_heads, batch);
   cfg.blockDim = dim3(kDecodeThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
@@ -567,7 +589,7 @@ static int launch_decode(const DecodeParams& p, int batch, int cluster, cudaStre
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<G>, p);
+  e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<G, kStages>, p);
   if (e != cudaSuccess) {
     set_error("attn_decode: launch: %s", cudaGetErrorString(e));
     return B200_E_CUDA;
@@ -628,7 +650,7 @@ extern "C" int b200_kv_store_codes(const int8_t* k8, const int8_t* v8, const int
 static int attn_common(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
                        const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
                        const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
-                       const int32_t* row_seq, const int32_t* row_limit,
+                       const int32_t* row_seq, const int32_t* row_limit, const int32_t* row_order,
                        int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax, int batch,
                        int q_heads, int kv_heads, int64_t num_pages, int max_kv_len, int cluster,
                        b200_stream_t s) {
@@ -649,39 +671,48 @@ static int attn_common(const int8_t* q, const int32_t* q_mul, const int32_t* q_s
                (long long)table_pitch, max_pages);
   B200_REQUIRE(aligned16(q) && aligned16(k_codes) && aligned16(v_codes) && aligned16(meta), B200_E_ALIGN,
                "attn_decode: q and pool buffers must be 16-byte aligned");
+  // Configuration: the per-CTA fixed work (set-up, exchanges) is paid once per CTA, so the fewest CTAs per
+  // (row, KV head) whose slice state still lets two CTAs share an SM win; one CTA with single ring slots
+  // is preferred, then the smallest cluster with two slots per warp, then whatever fits at all.
+  auto slice_keys = [&](int c) { return ((((max_pages + c - 1) / c) * kPage + 31) / 32) * 32; };
+  const size_t two_per_sm = 110 * 1024;
+  int stages = 2;
   if (cluster == 0) {
-    // fewest CTAs per (sequence, KV head) whose slice state still lets two CTAs share an SM
-    cluster = 1;
-    while (cluster < 8 &&
-           decode_smem_bytes(G, ((((max_pages + cluster - 1) / cluster) * kPage + 31) / 32) * 32) > 110 * 1024)
-      cluster *= 2;
+    if (decode_smem_bytes(G, slice_keys(1), 1) <= two_per_sm) {
+      cluster = 1;
+    } else {
+      cluster = 2;
+      while (cluster < 8 && decode_smem_bytes(G, slice_keys(cluster), 2) > two_per_sm) cluster *= 2;
+    }
   }
   B200_REQUIRE(cluster == 1 || cluster == 2 || cluster == 4 || cluster == 8, B200_E_UNSUPPORTED,
                "attn_decode: cluster=%d (1, 2, 4 or 8)", cluster);
+  if (decode_smem_bytes(G, slice_keys(cluster), 2) > two_per_sm) stages = 1;
   if (batch == 0) return B200_OK;
   DecodeParams p;
   p.q = q; p.q_mul = q_mul; p.q_shift = q_shift; p.k_codes = k_codes; p.v_codes = v_codes; p.meta = meta;
   p.page_table = page_table; p.table_pitch = table_pitch; p.kv_lens = kv_lens; p.out_q15 = out_q15;
   p.out_codes = out_codes; p.out_absmax = out_absmax; p.q_heads = q_heads; p.kv_heads = kv_heads;
-  p.num_pages = num_pages; p.max_kv_len = max_kv_len; p.row_seq = row_seq; p.row_limit = row_limit;
+  p.num_pages = num_pages; p.max_kv_len = max_kv_len; p.row_seq = row_seq; p.row_limit = row_limit; p.row_order = row_order;
   const int ppc = (max_pages + cluster - 1) / cluster;
   p.s_max = ((ppc * kPage + 31) / 32) * 32;
   cudaStream_t st = (cudaStream_t)s;
   switch (G) {
-    case 1: return launch_decode<1>(p, batch, cluster, st);
-    case 2: return launch_decode<2>(p, batch, cluster, st);
-    case 4: return launch_decode<4>(p, batch, cluster, st);
-    default: return launch_decode<8>(p, batch, cluster, st);
+    case 1: return stages == 1 ? launch_decode<1, 1>(p, batch, cluster, st) : launch_decode<1, 2>(p, batch, cluster, st);
+    case 2: return stages == 1 ? launch_decode<2, 1>(p, batch, cluster, st) : launch_decode<2, 2>(p, batch, cluster, st);
+    case 4: return stages == 1 ? launch_decode<4, 1>(p, batch, cluster, st) : launch_decode<4, 2>(p, batch, cluster, st);
+    default: return stages == 1 ? launch_decode<8, 1>(p, batch, cluster, st) : launch_decode<8, 2>(p, batch, cluster, st);
   }
 }
 
 extern "C" int b200_attn_decode(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
                                 const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
                                 const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                                const int32_t* row_order,
                                 int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax, int batch,
                                 int q_heads, int kv_heads, int64_t num_pages, int max_kv_len, int cluster,
                                 b200_stream_t s) {
-  return attn_common(q, q_mul, q_shift, k_codes, v_codes, meta, page_table, table_pitch, kv_lens, nullptr, nullptr,
+  return attn_common(q, q_mul, q_shift, k_codes, v_codes, meta, page_table, table_pitch, kv_lens, nullptr, nullptr, row_order,
                      out_q15, out_codes, out_absmax, batch, q_heads, kv_heads, num_pages, max_kv_len, cluster, s);
 }
 
@@ -693,6 +724,6 @@ extern "C" int b200_attn_extend(const int8_t* q, const int32_t* q_mul, const int
                                 int q_heads, int kv_heads, int64_t num_pages, int max_kv_len, int cluster,
                                 b200_stream_t s) {
   B200_REQUIRE(row_seq && row_limit, B200_E_NULL, "attn_extend: row_seq or row_limit is null");
-  return attn_common(q, q_mul, q_shift, k_codes, v_codes, meta, page_table, table_pitch, kv_lens, row_seq, row_limit,
+  return attn_common(q, q_mul, q_shift, k_codes, v_codes, meta, page_table, table_pitch, kv_lens, row_seq, row_limit, nullptr,
                      out_q15, out_codes, out_absmax, rows, q_heads, kv_heads, num_pages, max_kv_len, cluster, s);
 }

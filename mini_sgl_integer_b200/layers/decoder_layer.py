@@ -31,6 +31,7 @@ class AttnBatch:
     kv_lens: torch.Tensor        # int32 [batch]  keys per sequence including the new tokens
     q_lens: Optional[torch.Tensor]  # int32 [batch] new tokens per sequence; None = decode (one each)
     max_kv_len: int
+    row_order: Optional[torch.Tensor] = None   # int32 [batch] rows by descending kv length (decode scheduling hint)
 
 
 class _Linear(torch.nn.Module):
@@ -88,7 +89,7 @@ class Qwen3DecoderLayerInteger:
         t["q8"] = q8
         if batch.q_lens is None:
             attn = decode_attention_int8_paged(q8, q_mul, q_shift, self.pool, self.layer_id, batch.page_table,
-                                               batch.kv_lens, batch.max_kv_len)
+                                               batch.kv_lens, batch.max_kv_len, row_order=batch.row_order)
         else:
             attn = extend_attention_int8_paged(q8, q_mul, q_shift, self.pool, self.layer_id, batch.page_table,
                                                batch.kv_lens, batch.q_lens, batch.max_kv_len)

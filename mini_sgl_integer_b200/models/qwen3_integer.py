@@ -94,11 +94,13 @@ class DecodeBatch:
         self.positions = torch.zeros(self.batch, dtype=torch.int32, device=dev)
         self.out_loc = torch.zeros(self.batch, dtype=torch.int32, device=dev)
         self.kv_lens = torch.zeros(self.batch, dtype=torch.int32, device=dev)
+        # every sequence grows by one token per step, so the order by length never changes
+        self.row_order = torch.argsort(self.seq_lens, descending=True, stable=True).to(torch.int32)
 
     def advance(self) -> AttnBatch:
         call("b200_decode_prepare", ptr(self.page_table), self.page_table.stride(0), ptr(self.seq_lens), ptr(self.positions),
              ptr(self.out_loc), ptr(self.kv_lens), self.batch, self.max_len, stream())
-        return AttnBatch(self.positions, self.out_loc, self.page_table, self.kv_lens, None, self.max_len)
+        return AttnBatch(self.positions, self.out_loc, self.page_table, self.kv_lens, None, self.max_len, self.row_order)
 
 
 class Qwen3ModelInteger:

@@ -60,11 +60,11 @@ def test_bad_arguments_are_rejected_before_launch():
         _lib.call("b200_silu_mul_q15", one, one, None, None, None, 4, 200, 128, None)
     assert e.value.code == -4
     with pytest.raises(_lib.B200Error) as e:
-        _lib.call("b200_attn_decode", one, one, one, one, one, one, one, 4, one, one, None, None,
+        _lib.call("b200_attn_decode", one, one, one, one, one, one, one, 4, one, None, one, None, None,
                   2, 12, 5, 10, 64, 0, None)
     assert e.value.code == -2  # q_heads not a multiple of kv_heads
     with pytest.raises(_lib.B200Error) as e:
-        _lib.call("b200_attn_decode", one, one, one, one, one, one, one, 1, one, one, None, None,
+        _lib.call("b200_attn_decode", one, one, one, one, one, one, one, 1, one, None, one, None, None,
                   2, 8, 2, 10, 640, 0, None)
     assert e.value.code == -2 and "table_pitch" in str(e.value)
 

@@ -246,14 +246,32 @@ def test_extend_without_prefix_reduces_to_reference(golden):
     eq(oattn.q15_to_bf16_bits(got.astype(np.int64)), golden["attn_out_bf16_bits"])
 
 
+def test_row_order_hint_does_not_change_results():
+    lens = [700, 33, 1, 256, 2049, 16, 900]
+    case = make_case(9, lens, 8, 2, 300)
+    pool = device_pool(case, 300, 2)
+    want = oracle_decode(case)
+    order = np.argsort(-np.asarray(lens), kind="stable").astype(np.int32)
+    for ro in (None, order, order[::-1].copy(), np.arange(len(lens), dtype=np.int32)):
+        got = run_decode(case, pool, 2049, row_order=None if ro is None else d(ro)).cpu().numpy()
+        eq(got, want)
+    # more rows than the in-kernel ranking handles (64): given order and caller's order
+    lens = list(np.random.default_rng(3).integers(1, 90, 80))
+    case = make_case(10, lens, 4, 1, 600)
+    pool = device_pool(case, 600, 1)
+    want = oracle_decode(case)
+    eq(run_decode(case, pool, 96).cpu().numpy(), want)
+    eq(run_decode(case, pool, 96, row_order=d(np.argsort(-np.asarray(lens), kind="stable").astype(np.int32))).cpu().numpy(), want)
+
+
 def test_auto_falls_back_to_workspace_passes_for_long_contexts():
-    """A context too long for the cluster kernel's shared memory (eight query heads per KV head, 40k keys)."""
+    """A context too long for the cluster kernel's shared memory (eight query heads per KV head, 48k keys)."""
     from mini_sgl_integer_b200.attention.ops import _cluster_fits
-    assert _cluster_fits(4, 4096) and not _cluster_fits(8, 40000)
-    lens = [40000, 33]
-    case = make_case(5, lens, 8, 1, 2600)
-    pool = device_pool(case, 2600, 1)
-    got = run_decode(case, pool, 40000).cpu().numpy()          # impl="auto"
+    assert _cluster_fits(4, 4096) and not _cluster_fits(8, 48000)
+    lens = [48000, 33]
+    case = make_case(5, lens, 8, 1, 3100)
+    pool = device_pool(case, 3100, 1)
+    got = run_decode(case, pool, 48000).cpu().numpy()          # impl="auto"
     eq(got, oracle_decode(case))
 
 
@@ -263,3 +281,53 @@ def test_extend_empty_batch():
     z = lambda *s, dt=torch.int32: torch.zeros(s, dtype=dt, device="cuda")
     out = extend_attention_int8_paged(z(0, 4, 128, dt=torch.int8), z(0, 4), z(0, 4), pool, 0, z(1, 2), z(1), z(1), 32)
     assert out.shape == (0, 4, 128)
+
+
+@pytest.mark.parametrize("phase", ["prefill", "decode"])
+def test_backend_forward_matches_oracle(phase):
+    """The plug-in class end to end: metadata from requests, K/V quantised into the pool, q quantised, attention."""
+    from types import SimpleNamespace
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    from mini_sgl_integer_b200.attention.backend import B200Int8Backend, token_locations
+    from oracle import fixed_point as ofp
+    rng = np.random.default_rng(31)
+    HQ, HK, P = 8, 2, 24
+    table = rng.permutation(P).astype(np.int32).reshape(4, 6)            # 4 request slots x 6 pages
+    if phase == "prefill":
+        reqs = [(2, 0, 37), (0, 0, 5), (3, 0, 64)]                         # (table_idx, cached_len, device_len)
+    else:
+        reqs = [(2, 36, 37), (0, 4, 5), (3, 63, 64)]
+    ref_pool = oattn.PagedKV(P, HK, 128)
+    pool = Int8PagedKVCache(HK, 1, 128, P, "cuda")
+    if phase == "decode":                                                 # cached prefixes
+        for t, c, _ in reqs:
+            loc = (table[t][np.arange(c) // 16] * 16 + np.arange(c) % 16).astype(np.int32)
+            k8 = rng.integers(-127, 128, (c, HK, 128), dtype=np.int8); v8 = rng.integers(-127, 128, (c, HK, 128), dtype=np.int8)
+            km = rng.integers(2**30, 2**31, (c, HK)); ks = rng.integers(35, 39, (c, HK))
+            vm = rng.integers(2**30, 2**31, (c, HK)); vs = rng.integers(33, 38, (c, HK))
+            ref_pool.store_codes(loc, k8, v8, km, ks, vm, vs)
+            pool.store_codes(d(k8), d(v8), d(km.astype(np.int32)), d(ks.astype(np.int32)), d(vm.astype(np.int32)),
+                             d(vs.astype(np.int32)), d(loc), 0)
+    q_lens = [dl - c for _, c, dl in reqs]
+    T = sum(q_lens)
+    q = rng.integers(-(2**20), 2**20, (T, HQ * 128)).astype(np.int32)
+    k = rng.integers(-(2**20), 2**20, (T, HK * 128)).astype(np.int32)
+    v = rng.integers(-(2**20), 2**20, (T, HK * 128)).astype(np.int32)
+    positions = np.concatenate([np.arange(c, dl) for _, c, dl in reqs]).astype(np.int32)
+    row_of = np.concatenate([np.full(n, i) for i, n in enumerate(q_lens)])
+    rq = [SimpleNamespace(table_idx=t, cached_len=c, device_len=dl, extend_len=dl - c) for t, c, dl in reqs]
+    batch = SimpleNamespace(reqs=rq, padded_reqs=rq, phase=phase, is_prefill=phase == "prefill", is_decode=phase == "decode",
+                            size=len(rq), padded_size=len(rq))
+    be = B200Int8Backend(HQ, HK, pool, d(table))
+    be.prepare_metadata(batch)
+    batch.out_loc = token_locations(batch.attn_metadata.page_table, d(positions), d(row_of))
+    got = be.forward(d(q), d(k), d(v), 0, batch).cpu().numpy()
+
+    out_loc = np.concatenate([table[t][np.arange(c, dl) // 16] * 16 + np.arange(c, dl) % 16 for t, c, dl in reqs]).astype(np.int32)
+    eq(batch.out_loc.cpu().numpy(), out_loc)
+    ref_pool.store_q15(out_loc, k, v)
+    q8, _, qm = ofp.per_token_quant_from_q15(q.reshape(T, HQ, 128))
+    q_mul, q_shift = oattn.absmax_to_mul_shift(qm[..., 0])
+    want = oattn.paged_attention(q8, q_mul, q_shift, ref_pool, [table[t] for t, _, _ in reqs], [dl for _, _, dl in reqs], q_lens)
+    eq(got.reshape(T, HQ, 128), want)
+    assert batch.attn_metadata.get_last_indices(3).tolist() == (np.cumsum(q_lens) - 1).tolist()
