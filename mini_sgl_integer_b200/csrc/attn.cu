@@ -143,7 +143,7 @@ attn_decode_kernel(const DecodeParams p) {
   } else {
     const int rows = (int)gridDim.z;
     if (rows > 1 && rows <= 64) {
-      __shared__ int len_s[kDecodeThreads];
+      __shared__ int len_s[64];
       __shared__ int order_s;
       if (tid < rows) {
         const int sq = p.row_seq ? p.row_seq[tid] : tid;
@@ -191,7 +191,10 @@ attn_decode_kernel(const DecodeParams p) {
   const int L_all = max(0, min(p.kv_lens[seq], p.max_kv_len));
   const int L = p.row_limit ? max(0, min(p.row_limit[b], L_all)) : L_all;
   const int n_pages = (L + kPage - 1) / kPage;
-  const int ppc = (n_pages + C - 1) / C;                 // pages per CTA
+  const int Ce = C;   // CTAs that work on this row
+  // a CTA on its own needs no cluster barrier (and the plain one is cheaper)
+  auto row_sync = [&]() { if (Ce > 1) cluster.sync(); else __syncthreads(); };
+  const int ppc = (n_pages + Ce - 1) / Ce;               // pages per CTA
   const int pg0 = min(n_pages, rank * ppc);
   const int pg1 = min(n_pages, pg0 + ppc);
   const int my_pages = pg1 - pg0;
@@ -384,19 +387,19 @@ attn_decode_kernel(const DecodeParams p) {
   }
   // The first V pairs are requested between the two halves of the cluster barrier: the release fence
   // of the arrival would otherwise wait for copies that are still in flight.
-  cluster.barrier_arrive();
+  if (Ce > 1) cluster.barrier_arrive(); else __syncthreads();
 #pragma unroll
   for (int j = 0; j < kStages; ++j) issue_v(j);
-  cluster.barrier_wait();
+  if (Ce > 1) cluster.barrier_wait();
 
   // ---- exchange 1: row maxima and the V reference scale over the cluster
   if (tid < G) {
     int m = kNeg;
-    for (int r = 0; r < C; ++r) m = max(m, *cluster.map_shared_rank(&cta_max[tid], r));
+    for (int r = 0; r < Ce; ++r) m = max(m, *cluster.map_shared_rank(&cta_max[tid], r));
     g_max[tid] = m;
   }
   unsigned long long vref = ~0ull;
-  for (int r = 0; r < C; ++r) {
+  for (int r = 0; r < Ce; ++r) {
     const unsigned long long o = *cluster.map_shared_rank(&cta_vref, r);
     vref = o < vref ? o : vref;
   }
@@ -450,12 +453,12 @@ attn_decode_kernel(const DecodeParams p) {
       if (lane == 0) atomicAdd(&cta_sum[g], (unsigned long long)s);
     }
   }
-  cluster.sync();
+  row_sync();
 
   // ---- exchange 2: total of the exponentials -> inv = (2^31 - 1) / max(1, total)
   if (tid < G) {
     unsigned long long tot = 0;
-    for (int r = 0; r < C; ++r) tot += *cluster.map_shared_rank(&cta_sum[tid], r);
+    for (int r = 0; r < Ce; ++r) tot += *cluster.map_shared_rank(&cta_sum[tid], r);
     if (tot < 1ull) tot = 1ull;
     g_inv[tid] = (int)(2147483647ull / tot);
   }
@@ -537,16 +540,16 @@ attn_decode_kernel(const DecodeParams p) {
         if (head < G && v != 0) atomicAdd(&cta_acc[head][d], v);
       }
   }
-  cluster.sync();
+  row_sync();
 
   // ---- exchange 3: head g is finished by rank g % C: sum the partial outputs of all CTAs over
   // distributed shared memory, requantise, and (for the int8 output) quantise the 128-wide row
   {
-    for (int g = rank; g < G; g += C) {   // uniform per CTA
+    for (int g = rank; g < G; g += Ce) {   // uniform per CTA
       const int d = tid & (kD - 1);        // threads beyond kD repeat a d and keep quiet
       const bool act = tid < kD;
       long long a = 0;
-      for (int r = 0; r < C; ++r) a += *cluster.map_shared_rank(&cta_acc[g][d], r);
+      for (int r = 0; r < Ce; ++r) a += *cluster.map_shared_rank(&cta_acc[g][d], r);
       const int o = L > 0 ? mul_shift_sat32_wide(a, v_mul_ref, v_shift_ref - 1) : 0;
       const int64_t row = ((int64_t)b * p.q_heads + kh * G + g) * kD;
       if (p.out_q15 && act) p.out_q15[row + d] = o;
@@ -557,7 +560,7 @@ attn_decode_kernel(const DecodeParams p) {
       }
     }
   }
-  cluster.sync();  // nobody leaves while a peer still reads its shared memory
+  row_sync();  // nobody leaves while a peer still reads its shared memory
 }
 
 static size_t decode_smem_bytes(int G, int s_max, int stages) {
@@ -675,27 +678,35 @@ static int attn_common(const int8_t* q, const int32_t* q_mul, const int32_t* q_s
   // (row, KV head) whose slice state still lets two CTAs share an SM win; one CTA with single ring slots
   // is preferred, then the smallest cluster with two slots per warp, then whatever fits at all.
   auto slice_keys = [&](int c) { return ((((max_pages + c - 1) / c) * kPage + 31) / 32) * 32; };
-  const size_t two_per_sm = 110 * 1024;
-  int stages = 2;
+  // Configuration.  Set-up, barriers and the final exchange are paid per CTA and a lone CTA needs no
+  // cluster barrier, so one CTA per (row, KV head) wins whenever its slice state lets two CTAs share an
+  // SM - with two ring slots per warp if that still fits, else one; longer contexts take the smallest
+  // cluster whose slices fit with two slots.
+  const int G_static = 1536 + G * kD * 4 + 1024;   // the kernel's static shared arrays plus the per-CTA reserve
+  const size_t two_per_sm = (size_t)(233472 / 2 - G_static);
+  auto fits2 = [&](int c, int st) { return decode_smem_bytes(G, slice_keys(c), st) <= two_per_sm; };
+  int stages;
   if (cluster == 0) {
-    if (decode_smem_bytes(G, slice_keys(1), 1) <= two_per_sm) {
-      cluster = 1;
-    } else {
+    if (fits2(1, 2)) { cluster = 1; stages = 2; }
+    else if (fits2(1, 1)) { cluster = 1; stages = 1; }
+    else {
       cluster = 2;
-      while (cluster < 8 && decode_smem_bytes(G, slice_keys(cluster), 2) > two_per_sm) cluster *= 2;
+      while (cluster < 8 && !fits2(cluster, 2)) cluster *= 2;
+      stages = fits2(cluster, 2) ? 2 : 1;
     }
+  } else {
+    B200_REQUIRE(cluster == 1 || cluster == 2 || cluster == 4 || cluster == 8, B200_E_UNSUPPORTED,
+                 "attn_decode: cluster=%d (1, 2, 4 or 8)", cluster);
+    stages = fits2(cluster, 2) ? 2 : 1;
   }
-  B200_REQUIRE(cluster == 1 || cluster == 2 || cluster == 4 || cluster == 8, B200_E_UNSUPPORTED,
-               "attn_decode: cluster=%d (1, 2, 4 or 8)", cluster);
-  if (decode_smem_bytes(G, slice_keys(cluster), 2) > two_per_sm) stages = 1;
+  const int s_max = slice_keys(cluster);
   if (batch == 0) return B200_OK;
   DecodeParams p;
   p.q = q; p.q_mul = q_mul; p.q_shift = q_shift; p.k_codes = k_codes; p.v_codes = v_codes; p.meta = meta;
   p.page_table = page_table; p.table_pitch = table_pitch; p.kv_lens = kv_lens; p.out_q15 = out_q15;
   p.out_codes = out_codes; p.out_absmax = out_absmax; p.q_heads = q_heads; p.kv_heads = kv_heads;
   p.num_pages = num_pages; p.max_kv_len = max_kv_len; p.row_seq = row_seq; p.row_limit = row_limit; p.row_order = row_order;
-  const int ppc = (max_pages + cluster - 1) / cluster;
-  p.s_max = ((ppc * kPage + 31) / 32) * 32;
+  p.s_max = s_max;
   cudaStream_t st = (cudaStream_t)s;
   switch (G) {
     case 1: return stages == 1 ? launch_decode<1, 1>(p, batch, cluster, st) : launch_decode<1, 2>(p, batch, cluster, st);
