@@ -123,6 +123,18 @@ __device__ __forceinline__ int quant_code_fast(int x, float mf, float y) {
     t = __fadd_rn(__fdiv_rn(a, mf), 12582912.0f);
   return __float_as_int(t) - 0x4B400000;
 }
+// quant_code_fast for rows whose absmax is below 2^22: int -> float by placing the value in the mantissa
+// of 1.5 * 2^23 (exact for |x| < 2^22) instead of the conversion unit.
+__device__ __forceinline__ int quant_code_fast_small(int x, float mf, float y) {
+  const float xf = __int_as_float(0x4B400000 + x) - 12582912.0f;
+  const float a = __fmul_rn(xf, 127.0f);
+  const float q0 = __fmul_rn(a, y);
+  float q1 = __fmaf_rn(__fmaf_rn(-mf, q0, a), y, q0);
+  float t = __fadd_rn(q1, 12582912.0f);
+  if (fabsf(__fsub_rn(q1, __fsub_rn(t, 12582912.0f))) > 0.4990234375f)
+    t = __fadd_rn(__fdiv_rn(a, mf), 12582912.0f);
+  return __float_as_int(t) - 0x4B400000;
+}
 __device__ __forceinline__ float quant_scale(float mf) { return __fdiv_rn(mf, 8323072.0f); }
 
 __device__ __forceinline__ unsigned pack4(int a, int b, int c, int d) {

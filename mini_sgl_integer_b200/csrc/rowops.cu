@@ -119,12 +119,23 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
   const float mf = __int2float_rn(m2);
   const float my = __frcp_rn(mf);
   unsigned* co = reinterpret_cast<unsigned*>(codes + row * H);
+  if (m2 < (1 << 22)) {   // block-uniform: conversions without the conversion unit
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int idx = threadIdx.x + i * blockDim.x;
-    if (idx < nvec) {
-      co[idx] = pack4(quant_code_fast(v[i].x, mf, my), quant_code_fast(v[i].y, mf, my),
-                      quant_code_fast(v[i].z, mf, my), quant_code_fast(v[i].w, mf, my));
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      if (idx < nvec) {
+        co[idx] = pack4(quant_code_fast_small(v[i].x, mf, my), quant_code_fast_small(v[i].y, mf, my),
+                        quant_code_fast_small(v[i].z, mf, my), quant_code_fast_small(v[i].w, mf, my));
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      if (idx < nvec) {
+        co[idx] = pack4(quant_code_fast(v[i].x, mf, my), quant_code_fast(v[i].y, mf, my),
+                        quant_code_fast(v[i].z, mf, my), quant_code_fast(v[i].w, mf, my));
+      }
     }
   }
   if (threadIdx.x == 0) {
@@ -251,7 +262,12 @@ __device__ __forceinline__ int silu_mul_elem(int g, int u, const int32_t* __rest
   // sneg = floor(E * 2^16 / (2^16 + E)): float estimate (off by at most 1), exact correction
   const unsigned den = 65536u + E;
   const unsigned num = E << 16;                                  // wraps only for E == 2^16 (handled below)
-  unsigned sneg = (unsigned)__fdividef((float)E * 65536.0f, (float)den);
+  // E and den are below 2^23, so they convert to float exactly by being placed in the mantissa of 2^23
+  // (an OR and an FP add instead of the conversion unit), and the estimate goes back the same way
+  // (rounded to nearest instead of truncated: still within one of the quotient).
+  const float Ef = __uint_as_float(0x4B000000u | E) - 8388608.0f;
+  const float denf = __uint_as_float(0x4B000000u | den) - 8388608.0f;
+  unsigned sneg = __float_as_uint(__fdividef(Ef * 65536.0f, denf) + 8388608.0f) - 0x4B000000u;
   const int rem = (int)(num - sneg * den);
   sneg += rem < 0 ? -1 : (rem >= (int)den ? 1 : 0);
   sneg = (E == 65536u) ? 32768u : sneg;
@@ -408,10 +424,18 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   const float mf = __int2float_rn(m);
   const float my = __frcp_rn(mf);
   unsigned* co = reinterpret_cast<unsigned*>(codes + row * (int64_t)I);
-  for (int i = threadIdx.x; i < (I >> 2); i += blockDim.x) {
-    const int4 v = reinterpret_cast<const int4*>(rowbuf)[i];
-    co[i] = pack4(quant_code_fast(v.x, mf, my), quant_code_fast(v.y, mf, my), quant_code_fast(v.z, mf, my),
-                  quant_code_fast(v.w, mf, my));
+  if (m < (1 << 22)) {   // the usual case (block-uniform): conversions without the conversion unit
+    for (int i = threadIdx.x; i < (I >> 2); i += blockDim.x) {
+      const int4 v = reinterpret_cast<const int4*>(rowbuf)[i];
+      co[i] = pack4(quant_code_fast_small(v.x, mf, my), quant_code_fast_small(v.y, mf, my),
+                    quant_code_fast_small(v.z, mf, my), quant_code_fast_small(v.w, mf, my));
+    }
+  } else {
+    for (int i = threadIdx.x; i < (I >> 2); i += blockDim.x) {
+      const int4 v = reinterpret_cast<const int4*>(rowbuf)[i];
+      co[i] = pack4(quant_code_fast(v.x, mf, my), quant_code_fast(v.y, mf, my), quant_code_fast(v.z, mf, my),
+                    quant_code_fast(v.w, mf, my));
+    }
   }
   if (threadIdx.x == 0) {
     scale[row] = quant_scale(mf);
