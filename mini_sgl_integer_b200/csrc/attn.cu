@@ -310,29 +310,21 @@ attn_decode_kernel(const DecodeParams p) {
       __syncwarp();
       const unsigned char* slot0 = ring + (it % kStages) * kRingSlot;
       const unsigned char* slot = slot0 + fr * 128;   // rows fr, fr + 8: same parity
+      // everything the pair needs moves to registers first, so that the slot can be refilled while the
+      // warp is still busy with this pair
+      uint4 kq[2][4];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        int c[4] = {0, 0, 0, 0};
-        if (2 * pp + h < my_pages) {
-          const unsigned char* r0 = slot + h * 2048;
-          const uint4 k00 = *reinterpret_cast<const uint4*>(r0 + o0);
-          const uint4 k01 = *reinterpret_cast<const uint4*>(r0 + o1);
-          const uint4 k10 = *reinterpret_cast<const uint4*>(r0 + 1024 + o0);
-          const uint4 k11 = *reinterpret_cast<const uint4*>(r0 + 1024 + o1);
-          mma_s8s8(c, k00.x, k10.x, k00.y, k10.y, qw[0], qw[1]);
-          mma_s8s8(c, k00.z, k10.z, k00.w, k10.w, qw[2], qw[3]);
-          mma_s8s8(c, k01.x, k11.x, k01.y, k11.y, qw[4], qw[5]);
-          mma_s8s8(c, k01.z, k11.z, k01.w, k11.w, qw[6], qw[7]);
-        }
-        // c[0]: (key fr, head 2fc)  c[1]: (fr, 2fc+1)  c[2]: (fr + 8, 2fc)  c[3]: (fr + 8, 2fc+1)
-        const int kl = (2 * pp + h) * 16;
-        if (h0) { sc0[kl] = c[0]; sc0[kl + 8] = c[2]; }
-        if (h1) { sc1[kl] = c[1]; sc1[kl + 8] = c[3]; }
+        const unsigned char* r0 = slot + h * 2048;
+        kq[h][0] = *reinterpret_cast<const uint4*>(r0 + o0);
+        kq[h][1] = *reinterpret_cast<const uint4*>(r0 + o1);
+        kq[h][2] = *reinterpret_cast<const uint4*>(r0 + 1024 + o0);
+        kq[h][3] = *reinterpret_cast<const uint4*>(r0 + 1024 + o1);
       }
       const int kl = pp * 32 + lane;
       int km = 0, ks = 0, vs = 0;
       unsigned vm = 0;
-      if (kl < my_keys) {   // this lane's key: its scales, read before the slot is handed back
+      if (kl < my_keys) {   // this lane's key: its scales
         const int32_t* mt = reinterpret_cast<const int32_t*>(slot0 + kSlotBytes + (lane >> 4) * kMetaBytes);
         const int tok = lane & 15;
         km = mt[tok];
@@ -341,7 +333,23 @@ attn_decode_kernel(const DecodeParams p) {
         vs = reinterpret_cast<const int8_t*>(mt + 36)[tok];
       }
       __syncwarp();
-      issue_k(it + kStages);     // the slot is free again: refill it before the scalar work
+      issue_k(it + kStages);     // the slot is free again
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        int c[4] = {0, 0, 0, 0};
+        if (2 * pp + h < my_pages) {   // (a page that was not copied leaves stale bytes in the registers: unused)
+          const uint4 k00 = kq[h][0], k01 = kq[h][1], k10 = kq[h][2], k11 = kq[h][3];
+          mma_s8s8(c, k00.x, k10.x, k00.y, k10.y, qw[0], qw[1]);
+          mma_s8s8(c, k00.z, k10.z, k00.w, k10.w, qw[2], qw[3]);
+          mma_s8s8(c, k01.x, k11.x, k01.y, k11.y, qw[4], qw[5]);
+          mma_s8s8(c, k01.z, k11.z, k01.w, k11.w, qw[6], qw[7]);
+        }
+        // c[0]: (key fr, head 2fc)  c[1]: (fr, 2fc+1)  c[2]: (fr + 8, 2fc)  c[3]: (fr + 8, 2fc+1)
+        const int kp = (2 * pp + h) * 16;
+        if (h0) { sc0[kp] = c[0]; sc0[kp + 8] = c[2]; }
+        if (h1) { sc1[kp] = c[1]; sc1[kp + 8] = c[3]; }
+      }
+      __syncwarp();              // the pair's raw dots are in place for the lane-per-key pass
       if (kl < my_keys) {
         if (vs < best_s || (vs == best_s && vm > best_m)) { best_s = vs; best_m = vm; }
 #pragma unroll
@@ -488,12 +496,23 @@ attn_decode_kernel(const DecodeParams p) {
       cp_async_wait<kStages - 1>();
       __syncwarp();
       const unsigned char* slot0 = ring + (it % kStages) * kRingSlot;
+      // V operands and this lane's key scales go to registers, then the slot is refilled at once
+      const unsigned char* slot = slot0 + lane * 16;
+      const bool has_b = 2 * pp + 1 < my_pages;
+      uint4 va[4], vb[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        va[i] = *reinterpret_cast<const uint4*>(slot + i * 512);
+        vb[i] = has_b ? *reinterpret_cast<const uint4*>(slot + 2048 + i * 512) : make_uint4(0, 0, 0, 0);
+      }
+      const int32_t* mt = reinterpret_cast<const int32_t*>(slot0 + kSlotBytes + (lane >> 4) * kMetaBytes);
+      const unsigned vm = (unsigned)mt[16 + (lane & 15)];
+      const int vs = reinterpret_cast<const int8_t*>(mt + 36)[lane & 15];
+      __syncwarp();
+      issue_v(it + kStages);
       {
         // this lane's key: relative V scale from the scale block that came with the codes
         // (stale bytes for a key past the end: its probability is 0, so is its weight)
-        const int32_t* mt = reinterpret_cast<const int32_t*>(slot0 + kSlotBytes + (lane >> 4) * kMetaBytes);
-        const unsigned vm = (unsigned)mt[16 + (lane & 15)];
-        const int vs = reinterpret_cast<const int8_t*>(mt + 36)[lane & 15];
         const unsigned r = kl < my_keys ? rel_scale_q15(vm, (unsigned)v_mul_ref, vs - v_shift_ref) : 0u;
 #pragma unroll
         for (int g = 0; g < G; ++g) {
@@ -503,14 +522,6 @@ attn_decode_kernel(const DecodeParams p) {
         }
       }
       __syncwarp();
-      const unsigned char* slot = slot0 + lane * 16;
-      const bool has_b = 2 * pp + 1 < my_pages;
-      uint4 va[4], vb[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        va[i] = *reinterpret_cast<const uint4*>(slot + i * 512);
-        vb[i] = has_b ? *reinterpret_cast<const uint4*>(slot + 2048 + i * 512) : make_uint4(0, 0, 0, 0);
-      }
       unsigned bh0 = 0, bh1 = 0, bl0 = 0, bl1 = 0;   // W^T: head fr, tokens 4 fc .. of page A / B
       if (fr < G) {
         bh0 = *reinterpret_cast<const unsigned*>(ph);
@@ -525,8 +536,7 @@ attn_decode_kernel(const DecodeParams p) {
         mma_s8u8(acc_hi[m], a0, a1, a2, a3, bh0, bh1);
         mma_s8u8(acc_lo[m], a0, a1, a2, a3, bl0, bl1);
       }
-      __syncwarp();
-      issue_v(it + kStages);
+      __syncwarp();              // the limb bytes are rewritten by the next pair
     }
     cp_async_wait<0>();
     // C tile: [0] (d = 16m + fr, head 2fc)  [1] (.., 2fc+1)  [2] (d + 8, 2fc)  [3] (d + 8, 2fc+1)

@@ -76,6 +76,16 @@ def argmax_int32(logits: torch.Tensor, index_offset: int = 0, return_values: boo
     return (idx, val) if return_values else idx
 
 
+def merge_sharded_argmax(values: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    """Global arg-max from per-shard results: ``values`` / ``indices`` int32 [shards, rows], the shards' local
+    maxima and their GLOBAL vocabulary ids.  The largest value wins, the lowest id among equal values - the
+    same token a single arg-max over the whole vocabulary picks."""
+    v64 = values.to(torch.int64)
+    best = v64.max(dim=0, keepdim=True).values
+    ids = torch.where(v64 == best, indices.to(torch.int64), torch.full_like(v64, 2**62))
+    return ids.min(dim=0).values.to(torch.int32)
+
+
 class DecodeBatch:
     """Device-resident state of a decode batch: page table, lengths and the per-step views derived from them.
 
@@ -109,8 +119,15 @@ class Qwen3ModelInteger:
     def __init__(self, cfg: Qwen3IntegerConfig, weights: dict, pool: Int8PagedKVCache,
                  comm: Optional[DistributedCommunicator] = None):
         """``weights``: "embed" bf16 [vocab, hidden]; "layers": list of per-layer dicts (see
-        Qwen3DecoderLayerInteger); "final_norm" int32 [hidden] (Q15.16)."""
+        Qwen3DecoderLayerInteger); "final_norm" int32 [hidden] (Q15.16).
+
+        Under tensor parallelism ``cfg`` carries this rank's head counts and intermediate size, the layer
+        weights are this rank's shards, and "embed" holds this rank's block of vocabulary rows starting at
+        ``weights["vocab_start"]`` (VocabParallelEmbedding, layers/embedding.py:14-42): ids of other ranks give
+        zero rows and the sum over ranks restores the embedding."""
         self.cfg, self.w, self.pool = cfg, weights, pool
+        self.comm = comm if comm is not None else DistributedCommunicator()
+        self.vocab_start = int(weights.get("vocab_start", 0))
         self.cache = rope_cache_q15(cfg.max_pos, cfg.rope_base, cfg.head_dim).to(pool.device)
         self.layers = [
             Qwen3DecoderLayerInteger(i, cfg.num_qo_heads, cfg.num_kv_heads, cfg.hidden, cfg.inter, weights["layers"][i],
@@ -120,7 +137,9 @@ class Qwen3ModelInteger:
 
     def forward(self, input_ids: torch.Tensor, batch: AttnBatch):
         """Returns the final norm's output as int8 codes [tokens, hidden] with the per-token absmax [tokens]."""
-        x = embedding_to_fixed(self.w["embed"], input_ids)
+        x = embedding_to_fixed(self.w["embed"], input_ids, self.vocab_start)
+        if self.comm.size > 1:
+            x = self.comm.all_reduce(x)
         residual = None
         for layer in self.layers:
             x, residual = layer.forward_q15(x, residual, batch)
@@ -131,8 +150,11 @@ class Qwen3ModelInteger:
 class Qwen3ForCausalLMInteger:
     def __init__(self, cfg: Qwen3IntegerConfig, weights: dict, pool: Int8PagedKVCache,
                  comm: Optional[DistributedCommunicator] = None):
-        """``weights`` additionally holds "lm_head": _Linear with int8 [vocab, hidden] and its channel scales."""
+        """``weights`` additionally holds "lm_head": _Linear with int8 [vocab, hidden] and its channel scales
+        (under tensor parallelism this rank's vocabulary rows, ParallelLMHead, layers/embedding.py:46-110)."""
         self.model = Qwen3ModelInteger(cfg, weights, pool, comm)
+        self.comm = self.model.comm
+        self.vocab_start = self.model.vocab_start
         self.lm_head = weights["lm_head"]
         self.method = W8A8Int8LinearMethod()
 
@@ -146,8 +168,16 @@ class Qwen3ForCausalLMInteger:
         return self.method.apply_quantised(self.lm_head, codes, absmax)
 
     def greedy(self, input_ids: torch.Tensor, batch: AttnBatch, last_indices: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Next token ids int32 [rows] (integer arg-max, lowest index on ties)."""
-        return argmax_int32(self.forward(input_ids, batch, last_indices))
+        """Next token ids int32 [rows] (integer arg-max, lowest index on ties).  With a sharded vocabulary every
+        rank takes the arg-max of its rows and the (value, id) pairs are merged - two tiny all-gathers instead
+        of the reference's all-gather of the full logits (layers/embedding.py:100-110)."""
+        logits = self.forward(input_ids, batch, last_indices)
+        if self.comm.size == 1:
+            return argmax_int32(logits)
+        idx, val = argmax_int32(logits, index_offset=self.vocab_start, return_values=True)
+        rows = idx.shape[0]
+        both = self.comm.all_gather(torch.stack((val, idx)).reshape(1, 2, rows))        # [ranks, 2, rows]
+        return merge_sharded_argmax(both[:, 0], both[:, 1])
 
 
 def random_weights(cfg: Qwen3IntegerConfig, seed: int, device="cuda", qk_norm: bool = True,

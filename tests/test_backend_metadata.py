@@ -61,3 +61,10 @@ def test_token_locations():
     row = torch.tensor([0, 0, 1, 1])
     want = [int(rows[0, 0]) * 16, int(rows[0, 0]) * 16 + 15, int(rows[1, 1]) * 16, int(rows[1, 2]) * 16 + 7]
     assert token_locations(rows, pos, row).tolist() == want
+
+
+def test_merge_sharded_argmax_prefers_value_then_lowest_id():
+    from mini_sgl_integer_b200.models import merge_sharded_argmax
+    vals = torch.tensor([[5, -7, 2**31 - 1, -2**31], [5, -3, 2**31 - 1, -2**31], [4, -3, 0, -2**31]], dtype=torch.int32)
+    ids = torch.tensor([[10, 11, 12, 13], [110, 111, 112, 113], [210, 211, 212, 213]], dtype=torch.int32)
+    assert merge_sharded_argmax(vals, ids).tolist() == [10, 111, 12, 13]

@@ -99,3 +99,81 @@ def test_two_gpu_layer_equals_one_gpu(tmp_path):
         z = np.load(tmp_path / f"r{r}.npz")
         assert np.array_equal(z["out"], want_out), f"rank {r}: layer output differs from one GPU"
         assert np.array_equal(z["resid"], want_res)
+
+
+# ---------------------------------------------------------------------------------------------- whole model
+M_L, M_HID, M_HQ, M_HK, M_INTER, M_VOCAB = 2, 256, 4, 2, 512, 1000
+
+
+def _model_case():
+    rng = np.random.default_rng(8)
+    prompt_lens = [7, 20]
+    table = rng.permutation(8).astype(np.int32).reshape(2, 4)
+    ids = rng.integers(0, M_VOCAB, sum(prompt_lens)).astype(np.int32)
+    positions = np.concatenate([np.arange(n) for n in prompt_lens]).astype(np.int32)
+    out_loc = np.concatenate([table[b][np.arange(n) // 16] * 16 + np.arange(n) % 16 for b, n in enumerate(prompt_lens)]).astype(np.int32)
+    return prompt_lens, table, ids, positions, out_loc
+
+
+def _run_model(rank, world, comm, steps=3):
+    """Prefill two prompts and decode `steps` tokens greedily; this rank's shard of every weight."""
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    from mini_sgl_integer_b200.distributed import shard_cols, shard_rows
+    from mini_sgl_integer_b200.layers.decoder_layer import AttnBatch, _Linear
+    from mini_sgl_integer_b200.models import DecodeBatch, Qwen3ForCausalLMInteger, Qwen3IntegerConfig, random_weights
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    full = Qwen3IntegerConfig(M_L, M_HID, M_HQ, M_HK, M_INTER, M_VOCAB, max_pos=128)
+    w = random_weights(full, seed=21)                          # the same full weights on every rank
+    hq, hk, inter, vs = M_HQ // world, M_HK // world, M_INTER // world, M_VOCAB // world
+    if world > 1:
+        def rows(l, idx):
+            return _Linear(l.weight[idx].contiguous(), weight_mul=l.weight_mul[idx].contiguous(), weight_shift=l.weight_shift[idx].contiguous())
+
+        def cols(l, per):
+            return _Linear(l.weight[:, rank * per:(rank + 1) * per].contiguous(), weight_mul=l.weight_mul, weight_shift=l.weight_shift)
+        ar = lambda a, b: torch.arange(a, b, device="cuda")
+        for lw in w["layers"]:
+            q0, k0, v0 = 0, M_HQ * 128, (M_HQ + M_HK) * 128
+            lw["qkv"] = rows(lw["qkv"], torch.cat([ar(q0 + rank * hq * 128, q0 + (rank + 1) * hq * 128),
+                                                   ar(k0 + rank * hk * 128, k0 + (rank + 1) * hk * 128),
+                                                   ar(v0 + rank * hk * 128, v0 + (rank + 1) * hk * 128)]))
+            lw["gate_up"] = rows(lw["gate_up"], torch.cat([ar(rank * inter, (rank + 1) * inter), M_INTER + ar(rank * inter, (rank + 1) * inter)]))
+            lw["o"], lw["down"] = cols(lw["o"], hq * 128), cols(lw["down"], inter)
+        w["embed"] = w["embed"][rank * vs:(rank + 1) * vs].contiguous()
+        w["lm_head"] = rows(w["lm_head"], ar(rank * vs, (rank + 1) * vs))
+        w["vocab_start"] = rank * vs
+    cfg = Qwen3IntegerConfig(M_L, M_HID, hq, hk, inter, M_VOCAB, max_pos=128)
+    prompt_lens, table, ids, positions, out_loc = _model_case()
+    pool = Int8PagedKVCache(hk, M_L, 128, 8, "cuda")
+    lm = Qwen3ForCausalLMInteger(cfg, w, pool, comm)
+    pl = d(np.asarray(prompt_lens, np.int32))
+    pre = AttnBatch(d(positions), d(out_loc), d(table), pl, pl, 64)
+    toks = [lm.greedy(d(ids), pre, d((np.cumsum(prompt_lens) - 1).astype(np.int32)))]
+    state = DecodeBatch(d(table), pl, 64)
+    for _ in range(steps):
+        toks.append(lm.greedy(toks[-1], state.advance()))
+    torch.cuda.synchronize()
+    return np.stack([t.cpu().numpy() for t in toks])
+
+
+def _model_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from mini_sgl_integer_b200.distributed import DistributedCommunicator
+    toks = _run_model(rank, world, DistributedCommunicator())
+    np.save(os.path.join(out_dir, f"m{rank}.npy"), toks)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_model_tokens_equal_one_gpu(tmp_path):
+    """Vocabulary-parallel embedding and lm_head, head / column / row split layers: same greedy tokens as one GPU."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    want = _run_model(0, 1, None)
+    mp.spawn(_model_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        assert np.array_equal(np.load(tmp_path / f"m{r}.npy"), want), f"rank {r}: tokens differ from one GPU"
