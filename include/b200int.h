@@ -237,6 +237,12 @@ B200_API int b200_decode_prepare(const int32_t* page_table, int64_t table_pitch,
                                  int32_t* positions, int32_t* out_loc, int32_t* kv_lens, int batch, int max_len,
                                  b200_stream_t s);
 
+/* ---- Static activation quantisation for checkpoints that carry an `input_scale`:
+ * codes = clamp(rint((fp32(x) / 65536) / input_scale), -128, 127) in fp32 with IEEE division, i.e.
+ * per_tensor_quant_int8_static (layers/quantization/w8a8_int8.py:75-92) applied to from_fixed(x) as in
+ * apply_weights_q15 (:251-254).  x int32 [n] (Q15.16), n % 4 == 0. */
+B200_API int b200_static_quant_q15(const int32_t* x, float input_scale, int8_t* codes, int64_t n, b200_stream_t s);
+
 /* ---- W8A8 linear: int8 x int8 -> int32 on the tcgen05 tensor cores, fixed-point requant.
  * Stands in for the GEMM + epilogue inside W8A8Int8LinearMethod.apply_weights_q15
  * (layers/quantization/w8a8_int8.py:242-286), i.e. the sgl_kernel.int8_scaled_mm call at :272-279

@@ -197,6 +197,21 @@ __global__ void quant_given_absmax_kernel(const int32_t* __restrict__ x, const i
   }
 }
 
+// Static per-tensor quantisation (per_tensor_quant_int8_static on from_fixed(x), w8a8_int8.py:75-92, :251-254):
+// code = clamp(rint((fp32(x) / 65536) / scale)), fp32 arithmetic with IEEE division.
+__global__ void static_quant_kernel(const int32_t* __restrict__ x, float scale, int8_t* __restrict__ codes, int64_t n4) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    const int4 v = reinterpret_cast<const int4*>(x)[i];
+    int c[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float q = __fdiv_rn(__fdiv_rn(__int2float_rn(c[j]), 65536.0f), scale);
+      c[j] = max(-128, min(127, __float2int_rn(q)));
+    }
+    reinterpret_cast<unsigned*>(codes)[i] = pack4(c[0], c[1], c[2], c[3]);
+  }
+}
+
 // The GEMM's fixed-point epilogue on its own: out = sat32(mul_shift(acc, (x_mul*w_mul)>>32, x_shift+w_shift-48)).
 // acc and out may be the same buffer (each element is read, then written, by one thread).
 __global__ void requant_kernel(const int32_t* acc, const int32_t* __restrict__ x_mul,
@@ -817,4 +832,15 @@ extern "C" int b200_requant_q15(const int32_t* acc, const int32_t* x_mul, const 
   if (m == 0) return B200_OK;
   requant_kernel<<<elementwise_grid(m * n, 256), 256, 0, (cudaStream_t)s>>>(acc, x_mul, x_shift, w_mul, w_shift, out, m, (int)n);
   return check_launch("requant_q15");
+}
+
+extern "C" int b200_static_quant_q15(const int32_t* x, float input_scale, int8_t* codes, int64_t n, b200_stream_t s) {
+  B200_REQUIRE(n >= 0 && n % 4 == 0, B200_E_SHAPE, "static_quant_q15: n=%lld must be a multiple of 4", (long long)n);
+  B200_REQUIRE(input_scale > 0.0f, B200_E_SHAPE, "static_quant_q15: input_scale must be positive");
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(x && codes, B200_E_NULL, "static_quant_q15: null pointer");
+  B200_REQUIRE(aligned16(x) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN, "static_quant_q15: x must be 16-byte and codes 4-byte aligned");
+  const float scale = input_scale < 1e-10f ? 1e-10f : input_scale;
+  static_quant_kernel<<<elementwise_grid(n / 4, 256), 256, 0, (cudaStream_t)s>>>(x, scale, codes, n / 4);
+  return check_launch("static_quant_q15");
 }

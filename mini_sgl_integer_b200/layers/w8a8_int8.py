@@ -22,7 +22,26 @@ import torch
 from .._lib import call, ptr, require_cuda, stream
 from ..kernel.fixed_point import absmax_to_mul_shift, assert_q15, per_token_quant_int8_from_q15
 
-__all__ = ["W8A8Int8LinearMethod", "int8_gemm_q15", "weight_scale_to_mul_shift", "per_token_quant_int8_from_q15"]
+__all__ = ["W8A8Int8LinearMethod", "int8_gemm_q15", "weight_scale_to_mul_shift", "per_token_quant_int8_from_q15",
+           "per_tensor_quant_int8_static_from_q15"]
+
+
+def per_tensor_quant_int8_static_from_q15(x_q15: torch.Tensor, input_scale: torch.Tensor | float) -> torch.Tensor:
+    """int8 codes of a Q15.16 tensor under a checkpoint-provided per-tensor ``input_scale``: what
+    per_tensor_quant_int8_static gives on from_fixed(x) (layers/quantization/w8a8_int8.py:75-92, :251-254);
+    a multi-element scale is reduced to its maximum like the reference (:82-83)."""
+    assert_q15(x_q15, "x_q15")
+    require_cuda(x_q15)
+    scale = float(input_scale.max()) if isinstance(input_scale, torch.Tensor) else float(input_scale)
+    if not scale > 0:
+        raise ValueError(f"input_scale must be positive, got {scale}")
+    x = x_q15.contiguous()
+    if x.numel() % 4:
+        raise ValueError("the number of elements must be a multiple of 4")
+    codes = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    if x.numel():
+        call("b200_static_quant_q15", ptr(x), scale, ptr(codes), x.numel(), stream())
+    return codes
 
 
 def weight_scale_to_mul_shift(weight_scale: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -96,12 +115,23 @@ class W8A8Int8LinearMethod:
     def apply_weights_q15(self, layer, x_q15: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Q15.16 int32 [..., K] -> Q15.16 int32 [..., N] (:242-286)."""
         assert_q15(x_q15, "x_q15")
-        if getattr(layer, "input_scale", None) is not None and layer.input_scale.numel() > 0:
-            raise NotImplementedError("static input_scale checkpoints are not supported by the integer epilogue yet")
         if getattr(layer, "weight_mul", None) is None:
             self.process_weights_after_loading(layer)
         lead = x_q15.shape[:-1]
         x2 = x_q15.reshape(-1, x_q15.shape[-1])
+        static = getattr(layer, "input_scale", None)
+        if isinstance(static, torch.Tensor) and static.numel() > 0:
+            # static per-tensor activation scale (:95-101, :251-254): same codes as the reference, and the
+            # scale enters the fixed-point epilogue as one (multiplier, shift) for every token
+            if getattr(layer, "input_mul", None) is None:
+                layer.input_mul, layer.input_shift = weight_scale_to_mul_shift(static.max().reshape(1).to(torch.float32))
+            codes = per_tensor_quant_int8_static_from_q15(x2, static)
+            rows = x2.shape[0]
+            out = int8_gemm_q15(codes, layer.input_mul.expand(rows), layer.input_shift.expand(rows), layer.weight,
+                                layer.weight_mul, layer.weight_shift)
+            if bias is not None:
+                out = self._add_bias(out, bias)
+            return out.reshape(*lead, -1)
         codes, _scale, absmax = per_token_quant_int8_from_q15(x2, return_absmax=True)
         return self.apply_quantised(layer, codes, absmax, bias).reshape(*lead, -1)
 
@@ -113,7 +143,11 @@ class W8A8Int8LinearMethod:
         out = int8_gemm_q15(codes.reshape(-1, codes.shape[-1]), None, None, layer.weight, layer.weight_mul,
                             layer.weight_shift, x_absmax=absmax.reshape(-1))
         if bias is not None:
-            b = bias if bias.dtype == torch.int32 else torch.clamp(
-                torch.round(bias.to(torch.float32) * 65536.0), -(2 ** 31), 2 ** 31 - 1).to(torch.int32)
-            out = torch.clamp(out.to(torch.int64) + b.to(torch.int64), -(2 ** 31), 2 ** 31 - 1).to(torch.int32)
+            out = self._add_bias(out, bias)
         return out
+
+    @staticmethod
+    def _add_bias(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+        b = bias if bias.dtype == torch.int32 else torch.clamp(
+            torch.round(bias.to(torch.float32) * 65536.0), -(2 ** 31), 2 ** 31 - 1).to(torch.int32)
+        return torch.clamp(out.to(torch.int64) + b.to(torch.int64), -(2 ** 31), 2 ** 31 - 1).to(torch.int32)

@@ -266,3 +266,13 @@ def per_token_quant_from_q15(x: np.ndarray):
     scale = m.astype(np.float32) / np.float32(127.0 * float(FIXED_POINT_SCALE))
     lead = x.shape[:-1] + (1,)
     return q.reshape(x.shape), scale.reshape(lead), m.reshape(lead)
+
+
+def static_quant_from_q15(x: np.ndarray, input_scale: float) -> np.ndarray:
+    """Static per-tensor int8 codes of a Q15.16 tensor: from_fixed (fp32(x) / 65536), divided by the checkpoint's
+    fp32 ``input_scale``, rounded half to even, clamped (per_tensor_quant_int8_static, w8a8_int8.py:75-92, on the
+    from_fixed value of apply_weights_q15, :251-254).  All arithmetic in fp32."""
+    scale = np.maximum(np.float32(input_scale), np.float32(1e-10))
+    xf = x.astype(np.float32) / np.float32(65536.0)
+    q = np.rint((xf / scale).astype(np.float32))
+    return np.clip(q, -128, 127).astype(np.int8)

@@ -52,7 +52,7 @@ def main() -> None:
     from minisgl.kernel.triton.int8_attention_kernels import (
         _exp2_lut_i32, int8_context_attention_fwd, quantize_per_tensor_int8_ms,
     )
-    from minisgl.layers.quantization.w8a8_int8 import per_token_quant_int8_from_q15
+    from minisgl.layers.quantization.w8a8_int8 import per_tensor_quant_int8_static, per_token_quant_int8_from_q15
     from minisgl.layers.rotary_integer import RotaryEmbeddingInteger
     from minisgl.models.utils_integer import apply_blockwise_fwht_q15
 
@@ -212,6 +212,14 @@ def main() -> None:
     k8, kmul, ksh = quantize_per_tensor_int8_ms(kq)
     put("ptq_in_bf16_bits", kq.view(torch.int16)); put("ptq_codes", k8)
     put("ptq_ms", np.array([int(kmul), int(ksh)], dtype=np.int64))
+
+    # static (checkpoint-provided) input scale: from_fixed(x) / scale, rounded and clamped (w8a8_int8.py:75-92, :251-254)
+    sq = rj(-(2**20), 2**20, (6, 384))
+    sq[0, :6] = torch.tensor([0, 1, -1, 2**31 - 1, -(2**31), 32768], dtype=torch.int32)
+    for i, scale in enumerate((0.013671875, 0.05, 1e-3)):
+        c8, sc = per_tensor_quant_int8_static(from_fixed(sq, torch.float32), torch.tensor([scale], dtype=torch.float32))
+        put(f"static_codes_{i}", c8)
+    put("static_in", sq); put("static_scales", np.array([0.013671875, 0.05, 1e-3], dtype=np.float32))
 
     np.savez_compressed(os.path.join(HERE, "ref_vectors.npz"), **vec)
     with open(os.path.join(HERE, "ref_hashes.json"), "w") as fjs:

@@ -148,3 +148,32 @@ def test_gemm_empty_and_bad_k():
     with pytest.raises(_lib.B200Error, match="multiple of 16"):
         int8_gemm_q15(torch.zeros((4, 24), dtype=torch.int8, device="cuda"), None, None,
                       torch.zeros((8, 24), dtype=torch.int8, device="cuda"), None, want_q15=False, want_acc=True)
+
+
+def test_static_input_scale_path(golden):
+    """Checkpoints with an `input_scale`: the reference's static codes, then the GEMM with one token scale."""
+    from mini_sgl_integer_b200.layers import W8A8Int8LinearMethod
+    from mini_sgl_integer_b200.layers.w8a8_int8 import per_tensor_quant_int8_static_from_q15, weight_scale_to_mul_shift
+    x = golden["static_in"]
+    for i, scale in enumerate(golden["static_scales"]):
+        got = per_tensor_quant_int8_static_from_q15(d(x), torch.tensor([scale], dtype=torch.float32).cuda())
+        np.testing.assert_array_equal(got.cpu().numpy(), golden[f"static_codes_{i}"])
+    rng = np.random.default_rng(12)
+    N, K = 256, x.shape[1]
+    layer = torch.nn.Module()
+    layer.weight = d(rng.integers(-127, 128, (N, K), dtype=np.int8))
+    layer.weight_scale = d(rng.uniform(1e-3, 3e-2, (N, 1)).astype(np.float32))
+    layer.input_scale = torch.tensor([0.05], dtype=torch.float32).cuda()
+    out = W8A8Int8LinearMethod().apply_weights_q15(layer, d(x))
+    torch.cuda.synchronize()
+    assert gemm_status() == 0
+    codes = ofp.static_quant_from_q15(x, np.float32(0.05))
+    w_mul, w_shift = olin.weight_scale_to_mul_shift(layer.weight_scale.cpu().numpy().reshape(-1))
+    x_mul, x_shift = olin.weight_scale_to_mul_shift(np.array([0.05], dtype=np.float32))
+    want = olin.requant_q15(olin.int32_accumulate(codes, layer.weight.cpu().numpy()), np.repeat(x_mul, x.shape[0]),
+                            np.repeat(x_shift, x.shape[0]), w_mul, w_shift)
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+    # sanity against the float formula of the reference's fallback (w8a8_int8.py:280-284)
+    ref = (codes.astype(np.float64) * 0.05) @ (layer.weight.cpu().numpy().astype(np.float64) * layer.weight_scale.cpu().numpy().astype(np.float64)).T
+    err = np.abs(out.cpu().numpy() / 65536.0 - ref).max()
+    assert err < 2e-3 * max(1.0, np.abs(ref).max()), err

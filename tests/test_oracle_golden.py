@@ -191,3 +191,10 @@ def test_error_behaviour_mirrors_reference():
         ofp.rmsnorm_v2(np.zeros((2, 100), dtype=np.int32), np.ones(64, dtype=np.int32))
     with pytest.raises(ValueError):
         ofp.blockwise_fwht_q15(np.zeros((2, 100), dtype=np.int32), 64)
+
+
+def test_static_input_scale_quant_matches_reference(golden):
+    """per_tensor_quant_int8_static on from_fixed(x) for three checkpoint scales, incl. the int32 extremes."""
+    x = golden["static_in"]
+    for i, scale in enumerate(golden["static_scales"]):
+        np.testing.assert_array_equal(ofp.static_quant_from_q15(x, scale), golden[f"static_codes_{i}"])
