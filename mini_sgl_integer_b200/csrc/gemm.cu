@@ -385,6 +385,201 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
+// ----------------------------------------------------------------------------- two-CTA tiles
+// Large M: a pair of CTAs (a cluster of two, on neighbouring SMs) computes one 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 token rows of x and only HALF of the tile's weight
+// rows (128 of 256), so the shared-memory traffic per MMA drops by a third against two independent
+// 128 x 256 tiles - on one CTA the operand reads of an N = 256 MMA alone take three quarters of the
+// shared-memory bandwidth.  Protocol (one elected thread each):
+//   both CTAs    TMA warp: waits for its own "empty" barrier, loads its A and B halves; the bytes of both
+//                CTAs are counted on the LEADER's "full" barrier (barrier address with the peer bit cleared)
+//   leader CTA   MMA warp: waits for "full", issues four MMAs per k-block, commits to the "empty" barriers
+//                of both CTAs (multicast commit), and after the last k-block to both "accumulator full" barriers
+//   both CTAs    epilogue warps drain their own 128 rows of the accumulator from their own tensor memory and
+//                arrive on the leader's "accumulator empty" barrier
+// Every wait is bounded as in the one-CTA kernel; both CTAs meet at a cluster barrier before tensor memory is freed.
+constexpr unsigned kPeerBitMask = 0xFEFFFFFFu;   // shared::cluster address of the same offset in the pair's even CTA
+
+__device__ __forceinline__ void tma_load_2d_2sm(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void umma_i8_2sm(unsigned tmem_d, uint64_t desc_a, uint64_t desc_b, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(unsigned bar) {   // arrives on `bar` in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(unsigned bar) {    // arrive on the leader CTA's barrier at this offset
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kPeerBitMask) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.aligned;\nbarrier.cluster.wait.aligned;" ::: "memory");
+}
+
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const GemmParams p) {
+  constexpr int BN = 256;                      // tile columns of the pair; each CTA stages BN / 2 weight rows
+  constexpr int kABytes = kBM * kBK;           // 128 token rows
+  constexpr int kBBytes = (BN / 2) * kBK;      // 128 weight rows
+  constexpr int kStageBytes = kABytes + kBBytes;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * kStageBytes);   // full[S], empty[S], tfull[2], tempty[2]
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 4);
+  int32_t* col_scale = reinterpret_cast<int32_t*>(tmem_slot + 4);               // [2 slots][mul BN | shift BN]
+  int32_t* stage_all = col_scale + 4 * BN;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+  const int m_tiles = (p.M + 2 * kBM - 1) / (2 * kBM), n_tiles = (p.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const unsigned tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);             // the leader's expect-tx arrival (bytes of both CTAs)
+      mbar_init(empty0 + 8 * s, 1);            // one multicast commit
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull0 + 8 * s, 1);
+      mbar_init(tempty0 + 8 * s, 2 * kEpiWarps);   // the epilogue warps of both CTAs (used on the leader only)
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // one warp of each CTA, same warp index: the pair's allocation (all 512 columns: 2 x BN)
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_barrier();       // the peer's barriers exist before anything is signalled across the pair
+  tcgen05_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      unsigned it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int n_blk = tile / m_tiles, m_blk = tile - n_blk * m_tiles;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
+          ok = mbar_wait(empty0 + 8 * s, ph ^ 1, 1);
+          if (!ok) break;
+          if (leader) mbar_expect_tx(full0 + 8 * s, 2 * kStageBytes);
+          const unsigned a_dst = smem_u32(tiles + s * kStageBytes);
+          const unsigned lbar = (full0 + 8 * s) & kPeerBitMask;
+          tma_load_2d_2sm(a_dst, &map_a, kb * kBK, m_blk * 2 * kBM + (int)rank * kBM, lbar);
+          tma_load_2d_2sm(a_dst + kABytes, &map_b, kb * kBK, n_blk * BN + (int)rank * (BN / 2), lbar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr unsigned idesc = make_idesc(2 * kBM, BN);
+      unsigned it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++lt) {
+        const unsigned slot = lt & 1, aph = (lt >> 1) & 1;
+        ok = mbar_wait(tempty0 + 8 * slot, aph ^ 1, 4);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const unsigned tmem_d = tmem_base + slot * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
+          ok = mbar_wait(full0 + 8 * s, ph, 2);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const unsigned a_addr = smem_u32(tiles + s * kStageBytes);
+          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_i8_2sm(tmem_d, da + (uint64_t)(k * kUmmaK >> 4), db + (uint64_t)(k * kUmmaK >> 4), idesc,
+                        (kb > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit_pair(empty0 + 8 * s);
+        }
+        tcgen05_commit_pair(tfull0 + 8 * slot);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int et = threadIdx.x - 64;
+    int32_t* stage = stage_all + (warp - 2) * (32 * kStagePitch);
+    unsigned lt = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++lt) {
+      const int n_blk = tile / m_tiles, m_blk = tile - n_blk * m_tiles;
+      const unsigned slot = lt & 1, aph = (lt >> 1) & 1;
+      const int r_base = m_blk * 2 * kBM + (int)rank * kBM + q * 32;
+      const int row = r_base + lane;
+      int32_t* cs = col_scale + slot * 2 * BN;
+      if (p.out_q15) {
+        for (int c = et; c < BN; c += 32 * kEpiWarps) {
+          const int col = min(n_blk * BN + c, p.N - 1);
+          cs[c] = __ldg(p.w_mul + col);
+          cs[BN + c] = (p.w_shift ? __ldg(p.w_shift + col) : 31) - 48;
+        }
+      }
+      int xm = 0, xs = 0;
+      if (row < p.M && p.out_q15) {
+        if (p.x_absmax) absmax_to_ms_dev(__ldg(p.x_absmax + row), &xm, &xs);
+        else { xm = __ldg(p.x_mul + row); xs = __ldg(p.x_shift + row); }
+      }
+      epilogue_bar_sync();
+      if (ok) ok = mbar_wait(tfull0 + 8 * slot, aph, 3);
+      tcgen05_fence_after();
+#pragma unroll 1
+      for (int c0 = half * 32; c0 < BN; c0 += 64) {
+        int v[32];
+        tmem_ld_32x32(tmem_base + ((unsigned)(q * 32) << 16) + slot * BN + (unsigned)c0, v);
+        const int col0 = n_blk * BN + c0;
+        if (!ok || col0 >= p.N) continue;
+        const bool vec = (p.N & 3) == 0;
+        if (p.acc_out) store_chunk(stage, lane, v, p.acc_out, r_base, col0, p.M, p.N, vec);
+        if (p.out_q15) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const int4 wm = *reinterpret_cast<const int4*>(cs + c0 + j);
+            const int4 ws = *reinterpret_cast<const int4*>(cs + BN + c0 + j);
+            v[j + 0] = requant_one(v[j + 0], __mulhi(xm, wm.x), xs + ws.x);
+            v[j + 1] = requant_one(v[j + 1], __mulhi(xm, wm.y), xs + ws.y);
+            v[j + 2] = requant_one(v[j + 2], __mulhi(xm, wm.z), xs + ws.z);
+            v[j + 3] = requant_one(v[j + 3], __mulhi(xm, wm.w), xs + ws.w);
+          }
+          store_chunk(stage, lane, v, p.out_q15, r_base, col0, p.M, p.N, vec);
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(tempty0 + 8 * slot);
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_barrier();       // the leader's MMAs read the peer's shared memory and write its tensor memory until here
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+  }
+}
+
 // The epilogue on its own, for the split-K parts gathered in `partial` ([M, N] int32; may be `out` itself):
 // four consecutive channels of one token per thread.
 __global__ void __launch_bounds__(256)
@@ -470,6 +665,22 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   return check_launch("gemm_w8a8");
 }
 
+template <int STAGES>
+static int launch_gemm_2sm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
+  constexpr int BN = 256;
+  constexpr size_t smem = (size_t)STAGES * (kBM * kBK + (BN / 2) * kBK) + 1024 + (2 * STAGES + 4) * 8 + 16 + 4 * BN * 4 + kEpiWarps * 32 * kStagePitch * 4;
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  cudaError_t e = cudaFuncSetAttribute(gemm_w8a8_2sm_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_error("gemm_w8a8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    return B200_E_CUDA;
+  }
+  const int tiles = ((p.N + BN - 1) / BN) * ((p.M + 2 * kBM - 1) / (2 * kBM));
+  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  gemm_w8a8_2sm_kernel<STAGES><<<2 * pairs, kGemmThreads, smem, st>>>(ma, mb, p);
+  return check_launch("gemm_w8a8 (two-CTA tiles)");
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -524,6 +735,11 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
     return check_launch("gemm_w8a8 (split-K epilogue)");
   }
   B200_REQUIRE(make_map(&ma, x8, m, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");
+  // large problems: 256 x 256 tiles on CTA pairs, when there are enough of them to occupy every pair
+  if (((m + 2 * kBM - 1) / (2 * kBM)) * ((n + 255) / 256) >= sm_count() / 2) {
+    B200_REQUIRE(make_map(&mb, w8, n, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for w8");
+    return launch_gemm_2sm<6>(ma, mb, p, st);
+  }
   // tile width: wide tiles for throughput at large M; narrow ones at decode sizes so that enough CTAs
   // stream the weights (one m block there, so the tile count is n / BN)
   const int64_t m_tiles = (m + kBM - 1) / kBM;

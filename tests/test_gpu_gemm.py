@@ -92,6 +92,13 @@ def test_token_scale_from_absmax(M, N, K):
     np.testing.assert_array_equal(out.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("M,N,K", [(2304, 2304, 256), (2050, 2400, 1040), (4096, 1280, 2048)])
+def test_two_cta_tiles(M, N, K):
+    """Problems with at least one 256 x 256 tile per CTA pair run on tcgen05.mma.cta_group::2 (ragged edges,
+    k-blocks that wrap the stage ring several times)."""
+    run_case(M, N, K, M + N + K, per_channel_shift=True)
+
+
 def test_gemm_per_channel_shifts_and_deep_k():
     run_case(96, 256, 12288, 7, per_channel_shift=True)
 
