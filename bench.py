@@ -46,6 +46,14 @@ def draw_lens(seed: int) -> np.ndarray:
     return np.random.default_rng(seed).integers(WORKLOAD["ctx_lo"], WORKLOAD["ctx_hi"] + 1, WORKLOAD["batch"])
 
 
+def row_order_hint(lens: np.ndarray, scheme: str) -> np.ndarray:
+    """The order in which the decode kernel should take the batch rows (a permutation, int32): longest first
+    ("lpt", what a scheduler that knows the lengths passes) or as given ("identity")."""
+    if scheme == "identity":
+        return np.arange(len(lens), dtype=np.int32)
+    return np.argsort(-lens, kind="stable").astype(np.int32)
+
+
 def algorithmic_bytes(lens: np.ndarray) -> int:
     """Minimum HBM traffic of one launch: K and V codes, their scales, page ids, q in, int8 out."""
     w = WORKLOAD
@@ -211,7 +219,7 @@ def run_ours(args) -> None:
     h_table = torch.from_numpy(table_np).pin_memory()
     h_lens = torch.from_numpy(lens_np.astype(np.int32)).pin_memory()
     # the batch rows by descending length: a scheduling hint that whoever builds the batch can give (part of the inputs)
-    h_order = torch.from_numpy(np.argsort(-lens_np, kind="stable").astype(np.int32)).pin_memory()
+    h_order = torch.from_numpy(row_order_hint(lens_np, args.row_order)).pin_memory()
     h_out = torch.empty((B, Hq, D), dtype=torch.int8).pin_memory()
     h_absmax = torch.empty((B, Hq), dtype=torch.int32).pin_memory()
     d_q, d_qm, d_qs, d_table, d_lens, d_order = (t.to(dev) for t in (h_q, h_qm, h_qs, h_table, h_lens, h_order))
@@ -598,6 +606,8 @@ def main() -> None:
     ap.add_argument("--cluster", type=int, default=0, help="CTAs per (sequence, KV head); 0 = library default")
     ap.add_argument("--attn-impl", default="cluster", choices=["split", "cluster"],
                     help="split = grid-wide passes over a workspace (5 launches per step); cluster = one kernel per step")
+    ap.add_argument("--row-order", default="lpt", choices=["lpt", "identity"],
+                    help="scheduling hint passed to the decode kernel (see row_order_hint)")
     ap.add_argument("--pool-pages", type=int, default=WORKLOAD["pool_pages"],
                     help="pages in the KV pool (smaller pools are for profiler captures only)")
     ap.add_argument("--sustain-s", type=float, default=1.0,
