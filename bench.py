@@ -467,10 +467,26 @@ def run_tp_layer(args) -> None:
                       d(np.argsort(-lens, kind="stable").astype(np.int32)))
     x = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
     res = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
-    step = lambda: layer.forward_q15(x, res, batch)
+    eager = lambda: layer.forward_q15(x, res, batch)
     for _ in range(max(args.warmup, 3)):
-        step()
+        eager()
     torch.cuda.synchronize()
+    step = eager
+    if args.graph and world == 1:
+        # the layer step replayed from one CUDA graph, as the engine's decode does (single rank only: capturing
+        # the NCCL collectives of a multi-rank step did not complete on this pool and stays off)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            eager()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            eager()
+        step = graph.replay
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -493,7 +509,7 @@ def run_tp_layer(args) -> None:
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": "one Qwen3-32B-shaped decoder layer, decode batch %d, ctx U[1024,8192], TP=%d" % (B, world),
-                       "per_gpu_tok_s": B / (LAYERS * ms * 1e-3) / world, "eager_launches": True},
+                       "per_gpu_tok_s": B / (LAYERS * ms * 1e-3) / world, "cuda_graph": bool(args.graph and world == 1)},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
                          "peak_source": how, "bytes_per_rank": w_bytes + kv_bytes},
         }))
@@ -618,6 +634,7 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=4096, help="M for --workload gemm")
     ap.add_argument("--tp-batch", type=int, default=256, help="decode batch for --workload tp_layer / model")
     ap.add_argument("--model-layers", type=int, default=36, help="layers for --workload model")
+    ap.add_argument("--graph", action="store_true", help="tp_layer on one GPU: replay the layer step from a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
