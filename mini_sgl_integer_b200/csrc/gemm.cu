@@ -395,8 +395,9 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 //                CTAs are counted on the LEADER's "full" barrier (barrier address with the peer bit cleared)
 //   leader CTA   MMA warp: waits for "full", issues four MMAs per k-block, commits to the "empty" barriers
 //                of both CTAs (multicast commit), and after the last k-block to both "accumulator full" barriers
-//   both CTAs    epilogue warps drain their own 128 rows of the accumulator from their own tensor memory and
-//                arrive on the leader's "accumulator empty" barrier
+//   both CTAs    sixteen epilogue warps drain their own 128 rows of the accumulator from their own tensor memory
+//                and arrive on the leader's "accumulator empty" barrier (the requant is about a dozen integer
+//                instructions per output: with eight warps the epilogue of a tile outlasted its MMAs)
 // Every wait is bounded as in the one-CTA kernel; both CTAs meet at a cluster barrier before tensor memory is freed.
 constexpr unsigned kPeerBitMask = 0xFEFFFFFFu;   // shared::cluster address of the same offset in the pair's even CTA
 
@@ -425,8 +426,11 @@ __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.aligned;\nbarrier.cluster.wait.aligned;" ::: "memory");
 }
 
+constexpr int kEpiWarps2 = 16;        // the two-CTA kernel: four per 32-lane quarter, a quarter of the columns each
+constexpr int kGemmThreads2 = 64 + 32 * kEpiWarps2;
+
 template <int STAGES>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads2, 1)
 gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const GemmParams p) {
   constexpr int BN = 256;                      // tile columns of the pair; each CTA stages BN / 2 weight rows
@@ -458,7 +462,7 @@ gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(tfull0 + 8 * s, 1);
-      mbar_init(tempty0 + 8 * s, 2 * kEpiWarps);   // the epilogue warps of both CTAs (used on the leader only)
+      mbar_init(tempty0 + 8 * s, 2 * kEpiWarps2);  // the epilogue warps of both CTAs (used on the leader only)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -519,7 +523,7 @@ gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     }
   } else {
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;          // which of the interleaved 32-column chunks this warp takes
     const int et = threadIdx.x - 64;
     int32_t* stage = stage_all + (warp - 2) * (32 * kStagePitch);
     unsigned lt = 0;
@@ -531,7 +535,7 @@ gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const int row = r_base + lane;
       int32_t* cs = col_scale + slot * 2 * BN;
       if (p.out_q15) {
-        for (int c = et; c < BN; c += 32 * kEpiWarps) {
+        for (int c = et; c < BN; c += 32 * kEpiWarps2) {
           const int col = min(n_blk * BN + c, p.N - 1);
           cs[c] = __ldg(p.w_mul + col);
           cs[BN + c] = (p.w_shift ? __ldg(p.w_shift + col) : 31) - 48;
@@ -542,11 +546,11 @@ gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (p.x_absmax) absmax_to_ms_dev(__ldg(p.x_absmax + row), &xm, &xs);
         else { xm = __ldg(p.x_mul + row); xs = __ldg(p.x_shift + row); }
       }
-      epilogue_bar_sync();
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps2) : "memory");
       if (ok) ok = mbar_wait(tfull0 + 8 * slot, aph, 3);
       tcgen05_fence_after();
 #pragma unroll 1
-      for (int c0 = half * 32; c0 < BN; c0 += 64) {
+      for (int c0 = part * 32; c0 < BN; c0 += 32 * (kEpiWarps2 / 4)) {
         int v[32];
         tmem_ld_32x32(tmem_base + ((unsigned)(q * 32) << 16) + slot * BN + (unsigned)c0, v);
         const int col0 = n_blk * BN + c0;
@@ -668,7 +672,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
 template <int STAGES>
 static int launch_gemm_2sm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t st) {
   constexpr int BN = 256;
-  constexpr size_t smem = (size_t)STAGES * (kBM * kBK + (BN / 2) * kBK) + 1024 + (2 * STAGES + 4) * 8 + 16 + 4 * BN * 4 + kEpiWarps * 32 * kStagePitch * 4;
+  constexpr size_t smem = (size_t)STAGES * (kBM * kBK + (BN / 2) * kBK) + 1024 + (2 * STAGES + 4) * 8 + 16 + 4 * BN * 4 + kEpiWarps2 * 32 * kStagePitch * 4;
   static_assert(smem <= 227 * 1024, "shared memory budget");
   cudaError_t e = cudaFuncSetAttribute(gemm_w8a8_2sm_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
@@ -677,7 +681,7 @@ static int launch_gemm_2sm(const CUtensorMap& ma, const CUtensorMap& mb, const G
   }
   const int tiles = ((p.N + BN - 1) / BN) * ((p.M + 2 * kBM - 1) / (2 * kBM));
   const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-  gemm_w8a8_2sm_kernel<STAGES><<<2 * pairs, kGemmThreads, smem, st>>>(ma, mb, p);
+  gemm_w8a8_2sm_kernel<STAGES><<<2 * pairs, kGemmThreads2, smem, st>>>(ma, mb, p);
   return check_launch("gemm_w8a8 (two-CTA tiles)");
 }
 
@@ -738,7 +742,7 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
   // large problems: 256 x 256 tiles on CTA pairs, when there are enough of them to occupy every pair
   if (((m + 2 * kBM - 1) / (2 * kBM)) * ((n + 255) / 256) >= sm_count() / 2) {
     B200_REQUIRE(make_map(&mb, w8, n, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for w8");
-    return launch_gemm_2sm<6>(ma, mb, p, st);
+    return launch_gemm_2sm<5>(ma, mb, p, st);
   }
   // tile width: wide tiles for throughput at large M; narrow ones at decode sizes so that enough CTAs
   // stream the weights (one m block there, so the tile count is n / BN)
