@@ -39,7 +39,7 @@ WORKLOAD = dict(batch=64, q_heads=32, kv_heads=8, head_dim=128, page=16, ctx_lo=
 METRIC = "int8 paged decode attention throughput (decode tokens/s; HBM GB/s in roofline)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
 # profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES = None
+NCU_TRAFFIC_BYTES = 334636800   # dram__bytes_read + dram__bytes_write of one launch (ncu capture of this kernel)
 
 
 def draw_lens(seed: int) -> np.ndarray:
