@@ -462,7 +462,11 @@ def run_tp_layer(args) -> None:
     cache = torch.clamp(torch.round(torch.cat((fr.cos(), fr.sin()), -1) * 32768), -32768, 32767).to(torch.int32).to(dev)
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
     comm = DistributedCommunicator()
-    layer = Qwen3DecoderLayerInteger(0, hq, hk, HID, inter, weights, cache, pool, comm=comm)
+    bufs = None
+    if world > 1 and args.fused_reduce:
+        from mini_sgl_integer_b200.layers.tp_linear import PeerReduceBuffers
+        bufs = PeerReduceBuffers(comm, B, HID, dev)
+    layer = Qwen3DecoderLayerInteger(0, hq, hk, HID, inter, weights, cache, pool, comm=comm, peer_buffers=bufs)
     batch = AttnBatch(d((lens - 1).astype(np.int32)), d(out_loc), d(table), d(lens.astype(np.int32)), None, 8192,
                       d(np.argsort(-lens, kind="stable").astype(np.int32)))
     x = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
@@ -509,7 +513,8 @@ def run_tp_layer(args) -> None:
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": "one Qwen3-32B-shaped decoder layer, decode batch %d, ctx U[1024,8192], TP=%d" % (B, world),
-                       "per_gpu_tok_s": B / (LAYERS * ms * 1e-3) / world, "cuda_graph": bool(args.graph and world == 1)},
+                       "per_gpu_tok_s": B / (LAYERS * ms * 1e-3) / world, "cuda_graph": bool(args.graph and world == 1),
+                       "row_parallel_sum": "in the GEMM kernel over peer memory" if bufs is not None else "NCCL all-reduce"},
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
                          "peak_source": how, "bytes_per_rank": w_bytes + kv_bytes},
         }))
@@ -634,6 +639,8 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=4096, help="M for --workload gemm")
     ap.add_argument("--tp-batch", type=int, default=256, help="decode batch for --workload tp_layer / model")
     ap.add_argument("--model-layers", type=int, default=36, help="layers for --workload model")
+    ap.add_argument("--fused-reduce", action="store_true",
+                    help="tp_layer on several GPUs: the row-parallel GEMMs add their partial sums over NVLink peer memory themselves")
     ap.add_argument("--graph", action="store_true", help="tp_layer on one GPU: replay the layer step from a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -281,6 +281,18 @@ B200_API int b200_requant_q15(const int32_t* acc, const int32_t* x_mul, const in
                               const int32_t* w_mul, const int32_t* w_shift, int32_t* out,
                               int64_t m, int64_t n, b200_stream_t s);
 
+/* ---- Row-parallel GEMM fused with the tensor-parallel sum over peer memory (decode sizes, m <= 256).
+ * Every rank calls it with its K-slice (x8 int8 [m, k_local], w8 int8 [n, k_local]); each accumulator tile is
+ * added, as it leaves tensor memory, into peer_acc[0 .. n_peers-1]: the int32 [m, n] accumulators of ALL ranks
+ * (this rank's own included), device pointers valid in this process (NVLink peer / symmetric memory).  The
+ * transfer overlaps the MMAs tile by tile; integer addition makes the sums identical on every rank.  The caller
+ * zeroes the accumulators before any rank starts, separates this call from the reads of the result by a
+ * cross-rank barrier on the stream, and applies b200_requant_q15.  peer_acc is a HOST array of n_peers device
+ * pointers.  Replaces GEMM + all-reduce of LinearOProj / LinearRowParallel (layers/linear.py:108-160,
+ * distributed/impl.py:63-70). */
+B200_API int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, int32_t* const* peer_acc, int n_peers,
+                                         int64_t m, int64_t n, int64_t k, b200_stream_t s);
+
 /* Reads (and optionally clears) the device-side status word of the GEMM kernels: 0 = fine,
  * non-zero = a bounded wait inside a kernel expired (1 producer, 2 MMA issuer, 3 epilogue).
  * Synchronises with the device.  No counterpart in the reference. */

@@ -43,6 +43,7 @@ SIGNATURES: dict[str, list] = {
     "b200_static_quant_q15": [P, ctypes.c_float, P, L, P],
     "b200_gemm_w8a8": [P, P, P, P, P, P, P, P, L, L, L, P],
     "b200_gemm_w8a8_absmax": [P, P, P, P, P, P, P, L, L, L, P],
+    "b200_gemm_w8a8_reduce_peers": [P, P, P, I, L, L, L, P],
     "b200_gemm_status": [P, I],
     "b200_quant_given_absmax_q15": [P, P, P, L, I, P],
     "b200_requant_q15": [P, P, P, P, P, P, L, L, P],

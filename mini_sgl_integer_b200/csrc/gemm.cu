@@ -120,6 +120,8 @@ struct GemmParams {
   int M, N, K;
   int splits;               // weights-stationary mode: parts of K per block of weight rows (1 = none)
   int32_t* partial;         // splits > 1: int32 [M, N] that the parts are added into (zeroed before the launch)
+  int n_peers;              // > 0: tensor-parallel reduction - every part is added into each of these [M, N] buffers
+  int32_t* peer[8];         //      (this rank's and its peers', mapped into this process: NVLink peer memory)
 };
 
 __device__ __forceinline__ void mbar_arrive(unsigned bar) {
@@ -285,7 +287,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (WS) {
         // rows of the accumulator tile are weight channels, columns are tokens
         const int ch = n_blk * kBM + q * 32 + lane;
-        const bool direct = p.splits == 1;
+        const bool direct = p.splits == 1 && p.n_peers == 0;
         const bool empty_part = m_blk * kb_per >= num_kb;      // a part of K with no k-blocks: nothing was accumulated
         if (direct && p.out_q15) {
           for (int c = et; c < BN; c += 32 * kEpiWarps) {
@@ -307,7 +309,17 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           int v[32];
           tmem_ld_32x32(tmem_base + ((unsigned)(q * 32) << 16) + slot * BN + (unsigned)c0, v);
           if (!ok || c0 >= p.M || ch >= p.N || empty_part) continue;
-          if (!direct) {
+          if (p.n_peers > 0) {
+            // tensor-parallel sum: the tile's partial sums go straight into every rank's accumulator (a warp's
+            // 32 channels of one token are one 128-byte reduction over NVLink); integer adds commute, so every
+            // rank ends up with the same bits whatever the arrival order
+            for (int r = 0; r < p.n_peers; ++r) {
+              int32_t* dst = p.peer[r];
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (c0 + j < p.M) atomicAdd(dst + (int64_t)(c0 + j) * p.N + ch, v[j]);
+            }
+          } else if (!direct) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (c0 + j < p.M) atomicAdd(p.partial + (int64_t)(c0 + j) * p.N + ch, v[j]);   // result unused: a reduction
@@ -706,7 +718,7 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
   GemmParams p;
   p.x_absmax = x_absmax; p.x_mul = x_mul; p.x_shift = x_shift; p.w_mul = w_mul; p.w_shift = w_shift;
   p.out_q15 = out_q15; p.acc_out = acc_out; p.M = (int)m; p.N = (int)n; p.K = (int)k;
-  p.splits = 1; p.partial = nullptr;
+  p.splits = 1; p.partial = nullptr; p.n_peers = 0;
   cudaStream_t st = (cudaStream_t)s;
   const int w_blocks = (int)((n + kBM - 1) / kBM), num_kb = (int)((k + kBK - 1) / kBK);
   if (m <= 128 || (m <= 256 && w_blocks < sm_count())) {
@@ -769,6 +781,42 @@ extern "C" int b200_gemm_w8a8_absmax(const int8_t* x8, const int8_t* w8, const i
                                      int64_t k, b200_stream_t s) {
   B200_REQUIRE(x_absmax || !out_q15, B200_E_NULL, "gemm_w8a8_absmax: x_absmax is null");
   return gemm_impl(x8, w8, x_absmax, nullptr, nullptr, w_mul, w_shift, out_q15, acc_out, m, n, k, s);
+}
+
+extern "C" int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, int32_t* const* peer_acc, int n_peers,
+                                           int64_t m, int64_t n, int64_t k, b200_stream_t s) {
+  B200_REQUIRE(x8 && w8 && peer_acc, B200_E_NULL, "gemm_w8a8_reduce_peers: null pointer");
+  B200_REQUIRE(n_peers >= 1 && n_peers <= 8, B200_E_SHAPE, "gemm_w8a8_reduce_peers: n_peers=%d (1..8)", n_peers);
+  B200_REQUIRE(m >= 0 && m <= 256 && n > 0 && k > 0 && n < (1ll << 31) && k < (1ll << 31), B200_E_UNSUPPORTED,
+               "gemm_w8a8_reduce_peers: m=%lld n=%lld k=%lld (decode sizes: m <= 256)", (long long)m, (long long)n, (long long)k);
+  B200_REQUIRE(k % 16 == 0, B200_E_UNSUPPORTED, "gemm_w8a8_reduce_peers: k=%lld must be a multiple of 16", (long long)k);
+  if (m == 0) return B200_OK;
+  B200_REQUIRE(aligned16(x8) && aligned16(w8), B200_E_ALIGN, "gemm_w8a8_reduce_peers: operands must be 16-byte aligned");
+  GemmParams p;
+  p.x_absmax = nullptr; p.x_mul = nullptr; p.x_shift = nullptr; p.w_mul = nullptr; p.w_shift = nullptr;
+  p.out_q15 = nullptr; p.acc_out = nullptr; p.M = (int)m; p.N = (int)n; p.K = (int)k; p.partial = nullptr;
+  p.n_peers = n_peers;
+  for (int r = 0; r < 8; ++r) {
+    p.peer[r] = r < n_peers ? peer_acc[r] : nullptr;
+    B200_REQUIRE(r >= n_peers || p.peer[r] != nullptr, B200_E_NULL, "gemm_w8a8_reduce_peers: peer_acc[%d] is null", r);
+  }
+  const int w_blocks = (int)((n + kBM - 1) / kBM), num_kb = (int)((k + kBK - 1) / kBK);
+  int splits = sm_count() / w_blocks;
+  splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
+  while (splits > 1 && num_kb / splits < 4) --splits;
+  while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;
+  p.splits = splits;
+  CUtensorMap ma, mb;
+  const int bn = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
+  B200_REQUIRE(make_map(&ma, w8, n, k, kBM), B200_E_CUDA, "gemm_w8a8_reduce_peers: cuTensorMapEncodeTiled failed for w8");
+  B200_REQUIRE(make_map(&mb, x8, m, k, bn), B200_E_CUDA, "gemm_w8a8_reduce_peers: cuTensorMapEncodeTiled failed for x8");
+  cudaStream_t st = (cudaStream_t)s;
+  switch (bn) {
+    case 256: return launch_gemm<256, 4, true>(ma, mb, p, st);
+    case 128: return launch_gemm<128, 6, true>(ma, mb, p, st);
+    case 64: return launch_gemm<64, 8, true>(ma, mb, p, st);
+    default: return launch_gemm<32, 10, true>(ma, mb, p, st);
+  }
 }
 
 extern "C" int b200_gemm_status(int* out_host, int reset) {

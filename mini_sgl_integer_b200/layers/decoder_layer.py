@@ -17,7 +17,7 @@ import torch
 from ..attention import Int8PagedKVCache, decode_attention_int8_paged, extend_attention_int8_paged
 from ..kernel import fixed_point as fp
 from ..distributed import DistributedCommunicator
-from .tp_linear import row_parallel_q15
+from .tp_linear import PeerReduceBuffers, row_parallel_q15, row_parallel_q15_fused
 from .w8a8_int8 import W8A8Int8LinearMethod
 
 
@@ -49,7 +49,8 @@ class _Linear(torch.nn.Module):
 class Qwen3DecoderLayerInteger:
     def __init__(self, layer_id: int, num_qo_heads: int, num_kv_heads: int, hidden: int, inter: int,
                  weights: dict, cos_sin_cache_q15: torch.Tensor, pool: Int8PagedKVCache,
-                 hadamard_block: int = 128, comm: Optional[DistributedCommunicator] = None):
+                 hadamard_block: int = 128, comm: Optional[DistributedCommunicator] = None,
+                 peer_buffers: Optional[PeerReduceBuffers] = None):
         """``weights``: qkv/o/gate_up/down -> _Linear; input_norm/post_norm int32 [hidden];
         q_norm/k_norm int32 [128] or None (Q15.16; q_norm already carries head_dim**-0.5).
 
@@ -64,6 +65,9 @@ class Qwen3DecoderLayerInteger:
         self.pool = pool
         self.hadamard_block = hadamard_block
         self.method = W8A8Int8LinearMethod()
+        # tensor parallel: with peer buffers the o / down GEMMs add their partial sums into every rank's
+        # accumulator themselves (decode sizes); without, an NCCL all-reduce follows the GEMM
+        self.peer_buffers = peer_buffers
 
     def forward_q15(self, x_q15: torch.Tensor, residual_q15: Optional[torch.Tensor], batch: AttnBatch,
                     trace: Optional[dict] = None):
@@ -95,7 +99,9 @@ class Qwen3DecoderLayerInteger:
                                                batch.kv_lens, batch.q_lens, batch.max_kv_len)
         t["attn"] = attn
         tp = self.comm.size > 1
-        o = row_parallel_q15(m, w["o"], attn.view(T, qd), self.comm) if tp else m.apply_weights_q15(w["o"], attn.view(T, qd))
+        rowp = (lambda l, x: row_parallel_q15_fused(m, l, x, self.comm, self.peer_buffers)) if self.peer_buffers is not None \
+            else (lambda l, x: row_parallel_q15(m, l, x, self.comm))
+        o = rowp(w["o"], attn.view(T, qd)) if tp else m.apply_weights_q15(w["o"], attn.view(T, qd))
         t["o"] = o
         # post_attention_layernorm (+ residual add) -> codes for gate_up_proj
         codes, _, absmax, residual, _ = fp.fused_add_rmsnorm_quant(o, residual, w["post_norm"])
@@ -103,7 +109,7 @@ class Qwen3DecoderLayerInteger:
         gate_up = m.apply_quantised(w["gate_up"], codes, absmax)
         t["gate_up"] = gate_up
         if tp:   # the token's absmax spans all ranks' columns: rotate locally, agree on the scale, then quantise
-            down = row_parallel_q15(m, w["down"], fp.silu_mul_fwht_q15(gate_up, self.hadamard_block), self.comm)
+            down = rowp(w["down"], fp.silu_mul_fwht_q15(gate_up, self.hadamard_block))
         else:
             codes, _, absmax, _ = fp.silu_mul_fwht_quant(gate_up, self.hadamard_block)
             t["act_codes"], t["act_absmax"] = codes, absmax

@@ -7,8 +7,15 @@ reference quantises each rank's slice with its own absmax and all-reduces the Q1
 result depend on the rank count.  Here the ranks first agree on the token's absmax (a [tokens] int32 max
 all-reduce), quantise their slices with it, all-reduce the exact int32 accumulators and requantise once:
 bit-identical to a single GPU.
+
+The sum of the accumulators comes in two forms: an NCCL all-reduce after the GEMM (`row_parallel_q15`), or, at
+decode sizes, inside the GEMM kernel itself (`row_parallel_q15_fused`): every accumulator tile is added, as it
+leaves tensor memory, into the accumulators of all ranks through NVLink peer memory (`PeerReduceBuffers`), so
+the transfer overlaps the MMAs and no separate collective kernel runs.
 """
 from __future__ import annotations
+
+import ctypes
 
 import torch
 
@@ -69,3 +76,50 @@ def row_parallel_q15(method: W8A8Int8LinearMethod, layer, x_q15_local: torch.Ten
     acc = comm.all_reduce(acc)
     x_mul, x_shift = absmax_to_mul_shift(absmax)
     return requant_q15(acc, x_mul, x_shift, layer.weight_mul, layer.weight_shift)
+
+
+class PeerReduceBuffers:
+    """int32 accumulators [2][m_max, n] in symmetric memory, one set per rank, every rank's mapped into every
+    process (``torch.distributed._symmetric_memory``).  Two halves are used alternately: a half is zeroed right
+    after its result has been read, and the barrier of the following call (on the other half) orders that
+    zeroing before any peer adds into it again."""
+
+    def __init__(self, comm: DistributedCommunicator, m_max: int, n: int, device):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.m_max, self.n, self.size = int(m_max), int(n), comm.size
+        self.buf = symm_mem.empty((2, self.m_max, self.n), dtype=torch.int32, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, comm.group if comm.group is not None else dist.group.WORLD)
+        self.buf.zero_()
+        self.handle.barrier(channel=0)
+        half_bytes = self.m_max * self.n * 4
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        self.peer_ptrs = [(ctypes.c_void_p * self.size)(*[b + h * half_bytes for b in bases]) for h in (0, 1)]
+        self.calls = 0
+
+
+def row_parallel_q15_fused(method: W8A8Int8LinearMethod, layer, x_q15_local: torch.Tensor,
+                           comm: DistributedCommunicator, bufs: PeerReduceBuffers) -> torch.Tensor:
+    """`row_parallel_q15` with the sum of the accumulators done by the GEMM kernel over peer memory (tokens <= 256
+    and <= bufs.m_max, layer.weight.shape[0] == bufs.n); same bits."""
+    assert_q15(x_q15_local, "x_q15_local")
+    if getattr(layer, "weight_mul", None) is None:
+        method.process_weights_after_loading(layer)
+    x2 = x_q15_local.reshape(-1, x_q15_local.shape[-1])
+    m, k = x2.shape
+    n = layer.weight.shape[0]
+    if m > min(256, bufs.m_max) or n != bufs.n:
+        return row_parallel_q15(method, layer, x_q15_local, comm)
+    absmax = comm.all_reduce_max(row_absmax_q15(x2))
+    codes = quant_given_absmax(x2, absmax)
+    half = bufs.calls & 1
+    bufs.calls += 1
+    if m:
+        call("b200_gemm_w8a8_reduce_peers", ptr(codes), ptr(layer.weight.contiguous()), bufs.peer_ptrs[half], bufs.size,
+             m, n, k, stream())
+    bufs.handle.barrier(channel=half)                  # every rank's additions have landed
+    acc = bufs.buf[half, :m]
+    x_mul, x_shift = absmax_to_mul_shift(absmax)
+    out = requant_q15(acc, x_mul, x_shift, layer.weight_mul, layer.weight_shift)
+    acc.zero_()                                        # ready for its next use, two calls from now
+    return out

@@ -37,8 +37,9 @@ def _inputs():
     return w, cache, pre, table, positions, out_loc, kv_lens, x, res
 
 
-def _run_layer(rank, world, comm):
-    """Build this rank's shard of the layer and run one decode step; world == 1 is the single-GPU layer."""
+def _run_layer(rank, world, comm, fused=False):
+    """Build this rank's shard of the layer and run one decode step; world == 1 is the single-GPU layer.
+    ``fused``: the row-parallel GEMMs sum their accumulators over peer memory inside the kernel."""
     from mini_sgl_integer_b200.attention import Int8PagedKVCache
     from mini_sgl_integer_b200.layers.decoder_layer import AttnBatch, Qwen3DecoderLayerInteger, _Linear
     d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
@@ -70,9 +71,17 @@ def _run_layer(rank, world, comm):
     for b, (k8, v8, km, ks, vm, vs, l) in pre.items():
         sl = slice(rank * hk, (rank + 1) * hk)
         pool.store_codes(d(k8[:, sl]), d(v8[:, sl]), d(km[:, sl]), d(ks[:, sl]), d(vm[:, sl]), d(vs[:, sl]), d(l), 0)
-    layer = Qwen3DecoderLayerInteger(0, hq, hk, HID, inter, weights, d(cache), pool, comm=comm)
+    bufs = None
+    if fused:
+        from mini_sgl_integer_b200.layers.tp_linear import PeerReduceBuffers
+        bufs = PeerReduceBuffers(comm, 8, HID, "cuda")
+    layer = Qwen3DecoderLayerInteger(0, hq, hk, HID, inter, weights, d(cache), pool, comm=comm, peer_buffers=bufs)
     batch = AttnBatch(d(positions), d(out_loc), d(table), d(np.asarray(kv_lens, np.int32)), None, 128)
     out, resid = layer.forward_q15(d(x), d(res), batch)
+    if fused:                                   # twice more on the same inputs: both halves of the buffers get reused
+        for _ in range(2):
+            out2, _ = layer.forward_q15(d(x), d(res), batch)
+            assert torch.equal(out2, out)
     torch.cuda.synchronize()
     return out.cpu().numpy(), resid.cpu().numpy()
 
@@ -86,19 +95,24 @@ def _worker(rank, world, port, out_dir):
     out, resid = _run_layer(rank, world, DistributedCommunicator())
     np.savez(os.path.join(out_dir, f"r{rank}.npz"), out=out, resid=resid)
     dist.barrier()
+    out, resid = _run_layer(rank, world, DistributedCommunicator(), fused=True)
+    np.savez(os.path.join(out_dir, f"f{rank}.npz"), out=out, resid=resid)
+    dist.barrier()
     dist.destroy_process_group()
 
 
 def test_two_gpu_layer_equals_one_gpu(tmp_path):
+    """NCCL all-reduce after the GEMM, and the sum done by the GEMM kernel over peer memory: both give one GPU's bits."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     want_out, want_res = _run_layer(0, 1, None)
     mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    for r in range(2):
-        z = np.load(tmp_path / f"r{r}.npz")
-        assert np.array_equal(z["out"], want_out), f"rank {r}: layer output differs from one GPU"
-        assert np.array_equal(z["resid"], want_res)
+    for kind in "rf":
+        for r in range(2):
+            z = np.load(tmp_path / f"{kind}{r}.npz")
+            assert np.array_equal(z["out"], want_out), f"{kind} rank {r}: layer output differs from one GPU"
+            assert np.array_equal(z["resid"], want_res)
 
 
 # ---------------------------------------------------------------------------------------------- whole model
