@@ -188,6 +188,11 @@ attn_decode_kernel(const DecodeParams p) {
   // b is the query row; its keys come from sequence `seq`.  In an extend batch a row sees only the
   // first `row_limit` keys, but the reference V scale is taken over all L_all keys of the sequence.
   const int seq = p.row_seq ? p.row_seq[b] : b;
+  // A lone CTA's slice starts at page 0 whatever the length: its page ids are requested before the length
+  // is known (one dependent memory round trip less); ids past the row's last page are never used.
+  int64_t pid_early = 0;
+  const int cap_pages = (int)min((int64_t)(S / kPage), p.table_pitch);
+  if (C == 1 && tid < cap_pages) pid_early = p.page_table[(int64_t)seq * p.table_pitch + tid];
   const int L_all = max(0, min(p.kv_lens[seq], p.max_kv_len));
   const int L = p.row_limit ? max(0, min(p.row_limit[b], L_all)) : L_all;
   const int n_pages = (L + kPage - 1) / kPage;
@@ -214,7 +219,7 @@ attn_decode_kernel(const DecodeParams p) {
   if (tid == 0) cta_vref = ~0ull;
   for (int i = tid; i < G * kD; i += kDecodeThreads) (&cta_acc[0][0])[i] = 0;
   for (int i = tid; i < my_pages; i += kDecodeThreads) {
-    int64_t pid = p.page_table[(int64_t)seq * p.table_pitch + pg0 + i];
+    int64_t pid = (C == 1 && i < kDecodeThreads) ? pid_early : p.page_table[(int64_t)seq * p.table_pitch + pg0 + i];
     pid = pid < 0 ? 0 : (pid >= p.num_pages ? p.num_pages - 1 : pid);
     pages[i] = (int)pid;
   }
@@ -555,18 +560,32 @@ attn_decode_kernel(const DecodeParams p) {
   // ---- exchange 3: head g is finished by rank g % C: sum the partial outputs of all CTAs over
   // distributed shared memory, requantise, and (for the int8 output) quantise the 128-wide row
   {
-    for (int g = rank; g < G; g += Ce) {   // uniform per CTA
-      const int d = tid & (kD - 1);        // threads beyond kD repeat a d and keep quiet
-      const bool act = tid < kD;
-      long long a = 0;
-      for (int r = 0; r < Ce; ++r) a += *cluster.map_shared_rank(&cta_acc[g][d], r);
-      const int o = L > 0 ? mul_shift_sat32_wide(a, v_mul_ref, v_shift_ref - 1) : 0;
+    static_assert(kDecodeThreads == 2 * kD, "two heads are finished at a time, 128 threads each");
+    const int d = tid & (kD - 1);
+    const int sub = tid >> 7;                          // which of the two heads in flight
+    const int my_heads = (G - rank + Ce - 1) / Ce;     // heads rank, rank + Ce, ...: uniform per CTA
+    for (int i0 = 0; i0 < my_heads; i0 += 2) {
+      const int hi = i0 + sub;
+      const bool act = hi < my_heads;
+      const int g = rank + hi * Ce;
       const int64_t row = ((int64_t)b * p.q_heads + kh * G + g) * kD;
-      if (p.out_q15 && act) p.out_q15[row + d] = o;
-      if (p.out_codes) {
-        const int m = max(1, block_max(abs_wrap(o), red_s));
-        if (act) p.out_codes[row + d] = (int8_t)quant_code(o, __int2float_rn(m));
-        if (tid == 0) p.out_absmax[(int64_t)b * p.q_heads + kh * G + g] = m;
+      int o = 0;
+      if (act) {
+        long long a = 0;
+        for (int r = 0; r < Ce; ++r) a += *cluster.map_shared_rank(&cta_acc[g][d], r);
+        o = L > 0 ? mul_shift_sat32_wide(a, v_mul_ref, v_shift_ref - 1) : 0;
+        if (p.out_q15) p.out_q15[row + d] = o;
+      }
+      if (p.out_codes) {   // row quant of the head: its 128 values sit in four warps
+        const int wm = warp_max(abs_wrap(o));
+        if (lane == 0) red_s[warp] = wm;
+        __syncthreads();
+        const int m = max(1, max(max(red_s[4 * sub], red_s[4 * sub + 1]), max(red_s[4 * sub + 2], red_s[4 * sub + 3])));
+        if (act) {
+          p.out_codes[row + d] = (int8_t)quant_code(o, __int2float_rn(m));
+          if (d == 0) p.out_absmax[(int64_t)b * p.q_heads + kh * G + g] = m;
+        }
+        __syncthreads();   // red_s is rewritten by the next pair of heads
       }
     }
   }
