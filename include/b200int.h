@@ -136,6 +136,21 @@ B200_API int b200_kv_store_codes(const int8_t* k8, const int8_t* v8, const int32
                         const int32_t* out_loc, int8_t* k_codes, int8_t* v_codes, int32_t* meta,
                         int64_t tokens, int kv_heads, int64_t num_pages, b200_stream_t s);
 
+/* ---- Everything between the qkv projection and attention in one launch: per (token, head) row,
+ * q-norm / k-norm (nullable weights) + RoPE + Hadamard rotation of q and k as b200_qk_rope_q15, then
+ *   q rows: per-row int8 codes (b200_per_token_quant_q15) -> q8 int8 [tokens, q_heads, 128] and their
+ *           (multiplier, shift) (b200_absmax_to_mul_shift) -> q_mul, q_shift int32 [tokens, q_heads];
+ *   k rows and the untouched v rows: quantised and scattered into the pool as b200_kv_store_q15.
+ * Same bits as those four calls in sequence.  Stands in for the part of AttentionLayerInteger.forward_q15
+ * between qkv_proj and the backend (models/utils_integer.py:209-227) plus the backend's store_kv
+ * (attention/triton_int8.py:125). */
+B200_API int b200_qkv_prepare_q15(const int32_t* positions, const int32_t* q, int64_t q_pitch, const int32_t* k,
+                                  int64_t k_pitch, const int32_t* v, int64_t v_pitch, const int32_t* cos_sin,
+                                  int max_pos, const int32_t* q_norm_w, const int32_t* k_norm_w,
+                                  const int32_t* out_loc, int8_t* k_codes, int8_t* v_codes, int32_t* meta,
+                                  int8_t* q8, int32_t* q_mul, int32_t* q_shift, int64_t tokens, int q_heads,
+                                  int kv_heads, int64_t num_pages, int with_fwht, b200_stream_t s);
+
 /* ---- Decode attention over the int8 paged pool with an exact fixed-point softmax.
  * Stands in for Int8Backend._forward_decode (attention/triton_int8.py:155-176), which in the
  * reference runs a bf16 kernel; the integer arithmetic follows int8_context_attention_fwd

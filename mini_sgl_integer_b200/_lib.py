@@ -41,6 +41,7 @@ SIGNATURES: dict[str, list] = {
     "b200_argmax_i32": [P, L, L, L, I, P, P, P],
     "b200_decode_prepare": [P, L, P, P, P, P, I, I, P],
     "b200_static_quant_q15": [P, ctypes.c_float, P, L, P],
+    "b200_qkv_prepare_q15": [P, P, L, P, L, P, L, P, I, P, P, P, P, P, P, P, P, P, L, I, I, L, I, P],
     "b200_gemm_w8a8": [P, P, P, P, P, P, P, P, L, L, L, P],
     "b200_gemm_w8a8_absmax": [P, P, P, P, P, P, P, L, L, L, P],
     "b200_gemm_w8a8_reduce_peers": [P, P, P, I, L, L, L, P],

@@ -140,3 +140,38 @@ def extend_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
     if out_q15 and out_int8:
         return o32, o8, om
     return o32 if out_q15 else (o8, om)
+
+
+def qkv_rope_quant_store(positions: torch.Tensor, qkv_q15: torch.Tensor, q_heads: int, pool: Int8PagedKVCache,
+                         layer_id: int, out_loc: torch.Tensor, cos_sin_cache_q15: torch.Tensor,
+                         q_norm_weight: torch.Tensor | None = None, k_norm_weight: torch.Tensor | None = None,
+                         with_fwht: bool = True):
+    """One launch for everything between the qkv projection and attention: q/k-norm + RoPE + Hadamard rotation,
+    the new K/V rows quantised into the pool at ``out_loc``, q quantised per (token, head).
+
+    ``qkv_q15``: int32 [tokens, (q_heads + 2*kv_heads)*128] as the qkv projection leaves it (q | k | v blocks).
+    Returns (q8 int8 [tokens, q_heads, 128], q_mul, q_shift int32 [tokens, q_heads]).  Same bits as
+    qk_norm_rope_fwht -> pool.store_kv -> per_token_quant_int8_from_q15 -> absmax_to_mul_shift
+    (models/utils_integer.py:209-227, attention/triton_int8.py:125)."""
+    if qkv_q15.dtype != torch.int32 or qkv_q15.ndim != 2:
+        raise TypeError(f"qkv_q15 must be int32 [tokens, width], got {qkv_q15.dtype} {tuple(qkv_q15.shape)}")
+    hk = pool.kv_heads
+    if qkv_q15.shape[1] != (q_heads + 2 * hk) * HEAD_DIM:
+        raise ValueError(f"qkv width {qkv_q15.shape[1]} != (q_heads + 2*kv_heads)*{HEAD_DIM}")
+    require_cuda(positions, qkv_q15, out_loc, cos_sin_cache_q15, q_norm_weight, k_norm_weight)
+    if qkv_q15.stride(1) != 1 or qkv_q15.stride(0) % 4 or qkv_q15.data_ptr() % 16:
+        qkv_q15 = qkv_q15.contiguous()
+    tokens, pitch = qkv_q15.shape[0], qkv_q15.stride(0)
+    qd, kd = q_heads * HEAD_DIM, hk * HEAD_DIM
+    q, k, v = qkv_q15[:, :qd], qkv_q15[:, qd:qd + kd], qkv_q15[:, qd + kd:]
+    c = lambda t: None if t is None else t.to(torch.int32).contiguous()
+    q8 = torch.empty((tokens, q_heads, HEAD_DIM), dtype=torch.int8, device=qkv_q15.device)
+    q_mul = torch.empty((tokens, q_heads), dtype=torch.int32, device=qkv_q15.device)
+    q_shift = torch.empty_like(q_mul)
+    cache = c(cos_sin_cache_q15)
+    if tokens:
+        call("b200_qkv_prepare_q15", ptr(c(positions)), ptr(q), pitch, ptr(k), pitch, ptr(v), pitch, ptr(cache),
+             cache.shape[0], ptr(c(q_norm_weight)), ptr(c(k_norm_weight)), ptr(c(out_loc)), ptr(pool.k_cache(layer_id)),
+             ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(q8), ptr(q_mul), ptr(q_shift), tokens, q_heads, hk,
+             pool.num_pages, int(with_fwht), stream())
+    return q8, q_mul, q_shift

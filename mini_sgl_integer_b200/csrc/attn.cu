@@ -17,6 +17,7 @@
 
 #include "attn_common.cuh"
 #include "luts.cuh"
+#include "rope.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -81,6 +82,82 @@ kv_store_kernel(const void* __restrict__ k_in, int64_t k_pitch, const void* __re
     mt[16 + tok] = vmul;
     reinterpret_cast<int8_t*>(mt + 32)[tok] = (int8_t)kshift;
     reinterpret_cast<int8_t*>(mt + 36)[tok] = (int8_t)vshift;
+  }
+}
+
+// ============================================================================ q/k/v preparation
+// Everything between the qkv projection and attention in one launch, one warp per (token, head) of the
+// q | k | v heads: q heads get q-norm + RoPE + Hadamard rotation, per-row int8 quantisation and their
+// (multiplier, shift); k heads the same and go straight into their page; v heads are quantised and stored
+// in operand order.  Same arithmetic, row by row, as qk_rope_kernel, quant_rows_kernel, absmax_to_ms_kernel
+// and kv_store_kernel<true> run one after the other.
+__global__ void __launch_bounds__(256)
+qkv_prepare_kernel(const int32_t* __restrict__ positions, const int32_t* __restrict__ q, int64_t q_pitch,
+                   const int32_t* __restrict__ k, int64_t k_pitch, const int32_t* __restrict__ v, int64_t v_pitch,
+                   const int32_t* __restrict__ cos_sin, int max_pos, const int32_t* __restrict__ q_norm_w,
+                   const int32_t* __restrict__ k_norm_w, const int32_t* __restrict__ out_loc,
+                   int8_t* __restrict__ k_codes, int8_t* __restrict__ v_codes, int32_t* __restrict__ meta,
+                   int8_t* __restrict__ q8, int32_t* __restrict__ q_mul, int32_t* __restrict__ q_shift,
+                   int64_t tokens, int q_heads, int kv_heads, int64_t num_pages, int with_fwht) {
+  const int lane = threadIdx.x & 31;
+  const int heads = q_heads + 2 * kv_heads;
+  const int64_t wid = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  if (wid >= tokens * heads) return;   // whole warps leave together
+  const int64_t t = wid / heads;
+  const int h = (int)(wid - t * heads);
+  const int64_t loc = out_loc[t];
+  const int64_t pid = loc >> 4;
+  const int tok = (int)(loc & 15);
+  const bool in_pool = loc >= 0 && pid < num_pages;     // out-of-pool locations are dropped, never written
+  if (h < q_heads + kv_heads) {
+    const bool is_q = h < q_heads;
+    const int hh = is_q ? h : h - q_heads;
+    if (!is_q && !in_pool) return;
+    const int32_t* src = is_q ? q + t * q_pitch + (int64_t)hh * kD : k + t * k_pitch + (int64_t)hh * kD;
+    int a0, a1, b0, b1;
+    rope_row(src, is_q ? q_norm_w : k_norm_w, positions[t], cos_sin, max_pos, with_fwht, lane, a0, a1, b0, b1);
+    int m = max(max(0, abs_wrap(a0)), max(abs_wrap(a1), max(abs_wrap(b0), abs_wrap(b1))));
+    m = max(1, warp_max(m));
+    const float mf = __int2float_rn(m), my = __frcp_rn(mf);
+    const unsigned lo = (unsigned)(quant_code_fast(a0, mf, my) & 0xff) | ((unsigned)(quant_code_fast(a1, mf, my) & 0xff) << 8);
+    const unsigned hi = (unsigned)(quant_code_fast(b0, mf, my) & 0xff) | ((unsigned)(quant_code_fast(b1, mf, my) & 0xff) << 8);
+    int mul, shift;
+    absmax_to_ms_dev(m, &mul, &shift);
+    int8_t* row;
+    if (is_q) {
+      row = q8 + (t * q_heads + hh) * kD;
+      if (lane == 0) { q_mul[t * q_heads + hh] = mul; q_shift[t * q_heads + hh] = shift; }
+    } else {
+      const int64_t chunk = pid * kv_heads + hh;
+      row = k_codes + (chunk * kPage + tok) * kD;
+      if (lane == 0) {
+        int32_t* mt = meta + chunk * kMetaWords;
+        mt[tok] = mul;
+        reinterpret_cast<int8_t*>(mt + 32)[tok] = (int8_t)shift;
+      }
+    }
+    reinterpret_cast<unsigned short*>(row)[lane] = (unsigned short)lo;            // elements 2l, 2l+1
+    reinterpret_cast<unsigned short*>(row + 64)[lane] = (unsigned short)hi;       // elements 64+2l, 64+2l+1
+  } else {
+    if (!in_pool) return;
+    const int hh = h - q_heads - kv_heads;
+    const int4 b = *reinterpret_cast<const int4*>(v + t * v_pitch + (int64_t)hh * kD + 4 * lane);
+    int mv = max(max(0, abs_wrap(b.x)), max(abs_wrap(b.y), max(abs_wrap(b.z), abs_wrap(b.w))));
+    mv = max(1, warp_max(mv));
+    const float fv = __int2float_rn(mv), yv = __frcp_rn(fv);
+    const unsigned vw = pack4(quant_code_fast(b.x, fv, yv), quant_code_fast(b.y, fv, yv), quant_code_fast(b.z, fv, yv),
+                              quant_code_fast(b.w, fv, yv));
+    int mul, shift;
+    absmax_to_ms_dev(mv, &mul, &shift);
+    const int64_t chunk = pid * kv_heads + hh;
+    int8_t* vdst = v_codes + chunk * (kD * kPage);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) vdst[v_chunk_offset(4 * lane + e, tok)] = (int8_t)((vw >> (8 * e)) & 0xff);
+    if (lane == 0) {
+      int32_t* mt = meta + chunk * kMetaWords;
+      mt[16 + tok] = mul;
+      reinterpret_cast<int8_t*>(mt + 36)[tok] = (int8_t)shift;
+    }
   }
 }
 
@@ -662,6 +739,35 @@ static int store_common(bool quant, const void* k, int64_t k_pitch, const void* 
     kv_store_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(k, 0, v, 0, k_mul, k_shift, v_mul, v_shift, out_loc,
                                                             k_codes, v_codes, meta, tokens, kv_heads, num_pages);
   return check_launch(name);
+}
+
+extern "C" int b200_qkv_prepare_q15(const int32_t* positions, const int32_t* q, int64_t q_pitch, const int32_t* k,
+                                    int64_t k_pitch, const int32_t* v, int64_t v_pitch, const int32_t* cos_sin,
+                                    int max_pos, const int32_t* q_norm_w, const int32_t* k_norm_w,
+                                    const int32_t* out_loc, int8_t* k_codes, int8_t* v_codes, int32_t* meta,
+                                    int8_t* q8, int32_t* q_mul, int32_t* q_shift, int64_t tokens, int q_heads,
+                                    int kv_heads, int64_t num_pages, int with_fwht, b200_stream_t s) {
+  B200_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && max_pos > 0 && num_pages > 0, B200_E_SHAPE,
+               "qkv_prepare_q15: tokens=%lld q_heads=%d kv_heads=%d max_pos=%d num_pages=%lld", (long long)tokens, q_heads,
+               kv_heads, max_pos, (long long)num_pages);
+  if (tokens == 0) return B200_OK;
+  B200_REQUIRE(positions && q && k && v && cos_sin && out_loc && k_codes && v_codes && meta && q8 && q_mul && q_shift,
+               B200_E_NULL, "qkv_prepare_q15: null pointer");
+  B200_REQUIRE(q_pitch >= (int64_t)q_heads * kD && k_pitch >= (int64_t)kv_heads * kD && v_pitch >= (int64_t)kv_heads * kD,
+               B200_E_SHAPE, "qkv_prepare_q15: row pitch smaller than heads*128");
+  auto a8 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; };
+  B200_REQUIRE(a8(q) && a8(k) && aligned16(v) && a8(cos_sin) && a8(q_norm_w) && a8(k_norm_w) && q_pitch % 2 == 0 &&
+                   k_pitch % 2 == 0 && v_pitch % 4 == 0 && aligned16(k_codes) && aligned16(v_codes) && aligned16(meta) &&
+                   (reinterpret_cast<uintptr_t>(q8) & 3u) == 0,
+               B200_E_ALIGN, "qkv_prepare_q15: q/k rows 8-byte, v rows and pool buffers 16-byte, q8 4-byte aligned");
+  const int64_t warps = tokens * (q_heads + 2 * kv_heads);
+  const int64_t blocks = (warps + 7) / 8;
+  B200_REQUIRE(blocks < (1ll << 31), B200_E_SHAPE, "qkv_prepare_q15: too many rows");
+  qkv_prepare_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)s>>>(positions, q, q_pitch, k, k_pitch, v, v_pitch, cos_sin,
+                                                                    max_pos, q_norm_w, k_norm_w, out_loc, k_codes, v_codes,
+                                                                    meta, q8, q_mul, q_shift, tokens, q_heads, kv_heads,
+                                                                    num_pages, with_fwht);
+  return check_launch("qkv_prepare_q15");
 }
 
 extern "C" int b200_kv_store_q15(const int32_t* k, int64_t k_pitch, const int32_t* v, int64_t v_pitch,

@@ -14,7 +14,7 @@ from typing import Optional
 
 import torch
 
-from ..attention import Int8PagedKVCache, decode_attention_int8_paged, extend_attention_int8_paged
+from ..attention import Int8PagedKVCache, decode_attention_int8_paged, extend_attention_int8_paged, qkv_rope_quant_store
 from ..kernel import fixed_point as fp
 from ..distributed import DistributedCommunicator
 from .tp_linear import PeerReduceBuffers, row_parallel_q15, row_parallel_q15_fused
@@ -83,13 +83,19 @@ class Qwen3DecoderLayerInteger:
         qkv = m.apply_quantised(w["qkv"], codes, absmax)
         t["qkv"] = qkv
         qd, kd = self.hq * 128, self.hk * 128
-        q, k, v = qkv[:, :qd].view(T, self.hq, 128), qkv[:, qd:qd + kd], qkv[:, qd + kd:]
-        q, k = fp.qk_norm_rope_fwht(batch.positions, q, k, self.cache, w.get("q_norm"), w.get("k_norm"))
-        t["q_rot"], t["k_rot"] = q, k
-        self.pool.store_kv(k, v, batch.out_loc, self.layer_id)
-        q8, _, q_absmax = fp.per_token_quant_int8_from_q15(q.reshape(T * self.hq, 128), return_absmax=True)
-        q_mul, q_shift = fp.absmax_to_mul_shift(q_absmax)
-        q8, q_mul, q_shift = q8.view(T, self.hq, 128), q_mul.view(T, self.hq), q_shift.view(T, self.hq)
+        if trace is None:
+            # one launch: q/k-norm, RoPE, rotation, K/V into the pool, q quantised
+            q8, q_mul, q_shift = qkv_rope_quant_store(batch.positions, qkv, self.hq, self.pool, self.layer_id, batch.out_loc,
+                                                      self.cache, w.get("q_norm"), w.get("k_norm"))
+        else:
+            # the same step by step, keeping the intermediates
+            q, k, v = qkv[:, :qd].view(T, self.hq, 128), qkv[:, qd:qd + kd], qkv[:, qd + kd:]
+            q, k = fp.qk_norm_rope_fwht(batch.positions, q, k, self.cache, w.get("q_norm"), w.get("k_norm"))
+            t["q_rot"], t["k_rot"] = q, k
+            self.pool.store_kv(k, v, batch.out_loc, self.layer_id)
+            q8, _, q_absmax = fp.per_token_quant_int8_from_q15(q.reshape(T * self.hq, 128), return_absmax=True)
+            q_mul, q_shift = fp.absmax_to_mul_shift(q_absmax)
+            q8, q_mul, q_shift = q8.view(T, self.hq, 128), q_mul.view(T, self.hq), q_shift.view(T, self.hq)
         t["q8"] = q8
         if batch.q_lens is None:
             attn = decode_attention_int8_paged(q8, q_mul, q_shift, self.pool, self.layer_id, batch.page_table,

@@ -331,3 +331,35 @@ def test_backend_forward_matches_oracle(phase):
     want = oattn.paged_attention(q8, q_mul, q_shift, ref_pool, [table[t] for t, _, _ in reqs], [dl for _, _, dl in reqs], q_lens)
     eq(got.reshape(T, HQ, 128), want)
     assert batch.attn_metadata.get_last_indices(3).tolist() == (np.cumsum(q_lens) - 1).tolist()
+
+
+def test_fused_qkv_preparation_equals_the_separate_steps():
+    """One launch for q/k-norm + RoPE + rotation + KV store + q quant gives the bits of the four-call sequence."""
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache, qkv_rope_quant_store
+    from mini_sgl_integer_b200.kernel import fixed_point as fp
+    rng = np.random.default_rng(17)
+    T, HQ, HK, P = 37, 8, 2, 12
+    qkv = rng.integers(-(2**21), 2**21, (T, (HQ + 2 * HK) * 128)).astype(np.int32)
+    qkv[3, HQ * 128: (HQ + 1) * 128] = 0                            # an all-zero K head row
+    qkv[5, :128] = 0                                                # an all-zero q head row
+    loc = rng.permutation(P * 16)[:T].astype(np.int32)
+    loc[7] = P * 16 + 3                                             # outside the pool: dropped
+    pos = rng.integers(0, 64, T).astype(np.int32)
+    inv = 1.0 / (1000000.0 ** (torch.arange(0, 128, 2, dtype=torch.float) / 128))
+    fr = torch.einsum("i,j -> ij", torch.arange(64, dtype=torch.float), inv)
+    cache = torch.clamp(torch.round(torch.cat((fr.cos(), fr.sin()), -1) * 32768), -32768, 32767).to(torch.int32).cuda()
+    qn = d(rng.integers(2**11, 2**13, 128).astype(np.int32)); kn = d(rng.integers(2**12, 2**14, 128).astype(np.int32))
+    for qnw, knw in ((qn, kn), (None, None)):
+        a, b = Int8PagedKVCache(HK, 1, 128, P, "cuda"), Int8PagedKVCache(HK, 1, 128, P, "cuda")
+        dq = d(qkv)
+        q8, q_mul, q_shift = qkv_rope_quant_store(d(pos), dq, HQ, a, 0, d(loc), cache, qnw, knw)
+        qd, kd = HQ * 128, HK * 128
+        q, k = fp.qk_norm_rope_fwht(d(pos), dq[:, :qd].view(T, HQ, 128), dq[:, qd:qd + kd], cache, qnw, knw)
+        b.store_kv(k, dq[:, qd + kd:], d(loc), 0)
+        w8, _, am = fp.per_token_quant_int8_from_q15(q.reshape(T * HQ, 128), return_absmax=True)
+        wm, ws = fp.absmax_to_mul_shift(am)
+        eq(q8.cpu().numpy().reshape(T * HQ, 128), w8.cpu().numpy())
+        eq(q_mul.cpu().numpy().reshape(-1), wm.cpu().numpy().reshape(-1)); eq(q_shift.cpu().numpy().reshape(-1), ws.cpu().numpy().reshape(-1))
+        eq(a.k_cache(0).cpu().numpy(), b.k_cache(0).cpu().numpy())
+        eq(a.v_cache(0).cpu().numpy(), b.v_cache(0).cpu().numpy())
+        eq(a.meta(0).cpu().numpy(), b.meta(0).cpu().numpy())
