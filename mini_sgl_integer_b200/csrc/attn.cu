@@ -187,6 +187,7 @@ struct DecodeParams {
 constexpr int kDecodeWarps = 8;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 static_assert(kDecodeThreads >= kD, "the output stage maps one thread to one d");
+constexpr int kVPrefetchPages = 64;         // V pages per CTA requested into L2 during the exponential pass
 constexpr int kRingSlot = kSlotBytes + 384; // a pair of pages plus their two scale blocks (2 x 160 B), 128-byte granular
 // Both contractions run on the integer tensor-core MMA with the long dimension on M:
 //   dots^T [16 keys x 8 heads] = K page [16 x 128] . Q^T [128 x 8]        (4 k-steps of 32 d)
@@ -498,6 +499,13 @@ attn_decode_kernel(const DecodeParams p) {
   __syncthreads();
 
   // ---- phase 2: exponentials and their sum
+  // HBM idles while the CTAs of a wave, which start together, all sit in this scalar pass: ask L2 for the first
+  // V pages of the slice meanwhile (one 2 KB request per thread; 64 pages per CTA keep the resident CTAs'
+  // requests well inside L2 - 256 pages per CTA evicted them again and cost 8 %)
+  for (int i = tid; i < min(my_pages, kVPrefetchPages); i += kDecodeThreads) {
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.v_codes) + pages[i] * page_stride + (int64_t)kh * (kPage * kD);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], 2048;" ::"l"(src) : "memory");
+  }
   {
     int lsum[G];   // a thread sees at most S / threads keys, each e <= 2^16: no overflow
     int gm[G];
