@@ -363,3 +363,28 @@ def test_fused_qkv_preparation_equals_the_separate_steps():
         eq(a.k_cache(0).cpu().numpy(), b.k_cache(0).cpu().numpy())
         eq(a.v_cache(0).cpu().numpy(), b.v_cache(0).cpu().numpy())
         eq(a.meta(0).cpu().numpy(), b.meta(0).cpu().numpy())
+
+
+def test_decode_seeded_sweep_of_shapes_and_options():
+    """Random batches, group sizes, cluster sizes, row orders and output forms, both implementations."""
+    rng = np.random.default_rng(2024)
+    for trial in range(14):
+        G = int(rng.choice([1, 2, 4, 8]))
+        hk = int(rng.choice([1, 2]))
+        B = int(rng.integers(1, 10))
+        lens = rng.integers(0, 700, B).tolist()
+        if trial % 4 == 0:
+            lens[0] = 0
+        longest = max(max(lens), 1)
+        max_kv_len = int(longest + rng.integers(0, 40))
+        P = sum((l + 15) // 16 for l in lens) + 4
+        case = make_case(1000 + trial, lens, G * hk, hk, P)
+        pool = device_pool(case, P, hk)
+        want = oracle_decode(case)
+        want8, want_m = oattn.quant_heads_int8(want)
+        kw = dict(cluster=int(rng.choice([0, 1, 2, 4, 8])), impl="cluster",
+                  row_order=d(rng.permutation(B).astype(np.int32)) if trial % 2 else None)
+        o32, o8, om = run_decode(case, pool, max_kv_len, out_int8=True, **kw)
+        eq(o32.cpu().numpy(), want); eq(o8.cpu().numpy(), want8); eq(om.cpu().numpy(), want_m.reshape(B, -1))
+        o32 = run_decode(case, pool, max_kv_len, impl="split")
+        eq(o32.cpu().numpy(), want)
