@@ -824,19 +824,15 @@ static int attn_common(const int8_t* q, const int32_t* q_mul, const int32_t* q_s
   // Configuration.  Set-up, barriers and the final exchange are paid per CTA and a lone CTA needs no
   // cluster barrier, so one CTA per (row, KV head) wins whenever its slice state lets two CTAs share an
   // SM - with two ring slots per warp if that still fits, else one; longer contexts take the smallest
-  // cluster whose slices fit with two slots.
+  // cluster whose slices fit at all (fewer CTAs beat deeper rings in every measurement).
   const int G_static = 1536 + G * kD * 4 + 1024;   // the kernel's static shared arrays plus the per-CTA reserve
   const size_t two_per_sm = (size_t)(233472 / 2 - G_static);
   auto fits2 = [&](int c, int st) { return decode_smem_bytes(G, slice_keys(c), st) <= two_per_sm; };
   int stages;
   if (cluster == 0) {
-    if (fits2(1, 2)) { cluster = 1; stages = 2; }
-    else if (fits2(1, 1)) { cluster = 1; stages = 1; }
-    else {
-      cluster = 2;
-      while (cluster < 8 && !fits2(cluster, 2)) cluster *= 2;
-      stages = fits2(cluster, 2) ? 2 : 1;
-    }
+    cluster = 1;
+    while (cluster < 8 && !fits2(cluster, 1)) cluster *= 2;   // fewest CTAs per row first, ring depth second
+    stages = fits2(cluster, 2) ? 2 : 1;
   } else {
     B200_REQUIRE(cluster == 1 || cluster == 2 || cluster == 4 || cluster == 8, B200_E_UNSUPPORTED,
                  "attn_decode: cluster=%d (1, 2, 4 or 8)", cluster);
