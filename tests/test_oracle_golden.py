@@ -16,7 +16,7 @@ def _h(a):
 
 
 # sha256[:16] recorded from the reference when it was surveyed (independent of the fixtures file)
-SURVEYED = {
+KNOWN_HASHES = {
     "lut_inv_sqrt": "c7d47c832e40df55", "lut_exp2_silu": "223dc3376e651115", "lut_exp2_attn": "99d1c8dee3741fea",
     "A_rmsnorm": "3935613782a8f0b3", "B_fused_out": "1f86e04a20350267", "B_fused_res": "dce1cc6b7245a534",
     "C_silu": "d8d988a7612a6f06", "D_bfwht": "12bce265cebd12cb", "E_quant_codes": "8fd3c928e84ebcb7",
@@ -26,14 +26,14 @@ SURVEYED = {
 
 
 def test_fixture_hashes_match_survey(golden_hashes):
-    for k, v in SURVEYED.items():
+    for k, v in KNOWN_HASHES.items():
         assert golden_hashes[k] == v, k
 
 
 def test_luts_stored_and_recomputed():
-    assert _h(luts.inv_sqrt()) == SURVEYED["lut_inv_sqrt"]
-    assert _h(luts.exp2_silu()) == SURVEYED["lut_exp2_silu"]
-    assert _h(luts.exp2_attn()) == SURVEYED["lut_exp2_attn"]
+    assert _h(luts.inv_sqrt()) == KNOWN_HASHES["lut_inv_sqrt"]
+    assert _h(luts.exp2_silu()) == KNOWN_HASHES["lut_exp2_silu"]
+    assert _h(luts.exp2_attn()) == KNOWN_HASHES["lut_exp2_attn"]
     assert np.array_equal(luts.recompute_inv_sqrt(), luts.inv_sqrt())
     assert np.array_equal(luts.recompute_exp2_silu(), luts.exp2_silu())
     assert np.array_equal(luts.recompute_exp2_attn(), luts.exp2_attn())
@@ -41,10 +41,10 @@ def test_luts_stored_and_recomputed():
 
 def test_rmsnorm_chain(golden):
     out = ofp.rmsnorm_v2(golden["norm_x"], golden["norm_w"])
-    assert np.array_equal(out, golden["norm_out"]) and _h(out) == SURVEYED["A_rmsnorm"]
+    assert np.array_equal(out, golden["norm_out"]) and _h(out) == KNOWN_HASHES["A_rmsnorm"]
     o, r = ofp.fused_add_rmsnorm_v2(golden["norm_r"], golden["norm_x"], golden["norm_w"])
     assert np.array_equal(o, golden["fused_out"]) and np.array_equal(r, golden["fused_res"])
-    assert _h(o) == SURVEYED["B_fused_out"] and _h(r) == SURVEYED["B_fused_res"]
+    assert _h(o) == KNOWN_HASHES["B_fused_out"] and _h(r) == KNOWN_HASHES["B_fused_res"]
 
 
 def test_rmsnorm_edges(golden):
@@ -64,13 +64,13 @@ def test_rmsnorm_packed_and_wide(golden):
 
 def test_silu(golden):
     s = ofp.silu_and_mul(golden["silu_in"])
-    assert np.array_equal(s, golden["silu_out"]) and _h(s) == SURVEYED["C_silu"]
+    assert np.array_equal(s, golden["silu_out"]) and _h(s) == KNOWN_HASHES["C_silu"]
     assert np.array_equal(ofp.silu_and_mul(golden["silu_edge_in"]), golden["silu_edge_out"])
 
 
 def test_fwht(golden):
     f = ofp.blockwise_fwht_q15(golden["silu_out"], 128)
-    assert np.array_equal(f, golden["bfwht_out"]) and _h(f) == SURVEYED["D_bfwht"]
+    assert np.array_equal(f, golden["bfwht_out"]) and _h(f) == KNOWN_HASHES["D_bfwht"]
     for n in (64, 128, 256):
         assert np.array_equal(ofp.fwht_q15(golden[f"fwht{n}_in"]), golden[f"fwht{n}_out"])
     assert np.array_equal(ofp.fwht_q15(golden["fwht_sat_in"]), golden["fwht_sat_out"])
@@ -80,8 +80,8 @@ def test_fwht(golden):
 
 def test_quant(golden):
     q, s, _ = ofp.per_token_quant_from_q15(golden["bfwht_out"])
-    assert np.array_equal(q, golden["quant_codes"]) and _h(q) == SURVEYED["E_quant_codes"]
-    assert np.array_equal(s, golden["quant_scale"]) and _h(s) == SURVEYED["E_quant_scale"]
+    assert np.array_equal(q, golden["quant_codes"]) and _h(q) == KNOWN_HASHES["E_quant_codes"]
+    assert np.array_equal(s, golden["quant_scale"]) and _h(s) == KNOWN_HASHES["E_quant_scale"]
     q, s, _ = ofp.per_token_quant_from_q15(golden["quant_edge_in"])
     assert np.array_equal(q, golden["quant_edge_codes"])
     assert np.array_equal(s, golden["quant_edge_scale"])
@@ -97,7 +97,7 @@ def test_rope(golden):
     cache = _cache_from_rows(golden["rope_pos"], golden["rope_cache_rows"])
     q, k = ofp.rope_q15(golden["rope_pos"], golden["rope_q"], golden["rope_k"], cache)
     assert np.array_equal(q, golden["rope_q_out"]) and np.array_equal(k, golden["rope_k_out"])
-    assert _h(q) == SURVEYED["F_rope_q"] and _h(k) == SURVEYED["F_rope_k"]
+    assert _h(q) == KNOWN_HASHES["F_rope_q"] and _h(k) == KNOWN_HASHES["F_rope_k"]
     q, k = ofp.rope_fwht_q15(golden["rope_pos"], golden["rope_q"], golden["rope_k"], cache)
     assert np.array_equal(q, golden["ropefwht_q_out"]) and np.array_equal(k, golden["ropefwht_k_out"])
     cache = _cache_from_rows(golden["rope_edge_pos"], golden["rope_edge_cache_rows"])
@@ -128,7 +128,7 @@ def test_context_attention(golden):
                                       ms[0], ms[1], ms[2], [0, 16], [16, 32], causal)
         bits = oattn.q15_to_bf16_bits(out)
         assert np.array_equal(bits, golden[key])
-    assert _h(golden["attn_out_bf16_bits"]) == SURVEYED["H_attn_bf16"]
+    assert _h(golden["attn_out_bf16_bits"]) == KNOWN_HASHES["H_attn_bf16"]
 
 
 def _uniform_pool(k8, v8, k_ms, v_ms, pages):
