@@ -297,6 +297,26 @@ __device__ __forceinline__ int silu_mul_elem(int g, int u, const int32_t* __rest
   return (hi >> 15) == (res >> 31) ? res : (hi < 0 ? (int)(-2147483647 - 1) : 2147483647);
 }
 
+// The same element with the sigmoid term read from a direct table: E and s = (E << 16) / (65536 + E) depend only
+// on key = (-|g| * 94549) >> 22 (the exponent's integer part and the 10 table bits), and s is 0 below key -19456.
+#include "silu_sneg.inc"
+constexpr int kSnegEntries = 19457;
+static __device__ __align__(16) const uint16_t g_silu_sneg[kSnegEntries] = {B200_LUT_kSiluSneg};
+
+__device__ __forceinline__ int silu_mul_elem_table(int g, int u, const uint16_t* __restrict__ sneg_tab) {
+  const int a = g > 0 ? -g : g;                                  // -|g|
+  const long long prod = (long long)a * 94549LL;
+  const int key = (int)(prod >> 22) + (kSnegEntries - 1);        // prod >> 22 >= -2^26: fits
+  const unsigned sneg = key < 0 ? 0u : (unsigned)sneg_tab[key];
+  const int sig = (int)(g > 0 ? 65536u - sneg : sneg);
+  const long long gs = (long long)g * (long long)sig;
+  const int t = (int)__funnelshift_r((unsigned)gs, (unsigned)(gs >> 32), 16);
+  const long long tu = (long long)t * (long long)u;
+  const int hi = (int)(tu >> 32);
+  const int res = (int)__funnelshift_r((unsigned)tu, (unsigned)hi, 16);
+  return (hi >> 15) == (res >> 31) ? res : (hi < 0 ? (int)(-2147483647 - 1) : 2147483647);
+}
+
 // FWHT-128 of a block spread over an 8-lane group: each lane holds 16 values, index
 // i = e + 4*lane8 + 32*k for val[4*k + e] (e = 0..3 inside an int4, k = 0..3).
 // Stage order is the reference's (step 1, 2, 4, ... 64), with saturation at every stage.
@@ -365,21 +385,30 @@ __device__ __forceinline__ void fwht128_group_nosat(int (&val)[16], int lane8) {
   }
 }
 
-// One CTA per row.  An 8-lane group takes the 128-blocks group, group + ngroups, ...; the
-// SiLU*up (+ rotation) results of the whole row are parked in shared memory until the row's
-// absmax is known, then quantised from there: gate and up are read from HBM once.
-template <bool FWHT, bool QUANT>
+// One CTA per row at a time (the CTAs walk the rows with the grid as stride, so the tables are staged once per
+// CTA).  An 8-lane group takes the 128-blocks group, group + ngroups, ...; the SiLU*up (+ rotation) results of
+// the whole row are parked in shared memory until the row's absmax is known, then quantised from there: gate
+// and up are read from HBM once.  TABLE: the sigmoid term comes from the 38 KB direct table instead of the exp2
+// table, a shift and an exact division (used whenever the row buffer leaves room for it).
+template <bool FWHT, bool QUANT, bool TABLE>
 __global__ void __launch_bounds__(512, 2)
 silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_out,
                  int8_t* __restrict__ codes, float* __restrict__ scale,
-                 int32_t* __restrict__ absmax, int I) {
-  extern __shared__ __align__(16) int32_t rowbuf[];   // QUANT: [I] results of the row; then the LUT
+                 int32_t* __restrict__ absmax, int64_t rows, int I) {
+  extern __shared__ __align__(16) int32_t rowbuf[];   // QUANT: [I] results of the row; then the table
   __shared__ int red32[33];
   int32_t* lut = rowbuf + (QUANT ? I : 0);
-  for (int i = threadIdx.x; i < 1024; i += blockDim.x) lut[i] = g_exp2_silu_lut[i];
+  const uint16_t* sneg_tab = reinterpret_cast<const uint16_t*>(lut);
+  if (TABLE) {
+    const int4* src = reinterpret_cast<const int4*>(g_silu_sneg);      // 19457 entries: 2432 int4 + one entry
+    for (int i = threadIdx.x; i < kSnegEntries / 8; i += blockDim.x) reinterpret_cast<int4*>(lut)[i] = src[i];
+    if (threadIdx.x == 0) reinterpret_cast<uint16_t*>(lut)[kSnegEntries - 1] = g_silu_sneg[kSnegEntries - 1];
+  } else {
+    for (int i = threadIdx.x; i < 1024; i += blockDim.x) lut[i] = g_exp2_silu_lut[i];
+  }
   __syncthreads();
 
-  const int64_t row = blockIdx.x;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
   const int lane8 = threadIdx.x & 7;
   const int group = threadIdx.x >> 3;
   const int ngroups = blockDim.x >> 3;
@@ -402,10 +431,17 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
         g = __ldcs(reinterpret_cast<const int4*>(gate + off));
         u = __ldcs(reinterpret_cast<const int4*>(up + off));
       }
-      val[4 * k + 0] = silu_mul_elem(g.x, u.x, lut);
-      val[4 * k + 1] = silu_mul_elem(g.y, u.y, lut);
-      val[4 * k + 2] = silu_mul_elem(g.z, u.z, lut);
-      val[4 * k + 3] = silu_mul_elem(g.w, u.w, lut);
+      if (TABLE) {
+        val[4 * k + 0] = silu_mul_elem_table(g.x, u.x, sneg_tab);
+        val[4 * k + 1] = silu_mul_elem_table(g.y, u.y, sneg_tab);
+        val[4 * k + 2] = silu_mul_elem_table(g.z, u.z, sneg_tab);
+        val[4 * k + 3] = silu_mul_elem_table(g.w, u.w, sneg_tab);
+      } else {
+        val[4 * k + 0] = silu_mul_elem(g.x, u.x, lut);
+        val[4 * k + 1] = silu_mul_elem(g.y, u.y, lut);
+        val[4 * k + 2] = silu_mul_elem(g.z, u.z, lut);
+        val[4 * k + 3] = silu_mul_elem(g.w, u.w, lut);
+      }
     }
     if (FWHT) {
 #pragma unroll
@@ -432,7 +468,7 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
       for (int j = 0; j < 16; ++j) m = max(m, abs_wrap(val[j]));
     }
   }
-  if (!QUANT) return;
+  if (!QUANT) continue;
   m = max(1, block_max(m, red32));     // its barriers also order the rowbuf writes before the reads
   const float mf = __int2float_rn(m);
   const float my = __frcp_rn(mf);
@@ -453,6 +489,8 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   if (threadIdx.x == 0) {
     scale[row] = quant_scale(mf);
     absmax[row] = m;
+  }
+  __syncthreads();                     // the row buffer and the reduction scratch are reused by the next row
   }
 }
 
@@ -663,21 +701,31 @@ static int launch_silu(const int32_t* gu, int32_t* q15, int8_t* codes, float* sc
   const int nblocks = inter / 128;
   int threads = ((nblocks * 8 + 31) / 32) * 32;
   if (threads > 512) threads = 512;
-  const size_t smem = (size_t)((quant ? inter : 0) + 1024) * sizeof(int32_t);
-#define B200_SILU_LAUNCH(F, Q)                                                                          \
-  do {                                                                                                  \
-    cudaError_t e = cudaFuncSetAttribute(silu_rows_kernel<F, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                         (int)smem);                                                    \
-    if (e != cudaSuccess) {                                                                             \
-      set_error("silu_mul_q15: cudaFuncSetAttribute: %s", cudaGetErrorString(e));                       \
-      return B200_E_CUDA;                                                                               \
-    }                                                                                                   \
-    silu_rows_kernel<F, Q><<<(unsigned)rows, threads, smem, st>>>(gu, q15, codes, scale, absmax, inter); \
+  // the direct sigmoid table (38 KB) is used when it fits beside the row buffer with two CTAs per SM
+  constexpr size_t kTableBytes = ((size_t)kSnegEntries * 2 + 15) / 16 * 16;
+  const size_t row_bytes = (size_t)(quant ? inter : 0) * sizeof(int32_t);
+  const bool table = row_bytes + kTableBytes <= 110 * 1024;
+  const size_t smem = row_bytes + (table ? kTableBytes : 1024 * sizeof(int32_t));
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    sms = 148;
+  const unsigned grid = (unsigned)(rows < 2 * (int64_t)sms ? rows : 2 * (int64_t)sms);
+#define B200_SILU_LAUNCH(F, Q, T)                                                                          \
+  do {                                                                                                     \
+    cudaError_t e = cudaFuncSetAttribute(silu_rows_kernel<F, Q, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                       \
+    if (e != cudaSuccess) {                                                                                \
+      set_error("silu_mul_q15: cudaFuncSetAttribute: %s", cudaGetErrorString(e));                          \
+      return B200_E_CUDA;                                                                                  \
+    }                                                                                                      \
+    silu_rows_kernel<F, Q, T><<<grid, threads, smem, st>>>(gu, q15, codes, scale, absmax, rows, inter);    \
   } while (0)
-  if (fwht && quant) B200_SILU_LAUNCH(true, true);
-  else if (fwht) B200_SILU_LAUNCH(true, false);
-  else if (quant) B200_SILU_LAUNCH(false, true);
-  else B200_SILU_LAUNCH(false, false);
+#define B200_SILU_LAUNCH_T(F, Q) do { if (table) B200_SILU_LAUNCH(F, Q, true); else B200_SILU_LAUNCH(F, Q, false); } while (0)
+  if (fwht && quant) B200_SILU_LAUNCH_T(true, true);
+  else if (fwht) B200_SILU_LAUNCH_T(true, false);
+  else if (quant) B200_SILU_LAUNCH_T(false, true);
+  else B200_SILU_LAUNCH_T(false, false);
+#undef B200_SILU_LAUNCH_T
 #undef B200_SILU_LAUNCH
   return check_launch("silu_mul_q15");
 }
