@@ -51,7 +51,8 @@ static int elementwise_grid(int64_t n, int threads) {
 
 // ============================================================================ RMSNorm rows
 // One CTA per row; thread t owns int4 vectors t, t+T, ... (VPT of them).
-template <int VPT>
+// FULL: the row is exactly blockDim.x * VPT vectors long (no bounds checks on the vector index).
+template <int VPT, bool FULL>
 __global__ void __launch_bounds__(1024)
 rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ res,
                     const int32_t* __restrict__ w, int32_t* __restrict__ res_out,
@@ -71,7 +72,7 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     int4 a = make_int4(0, 0, 0, 0);
-    if (idx < nvec) {
+    if (FULL || idx < nvec) {
       a = __ldcs(xr + idx);
       if (rr) {
         int4 b = __ldcs(rr + idx);
@@ -103,7 +104,7 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
-    if (idx < nvec) {
+    if (FULL || idx < nvec) {
       const int4 ww = __ldg(wr + idx);
       int4 o;
       o.x = nr.zero ? 0 : norm_apply(v[i].x, inv, ww.x, nr.p);
@@ -124,7 +125,7 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * blockDim.x;
-      if (idx < nvec) {
+      if (FULL || idx < nvec) {
         co[idx] = pack4(quant_code_fast_small(v[i].x, mf, my), quant_code_fast_small(v[i].y, mf, my),
                         quant_code_fast_small(v[i].z, mf, my), quant_code_fast_small(v[i].w, mf, my));
       }
@@ -133,7 +134,7 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * blockDim.x;
-      if (idx < nvec) {
+      if (FULL || idx < nvec) {
         co[idx] = pack4(quant_code_fast(v[i].x, mf, my), quant_code_fast(v[i].y, mf, my),
                         quant_code_fast(v[i].z, mf, my), quant_code_fast(v[i].w, mf, my));
       }
@@ -674,8 +675,13 @@ extern "C" int b200_rmsnorm_q15(const int32_t* x, const int32_t* residual, const
   B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(residual) && aligned16(residual_out) &&
                    aligned16(norm_out) && ((uintptr_t)codes & 3u) == 0,
                B200_E_ALIGN, "rmsnorm_q15: int32 buffers must be 16-byte aligned (codes 4-byte)");
-  DISPATCH_VPT(p.vpt, (rmsnorm_rows_kernel<V><<<(unsigned)rows, p.threads, 0, (cudaStream_t)s>>>(
-                          x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
+  if ((hidden >> 2) == p.threads * p.vpt) {
+    DISPATCH_VPT(p.vpt, (rmsnorm_rows_kernel<V, true><<<(unsigned)rows, p.threads, 0, (cudaStream_t)s>>>(
+                            x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
+  } else {
+    DISPATCH_VPT(p.vpt, (rmsnorm_rows_kernel<V, false><<<(unsigned)rows, p.threads, 0, (cudaStream_t)s>>>(
+                            x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
+  }
   return check_launch("rmsnorm_q15");
 }
 
