@@ -119,6 +119,8 @@ struct GemmParams {
   int32_t* acc_out;         // nullable
   int M, N, K;
   int splits;               // weights-stationary mode: parts of K per block of weight rows (1 = none)
+  int full_blocks;          // weights-stationary mode: the first full_blocks blocks of weight rows are never split
+                            // (one tile each, finished in the GEMM kernel); `splits` applies to the blocks after them
   int32_t* partial;         // splits > 1: int32 [M, N] that the parts are added into (zeroed before the launch)
   int n_peers;              // > 0: tensor-parallel reduction - every part is added into each of these [M, N] buffers
   int32_t* peer[8];         //      (this rank's and its peers', mapped into this process: NVLink peer memory)
@@ -129,6 +131,22 @@ __device__ __forceinline__ void mbar_arrive(unsigned bar) {
 }
 __device__ __forceinline__ void epilogue_bar_sync() {   // the epilogue threads only
   asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+}
+
+// Weights-stationary tile list: one whole-K tile per unsplit block, then `splits` parts of K per remaining block.
+struct WsTile { int n_blk, kb0, kb1; bool split; };
+__device__ __forceinline__ WsTile ws_tile(const GemmParams& p, int tile, int num_kb) {
+  WsTile t;
+  if (tile < p.full_blocks) {
+    t.n_blk = tile; t.kb0 = 0; t.kb1 = num_kb; t.split = false;
+    return t;
+  }
+  const int r = tile - p.full_blocks, blk = r / p.splits, kb_per = (num_kb + p.splits - 1) / p.splits;
+  t.n_blk = p.full_blocks + blk;
+  t.kb0 = (r - blk * p.splits) * kb_per;
+  t.kb1 = min(num_kb, t.kb0 + kb_per);
+  t.split = p.splits > 1;
+  return t;
 }
 
 __device__ __forceinline__ int requant_one(int acc, int cm, int s) {
@@ -194,10 +212,9 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (p.K + kBK - 1) / kBK;
   // WS: a tile is (block of 128 weight rows, part of K); otherwise (block of BN weight rows, block of 128 tokens)
-  const int m_tiles = WS ? p.splits : (p.M + kBM - 1) / kBM;
+  const int m_tiles = WS ? 1 : (p.M + kBM - 1) / kBM;
   const int n_tiles = WS ? (p.N + kBM - 1) / kBM : (p.N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
-  const int kb_per = WS ? (num_kb + p.splits - 1) / p.splits : num_kb;
+  const int num_tiles = WS ? p.full_blocks + (n_tiles - p.full_blocks) * p.splits : m_tiles * n_tiles;
   const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
   const unsigned tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
 
@@ -226,8 +243,11 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       unsigned it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int n_blk = tile / m_tiles, m_blk = tile - n_blk * m_tiles;
-        const int kb0 = WS ? m_blk * kb_per : 0, kb1 = WS ? min(num_kb, kb0 + kb_per) : num_kb;
+        int n_blk = tile / m_tiles, m_blk = tile - n_blk * m_tiles, kb0 = 0, kb1 = num_kb;
+        if (WS) {
+          const WsTile t = ws_tile(p, tile, num_kb);
+          n_blk = t.n_blk; kb0 = t.kb0; kb1 = t.kb1;
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
           ok = mbar_wait(empty0 + 8 * s, ph ^ 1, 1);
@@ -251,8 +271,11 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!ok) break;
         tcgen05_fence_after();
         const unsigned tmem_d = tmem_base + slot * BN;
-        const int m_blk = tile % m_tiles;
-        const int kb0 = WS ? m_blk * kb_per : 0, kb1 = WS ? min(num_kb, kb0 + kb_per) : num_kb;
+        int kb0 = 0, kb1 = num_kb;
+        if (WS) {
+          const WsTile t = ws_tile(p, tile, num_kb);
+          kb0 = t.kb0; kb1 = t.kb1;
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
           ok = mbar_wait(full0 + 8 * s, ph, 2);
@@ -286,9 +309,10 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int32_t* cs = col_scale + slot * 2 * BN;
       if (WS) {
         // rows of the accumulator tile are weight channels, columns are tokens
-        const int ch = n_blk * kBM + q * 32 + lane;
-        const bool direct = p.splits == 1 && p.n_peers == 0;
-        const bool empty_part = m_blk * kb_per >= num_kb;      // a part of K with no k-blocks: nothing was accumulated
+        const WsTile wt = ws_tile(p, tile, num_kb);
+        const int ch = wt.n_blk * kBM + q * 32 + lane;
+        const bool direct = !wt.split && p.n_peers == 0;
+        const bool empty_part = wt.kb0 >= wt.kb1;      // a part of K with no k-blocks: nothing was accumulated
         if (direct && p.out_q15) {
           for (int c = et; c < BN; c += 32 * kEpiWarps) {
             const int t = min(c, p.M - 1);
@@ -601,7 +625,7 @@ gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 __global__ void __launch_bounds__(256)
 splitk_epilogue_kernel(const int32_t* partial, const GemmParams p) {
   const int t = blockIdx.y;
-  const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
+  const int c = p.full_blocks * kBM + (blockIdx.x * 256 + threadIdx.x) * 4;   // only the split blocks' columns
   if (c >= p.N) return;
   int xm, xs;
   if (p.x_absmax) absmax_to_ms_dev(__ldg(p.x_absmax + t), &xm, &xs);
@@ -675,7 +699,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
     set_error("gemm_w8a8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return B200_E_CUDA;
   }
-  const int tiles = WS ? ((p.N + kBM - 1) / kBM) * p.splits : ((p.N + BN - 1) / BN) * ((p.M + kBM - 1) / kBM);
+  const int tiles = WS ? p.full_blocks + ((p.N + kBM - 1) / kBM - p.full_blocks) * p.splits
+                       : ((p.N + BN - 1) / BN) * ((p.M + kBM - 1) / kBM);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   gemm_w8a8_kernel<BN, STAGES, WS><<<grid, kGemmThreads, smem, st>>>(ma, mb, p);
   return check_launch("gemm_w8a8");
@@ -718,23 +743,30 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
   GemmParams p;
   p.x_absmax = x_absmax; p.x_mul = x_mul; p.x_shift = x_shift; p.w_mul = w_mul; p.w_shift = w_shift;
   p.out_q15 = out_q15; p.acc_out = acc_out; p.M = (int)m; p.N = (int)n; p.K = (int)k;
-  p.splits = 1; p.partial = nullptr; p.n_peers = 0;
+  p.splits = 1; p.full_blocks = 0; p.partial = nullptr; p.n_peers = 0;
   cudaStream_t st = (cudaStream_t)s;
   const int w_blocks = (int)((n + kBM - 1) / kBM), num_kb = (int)((k + kBK - 1) / kBK);
   if (m <= 128 || (m <= 256 && w_blocks < sm_count())) {
     // decode sizes: weights-stationary, K split so that about one CTA per SM streams the weights
     // (256 tokens against a weight matrix with at least one 128-row block per SM do as well on the other path)
-    int splits = sm_count() / w_blocks;
+    // With more blocks than SMs the whole waves run unsplit and only the blocks of the last, partial wave are
+    // split, so that it costs a fraction of a wave instead of a whole one.
+    const int tail = w_blocks % sm_count();
+    const int split_blocks = w_blocks < sm_count() ? w_blocks : tail;
+    int splits = split_blocks > 0 ? sm_count() / split_blocks : 1;
     splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
     while (splits > 1 && num_kb / splits < 4) --splits;
     while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;   // no empty part
     p.splits = splits;
+    p.full_blocks = splits > 1 ? w_blocks - split_blocks : 0;
+    const int64_t col0 = (int64_t)p.full_blocks * kBM;     // first column that parts are added into
     if (splits > 1) {
       // the parts are added into the exact-accumulator output if the caller wants it, else into the
       // Q15.16 output buffer itself, which the epilogue kernel then rewrites in place
       p.partial = acc_out ? acc_out : out_q15;
-      cudaError_t e = cudaMemsetAsync(p.partial, 0, (size_t)m * n * sizeof(int32_t), st);
-      B200_REQUIRE(e == cudaSuccess, B200_E_CUDA, "gemm_w8a8: cudaMemsetAsync: %s", cudaGetErrorString(e));
+      cudaError_t e = cudaMemset2DAsync(p.partial + col0, (size_t)n * sizeof(int32_t), 0, (size_t)(n - col0) * sizeof(int32_t),
+                                        (size_t)m, st);
+      B200_REQUIRE(e == cudaSuccess, B200_E_CUDA, "gemm_w8a8: cudaMemset2DAsync: %s", cudaGetErrorString(e));
     }
     const int bn = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
     B200_REQUIRE(make_map(&ma, w8, n, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for w8");
@@ -747,7 +779,7 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
       default: rc = launch_gemm<32, 10, true>(ma, mb, p, st); break;
     }
     if (rc != B200_OK || splits == 1 || !out_q15) return rc;
-    splitk_epilogue_kernel<<<dim3((unsigned)((n + 1023) / 1024), (unsigned)m), 256, 0, st>>>(p.partial, p);
+    splitk_epilogue_kernel<<<dim3((unsigned)((n - col0 + 1023) / 1024), (unsigned)m), 256, 0, st>>>(p.partial, p);
     return check_launch("gemm_w8a8 (split-K epilogue)");
   }
   B200_REQUIRE(make_map(&ma, x8, m, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");
@@ -806,6 +838,7 @@ extern "C" int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, i
   while (splits > 1 && num_kb / splits < 4) --splits;
   while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;
   p.splits = splits;
+  p.full_blocks = 0;
   CUtensorMap ma, mb;
   const int bn = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
   B200_REQUIRE(make_map(&ma, w8, n, k, kBM), B200_E_CUDA, "gemm_w8a8_reduce_peers: cuTensorMapEncodeTiled failed for w8");

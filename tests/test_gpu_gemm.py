@@ -48,12 +48,14 @@ def run_case(M, N, K, seed, per_channel_shift=False):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 128, 512), (64, 256, 1024), (1, 128, 256), (200, 384, 2048),
-                                   (130, 200, 144), (64, 4096, 1024), (64, 1024, 3072), (256, 6144, 1024)])
+                                   (130, 200, 144), (64, 4096, 1024), (64, 1024, 3072), (256, 6144, 1024),
+                                   (48, 24576, 512), (100, 19240, 1024)])   # more weight blocks than SMs: split tail
 def test_gemm_vs_oracle(M, N, K):
     run_case(M, N, K, M + N + K)
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 4096, 12288), (33, 1024, 3072), (129, 6144, 4096), (7, 200, 2064), (256, 24576, 1024)])
+@pytest.mark.parametrize("M,N,K", [(256, 4096, 12288), (33, 1024, 3072), (129, 6144, 4096), (7, 200, 2064), (256, 24576, 1024),
+                                   (64, 24576, 1024), (17, 19240, 2048)])
 def test_decode_sizes_without_accumulator_output(M, N, K):
     """M <= 256 runs weights-stationary with K split over CTAs; with only the Q15.16 output requested the
     partial sums are gathered in that buffer and requantised in place."""
