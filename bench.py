@@ -1,24 +1,33 @@
 #!/usr/bin/env python
-"""Benchmark of the int8 paged decode attention (the headline workload).
+"""Benchmark of the integer-only W8A8 forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
 
-One step = one decode-attention call over a batch of 64 sequences (32 query heads, 8 KV heads,
-head_dim 128, 16-token pages, contexts uniform in [512, 4096], page tables drawn from a
-200k-page int8 pool with a (multiplier, shift) per token and KV head).  Inputs are synthetic
-and seeded.  With N > 1 every rank holds its own pool and batch (independent sequences, no
-collective on the data path: weak scaling) and the rate is the sum over ranks.
+Default workload ("model"): one greedy DECODE STEP of a Qwen3-8B-shaped integer model (36 layers, hidden 4096,
+32 q / 8 kv heads, intermediate 12288, vocabulary 151936; random-init int8 weights) for a batch of 256 sequences
+whose contexts are drawn from U[100, 2048] (the spread of prompt + generated lengths of the offline run that
+the model configuration names), 16-token int8 KV pages.  One step = bookkeeping on the device, embedding,
+36 layers, final norm, integer lm_head, arg-max, the token fed back; captured once in a CUDA graph and replayed.
+With N > 1 (torchrun, one rank per GPU) the SAME step is split tensor-parallel over the N ranks - attention by
+KV head, qkv / gate_up by output channel, o / down by input feature with the int32 partial sums added over
+NVLink peer memory inside the GEMM kernel, lm_head by vocabulary rows - so N measures strong scaling, and a
+parity check inside the run compares a tensor-parallel layer with the unsplit layer bit for bit.
 
 The script prints ONE JSON line:
-  value      tokens/s with everything resident in HBM (CUDA-event time over the K steps, max over ranks)
-  e2e        the same rate through the C ABI with the step's inputs (queries, their scales, page table,
-             lengths) coming from pinned host memory and the int8 result copied back, every step; the
-             KV pool is the cache itself and stays resident
-  roofline   algorithmic bytes of one launch / mean kernel time, against the measured HBM copy peak
-  cpu_baseline  the CPU oracle (numpy port of the reference arithmetic) timed on this host
+  value        decode tokens/s of the whole job (batch / step time; CUDA events over K graph replays, max over ranks)
+  e2e          the same through the public model API with the step's token ids coming from pinned host memory and
+               the new ids copied back to it, every step
+  roofline     weights + KV bytes a rank must stream per step / step time, against the measured HBM copy peak;
+               `dominant_kernel` is the decode attention timed alone on the same batch
+  kernels      (N = 1) the other metric components: decode attention GB/s on the attention configuration,
+               W8A8 GEMM int8 TOPS at M = 4096 with the library's int8 GEMM beside it, the fused row kernels
+  tp_parity    (N > 1) "ok" when the tensor-parallel layer equals the unsplit layer on every rank
+  tp32b        (N > 1) one Qwen3-32B-shaped layer, batch 256, contexts U[1024, 8192], split over the same ranks
+  cpu_baseline (N = 1) the numpy oracle port of one decoder layer timed on the host cores, scaled to 36 layers
 
-``--impl reference`` times only the CPU oracle port on the host cores (the reference's attention is
-Python/torch code that cannot travel with this repository; its arithmetic is restated in oracle/).
+`--impl reference` times only that CPU port (the reference's Python/torch code cannot travel with this
+repository; its arithmetic is restated in oracle/).  Other workloads (`--workload attn|gemm|rowops|prefill|
+tp_layer`) print the same kind of line for one component.
 """
 from __future__ import annotations
 
@@ -35,31 +44,13 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-WORKLOAD = dict(batch=64, q_heads=32, kv_heads=8, head_dim=128, page=16, ctx_lo=512, ctx_hi=4096, pool_pages=200_000)
-METRIC = "int8 paged decode attention throughput (decode tokens/s; HBM GB/s in roofline)"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
-# profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES = 334636800   # dram__bytes_read + dram__bytes_write of one launch (ncu capture of this kernel)
-
-
-def draw_lens(seed: int) -> np.ndarray:
-    return np.random.default_rng(seed).integers(WORKLOAD["ctx_lo"], WORKLOAD["ctx_hi"] + 1, WORKLOAD["batch"])
-
-
-def row_order_hint(lens: np.ndarray, scheme: str) -> np.ndarray:
-    """The order in which the decode kernel should take the batch rows (a permutation, int32): longest first
-    ("lpt", what a scheduler that knows the lengths passes) or as given ("identity")."""
-    if scheme == "identity":
-        return np.arange(len(lens), dtype=np.int32)
-    return np.argsort(-lens, kind="stable").astype(np.int32)
-
-
-def algorithmic_bytes(lens: np.ndarray) -> int:
-    """Minimum HBM traffic of one launch: K and V codes, their scales, page ids, q in, int8 out."""
-    w = WORKLOAD
-    per_seq = lens.astype(np.int64) * w["kv_heads"] * w["head_dim"] * 2 + lens.astype(np.int64) * w["kv_heads"] * 2 * 5 \
-        + ((lens + 15) // 16).astype(np.int64) * 4
-    return int(per_seq.sum() + w["batch"] * w["q_heads"] * w["head_dim"] * 2)
+ATTN_CFG = dict(batch=64, q_heads=32, kv_heads=8, head_dim=128, page=16, ctx_lo=512, ctx_hi=4096, pool_pages=200_000)
+MODEL_CFG = dict(layers=36, hidden=4096, q_heads=32, kv_heads=8, inter=12288, vocab=151936, batch=256, ctx_lo=100, ctx_hi=2048)
+TP32B_CFG = dict(hidden=5120, q_heads=64, kv_heads=8, inter=25600, layers=64, batch=256, ctx_lo=1024, ctx_hi=8192)
+METRIC = "decode tokens/s, integer-only W8A8 Qwen3-8B-shaped model (tensor-parallel over the GPUs)"
+# DRAM bytes (read + write) of ONE launch of the decode-attention kernel on the attention configuration, from an
+# ncu capture of that kernel; a constant, not measured by this script - see `traffic_source` in the line
+ATTN_NCU_TRAFFIC = {"bytes": 334636800, "source": "ncu capture of attn_decode_kernel<4,1> on this workload (dram__bytes_read.sum + dram__bytes_write.sum), not re-measured by this run"}
 
 
 def measured_peak():
@@ -70,67 +61,8 @@ def measured_peak():
         return 6650.0, "fallback"
 
 
-# ----------------------------------------------------------------------------- CPU oracle leg
-def cpu_oracle_rate(seed: int, n_seq: int, repeats: int = 1):
-    """Tokens/s of the numpy oracle on the first ``n_seq`` sequences of the seeded batch."""
-    from oracle import attention as oattn
-    w = WORKLOAD
-    lens = draw_lens(seed)[:n_seq]
-    rng = np.random.default_rng(seed + 1)
-    n_pg = (lens + 15) // 16
-    pool = oattn.PagedKV(int(n_pg.sum()), w["kv_heads"], w["head_dim"])
-    pool.k_codes[:] = rng.integers(-127, 128, pool.k_codes.shape, dtype=np.int8)
-    pool.v_codes[:] = rng.integers(-127, 128, pool.v_codes.shape, dtype=np.int8)
-    pool.meta[:, :, 0:32] = rng.integers(2**30, 2**31, pool.meta[:, :, 0:32].shape)
-    pool.meta[:, :, 32:36].view(np.int8)[:] = rng.integers(35, 39, (pool.P, pool.H, 16))
-    pool.meta[:, :, 36:40].view(np.int8)[:] = rng.integers(33, 38, (pool.P, pool.H, 16))
-    perm = rng.permutation(pool.P)
-    tables, off = [], 0
-    for n in n_pg:
-        tables.append(perm[off:off + n]); off += n
-    q = rng.integers(-127, 128, (n_seq, w["q_heads"], w["head_dim"]), dtype=np.int8)
-    qm = rng.integers(2**30, 2**31, (n_seq, w["q_heads"])); qs = rng.integers(43, 46, (n_seq, w["q_heads"]))
-    t0 = time.perf_counter()
-    for _ in range(repeats):
-        out = oattn.paged_attention(q, qm, qs, pool, tables, lens, [1] * n_seq)
-        oattn.quant_heads_int8(out)
-    dt = (time.perf_counter() - t0) / repeats
-    return n_seq / dt, dt
-
-
-def host_threads() -> int:
-    try:
-        import torch
-        return int(torch.get_num_threads())
-    except Exception:
-        return os.cpu_count() or 1
-
-
-def run_reference(args) -> None:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    n_seq = 16
-    for _ in range(args.warmup):
-        cpu_oracle_rate(0, 4)
-    t0 = time.perf_counter()
-    total = 0.0
-    for _ in range(args.steps):
-        _, dt = cpu_oracle_rate(0, n_seq)
-        total += dt
-    rate = n_seq * args.steps / total
-    sample = f"{n_seq} of the 64 sequences per step (all 32 heads), numpy oracle port, BLAS threads for the dot products"
-    line = {
-        "impl": "reference", "metric": METRIC, "value": rate, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "int8 paged decode attention, batch 64, 32q/8kv heads, head_dim 128, page 16, "
-                               "ctx U[512,4096] (CPU sample)", **WORKLOAD},
-        "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": host_threads(), "kind": "port", "sample": sample},
-        "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
-    }
-    print(json.dumps(line))
+def env_ranks():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
 
 
 # ----------------------------------------------------------------------------- clocks sampler
@@ -177,508 +109,676 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
-# ----------------------------------------------------------------------------- GPU leg
-def run_ours(args) -> None:
-    import torch
-    import torch.distributed as dist
+# ----------------------------------------------------------------------------- CPU oracle legs
+def blas_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+        n = [int(i.get("num_threads", 1)) for i in threadpool_info() if i.get("user_api") == "blas"]
+        return max(n) if n else 1
+    except Exception:
+        return 1
 
-    from mini_sgl_integer_b200 import _lib
-    from mini_sgl_integer_b200.attention import Int8PagedKVCache
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    w = WORKLOAD
-    B, Hq, Hkv, D, P = w["batch"], w["q_heads"], w["kv_heads"], w["head_dim"], args.pool_pages
+def cpu_layer_sample(n_tok: int, seed: int = 0):
+    """One decoder layer of the 8B shape through the numpy oracle on `n_tok` decode tokens (contexts drawn like the
+    GPU batch).  Returns the seconds of the layer pass."""
+    from oracle import layer as olayer
+    from tests.layer_util import build, make_weights, rope_cache
+    c = MODEL_CFG
+    rng = np.random.default_rng(seed)
+    kv_lens = [int(v) for v in rng.integers(c["ctx_lo"], c["ctx_hi"] + 1, n_tok)]
+    q_lens = [1] * n_tok
+    pages = sum((l + 15) // 16 for l in kv_lens) + 4
+    key = (n_tok, seed)
+    st = _CPU_CACHE.get(key)
+    if st is None:
+        w = make_weights(rng, c["q_heads"], c["kv_heads"], c["hidden"], c["inter"], wide=True)
+        ref_pool, pre, tables, table, positions, out_loc = build(rng, kv_lens, q_lens, pages, c["kv_heads"])
+        x = np.clip(np.rint(rng.normal(0, 2**15, (n_tok, c["hidden"]))), -(2**23), 2**23).astype(np.int32)
+        res = np.clip(np.rint(rng.normal(0, 2**15, (n_tok, c["hidden"]))), -(2**23), 2**23).astype(np.int32)
+        st = (w, rope_cache(c["ctx_hi"] + 16), ref_pool, tables, positions, out_loc, kv_lens, q_lens, x, res)
+        _CPU_CACHE[key] = st
+    w, cache, ref_pool, tables, positions, out_loc, kv_lens, q_lens, x, res = st
+    t0 = time.perf_counter()
+    olayer.decoder_layer(x, res, w, cache, ref_pool, positions, out_loc, tables, kv_lens, q_lens, c["q_heads"], c["kv_heads"])
+    return time.perf_counter() - t0
 
-    # ---- seeded synthetic state and inputs (each rank its own draw)
-    lens_np = draw_lens(rank)
-    g = torch.Generator(device=dev).manual_seed(1000 + rank)
-    pool = Int8PagedKVCache(Hkv, 1, D, P, dev)
-    pool.k_cache(0).copy_(torch.randint(-127, 128, pool.k_cache(0).shape, dtype=torch.int8, device=dev, generator=g))
-    pool.v_cache(0).copy_(torch.randint(-127, 128, pool.v_cache(0).shape, dtype=torch.int8, device=dev, generator=g))
-    meta = pool.meta(0)
-    meta[:, :, 0:32] = torch.randint(2**30, 2**31, (P, Hkv, 32), dtype=torch.int64, device=dev, generator=g).to(torch.int32)
-    meta[:, :, 32:36] = torch.randint(35, 39, (P, Hkv, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
-    meta[:, :, 36:40] = torch.randint(33, 38, (P, Hkv, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
-    rng = np.random.default_rng(2000 + rank)
-    perm = rng.permutation(P)
-    n_pg = (lens_np + 15) // 16
-    pitch = int(((w["ctx_hi"] + 15) // 16))
-    table_np = np.zeros((B, pitch), dtype=np.int32)
-    off = 0
-    for b in range(B):
-        table_np[b, : n_pg[b]] = perm[off:off + n_pg[b]]; off += n_pg[b]
-    # The inputs of a step live in ONE pinned host buffer and one device buffer (256-byte aligned fields), the results
-    # likewise, so the end-to-end step is one host-to-device copy, one launch and one device-to-host copy.
-    fields = [("q", rng.integers(-127, 128, (B, Hq, D), dtype=np.int8)),
-              ("qm", rng.integers(2**30, 2**31, (B, Hq)).astype(np.int32)),
-              ("qs", rng.integers(43, 46, (B, Hq)).astype(np.int32)),
-              ("table", table_np), ("lens", lens_np.astype(np.int32)),
-              # the batch rows by descending length: a scheduling hint that whoever builds the batch can give
-              ("order", row_order_hint(lens_np, args.row_order))]
 
-    def layout(items):
-        offs, off = {}, 0
-        for name, nbytes in items:
-            offs[name] = off
-            off += (nbytes + 255) // 256 * 256
-        return offs, off
+_CPU_CACHE: dict = {}
+CPU_SAMPLE_TOKENS = 4
 
-    in_off, in_bytes = layout([(n, a.nbytes) for n, a in fields])
-    h_in = torch.empty(in_bytes, dtype=torch.uint8).pin_memory()
-    d_in = torch.empty(in_bytes, dtype=torch.uint8, device=dev)
-    for name, a in fields:
-        h_in[in_off[name]: in_off[name] + a.nbytes] = torch.from_numpy(np.ascontiguousarray(a).view(np.uint8).reshape(-1))
-    d_in.copy_(h_in)
 
-    def dview(buf, off, shape, dtype):
-        n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
-        return buf[off: off + n].view(dtype).view(shape)
+def cpu_sample_text(n_tok):
+    return (f"one decoder layer of the 8B shape on {n_tok} of the 256 decode tokens (contexts U[100,2048]) through the numpy "
+            f"oracle port, scaled to {MODEL_CFG['layers']} layers; embedding, final norm and lm_head not counted")
 
-    d_q = dview(d_in, in_off["q"], (B, Hq, D), torch.int8)
-    d_qm, d_qs = dview(d_in, in_off["qm"], (B, Hq), torch.int32), dview(d_in, in_off["qs"], (B, Hq), torch.int32)
-    d_table = dview(d_in, in_off["table"], (B, pitch), torch.int32)
-    d_lens, d_order = dview(d_in, in_off["lens"], (B,), torch.int32), dview(d_in, in_off["order"], (B,), torch.int32)
-    out_off, out_bytes = layout([("codes", B * Hq * D), ("absmax", B * Hq * 4)])
-    h_res = torch.empty(out_bytes, dtype=torch.uint8).pin_memory()
-    d_res = torch.empty(out_bytes, dtype=torch.uint8, device=dev)
-    d_out = dview(d_res, out_off["codes"], (B, Hq, D), torch.int8)
-    d_absmax = dview(d_res, out_off["absmax"], (B, Hq), torch.int32)
-    stream = torch.cuda.current_stream()
-    sp = _lib.c_void_p(stream.cuda_stream)
-    p = _lib.ptr
 
-    ws_bytes = int(_lib.load().b200_attn_workspace_bytes(B, Hq, Hkv, w["ctx_hi"]))
-    d_ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)      # caller-owned scratch of the workspace variant
-
-    def launch():
-        if args.attn_impl == "split":
-            _lib.call("b200_attn_paged_ws", p(d_q), p(d_qm), p(d_qs), p(pool.k_cache(0)), p(pool.v_cache(0)), p(pool.meta(0)),
-                      p(d_table), pitch, p(d_lens), None, None, None, p(d_out), p(d_absmax), B, Hq, Hkv, P, w["ctx_hi"],
-                      p(d_ws), ws_bytes, sp)
-        else:
-            _lib.call("b200_attn_decode", p(d_q), p(d_qm), p(d_qs), p(pool.k_cache(0)), p(pool.v_cache(0)), p(pool.meta(0)),
-                      p(d_table), pitch, p(d_lens), p(d_order), None, p(d_out), p(d_absmax), B, Hq, Hkv, P, w["ctx_hi"], args.cluster, sp)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident timing
+def run_reference(args) -> None:
+    rank, world, _ = env_ranks()
+    if rank != 0:
+        return
+    n_tok = CPU_SAMPLE_TOKENS
+    t_wall = time.perf_counter()
     for _ in range(args.warmup):
-        launch()
-    barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
-    t_sus = time.perf_counter()       # untimed load of the same kernel so that nvidia-smi can sample clocks
-    while time.perf_counter() - t_sus < args.sustain_s:
-        for _ in range(50):
-            launch()
-        torch.cuda.synchronize()
-    barrier()
-    t_wall0 = time.perf_counter()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for a, b in evs:
-        a.record(stream); launch(); b.record(stream)
-    e1.record(stream)
-    barrier()
-    t_wall1 = time.perf_counter()
-    total_ms = e0.elapsed_time(e1)
-    kern_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
-
-    # ---- end to end: host inputs -> device, launch, result -> host, every step
-    def e2e_step():
-        d_in.copy_(h_in, non_blocking=True)
-        launch()
-        h_res.copy_(d_res, non_blocking=True)
-        stream.synchronize()
-
-    for _ in range(args.warmup):
-        e2e_step()
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record(stream)
+        cpu_layer_sample(n_tok)
+    total = 0.0
     for _ in range(args.steps):
-        e2e_step()
-    f1.record(stream)
-    barrier()
-    e2e_ms = f0.elapsed_time(f1)
-    clocks = sampler.stop(t_sus, time.perf_counter()) if sampler else None
-
-    t = torch.tensor([total_ms, e2e_ms, kern_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, kern_ms = (float(x) for x in t.tolist())
-    if rank == 0:
-        alg = algorithmic_bytes(lens_np)
-        peak, how = measured_peak()
-        achieved = alg / (kern_ms * 1e-3) / 1e9
-        h2d = int(in_bytes)
-        d2h = int(out_bytes)
-        n_cpu = 8
-        cpu_rate, cpu_dt = cpu_oracle_rate(0, n_cpu)
-        line = {
-            "metric": METRIC, "value": world * B * args.steps / (total_ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": "int8 paged decode attention, batch 64 per GPU, 32q/8kv heads, head_dim 128, page 16, "
-                                   "ctx U[512,4096], 200k-page pool", **w, "sum_ctx": int(lens_np.sum()),
-                       "l2": "inputs larger than L2 (about 314 MB of KV touched per launch vs 126 MB)",
-                       "cluster": args.cluster, "attn_impl": args.attn_impl},
-            "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": args.steps * (5 if args.attn_impl == "split" else 1),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES, "peak_source": how, "algorithmic_bytes": alg,
-                         "kernel_ms": kern_ms, "kernel": "split_scores + split_expsum + split_pv (+ init, final)" if args.attn_impl == "split" else "attn_decode_kernel<4>",
-                         "workspace_bytes": ws_bytes if args.attn_impl == "split" else 0, "frac_of_8TBs": achieved / 8000.0},
-            "cpu_baseline": {"value": cpu_rate, "unit": "tokens/s", "cores": host_threads(), "kind": "port",
-                             "sample": f"{n_cpu} of the 64 sequences, one pass ({cpu_dt:.2f} s), numpy oracle port"},
-            "clocks": clocks, "wall_s": t_wall1 - t_wall0,
-        }
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+        total += cpu_layer_sample(n_tok)
+    per_layer = total / max(args.steps, 1)
+    rate = n_tok / (MODEL_CFG["layers"] * per_layer)
+    threads = blas_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": rate, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * per_layer, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": model_config_dict(1, args),
+        "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": threads, "threads_effective": threads,
+                         "host_cpus": os.cpu_count(), "kind": "port",
+                         "sample": cpu_sample_text(n_tok) + "; one step = one such layer pass"},
+        "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t_wall,
+    }
+    print(json.dumps(line))
 
 
+def model_config_dict(world: int, args) -> dict:
+    c = MODEL_CFG
+    return {"workload": "Qwen3-8B-shaped integer-only W8A8 model, greedy decode step, batch %d, ctx U[%d,%d], page 16, "
+                        "random-init int8 weights" % (args.batch, c["ctx_lo"], c["ctx_hi"]),
+            "layers": args.model_layers, "hidden": c["hidden"], "q_heads": c["q_heads"], "kv_heads": c["kv_heads"],
+            "inter": c["inter"], "vocab": c["vocab"], "global_batch": args.batch}
 
-# ----------------------------------------------------------------------------- secondary workloads
-def _time_cuda(fn, steps, warmup):
+
+# ----------------------------------------------------------------------------- timing helpers
+def time_launches(fn, launches: int, warmup: int = 3):
+    """Mean and median milliseconds of one call of `fn` on the current stream: CUDA events around the whole run of
+    `launches` back-to-back calls (mean) and around every call (median)."""
     import torch
+    st = torch.cuda.current_stream()
     for _ in range(max(warmup, 3)):
         fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
+    e0.record(st)
+    for _ in range(launches):
         fn()
-    e1.record()
+    e1.record(st)
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / steps
+    mean = e0.elapsed_time(e1) / launches
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(min(launches, 100))]
+    for a, b in evs:
+        a.record(st); fn(); b.record(st)
+    torch.cuda.synchronize()
+    return mean, float(np.median([a.elapsed_time(b) for a, b in evs]))
 
 
-def run_rowops(args) -> None:
-    """Configuration 3: add+RMSNorm+quant (A) on [rows, 5120] and SiLU*up+FWHT128+quant (B) on [rows, 2*17408]."""
+def fill_pool_random(pool, layers, gen, v_shift=(33, 38)):
     import torch
-    from mini_sgl_integer_b200.kernel import fixed_point as fp
-    from oracle import fixed_point as ofp
-    torch.cuda.set_device(0)
-    T, H, I = args.rows, 5120, 17408
-    g = torch.Generator(device="cuda").manual_seed(0)
-    clip = lambda t: t.round().clamp(-(2**23), 2**23).to(torch.int32)
-    x = clip(torch.randn(T, H, device="cuda", generator=g) * 4096.0)
-    r = clip(torch.randn(T, H, device="cuda", generator=g) * 4096.0)
-    w = torch.randint(2**13, 2**15 + 1, (H,), device="cuda", dtype=torch.int32, generator=g)
-    gu = (torch.randn(T, 2 * I, device="cuda", generator=g) * 2.0**17).round().to(torch.int32)
-    ms_a = _time_cuda(lambda: fp.fused_add_rmsnorm_quant(x, r, w), args.steps, args.warmup)
-    ms_b = _time_cuda(lambda: fp.silu_mul_fwht_quant(gu, 128), args.steps, args.warmup)
-    bytes_a, bytes_b = T * (13 * H + 8), T * (9 * I + 8)
+    dev = pool.device
+    for i in range(layers):
+        pool.k_cache(i).copy_(torch.randint(-127, 128, pool.k_cache(i).shape, dtype=torch.int8, device=dev, generator=gen))
+        pool.v_cache(i).copy_(torch.randint(-127, 128, pool.v_cache(i).shape, dtype=torch.int8, device=dev, generator=gen))
+        meta = pool.meta(i)
+        P, H = meta.shape[0], meta.shape[1]
+        meta[:, :, 0:32] = torch.randint(2**30, 2**31, (P, H, 32), dtype=torch.int64, device=dev, generator=gen).to(torch.int32)
+        meta[:, :, 32:36] = torch.randint(35, 39, (P, H, 16), dtype=torch.int8, device=dev, generator=gen).view(torch.int32)
+        meta[:, :, 36:40] = torch.randint(v_shift[0], v_shift[1], (P, H, 16), dtype=torch.int8, device=dev, generator=gen).view(torch.int32)
+
+
+def page_tables(rng, lens, pitch, extra_pages=0):
+    """Disjoint page-id runs out of a random permutation of the pool: (table [B, pitch] int32, pool pages)."""
+    n_pg = (np.asarray(lens) + 15) // 16 + extra_pages
+    P = int(n_pg.sum()) + 8
+    perm = rng.permutation(P)
+    table = np.zeros((len(lens), pitch), dtype=np.int32)
+    off = 0
+    for b, n in enumerate(n_pg):
+        table[b, :n] = perm[off:off + n]; off += n
+    return table, P
+
+
+# ----------------------------------------------------------------------------- component benchmarks (return dicts)
+def attn_micro(dev, launches=200, pool_pages=None, cluster=0, seed=0):
+    """The attention configuration: batch 64, 32 q / 8 kv heads, ctx U[512, 4096], 200k-page pool."""
+    import torch
+    from mini_sgl_integer_b200 import _lib
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    w = ATTN_CFG
+    B, Hq, Hkv, D = w["batch"], w["q_heads"], w["kv_heads"], w["head_dim"]
+    P = pool_pages or w["pool_pages"]
+    lens = np.random.default_rng(seed).integers(w["ctx_lo"], w["ctx_hi"] + 1, B)
+    g = torch.Generator(device=dev).manual_seed(1000 + seed)
+    pool = Int8PagedKVCache(Hkv, 1, D, P, dev)
+    fill_pool_random(pool, 1, g)
+    rng = np.random.default_rng(2000 + seed)
+    perm = rng.permutation(P)
+    n_pg = (lens + 15) // 16
+    pitch = (w["ctx_hi"] + 15) // 16
+    table = np.zeros((B, pitch), dtype=np.int32)
+    off = 0
+    for b in range(B):
+        table[b, : n_pg[b]] = perm[off:off + n_pg[b]]; off += n_pg[b]
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    q = t(rng.integers(-127, 128, (B, Hq, D), dtype=np.int8))
+    qm, qs = t(rng.integers(2**30, 2**31, (B, Hq)).astype(np.int32)), t(rng.integers(43, 46, (B, Hq)).astype(np.int32))
+    d_table, d_lens = t(table), t(lens.astype(np.int32))
+    order = t(np.argsort(-lens, kind="stable").astype(np.int32))
+    out = torch.empty((B, Hq, D), dtype=torch.int8, device=dev)
+    absmax = torch.empty((B, Hq), dtype=torch.int32, device=dev)
+    p, sp = _lib.ptr, _lib.stream()
+
+    def launch():
+        _lib.call("b200_attn_decode", p(q), p(qm), p(qs), p(pool.k_cache(0)), p(pool.v_cache(0)), p(pool.meta(0)), p(d_table),
+                  pitch, p(d_lens), p(order), None, p(out), p(absmax), B, Hq, Hkv, P, w["ctx_hi"], cluster, sp)
+    mean, median = time_launches(launch, launches)
+    alg = int((lens.astype(np.int64) * Hkv * D * 2 + lens.astype(np.int64) * Hkv * 10 + n_pg.astype(np.int64) * 4).sum() + B * Hq * D * 2)
     peak, how = measured_peak()
-    n_cpu = 64
-    t0 = time.perf_counter()
-    xo, ro, wo, go = (t[:n_cpu].cpu().numpy() if t.ndim == 2 else t.cpu().numpy() for t in (x, r, w, gu))
-    eo, _ = ofp.fused_add_rmsnorm_v2(ro, xo, wo); ofp.per_token_quant_from_q15(eo)
-    ofp.per_token_quant_from_q15(ofp.blockwise_fwht_q15(ofp.silu_and_mul(go), 128))
-    cpu_dt = time.perf_counter() - t0
-    kern = {"A_add_rmsnorm_quant": {"ms": ms_a, "GBs": bytes_a / ms_a / 1e6, "frac": bytes_a / ms_a / 1e6 / peak, "bytes": bytes_a},
-            "B_silu_fwht_quant": {"ms": ms_b, "GBs": bytes_b / ms_b / 1e6, "frac": bytes_b / ms_b / 1e6 / peak, "bytes": bytes_b}}
-    tot = ms_a + ms_b
-    print(json.dumps({
-        "metric": "fused fixed-point row kernels A+B (tokens/s; HBM GB/s in roofline)", "value": T / (tot * 1e-3),
-        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": tot,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32", "data": "synthetic",
-        "config": {"workload": f"add+RMSNorm+quant on [{T},5120] and SiLU*up+FWHT128+quant on [{T},2*17408]",
-                   "rows": T, "hidden": H, "inter": I, "l2": "inputs larger than L2"},
-        "gpu_launches": 2 * args.steps, "kernels": kern,
-        "roofline": {"bound": "hbm", "achieved": (bytes_a + bytes_b) / tot / 1e6, "peak": peak, "unit": "GB/s",
-                     "frac": (bytes_a + bytes_b) / tot / 1e6 / peak, "traffic": None, "peak_source": how},
-        "cpu_baseline": {"value": n_cpu / cpu_dt, "unit": "tokens/s", "cores": host_threads(), "kind": "port",
-                         "sample": f"{n_cpu} of the {T} rows through the vectorised numpy oracle ({cpu_dt:.2f} s)"},
-    }))
+    gbs = alg / (mean * 1e-3) / 1e9
+    return {"workload": "batch 64, 32q/8kv heads, head_dim 128, page 16, ctx U[512,4096], %d-page pool" % P,
+            "kernel_ms": mean, "kernel_ms_median": median, "launches_timed": launches, "GBs": gbs, "frac": gbs / peak,
+            "frac_of_8TBs": gbs / 8000.0, "peak": peak, "peak_source": how, "algorithmic_bytes": alg,
+            "tok_s": B / (mean * 1e-3), "traffic": ATTN_NCU_TRAFFIC["bytes"] if P == w["pool_pages"] else None,
+            "traffic_source": ATTN_NCU_TRAFFIC["source"], "sum_ctx": int(lens.sum())}
 
 
-def run_gemm(args) -> None:
-    """W8A8 GEMM micro-benchmark: the (N, K) pairs of the 8B-shaped model at the given M."""
+def gemm_micro(dev, M=4096, launches=20):
+    """The four linears of the 8B-shaped layer at the given M: int8 TOPS, and the library's int8 GEMM beside them."""
     import torch
     from mini_sgl_integer_b200.layers import int8_gemm_q15
-    torch.cuda.set_device(0)
-    M = args.m
     out = {}
+    g = torch.Generator(device=dev).manual_seed(3)
     for name, (N, K) in {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (24576, 4096), "down": (4096, 12288)}.items():
-        x8 = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda")
-        w8 = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda")
-        xm = torch.randint(2**30, 2**31 - 1, (M,), dtype=torch.int64, device="cuda").to(torch.int32)
-        xs = torch.full((M,), 40, dtype=torch.int32, device="cuda")
-        wm = torch.randint(2**29, 2**30, (N,), dtype=torch.int32, device="cuda")
-        ms = _time_cuda(lambda: int8_gemm_q15(x8, xm, xs, w8, wm), args.steps, args.warmup)
-        lib = _time_cuda(lambda: torch._int_mm(x8, w8.t()), args.steps, args.warmup) if M > 16 else float("nan")
+        x8 = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=g)
+        w8 = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=g)
+        xm = torch.randint(2**30, 2**31 - 1, (M,), dtype=torch.int64, device=dev, generator=g).to(torch.int32)
+        xs = torch.full((M,), 40, dtype=torch.int32, device=dev)
+        wm = torch.randint(2**29, 2**30, (N,), dtype=torch.int32, device=dev, generator=g)
+        ms, _ = time_launches(lambda: int8_gemm_q15(x8, xm, xs, w8, wm), launches)
+        lib = float("nan")
+        if M > 16:
+            lib, _ = time_launches(lambda: torch._int_mm(x8, w8.t()), launches)
         out[name] = {"N": N, "K": K, "ms": ms, "TOPS": 2 * M * N * K / ms / 1e9,
-                     "GBs": (M * K + N * K + 4 * M * N) / ms / 1e6, "library_int_mm_TOPS": 2 * M * N * K / lib / 1e9}
+                     "library_int_mm_TOPS": 2 * M * N * K / lib / 1e9, "weight_GBs": N * K / ms / 1e6}
     tot_ops = sum(2 * M * v["N"] * v["K"] for v in out.values())
     tot_ms = sum(v["ms"] for v in out.values())
-    print(json.dumps({
-        "metric": "W8A8 GEMM with fixed-point epilogue (int8 TOPS)", "value": tot_ops / tot_ms / 1e9, "unit": "TOPS",
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": tot_ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": f"four linears of the 8B-shaped layer at M={M}", "M": M}, "gpu_launches": 4 * args.steps,
-        "kernels": out,
-        "roofline": {"bound": "tensor", "achieved": tot_ops / tot_ms / 1e9, "peak": 4500.0, "unit": "TOPS",
-                     "frac": tot_ops / tot_ms / 1e9 / 4500.0, "traffic": None,
-                     "peak_source": "nominal dense int8 (no measured int8 figure in MEASURED_PEAKS.json)"},
-    }))
+    tops = tot_ops / tot_ms / 1e9
+    lib_ms = sum(2 * M * v["N"] * v["K"] / v["library_int_mm_TOPS"] / 1e9 for v in out.values())
+    return {"M": M, "TOPS": tops, "frac_nominal": tops / 4500.0, "nominal_peak_TOPS": 4500.0,
+            "frac_of_int_mm": lib_ms / tot_ms if lib_ms == lib_ms else None, "ms": tot_ms, "shapes": out,
+            "note": "int8 tensor peak is not in MEASURED_PEAKS.json: nominal dense 4.5 POPS and torch._int_mm on the same box"}
 
 
-def run_tp_layer(args) -> None:
-    """Configuration 5 proxy: ONE Qwen3-32B-shaped integer decoder layer, decode step of batch 256 with contexts
-    U[1024, 8192], tensor-parallel over the launched ranks (attention by KV head, column/row-split GEMMs, two
-    int32 all-reduces per layer over NCCL).  tokens/s are quoted for the 64-layer model (64 x this layer)."""
+def rowops_micro(dev, rows=16384, launches=20):
+    """The row-kernel configuration: add+RMSNorm+quant (A) on [rows, 5120], SiLU*up+FWHT128+quant (B) on [rows, 2*17408]."""
+    import torch
+    from mini_sgl_integer_b200.kernel import fixed_point as fp
+    T, H, I = rows, 5120, 17408
+    g = torch.Generator(device=dev).manual_seed(0)
+    clip = lambda t: t.round().clamp(-(2**23), 2**23).to(torch.int32)
+    x = clip(torch.randn(T, H, device=dev, generator=g) * 4096.0)
+    r = clip(torch.randn(T, H, device=dev, generator=g) * 4096.0)
+    w = torch.randint(2**13, 2**15 + 1, (H,), device=dev, dtype=torch.int32, generator=g)
+    gu = (torch.randn(T, 2 * I, device=dev, generator=g) * 2.0**17).round().to(torch.int32)
+    ms_a, _ = time_launches(lambda: fp.fused_add_rmsnorm_quant(x, r, w), launches)
+    ms_b, _ = time_launches(lambda: fp.silu_mul_fwht_quant(gu, 128), launches)
+    bytes_a, bytes_b = T * (13 * H + 8), T * (9 * I + 8)
+    peak, how = measured_peak()
+    tot = ms_a + ms_b
+    rec = {"rows": T, "A_add_rmsnorm_quant": {"ms": ms_a, "GBs": bytes_a / ms_a / 1e6, "frac": bytes_a / ms_a / 1e6 / peak, "bytes": bytes_a},
+           "B_silu_fwht_quant": {"ms": ms_b, "GBs": bytes_b / ms_b / 1e6, "frac": bytes_b / ms_b / 1e6 / peak, "bytes": bytes_b},
+           "A_plus_B": {"ms": tot, "GBs": (bytes_a + bytes_b) / tot / 1e6, "frac": (bytes_a + bytes_b) / tot / 1e6 / peak},
+           "peak": peak, "peak_source": how}
+    return rec, (x, r, w, gu)
+
+
+def prefill_micro(dev, launches=5):
+    """Prefill attention on prompts of the offline run's shape: 16 prompts of U[100, 1024] tokens, 32 q / 8 kv heads."""
+    import torch
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    from mini_sgl_integer_b200.attention import ops as aops
+    if not hasattr(aops, "prefill_attention_int8_paged"):
+        return None
+    rng = np.random.default_rng(5)
+    B, Hq, Hkv = 16, 32, 8
+    lens = rng.integers(100, 1025, B)
+    table, P = page_tables(rng, lens, 64)
+    pool = Int8PagedKVCache(Hkv, 1, 128, P, dev)
+    fill_pool_random(pool, 1, torch.Generator(device=dev).manual_seed(6))
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    T = int(lens.sum())
+    q = t(rng.integers(-127, 128, (T, Hq, 128), dtype=np.int8))
+    qm, qs = t(rng.integers(2**30, 2**31, (T, Hq)).astype(np.int32)), t(rng.integers(43, 46, (T, Hq)).astype(np.int32))
+    d_table, d_lens = t(table), t(lens.astype(np.int32))
+    fn = lambda: aops.prefill_attention_int8_paged(q, qm, qs, pool, 0, d_table, d_lens, d_lens, 1024, int(lens.max()))
+    ms, med = time_launches(fn, launches)
+    pairs = float((lens.astype(np.float64) * (lens + 1) / 2).sum()) * Hq
+    ops = pairs * 128 * 2 * 2                                   # QK^T and PV, causal half
+    kv_bytes = float(lens.sum()) * Hkv * 266
+    return {"workload": "16 prompts of U[100,1024] tokens, 32q/8kv heads, causal, no cached prefix", "tokens": T, "ms": ms,
+            "ms_median": med, "tok_s": T / (ms * 1e-3), "int8_TOPS_algorithmic": ops / ms / 1e9,
+            "kv_bytes_once": kv_bytes, "score_elements": pairs}
+
+
+# ----------------------------------------------------------------------------- the model step (default workload)
+def build_parity_case(dev, comm, exch, full_layer0, cache, rank, world):
+    """A tensor-parallel layer against the unsplit layer on 8 decode tokens: identical seeded inputs on every rank,
+    KV pools that hold the same codes (this rank's heads), outputs compared bit for bit.  Returns True / False."""
+    import torch
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    from mini_sgl_integer_b200.layers.decoder_layer import AttnBatch, Qwen3DecoderLayerInteger
+    from mini_sgl_integer_b200.models import shard_layer_weights
+    c = MODEL_CFG
+    HID, HQ, HK, INTER = c["hidden"], c["q_heads"], c["kv_heads"], c["inter"]
+    rng = np.random.default_rng(77)
+    T = 8
+    lens = rng.integers(20, 200, T)
+    table, P = page_tables(rng, lens, 16)
+    g = torch.Generator(device=dev).manual_seed(78)
+    pool_full = Int8PagedKVCache(HK, 1, 128, P, dev)
+    fill_pool_random(pool_full, 1, g)
+    hk = HK // world
+    pool_tp = Int8PagedKVCache(hk, 1, 128, P, dev)
+    sl = slice(rank * hk, (rank + 1) * hk)
+    pool_tp.k_cache(0).copy_(pool_full.k_cache(0)[:, sl]); pool_tp.v_cache(0).copy_(pool_full.v_cache(0)[:, sl])
+    pool_tp.meta(0).copy_(pool_full.meta(0)[:, sl])
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    out_loc = np.array([table[b, (lens[b] - 1) // 16] * 16 + (lens[b] - 1) % 16 for b in range(T)], dtype=np.int32)
+    batch = AttnBatch(t((lens - 1).astype(np.int32)), t(out_loc), t(table), t(lens.astype(np.int32)), None, 256)
+    x = (torch.randn(T, HID, device=dev, generator=g) * 30000.0).round().to(torch.int32)
+    res = (torch.randn(T, HID, device=dev, generator=g) * 30000.0).round().to(torch.int32)
+    full = Qwen3DecoderLayerInteger(0, HQ, HK, HID, INTER, full_layer0, cache, pool_full)
+    want, want_res = full.forward_q15(x, res, batch)
+    tp = Qwen3DecoderLayerInteger(0, HQ // world, hk, HID, INTER // world, shard_layer_weights(full_layer0, rank, world, HQ, HK, INTER),
+                                  cache, pool_tp, comm=comm, exchange=exch)
+    ok = True
+    for _ in range(3):                                       # three rounds: both halves of the exchange blocks
+        got, got_res = tp.forward_q15(x, res, batch)
+        ok = ok and bool(torch.equal(got, want)) and bool(torch.equal(got_res, want_res))
+    return ok and int(want.abs().max()) > 0
+
+
+def run_model(args) -> None:
     import torch
     import torch.distributed as dist
-    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    from mini_sgl_integer_b200 import _lib
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache, decode_attention_int8_paged
     from mini_sgl_integer_b200.distributed import DistributedCommunicator
-    from mini_sgl_integer_b200.layers.decoder_layer import AttnBatch, Qwen3DecoderLayerInteger, _Linear
+    from mini_sgl_integer_b200.layers.tp_linear import TpExchange
+    from mini_sgl_integer_b200.models import (DecodeBatch, Qwen3ForCausalLMInteger, Qwen3IntegerConfig, check_device_status,
+                                              random_weights, rope_cache_q15, shard_layer_weights)
 
-    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    rank, world, local = env_ranks()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    HID, HQ, HK, INTER, LAYERS, B = 5120, 64, 8, 25600, 64, args.tp_batch
-    hq, hk, inter = HQ // world, HK // world, INTER // world
-    g = torch.Generator(device=dev).manual_seed(7)            # same seed on every rank: replicated tensors agree
-    ri8 = lambda *shape: torch.randint(-127, 128, shape, dtype=torch.int8, device=dev, generator=g)
-    def lin(n, k):
-        l = _Linear(ri8(n, k), weight_mul=torch.randint(2**29, 2**30, (n,), dtype=torch.int32, device=dev, generator=g),
-                    weight_shift=torch.full((n,), 38, dtype=torch.int32, device=dev))
-        return l
-    weights = {"qkv": lin((hq + 2 * hk) * 128, HID), "o": lin(HID, hq * 128), "gate_up": lin(2 * inter, HID), "down": lin(HID, inter),
-               "input_norm": torch.randint(2**13, 2**15, (HID,), dtype=torch.int32, device=dev, generator=g),
-               "post_norm": torch.randint(2**13, 2**15, (HID,), dtype=torch.int32, device=dev, generator=g),
-               "q_norm": torch.randint(2**11, 2**13, (128,), dtype=torch.int32, device=dev, generator=g),
-               "k_norm": torch.randint(2**12, 2**14, (128,), dtype=torch.int32, device=dev, generator=g)}
-    rng = np.random.default_rng(11)
-    lens = rng.integers(1024, 8193, B)
-    n_pg = (lens + 15) // 16
-    P = int(n_pg.sum()) + 8
-    pool = Int8PagedKVCache(hk, 1, 128, P, dev)
-    pool.k_cache(0).copy_(ri8(*pool.k_cache(0).shape)); pool.v_cache(0).copy_(ri8(*pool.v_cache(0).shape))
-    meta = pool.meta(0)
-    meta[:, :, 0:32] = torch.randint(2**30, 2**31, (P, hk, 32), dtype=torch.int64, device=dev, generator=g).to(torch.int32)
-    meta[:, :, 32:36] = torch.randint(35, 39, (P, hk, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
-    meta[:, :, 36:40] = torch.randint(36, 40, (P, hk, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
-    perm = rng.permutation(P)
-    pitch = 512
-    table = np.zeros((B, pitch), dtype=np.int32)
-    off = 0
-    for b in range(B):
-        table[b, : n_pg[b]] = perm[off:off + n_pg[b]]; off += n_pg[b]
-    out_loc = np.array([table[b, (lens[b] - 1) // 16] * 16 + (lens[b] - 1) % 16 for b in range(B)], dtype=np.int32)
-    inv = 1.0 / (1000000.0 ** (torch.arange(0, 128, 2, dtype=torch.float) / 128))
-    fr = torch.einsum("i,j -> ij", torch.arange(8192, dtype=torch.float), inv)
-    cache = torch.clamp(torch.round(torch.cat((fr.cos(), fr.sin()), -1) * 32768), -32768, 32767).to(torch.int32).to(dev)
-    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    c = MODEL_CFG
+    HID, HQ, HK, INTER, VOCAB, L = c["hidden"], c["q_heads"], c["kv_heads"], c["inter"], c["vocab"], args.model_layers
+    if HK % world or VOCAB % world:
+        raise SystemExit(f"the model splits over 1, 2, 4 or 8 ranks, not {world}")
+    B = args.batch
     comm = DistributedCommunicator()
-    bufs = None
-    if world > 1 and args.fused_reduce:
-        from mini_sgl_integer_b200.layers.tp_linear import PeerReduceBuffers
-        bufs = PeerReduceBuffers(comm, B, HID, dev)
-    layer = Qwen3DecoderLayerInteger(0, hq, hk, HID, inter, weights, cache, pool, comm=comm, peer_buffers=bufs)
-    batch = AttnBatch(d((lens - 1).astype(np.int32)), d(out_loc), d(table), d(lens.astype(np.int32)), None, 8192,
-                      d(np.argsort(-lens, kind="stable").astype(np.int32)))
-    x = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
-    res = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
-    eager = lambda: layer.forward_q15(x, res, batch)
-    for _ in range(max(args.warmup, 3)):
-        eager()
-    torch.cuda.synchronize()
-    step = eager
-    if args.graph and world == 1:
-        # the layer step replayed from one CUDA graph, as the engine's decode does (single rank only: capturing
-        # the NCCL collectives of a multi-rank step did not complete on this pool and stays off)
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            eager()
-        torch.cuda.current_stream().wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            eager()
-        step = graph.replay
-        for _ in range(3):
-            step()
-        torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms)
-    if rank == 0:
-        w_bytes = ((HQ + 2 * HK) * 128 * HID + HID * HQ * 128 + 2 * INTER * HID + HID * INTER) / world
-        kv_bytes = float(lens.sum()) * hk * 266
-        peak, how = measured_peak()
-        ach = (w_bytes + kv_bytes) / (ms * 1e-3) / 1e9
-        print(json.dumps({
-            "metric": "decode tok/s of a 64-layer 32B-shaped integer model, from one tensor-parallel layer step", "value": B / (LAYERS * ms * 1e-3),
-            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": "one Qwen3-32B-shaped decoder layer, decode batch %d, ctx U[1024,8192], TP=%d" % (B, world),
-                       "per_gpu_tok_s": B / (LAYERS * ms * 1e-3) / world, "cuda_graph": bool(args.graph and world == 1),
-                       "row_parallel_sum": "in the GEMM kernel over peer memory" if bufs is not None else "NCCL all-reduce"},
-            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                         "peak_source": how, "bytes_per_rank": w_bytes + kv_bytes},
-        }))
-    if world > 1:
-        dist.destroy_process_group()
+    exch = TpExchange(comm, max(B, 8), HID, dev) if world > 1 else None
+    hq, hk, inter, vs = HQ // world, HK // world, INTER // world, VOCAB // world
 
+    # ---- weights: layer 0, the embedding and the lm_head are drawn at full size with one seed on every rank and
+    # sliced (so that the parity check can run the unsplit layer); the other layers are drawn at shard size
+    wf = random_weights(Qwen3IntegerConfig(1, HID, HQ, HK, INTER, VOCAB), seed=4, device=dev, generate_on_device=True)
+    cache = rope_cache_q15(4096).to(dev)
+    tp_parity = None
+    if world > 1:
+        ok = build_parity_case(dev, comm, exch, wf["layers"][0], cache, rank, world)
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        tp_parity = "ok" if int(flag) == 1 else "mismatch"
+    wl = random_weights(Qwen3IntegerConfig(max(L - 1, 0), HID, hq, hk, inter, 128), seed=1000 + rank, device=dev,
+                        generate_on_device=True)
+    weights = {"embed": wf["embed"], "embed_replicated": True, "final_norm": wf["final_norm"],
+               "layers": [shard_layer_weights(wf["layers"][0], rank, world, HQ, HK, INTER)] + wl["layers"]}
+    lmh = wf["lm_head"]
+    from mini_sgl_integer_b200.layers.decoder_layer import _Linear
+    weights["lm_head"] = _Linear(lmh.weight[rank * vs:(rank + 1) * vs].contiguous(), weight_mul=lmh.weight_mul[rank * vs:(rank + 1) * vs].contiguous(),
+                                 weight_shift=lmh.weight_shift[rank * vs:(rank + 1) * vs].contiguous())
+    weights["vocab_start"] = rank * vs
+    del wf, wl, lmh
+    torch.cuda.empty_cache()
 
-def run_model(args) -> None:
-    """Configuration 4's model on one GPU: a full Qwen3-8B-shaped integer model (36 layers, hidden 4096, 32/8 heads,
-    intermediate 12288, vocab 151936; random-init int8 weights), greedy decode of a batch of 256 sequences whose
-    contexts are drawn from U[100, 2048] (the spread of prompt + generated lengths of the offline run).  One step =
-    bookkeeping on the device, embedding, 36 layers, final norm, integer lm_head, arg-max, token fed back; the step
-    is captured once in a CUDA graph and replayed.  KV pages hold seeded random codes instead of a real prefill."""
-    import torch
-    from mini_sgl_integer_b200.attention import Int8PagedKVCache
-    from mini_sgl_integer_b200.models import DecodeBatch, Qwen3ForCausalLMInteger, Qwen3IntegerConfig, random_weights
-
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
-    cfg = Qwen3IntegerConfig(args.model_layers, 4096, 32, 8, 12288, 151936, max_pos=4096)
-    B = args.tp_batch
+    # ---- batch and KV pool (same lengths and page ids on every rank; each rank holds its KV heads)
     rng = np.random.default_rng(21)
-    lens = rng.integers(100, 2049, B)
-    total_steps = args.warmup + args.steps + 4
+    lens = rng.integers(c["ctx_lo"], c["ctx_hi"] + 1, B)
+    total_steps = 2 * args.warmup + 2 * args.steps + 16
     max_len = int(-(-(int(lens.max()) + total_steps + 1) // 16) * 16)
-    n_pg = (lens + total_steps + 16) // 16
-    P = int(n_pg.sum()) + 8
-    w = random_weights(cfg, seed=4, device=dev, generate_on_device=True)
-    pool = Int8PagedKVCache(cfg.num_kv_heads, cfg.num_layers, 128, P, dev)
-    g = torch.Generator(device=dev).manual_seed(5)
-    for i in range(cfg.num_layers):
-        pool.k_cache(i).copy_(torch.randint(-127, 128, pool.k_cache(i).shape, dtype=torch.int8, device=dev, generator=g))
-        pool.v_cache(i).copy_(torch.randint(-127, 128, pool.v_cache(i).shape, dtype=torch.int8, device=dev, generator=g))
-        meta = pool.meta(i)
-        meta[:, :, 0:32] = torch.randint(2**30, 2**31, (P, 8, 32), dtype=torch.int64, device=dev, generator=g).to(torch.int32)
-        meta[:, :, 32:36] = torch.randint(35, 39, (P, 8, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
-        meta[:, :, 36:40] = torch.randint(36, 40, (P, 8, 16), dtype=torch.int8, device=dev, generator=g).view(torch.int32)
-    perm = rng.permutation(P)
-    pitch = max_len // 16
-    table = np.zeros((B, pitch), dtype=np.int32)
-    off = 0
-    for b in range(B):
-        table[b, : n_pg[b]] = perm[off:off + n_pg[b]]; off += n_pg[b]
+    table, P = page_tables(rng, lens + total_steps, max_len // 16)
+    cfg = Qwen3IntegerConfig(L, HID, hq, hk, inter, VOCAB, max_pos=4096)
+    pool = Int8PagedKVCache(hk, L, 128, P, dev)
+    fill_pool_random(pool, L, torch.Generator(device=dev).manual_seed(5 + rank), v_shift=(36, 40))
     state = DecodeBatch(torch.from_numpy(table).to(dev), torch.from_numpy(lens.astype(np.int32)).to(dev), max_len)
-    lm = Qwen3ForCausalLMInteger(cfg, w, pool)
-    h_in = torch.from_numpy(rng.integers(0, cfg.vocab, B).astype(np.int32)).pin_memory()
+    lm = Qwen3ForCausalLMInteger(cfg, weights, pool, comm, exch)
+    h_in = torch.from_numpy(rng.integers(0, VOCAB, B).astype(np.int32)).pin_memory()
     h_out = torch.empty(B, dtype=torch.int32).pin_memory()
     cur = h_in.to(dev)
 
     def step():
         cur.copy_(lm.greedy(cur, state.advance()))
 
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
         step()                                              # loads modules, sizes attributes (outside the capture)
     torch.cuda.current_stream().wait_stream(side)
+    barrier()
+    calls0 = _lib.CALLS
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         step()
+    calls_per_step = _lib.CALLS - calls0
+    barrier()
     for _ in range(args.warmup):
         graph.replay()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(0)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
     t_wall0 = time.perf_counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
         graph.replay()
     e1.record()
-    torch.cuda.synchronize()
+    barrier()
     t_wall1 = time.perf_counter()
     ms = e0.elapsed_time(e1) / args.steps
-    # end to end: the scheduler's view of a step - tokens in from pinned host memory, tokens out to it
-    lens_after = state.seq_lens.cpu().numpy()
-    t0 = time.perf_counter()
-    e2e_steps = min(args.steps, 4)
-    for _ in range(e2e_steps):
+    check_device_status()
+
+    # ---- end to end: token ids in from pinned host memory, new ids back to it, every step
+    def e2e_step():
         cur.copy_(h_in, non_blocking=True)
         graph.replay()
         h_out.copy_(cur, non_blocking=True)
-        torch.cuda.synchronize()
+        torch.cuda.current_stream().synchronize()
         h_in.copy_(h_out)
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    clocks = sampler.stop(t_wall0, t_wall1)
-    per_layer_w = (32 + 16) * 128 * 4096 + 4096 * 32 * 128 + 2 * 12288 * 4096 + 4096 * 12288
-    w_bytes = cfg.num_layers * per_layer_w + cfg.vocab * cfg.hidden
-    kv_bytes = float(lens_after.mean()) * B * 8 * 266 * cfg.num_layers
+    for _ in range(min(args.warmup, 3)):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1) / args.steps
+    check_device_status()
+    clocks = sampler.stop(t_wall0, time.perf_counter()) if sampler else None
+    lens_after = state.seq_lens.cpu().numpy().astype(np.int64)
+
+    # ---- the dominant kernel on its own: the decode attention of one layer over this batch
+    q8 = torch.randint(-127, 128, (B, hq, 128), dtype=torch.int8, device=dev)
+    qm = torch.randint(2**30, 2**31, (B, hq), dtype=torch.int64, device=dev).to(torch.int32)
+    qs = torch.full((B, hq), 44, dtype=torch.int32, device=dev)
+    kv_lens = state.seq_lens.clone()
+    rot = [0]
+
+    def attn_launch():
+        rot[0] = (rot[0] + 1) % L                            # a different layer's pages every launch: nothing stays in L2
+        decode_attention_int8_paged(q8, qm, qs, pool, rot[0], state.page_table, kv_lens, max_len, row_order=state.row_order)
+    attn_ms, attn_med = time_launches(attn_launch, 200)
+    attn_bytes = int((lens_after * hk * 266 + ((lens_after + 15) // 16) * 4).sum() + B * hq * 128 * 5)
+
+    t = torch.tensor([ms, e2e_ms, attn_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, attn_ms = (float(v) for v in t.tolist())
+
+    per_layer_w = (HQ + 2 * HK) * 128 * HID + HID * HQ * 128 + 2 * INTER * HID + HID * INTER
+    w_bytes = (L * per_layer_w + VOCAB * HID) / world
+    kv_bytes = float(lens_after.sum()) * hk * 266 * L
     peak, how = measured_peak()
     ach = (w_bytes + kv_bytes) / (ms * 1e-3) / 1e9
-    print(json.dumps({
-        "metric": "decode tokens/s per GPU, full integer model", "value": B / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "Qwen3-8B-shaped integer model (%d layers), greedy decode, batch %d, ctx U[100,2048] (mean %.0f), page 16, CUDA graph"
-                               % (cfg.num_layers, B, float(lens_after.mean())), "l2": "weights + KV per step (%.1f GB) exceed L2" % ((w_bytes + kv_bytes) / 1e9)},
-        "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                     "peak_source": how, "weight_bytes": w_bytes, "kv_bytes": kv_bytes},
-        "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
-        "clocks": clocks,
-    }))
+    line = None
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": B / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8", "data": "synthetic",
+            "config": {**model_config_dict(world, args), "parallelism": f"tp{world}", "per_gpu_tok_s": B / (ms * 1e-3) / world,
+                       "mean_ctx": float(lens_after.mean()), "cuda_graph": True,
+                       "row_parallel_sum": "in the GEMM kernel over NVLink peer memory; no collective call in the step" if world > 1 else "none (one GPU)",
+                       "l2": "weights + KV streamed per step (%.1f GB per GPU) exceed L2" % ((w_bytes + kv_bytes) / 1e9)},
+            "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": 4 * B,
+                    "d2h_bytes_per_step": 4 * B},
+            "gpu_launches": calls_per_step * args.steps,
+            "gpu_launches_note": "entry-point calls of libb200int.so captured in one step x steps (a split-K GEMM call is three graph nodes)",
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "traffic_source": "not captured for the whole step; the decode-attention kernel's capture is under kernels.attn_cfg2",
+                         "peak_source": how, "weight_bytes_per_gpu": w_bytes, "kv_bytes_per_gpu": kv_bytes,
+                         "dominant_kernel": {"name": "attn_decode_kernel", "kernel_ms": attn_ms, "kernel_ms_median": attn_med,
+                                             "launches_timed": 200, "algorithmic_bytes": attn_bytes,
+                                             "achieved": attn_bytes / attn_ms / 1e6, "frac": attn_bytes / attn_ms / 1e6 / peak,
+                                             "share_of_step": attn_ms * L / ms}},
+            "clocks": clocks, "wall_s": t_wall1 - t_wall0,
+        }
+        if tp_parity is not None:
+            line["tp_parity"] = tp_parity
+    # ---- free the model before the component runs
+    del lm, pool, weights, state, graph
+    torch.cuda.empty_cache()
+    if world > 1 and not args.no_tp32b:
+        rec = tp32b_layer(dev, comm, rank, world, args)
+        if rank == 0:
+            line["tp32b"] = rec
+    if world == 1 and not args.no_kernels:
+        kern = {}
+        kern["attn_cfg2"] = attn_micro(dev, 200)
+        kern["gemm_m4096"] = gemm_micro(dev, 4096, 20)
+        rec, tensors = rowops_micro(dev, 16384, 20)
+        kern["rowops_cfg3"] = rec
+        del tensors
+        torch.cuda.empty_cache()
+        pre = prefill_micro(dev)
+        if pre is not None:
+            kern["prefill_attn"] = pre
+        line["kernels"] = kern
+        n_tok = CPU_SAMPLE_TOKENS
+        cpu_layer_sample(n_tok)
+        dt = min(cpu_layer_sample(n_tok), cpu_layer_sample(n_tok))
+        threads = blas_threads()
+        line["cpu_baseline"] = {"value": n_tok / (L * dt), "unit": "tokens/s", "cores": threads, "threads_effective": threads,
+                                "host_cpus": os.cpu_count(), "kind": "port",
+                                "sample": cpu_sample_text(n_tok) + " (%.2f s per layer pass, best of two)" % dt}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def tp32b_layer(dev, comm, rank, world, args):
+    """One Qwen3-32B-shaped decoder layer, decode batch 256, contexts U[1024, 8192], split over the ranks; replayed
+    from a CUDA graph.  tokens/s are quoted for the 64-layer model (64 x this layer)."""
+    import torch
+    import torch.distributed as dist
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    from mini_sgl_integer_b200.layers.decoder_layer import AttnBatch, Qwen3DecoderLayerInteger
+    from mini_sgl_integer_b200.layers.tp_linear import TpExchange
+    from mini_sgl_integer_b200.models import Qwen3IntegerConfig, check_device_status, random_weights, rope_cache_q15
+    c = TP32B_CFG
+    HID, HQ, HK, INTER, LAYERS, B = c["hidden"], c["q_heads"], c["kv_heads"], c["inter"], c["layers"], c["batch"]
+    hq, hk, inter = HQ // world, HK // world, INTER // world
+    w = random_weights(Qwen3IntegerConfig(1, HID, hq, hk, inter, 128), seed=9, device=dev, generate_on_device=True)["layers"][0]
+    rng = np.random.default_rng(11)
+    lens = rng.integers(c["ctx_lo"], c["ctx_hi"] + 1, B)
+    table, P = page_tables(rng, lens, 512)
+    pool = Int8PagedKVCache(hk, 1, 128, P, dev)
+    fill_pool_random(pool, 1, torch.Generator(device=dev).manual_seed(12), v_shift=(36, 40))
+    out_loc = np.array([table[b, (lens[b] - 1) // 16] * 16 + (lens[b] - 1) % 16 for b in range(B)], dtype=np.int32)
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    exch = TpExchange(comm, B, HID, dev) if world > 1 else None
+    layer = Qwen3DecoderLayerInteger(0, hq, hk, HID, inter, w, rope_cache_q15(8192).to(dev), pool, comm=comm, exchange=exch)
+    batch = AttnBatch(d((lens - 1).astype(np.int32)), d(out_loc), d(table), d(lens.astype(np.int32)), None, 8192,
+                      d(np.argsort(-lens, kind="stable").astype(np.int32)))
+    g = torch.Generator(device=dev).manual_seed(13)
+    x = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
+    res = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
+    run = lambda: layer.forward_q15(x, res, batch)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run()
+    torch.cuda.current_stream().wait_stream(side)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run()
+    for _ in range(5):
+        graph.replay()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    n = 30
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    check_device_status()
+    ms = torch.tensor([e0.elapsed_time(e1) / n], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms)
+    w_bytes = ((HQ + 2 * HK) * 128 * HID + HID * HQ * 128 + 2 * INTER * HID + HID * INTER) / world
+    kv_bytes = float(lens.sum()) * hk * 266
+    peak, _ = measured_peak()
+    ach = (w_bytes + kv_bytes) / (ms * 1e-3) / 1e9
+    return {"workload": "one Qwen3-32B-shaped decoder layer, decode batch %d, ctx U[1024,8192], TP=%d, CUDA graph" % (B, world),
+            "ms_per_layer": ms, "tok_s": B / (LAYERS * ms * 1e-3), "per_gpu_tok_s": B / (LAYERS * ms * 1e-3) / world,
+            "GBs_per_gpu": ach, "frac": ach / peak, "bytes_per_gpu": w_bytes + kv_bytes}
+
+
+# ----------------------------------------------------------------------------- single-component lines
+def component_line(metric, value, unit, ms, args, config, roofline, extra=None):
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+            "data": "synthetic", "config": config, "roofline": roofline}
+    line.update(extra or {})
+    print(json.dumps(line))
+
+
+def run_attn(args) -> None:
+    import torch
+    torch.cuda.set_device(0)
+    sampler = ClockSampler(0)
+    t0 = time.perf_counter()
+    r = attn_micro(torch.device("cuda", 0), max(args.steps, 200), args.pool_pages, args.cluster)
+    clocks = sampler.stop(t0, time.perf_counter())
+    component_line("int8 paged decode attention throughput (decode tokens/s; HBM GB/s in roofline)", r["tok_s"], "tokens/s",
+                   r["kernel_ms"], args, {"workload": "int8 paged decode attention, " + r["workload"], **ATTN_CFG, "sum_ctx": r["sum_ctx"],
+                                          "l2": "inputs larger than L2 (about 314 MB of KV touched per launch vs 126 MB)"},
+                   {"bound": "hbm", "achieved": r["GBs"], "peak": r["peak"], "unit": "GB/s", "frac": r["frac"], "traffic": r["traffic"],
+                    "traffic_source": r["traffic_source"], "peak_source": r["peak_source"], "algorithmic_bytes": r["algorithmic_bytes"],
+                    "kernel_ms": r["kernel_ms"], "kernel_ms_median": r["kernel_ms_median"], "frac_of_8TBs": r["frac_of_8TBs"]},
+                   {"gpu_launches": r["launches_timed"], "clocks": clocks})
+
+
+def run_rowops(args) -> None:
+    import torch
+    from oracle import fixed_point as ofp
+    torch.cuda.set_device(0)
+    rec, (x, r, w, gu) = rowops_micro(torch.device("cuda", 0), args.rows, args.steps)
+    n_cpu = 64
+    t0 = time.perf_counter()
+    xo, ro, wo, go = (t[:n_cpu].cpu().numpy() if t.ndim == 2 else t.cpu().numpy() for t in (x, r, w, gu))
+    eo, _ = ofp.fused_add_rmsnorm_v2(ro, xo, wo); ofp.per_token_quant_from_q15(eo)
+    ofp.per_token_quant_from_q15(ofp.blockwise_fwht_q15(ofp.silu_and_mul(go), 128))
+    cpu_dt = time.perf_counter() - t0
+    ab = rec["A_plus_B"]
+    component_line("fused fixed-point row kernels A+B (tokens/s; HBM GB/s in roofline)", args.rows / (ab["ms"] * 1e-3), "tokens/s",
+                   ab["ms"], args, {"workload": f"add+RMSNorm+quant on [{args.rows},5120] and SiLU*up+FWHT128+quant on [{args.rows},2*17408]",
+                                    "l2": "inputs larger than L2"},
+                   {"bound": "hbm", "achieved": ab["GBs"], "peak": rec["peak"], "unit": "GB/s", "frac": ab["frac"], "traffic": None,
+                    "peak_source": rec["peak_source"]},
+                   {"gpu_launches": 2 * args.steps, "kernels": rec,
+                    "cpu_baseline": {"value": n_cpu / cpu_dt, "unit": "tokens/s", "cores": blas_threads(), "kind": "port",
+                                     "sample": f"{n_cpu} of the {args.rows} rows through the vectorised numpy oracle ({cpu_dt:.2f} s)"}})
+
+
+def run_gemm(args) -> None:
+    import torch
+    torch.cuda.set_device(0)
+    r = gemm_micro(torch.device("cuda", 0), args.m, args.steps)
+    component_line("W8A8 GEMM with fixed-point epilogue (int8 TOPS)", r["TOPS"], "TOPS", r["ms"], args,
+                   {"workload": f"four linears of the 8B-shaped layer at M={args.m}", "M": args.m},
+                   {"bound": "tensor", "achieved": r["TOPS"], "peak": 4500.0, "unit": "TOPS", "frac": r["frac_nominal"], "traffic": None,
+                    "peak_source": "nominal dense int8 (no measured int8 figure in MEASURED_PEAKS.json)", "frac_of_int_mm": r["frac_of_int_mm"]},
+                   {"gpu_launches": 4 * args.steps, "kernels": r["shapes"]})
+
+
+def run_prefill(args) -> None:
+    import torch
+    torch.cuda.set_device(0)
+    r = prefill_micro(torch.device("cuda", 0), max(args.steps, 5))
+    if r is None:
+        raise SystemExit("the prefill attention kernel is not in this build")
+    component_line("int8 paged prefill attention (prompt tokens/s)", r["tok_s"], "tokens/s", r["ms"], args,
+                   {"workload": r["workload"]},
+                   {"bound": "tensor", "achieved": r["int8_TOPS_algorithmic"], "peak": 4500.0, "unit": "TOPS",
+                    "frac": r["int8_TOPS_algorithmic"] / 4500.0, "traffic": None, "peak_source": "nominal dense int8"},
+                   {"gpu_launches": args.steps, "kernels": {"prefill_attn": r}})
+
+
+def run_tp_layer(args) -> None:
+    import torch
+    import torch.distributed as dist
+    from mini_sgl_integer_b200.distributed import DistributedCommunicator
+    rank, world, local = env_ranks()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rec = tp32b_layer(dev, DistributedCommunicator(), rank, world, args)
+    if rank == 0:
+        peak, how = measured_peak()
+        line = {"metric": "decode tok/s of a 64-layer 32B-shaped integer model, from one tensor-parallel layer step", "value": rec["tok_s"],
+                "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": rec["ms_per_layer"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+                "config": {"workload": rec["workload"], "per_gpu_tok_s": rec["per_gpu_tok_s"]},
+                "roofline": {"bound": "hbm", "achieved": rec["GBs_per_gpu"], "peak": peak, "unit": "GB/s", "frac": rec["frac"],
+                             "traffic": None, "peak_source": how, "bytes_per_rank": rec["bytes_per_gpu"]}}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cluster", type=int, default=0, help="CTAs per (sequence, KV head); 0 = library default")
-    ap.add_argument("--attn-impl", default="cluster", choices=["split", "cluster"],
-                    help="split = grid-wide passes over a workspace (5 launches per step); cluster = one kernel per step")
-    ap.add_argument("--row-order", default="lpt", choices=["lpt", "identity"],
-                    help="scheduling hint passed to the decode kernel (see row_order_hint)")
-    ap.add_argument("--pool-pages", type=int, default=WORKLOAD["pool_pages"],
-                    help="pages in the KV pool (smaller pools are for profiler captures only)")
-    ap.add_argument("--sustain-s", type=float, default=1.0,
-                    help="seconds of untimed back-to-back launches before the timed region (clock sampling)")
-    ap.add_argument("--workload", default="attn", choices=["attn", "rowops", "gemm", "tp_layer", "model"],
-                    help="attn = the headline decode attention (default); rowops / gemm = the other kernels of the path")
+    ap.add_argument("--workload", default="model", choices=["model", "attn", "rowops", "gemm", "prefill", "tp_layer"],
+                    help="model = the decode step of the 8B-shaped model, tensor-parallel over the launched ranks (default); "
+                         "the others time one component")
+    ap.add_argument("--batch", type=int, default=MODEL_CFG["batch"], help="decode batch of --workload model")
+    ap.add_argument("--model-layers", type=int, default=MODEL_CFG["layers"], help="layers of --workload model (fewer: profiler captures)")
+    ap.add_argument("--no-kernels", action="store_true", help="model on one GPU: skip the component records")
+    ap.add_argument("--no-tp32b", action="store_true", help="model on several GPUs: skip the 32B-shaped layer record")
+    ap.add_argument("--cluster", type=int, default=0, help="attn: CTAs per (sequence, KV head); 0 = library default")
+    ap.add_argument("--pool-pages", type=int, default=ATTN_CFG["pool_pages"], help="attn: pages in the KV pool")
     ap.add_argument("--rows", type=int, default=16384, help="rows for --workload rowops")
     ap.add_argument("--m", type=int, default=4096, help="M for --workload gemm")
-    ap.add_argument("--tp-batch", type=int, default=256, help="decode batch for --workload tp_layer / model")
-    ap.add_argument("--model-layers", type=int, default=36, help="layers for --workload model")
-    ap.add_argument("--fused-reduce", action="store_true",
-                    help="tp_layer on several GPUs: the row-parallel GEMMs add their partial sums over NVLink peer memory themselves")
-    ap.add_argument("--graph", action="store_true", help="tp_layer on one GPU: replay the layer step from a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload == "rowops":
-        run_rowops(args)
-    elif args.workload == "gemm":
-        run_gemm(args)
-    elif args.workload == "tp_layer":
-        run_tp_layer(args)
-    elif args.workload == "model":
-        run_model(args)
     else:
-        run_ours(args)
+        {"model": run_model, "attn": run_attn, "rowops": run_rowops, "gemm": run_gemm, "prefill": run_prefill,
+         "tp_layer": run_tp_layer}[args.workload](args)
 
 
 if __name__ == "__main__":

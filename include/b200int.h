@@ -216,7 +216,11 @@ B200_API int b200_attn_paged_ws(const int8_t* q, const int32_t* q_mul, const int
  *    B200_ATTN_STATIC_SCRATCH_BYTES, otherwise B200_E_UNSUPPORTED with the two sizes in the message
  *    (16 MiB holds e.g. 16 rows x 32 query heads x 7680 keys); use b200_attn_paged_ws beyond that.
  *  - The first call on each device looks up the area's device address (the device must be current, as for
- *    every call here); make that first call during set-up, before any stream capture begins.
+ *    every call here); make that first call during set-up, before any stream capture begins.  With the CUDA
+ *    runtime's lazy module loading the area itself comes into being when this part of the library is first
+ *    used on the device, i.e. at that first call (or an earlier b200_attn_paged_ws): an engine that hands all
+ *    free memory to its KV pool must make the first call BEFORE it sizes the pool, or the look-up fails with
+ *    B200_E_CUDA.  From the second call on nothing changes in device memory.
  *  - There is one area per device and every call uses it: calls on the same device must not overlap on the
  *    GPU (issue them on one stream, or order them with events), else they corrupt each other's results.
  *    Nothing in the area has to be cleared by the caller: the first kernel of each call resets what the
@@ -251,6 +255,14 @@ B200_API int b200_argmax_i32(const int32_t* logits, int64_t rows, int64_t n, int
 B200_API int b200_decode_prepare(const int32_t* page_table, int64_t table_pitch, int32_t* seq_lens,
                                  int32_t* positions, int32_t* out_loc, int32_t* kv_lens, int batch, int max_len,
                                  b200_stream_t s);
+
+/* ---- Per-tensor int8 quantisation of a bf16 tensor with a (multiplier, shift) scale:
+ * quantize_per_tensor_int8_ms (kernel/triton/int8_attention_kernels.py:41-53), which the reference's prefill
+ * applies to q, k and v (attention/triton_int8.py:139-140,190).  x_bf16: n raw bf16 patterns; codes int8 [n];
+ * mul_shift int32 [2] = (multiplier, shift) with value ~ code * multiplier / 2^shift; scratch_word: one
+ * caller-owned uint32 on the device (holds the running maximum).  Three stream operations, no host sync. */
+B200_API int b200_quantize_per_tensor_int8_ms(const uint16_t* x_bf16, int64_t n, int8_t* codes, int32_t* mul_shift,
+                                              uint32_t* scratch_word, b200_stream_t s);
 
 /* ---- Static activation quantisation for checkpoints that carry an `input_scale`:
  * codes = clamp(rint((fp32(x) / 65536) / input_scale), -128, 127) in fp32 with IEEE division, i.e.
@@ -307,6 +319,49 @@ B200_API int b200_requant_q15(const int32_t* acc, const int32_t* x_mul, const in
  * distributed/impl.py:63-70). */
 B200_API int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, int32_t* const* peer_acc, int n_peers,
                                          int64_t m, int64_t n, int64_t k, b200_stream_t s);
+
+/* ---- Tensor-parallel exchange over NVLink peer memory without a collective library (decode sizes).
+ * They replace, for row-split linears at up to 256 tokens, DistributedCommunicator.all_reduce
+ * (distributed/impl.py:63-70) -> TorchDistributedImpl / PyNCCLDistributedImpl (:25-60) ->
+ * NCCLWrapper::all_reduce (kernel/csrc/src/pynccl.cu:93-134) as used by LinearOProj / LinearRowParallel
+ * (layers/linear.py:108-160), and the all-gather of ParallelLMHead (layers/embedding.py:100-110).
+ *
+ * Every rank owns one exchange block of b200_tp_block_bytes(m_max, n) bytes of device memory, 256-byte
+ * aligned, that is mapped into every rank's process (symmetric / peer memory); base[r] is rank r's block as
+ * seen from the calling process, base[rank] the caller's own.  Clear the own block once with
+ * b200_tp_block_clear and make sure (host barrier) that every rank has done so before the first exchange.
+ * All ranks must issue the same sequence of these calls.  A row-split linear is
+ *     b200_tp_absmax_put   the token's absmax over this rank's K-slice, folded into every rank's block
+ *     b200_tp_quant_wait   waits for all ranks, quantises the slice with the agreed absmax
+ *     b200_gemm_w8a8_tp    partial sums added straight from tensor memory into every rank's block
+ *     b200_tp_requant_wait waits for all ranks, applies the epilogue of b200_gemm_w8a8 to the sum
+ * and gives the bits of b200_gemm_w8a8 on the whole K on one GPU.  b200_tp_all_gather exchanges up to
+ * 2 * m_max words per rank (dst int32 [size][words], rank order).  Producer kernels end with a signal,
+ * consumer kernels start with a wait that is bounded (default 2 s, b200_tp_set_timeout_us): on expiry the
+ * kernel carries on with what the block holds and b200_tp_status reports channel + 1 (1 absmax, 2 sums,
+ * 3 gather).  Kernels only: a step made of these calls can be captured in a CUDA graph.  x: int32 rows with
+ * the given pitch (elements); k and n multiples of 4; rows, m <= m_max (and <= 256 for the GEMM). */
+typedef struct {
+  int rank;        /* this process's rank, 0 .. size-1 */
+  int size;        /* ranks, 1 .. 8 */
+  int m_max;       /* token rows the block is sized for */
+  int64_t n;       /* output channels of the row-split linears (the hidden size) */
+  void* base[8];   /* base[r]: rank r's block in this process's address space */
+} b200_tp_block;
+B200_API size_t b200_tp_block_bytes(int m_max, int64_t n);
+B200_API int b200_tp_block_clear(const b200_tp_block* blk, b200_stream_t s);
+B200_API int b200_tp_absmax_put(const b200_tp_block* blk, const int32_t* x, int64_t pitch, int rows, int k,
+                                b200_stream_t s);
+B200_API int b200_tp_quant_wait(const b200_tp_block* blk, const int32_t* x, int64_t pitch, int rows, int k,
+                                int8_t* codes, int32_t* absmax_out, b200_stream_t s);
+B200_API int b200_gemm_w8a8_tp(const b200_tp_block* blk, const int8_t* x8, const int8_t* w8, int64_t m, int64_t n,
+                               int64_t k, b200_stream_t s);
+B200_API int b200_tp_requant_wait(const b200_tp_block* blk, const int32_t* absmax, const int32_t* w_mul,
+                                  const int32_t* w_shift, int32_t* out_q15, int m, b200_stream_t s);
+B200_API int b200_tp_all_gather(const b200_tp_block* blk, const int32_t* src, int words, int32_t* dst,
+                                b200_stream_t s);
+B200_API int b200_tp_status(int* out_host, int reset);        /* synchronises with the device */
+B200_API int b200_tp_set_timeout_us(int64_t microseconds);    /* synchronises with the device */
 
 /* Reads (and optionally clears) the device-side status word of the GEMM kernels: 0 = fine,
  * non-zero = a bounded wait inside a kernel expired (1 producer, 2 MMA issuer, 3 epilogue).

@@ -49,8 +49,19 @@ SIGNATURES: dict[str, list] = {
     "b200_quant_given_absmax_q15": [P, P, P, L, I, P],
     "b200_requant_q15": [P, P, P, P, P, P, L, L, P],
     "b200_attn_decode": [P, P, P, P, P, P, P, L, P, P, P, P, P, I, I, I, L, I, I, P],
+    "b200_quantize_per_tensor_int8_ms": [P, L, P, P, P, P],
+    "b200_tp_block_bytes": [I, L],
+    "b200_tp_block_clear": [P, P],
+    "b200_tp_absmax_put": [P, P, L, I, I, P],
+    "b200_tp_quant_wait": [P, P, L, I, I, P, P, P],
+    "b200_gemm_w8a8_tp": [P, P, P, L, L, L, P],
+    "b200_tp_requant_wait": [P, P, P, P, P, I, P],
+    "b200_tp_all_gather": [P, P, I, P, P],
+    "b200_tp_status": [P, I],
+    "b200_tp_set_timeout_us": [L],
 }
-_RESTYPES = {"b200_last_error_string": c_char_p, "b200_attn_workspace_bytes": ctypes.c_size_t}
+_RESTYPES = {"b200_last_error_string": c_char_p, "b200_attn_workspace_bytes": ctypes.c_size_t,
+             "b200_tp_block_bytes": ctypes.c_size_t}
 
 _lib = None
 
@@ -80,8 +91,13 @@ def load() -> ctypes.CDLL:
     return _lib
 
 
+CALLS = 0      # entry-point calls made through `call` (bench.py counts the launches of a captured step with it)
+
+
 def call(name: str, *args) -> None:
+    global CALLS
     lib = load()
+    CALLS += 1
     rc = getattr(lib, name)(*args)
     if rc != 0:
         msg = lib.b200_last_error_string().decode("utf-8", "replace")

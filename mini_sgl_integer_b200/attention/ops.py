@@ -175,3 +175,20 @@ def qkv_rope_quant_store(positions: torch.Tensor, qkv_q15: torch.Tensor, q_heads
              ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(q8), ptr(q_mul), ptr(q_shift), tokens, q_heads, hk,
              pool.num_pages, int(with_fwht), stream())
     return q8, q_mul, q_shift
+
+
+def quantize_per_tensor_int8_ms(x: torch.Tensor):
+    """Per-tensor int8 quantisation with a (multiplier, shift) scale: same name, arguments and results as the
+    reference's quantiser of the prefill path (kernel/triton/int8_attention_kernels.py:41-53): returns
+    (int8 codes of x's shape, multiplier, shift) with 0-dim int32 tensors, value ~ code * multiplier / 2**shift.
+    ``x`` must be bfloat16 (what the reference's backend passes, attention/triton_int8.py:139-140)."""
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"x must be bfloat16, got {x.dtype}")
+    require_cuda(x)
+    xc = x.contiguous()
+    codes = torch.empty(xc.shape, dtype=torch.int8, device=xc.device)
+    ms = torch.empty(2, dtype=torch.int32, device=xc.device)
+    word = torch.empty(1, dtype=torch.int32, device=xc.device)
+    if xc.numel():
+        call("b200_quantize_per_tensor_int8_ms", ptr(xc), xc.numel(), ptr(codes), ptr(ms), ptr(word), stream())
+    return codes, ms[0], ms[1]

@@ -396,7 +396,7 @@ split_final_kernel(const SplitParams p) {
 }
 
 static size_t split_ws_bytes(int rows, int q_heads, int kv_heads, int max_kv_len, SplitParams* p, void* ws) {
-  const int ctx_pad = ((max_kv_len + 31) / 32) * 32;
+  const int ctx_pad = (int)((((int64_t)max_kv_len + 31) / 32) * 32 > 2147483616 ? 2147483616 : (((int64_t)max_kv_len + 31) / 32) * 32);
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~size_t(255); return o; };
   const size_t o_sc = take((size_t)rows * q_heads * ctx_pad * 4);

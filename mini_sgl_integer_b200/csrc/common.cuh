@@ -113,14 +113,16 @@ __device__ __forceinline__ int quant_code(int x, float mf) {
 // the correctly rounded quotient up to, at worst, a few units in the last place, so it can only
 // disagree with the division after rounding to an integer when it lies within a hair of a
 // half-integer; in that band (2^-10 wide, far above any such error) the true division is used.
-// Rounding to the nearest-even integer is done by adding 1.5 * 2^23 (|q| <= 127, no clamp needed).
+// Rounding to the nearest-even integer is done by adding 1.5 * 2^23 (-128 <= q <= 127 after the lower clamp).
 __device__ __forceinline__ int quant_code_fast(int x, float mf, float y) {
   const float a = __fmul_rn(__int2float_rn(x), 127.0f);
   const float q0 = __fmul_rn(a, y);
-  float q1 = __fmaf_rn(__fmaf_rn(-mf, q0, a), y, q0);
+  // x = -2^31 never enters the row's absmax (its |x| wraps to a negative), so its quotient can lie far below
+  // -128: the lower clamp of the reference is kept (an upper one is not needed: every other |x| <= absmax)
+  float q1 = fmaxf(__fmaf_rn(__fmaf_rn(-mf, q0, a), y, q0), -128.0f);
   float t = __fadd_rn(q1, 12582912.0f);                       // integer part now sits in the mantissa
   if (fabsf(__fsub_rn(q1, __fsub_rn(t, 12582912.0f))) > 0.4990234375f)   // within 2^-10 of a half-integer
-    t = __fadd_rn(__fdiv_rn(a, mf), 12582912.0f);
+    t = __fadd_rn(fmaxf(__fdiv_rn(a, mf), -128.0f), 12582912.0f);
   return __float_as_int(t) - 0x4B400000;
 }
 // quant_code_fast for rows whose absmax is below 2^22: int -> float by placing the value in the mantissa
@@ -129,10 +131,11 @@ __device__ __forceinline__ int quant_code_fast_small(int x, float mf, float y) {
   const float xf = __int_as_float(0x4B400000 + x) - 12582912.0f;
   const float a = __fmul_rn(xf, 127.0f);
   const float q0 = __fmul_rn(a, y);
-  float q1 = __fmaf_rn(__fmaf_rn(-mf, q0, a), y, q0);
+  // -2^31 (not counted in the absmax) comes out of the mantissa trick as -25165824: still far below -128 * absmax / 127
+  float q1 = fmaxf(__fmaf_rn(__fmaf_rn(-mf, q0, a), y, q0), -128.0f);
   float t = __fadd_rn(q1, 12582912.0f);
   if (fabsf(__fsub_rn(q1, __fsub_rn(t, 12582912.0f))) > 0.4990234375f)
-    t = __fadd_rn(__fdiv_rn(a, mf), 12582912.0f);
+    t = __fadd_rn(fmaxf(__fdiv_rn(a, mf), -128.0f), 12582912.0f);
   return __float_as_int(t) - 0x4B400000;
 }
 __device__ __forceinline__ float quant_scale(float mf) { return __fdiv_rn(mf, 8323072.0f); }

@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tp_block.cuh"
 
 namespace b200 {
 
@@ -124,6 +125,8 @@ struct GemmParams {
   int32_t* partial;         // splits > 1: int32 [M, N] that the parts are added into (zeroed before the launch)
   int n_peers;              // > 0: tensor-parallel reduction - every part is added into each of these [M, N] buffers
   int32_t* peer[8];         //      (this rank's and its peers', mapped into this process: NVLink peer memory)
+  int tp_on;                // the peers' buffers are the accumulator halves of tensor-parallel exchange blocks: the
+  TpView tp;                //      half follows the block's channel-1 epoch and the kernel ends with that channel's signal
 };
 
 __device__ __forceinline__ void mbar_arrive(unsigned bar) {
@@ -237,6 +240,12 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   tcgen05_fence_after();
   const unsigned tmem_base = *tmem_slot;
+  int64_t tp_off = 0;       // exchange-block mode: word offset of the accumulator half in use inside every rank's block
+  if (WS && p.tp_on) {
+    const TpLayout l = tp_layout(p.tp.m_max, p.tp.n);
+    const int half = *reinterpret_cast<volatile int32_t*>(p.tp.base[p.tp.rank] + 1) & 1;
+    tp_off = l.acc + (int64_t)half * l.acc_half;
+  }
 
   if (warp == 0) {
     if (lane == 0) {
@@ -291,7 +300,9 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           tcgen05_commit(empty0 + 8 * s);   // frees the stage once these MMAs have read it
         }
-        tcgen05_commit(tfull0 + 8 * slot);  // accumulators complete (or abandoned): release the epilogue
+        // accumulators complete: release the epilogue.  After an expired wait nothing is committed, so the
+        // epilogue's own wait runs out too and no partial sums are stored or added anywhere.
+        if (ok) tcgen05_commit(tfull0 + 8 * slot);
       }
     }
   } else {
@@ -338,7 +349,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // 32 channels of one token are one 128-byte reduction over NVLink); integer adds commute, so every
             // rank ends up with the same bits whatever the arrival order
             for (int r = 0; r < p.n_peers; ++r) {
-              int32_t* dst = p.peer[r];
+              int32_t* dst = p.tp_on ? p.tp.base[r] + tp_off : p.peer[r];
 #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (c0 + j < p.M) atomicAdd(dst + (int64_t)(c0 + j) * p.N + ch, v[j]);
@@ -413,12 +424,14 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (lane == 0) mbar_arrive(tempty0 + 8 * slot);
     }
   }
+  if (WS && p.tp_on) __threadfence_system();   // this thread's additions into the peers' blocks are out
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
+  if (WS && p.tp_on && threadIdx.x == 0) tp_signal_if_last(p.tp, 1, gridDim.x);
 }
 
 // ----------------------------------------------------------------------------- two-CTA tiles
@@ -554,7 +567,7 @@ gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                         (kb > 0 || k > 0) ? 1u : 0u);
           tcgen05_commit_pair(empty0 + 8 * s);
         }
-        tcgen05_commit_pair(tfull0 + 8 * slot);
+        if (ok) tcgen05_commit_pair(tfull0 + 8 * slot);   // nothing is released after an expired wait
       }
     }
   } else {
@@ -743,7 +756,7 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
   GemmParams p;
   p.x_absmax = x_absmax; p.x_mul = x_mul; p.x_shift = x_shift; p.w_mul = w_mul; p.w_shift = w_shift;
   p.out_q15 = out_q15; p.acc_out = acc_out; p.M = (int)m; p.N = (int)n; p.K = (int)k;
-  p.splits = 1; p.full_blocks = 0; p.partial = nullptr; p.n_peers = 0;
+  p.splits = 1; p.full_blocks = 0; p.partial = nullptr; p.n_peers = 0; p.tp_on = 0;
   cudaStream_t st = (cudaStream_t)s;
   const int w_blocks = (int)((n + kBM - 1) / kBM), num_kb = (int)((k + kBK - 1) / kBK);
   if (m <= 128 || (m <= 256 && w_blocks < sm_count())) {
@@ -828,6 +841,7 @@ extern "C" int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, i
   p.x_absmax = nullptr; p.x_mul = nullptr; p.x_shift = nullptr; p.w_mul = nullptr; p.w_shift = nullptr;
   p.out_q15 = nullptr; p.acc_out = nullptr; p.M = (int)m; p.N = (int)n; p.K = (int)k; p.partial = nullptr;
   p.n_peers = n_peers;
+  p.tp_on = 0;
   for (int r = 0; r < 8; ++r) {
     p.peer[r] = r < n_peers ? peer_acc[r] : nullptr;
     B200_REQUIRE(r >= n_peers || p.peer[r] != nullptr, B200_E_NULL, "gemm_w8a8_reduce_peers: peer_acc[%d] is null", r);
@@ -843,6 +857,47 @@ extern "C" int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, i
   const int bn = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
   B200_REQUIRE(make_map(&ma, w8, n, k, kBM), B200_E_CUDA, "gemm_w8a8_reduce_peers: cuTensorMapEncodeTiled failed for w8");
   B200_REQUIRE(make_map(&mb, x8, m, k, bn), B200_E_CUDA, "gemm_w8a8_reduce_peers: cuTensorMapEncodeTiled failed for x8");
+  cudaStream_t st = (cudaStream_t)s;
+  switch (bn) {
+    case 256: return launch_gemm<256, 4, true>(ma, mb, p, st);
+    case 128: return launch_gemm<128, 6, true>(ma, mb, p, st);
+    case 64: return launch_gemm<64, 8, true>(ma, mb, p, st);
+    default: return launch_gemm<32, 10, true>(ma, mb, p, st);
+  }
+}
+
+extern "C" int b200_gemm_w8a8_tp(const b200_tp_block* blk, const int8_t* x8, const int8_t* w8, int64_t m, int64_t n,
+                                 int64_t k, b200_stream_t s) {
+  B200_REQUIRE(blk && x8 && w8, B200_E_NULL, "gemm_w8a8_tp: null pointer");
+  B200_REQUIRE(blk->size >= 1 && blk->size <= kTpMaxRanks && blk->rank >= 0 && blk->rank < blk->size, B200_E_SHAPE,
+               "gemm_w8a8_tp: rank=%d size=%d", blk->rank, blk->size);
+  B200_REQUIRE(m >= 1 && m <= 256 && m <= blk->m_max && n == blk->n && k > 0 && k < (1ll << 31), B200_E_UNSUPPORTED,
+               "gemm_w8a8_tp: m=%lld (1..min(256, %d)) n=%lld (the block's %lld) k=%lld", (long long)m, blk->m_max,
+               (long long)n, (long long)blk->n, (long long)k);
+  B200_REQUIRE(k % 16 == 0, B200_E_UNSUPPORTED, "gemm_w8a8_tp: k=%lld must be a multiple of 16", (long long)k);
+  B200_REQUIRE(aligned16(x8) && aligned16(w8), B200_E_ALIGN, "gemm_w8a8_tp: operands must be 16-byte aligned");
+  GemmParams p;
+  p.x_absmax = nullptr; p.x_mul = nullptr; p.x_shift = nullptr; p.w_mul = nullptr; p.w_shift = nullptr;
+  p.out_q15 = nullptr; p.acc_out = nullptr; p.M = (int)m; p.N = (int)n; p.K = (int)k; p.partial = nullptr;
+  p.n_peers = blk->size;
+  p.tp_on = 1;
+  p.tp.rank = blk->rank; p.tp.size = blk->size; p.tp.m_max = blk->m_max; p.tp.n = blk->n;
+  for (int r = 0; r < 8; ++r) {
+    p.peer[r] = nullptr;
+    p.tp.base[r] = r < blk->size ? reinterpret_cast<int32_t*>(blk->base[r]) : nullptr;
+    B200_REQUIRE(r >= blk->size || p.tp.base[r] != nullptr, B200_E_NULL, "gemm_w8a8_tp: base[%d] is null", r);
+  }
+  const int w_blocks = (int)((n + kBM - 1) / kBM), num_kb = (int)((k + kBK - 1) / kBK);
+  int splits = sm_count() / w_blocks;
+  splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
+  while (splits > 1 && num_kb / splits < 4) --splits;
+  while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;
+  p.splits = splits;
+  p.full_blocks = 0;
+  CUtensorMap ma, mb;
+  const int bn = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
+  B200_REQUIRE(make_map(&ma, w8, n, k, kBM), B200_E_CUDA, "gemm_w8a8_tp: cuTensorMapEncodeTiled failed for w8");
+  B200_REQUIRE(make_map(&mb, x8, m, k, bn), B200_E_CUDA, "gemm_w8a8_tp: cuTensorMapEncodeTiled failed for x8");
   cudaStream_t st = (cudaStream_t)s;
   switch (bn) {
     case 256: return launch_gemm<256, 4, true>(ma, mb, p, st);

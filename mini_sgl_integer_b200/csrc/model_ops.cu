@@ -116,6 +116,49 @@ __global__ void decode_prepare_kernel(const int32_t* __restrict__ page_table, in
   seq_lens[b] = pos + 1;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Per-tensor int8 quantisation of a bf16 tensor with a (multiplier, shift) scale: the quantiser the
+// reference's prefill path applies to q, k and v (quantize_per_tensor_int8_ms).  Two passes: the
+// absolute maximum (bf16 bit patterns of non-negative values order like integers), then the codes.
+//   max_abs = max(|x|) clamped below at bf16(1e-8); e = ceil(bf16(log2(max_abs)));
+//   multiplier = int32(min(max_abs * 2^(31 - e), 2^31 - 1)); shift = 31 - e + 7;
+//   code = clamp(rint((fp32(x) / max_abs) * 127), -128, 127).
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+ptq_absmax_kernel(const uint16_t* __restrict__ x, int64_t n, unsigned* __restrict__ max_bits) {
+  unsigned m = 0;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const unsigned b = x[i] & 0x7fffu;
+    if (b <= 0x7f80u) m = max(m, b);            // NaNs do not take part
+  }
+  m = (unsigned)warp_max((int)m);
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(max_bits, m);
+}
+
+__device__ __forceinline__ float bf16_round(float v) {   // round to nearest even on the upper 16 bits
+  const unsigned u = __float_as_uint(v);
+  return __uint_as_float((u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u);
+}
+
+__global__ void __launch_bounds__(256)
+ptq_codes_kernel(const uint16_t* __restrict__ x, int64_t n, const unsigned* __restrict__ max_bits, int8_t* __restrict__ codes,
+                 int32_t* __restrict__ mul_shift) {
+  const float floor_v = __uint_as_float(0x322cu << 16);                    // bf16(1e-8)
+  const float mx = fmaxf(__uint_as_float(*max_bits << 16), floor_v);
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = __uint_as_float((unsigned)x[i] << 16);
+    const float q = __fmul_rn(__fdiv_rn(v, mx), 127.0f);
+    codes[i] = (int8_t)max(-128, min(127, __float2int_rn(q)));
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    const float e = ceilf(bf16_round(log2f(mx)));
+    const float sh = bf16_round(31.0f - e);                                 // the subtraction happens in bf16
+    const float mf = ldexpf(mx, (int)sh);                                   // max_abs * 2^shift, exact
+    mul_shift[0] = mf >= 2147483648.0f ? 2147483647 : (int)mf;
+    mul_shift[1] = (int)sh + 7;
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -155,4 +198,17 @@ extern "C" int b200_decode_prepare(const int32_t* page_table, int64_t table_pitc
   decode_prepare_kernel<<<(batch + 127) / 128, 128, 0, (cudaStream_t)s>>>(page_table, table_pitch, seq_lens, positions, out_loc,
                                                                         kv_lens, batch, max_len);
   return check_launch("decode_prepare");
+}
+
+extern "C" int b200_quantize_per_tensor_int8_ms(const uint16_t* x_bf16, int64_t n, int8_t* codes, int32_t* mul_shift,
+                                                uint32_t* scratch_word, b200_stream_t s) {
+  B200_REQUIRE(n >= 0 && n < (1ll << 40), B200_E_SHAPE, "quantize_per_tensor_int8_ms: n=%lld", (long long)n);
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(x_bf16 && codes && mul_shift && scratch_word, B200_E_NULL, "quantize_per_tensor_int8_ms: null pointer");
+  cudaError_t e = cudaMemsetAsync(scratch_word, 0, sizeof(uint32_t), (cudaStream_t)s);
+  B200_REQUIRE(e == cudaSuccess, B200_E_CUDA, "quantize_per_tensor_int8_ms: cudaMemsetAsync: %s", cudaGetErrorString(e));
+  const int grid = (int)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+  ptq_absmax_kernel<<<grid, 256, 0, (cudaStream_t)s>>>(x_bf16, n, scratch_word);
+  ptq_codes_kernel<<<grid, 256, 0, (cudaStream_t)s>>>(x_bf16, n, scratch_word, codes, mul_shift);
+  return check_launch("quantize_per_tensor_int8_ms");
 }

@@ -17,7 +17,7 @@ import torch
 from ..attention import Int8PagedKVCache, decode_attention_int8_paged, extend_attention_int8_paged, qkv_rope_quant_store
 from ..kernel import fixed_point as fp
 from ..distributed import DistributedCommunicator
-from .tp_linear import PeerReduceBuffers, row_parallel_q15, row_parallel_q15_fused
+from .tp_linear import PeerReduceBuffers, TpExchange, row_parallel_q15, row_parallel_q15_fused
 from .w8a8_int8 import W8A8Int8LinearMethod
 
 
@@ -50,7 +50,7 @@ class Qwen3DecoderLayerInteger:
     def __init__(self, layer_id: int, num_qo_heads: int, num_kv_heads: int, hidden: int, inter: int,
                  weights: dict, cos_sin_cache_q15: torch.Tensor, pool: Int8PagedKVCache,
                  hadamard_block: int = 128, comm: Optional[DistributedCommunicator] = None,
-                 peer_buffers: Optional[PeerReduceBuffers] = None):
+                 peer_buffers: Optional[PeerReduceBuffers] = None, exchange: Optional[TpExchange] = None):
         """``weights``: qkv/o/gate_up/down -> _Linear; input_norm/post_norm int32 [hidden];
         q_norm/k_norm int32 [128] or None (Q15.16; q_norm already carries head_dim**-0.5).
 
@@ -68,6 +68,9 @@ class Qwen3DecoderLayerInteger:
         # tensor parallel: with peer buffers the o / down GEMMs add their partial sums into every rank's
         # accumulator themselves (decode sizes); without, an NCCL all-reduce follows the GEMM
         self.peer_buffers = peer_buffers
+        # with an exchange block the absmax agreement and the ordering between the ranks run over peer memory too:
+        # no collective call in the layer (decode sizes; larger batches fall back to NCCL)
+        self.exchange = exchange
 
     def forward_q15(self, x_q15: torch.Tensor, residual_q15: Optional[torch.Tensor], batch: AttnBatch,
                     trace: Optional[dict] = None):
@@ -104,9 +107,13 @@ class Qwen3DecoderLayerInteger:
             attn = extend_attention_int8_paged(q8, q_mul, q_shift, self.pool, self.layer_id, batch.page_table,
                                                batch.kv_lens, batch.q_lens, batch.max_kv_len)
         t["attn"] = attn
-        tp = self.comm.size > 1
-        rowp = (lambda l, x: row_parallel_q15_fused(m, l, x, self.comm, self.peer_buffers)) if self.peer_buffers is not None \
-            else (lambda l, x: row_parallel_q15(m, l, x, self.comm))
+        tp = self.comm.size > 1 or (self.exchange is not None and self.exchange.size > 1)
+        if self.exchange is not None and self.exchange.fits(T, self.hidden):
+            rowp = lambda l, x: self.exchange.row_parallel_q15(m, l, x)
+        elif self.peer_buffers is not None:
+            rowp = lambda l, x: row_parallel_q15_fused(m, l, x, self.comm, self.peer_buffers)
+        else:
+            rowp = lambda l, x: row_parallel_q15(m, l, x, self.comm)
         o = rowp(w["o"], attn.view(T, qd)) if tp else m.apply_weights_q15(w["o"], attn.view(T, qd))
         t["o"] = o
         # post_attention_layernorm (+ residual add) -> codes for gate_up_proj

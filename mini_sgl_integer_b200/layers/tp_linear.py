@@ -8,10 +8,13 @@ result depend on the rank count.  Here the ranks first agree on the token's absm
 all-reduce), quantise their slices with it, all-reduce the exact int32 accumulators and requantise once:
 bit-identical to a single GPU.
 
-The sum of the accumulators comes in two forms: an NCCL all-reduce after the GEMM (`row_parallel_q15`), or, at
+The sum of the accumulators comes in three forms: an NCCL all-reduce after the GEMM (`row_parallel_q15`); at
 decode sizes, inside the GEMM kernel itself (`row_parallel_q15_fused`): every accumulator tile is added, as it
 leaves tensor memory, into the accumulators of all ranks through NVLink peer memory (`PeerReduceBuffers`), so
-the transfer overlaps the MMAs and no separate collective kernel runs.
+the transfer overlaps the MMAs and no separate collective kernel runs; and `TpExchange.row_parallel_q15`, where
+the absmax agreement and the cross-rank ordering run over peer memory as well (signal at the end of the
+producing kernel, bounded wait at the start of the consuming one), so that a tensor-parallel decode step
+contains no collective call at all and can be captured in a CUDA graph on every rank.
 """
 from __future__ import annotations
 
@@ -123,3 +126,111 @@ def row_parallel_q15_fused(method: W8A8Int8LinearMethod, layer, x_q15_local: tor
     out = requant_q15(acc, x_mul, x_shift, layer.weight_mul, layer.weight_shift)
     acc.zero_()                                        # ready for its next use, two calls from now
     return out
+
+
+class _TpBlockStruct(ctypes.Structure):
+    """b200_tp_block of include/b200int.h."""
+    _fields_ = [("rank", ctypes.c_int), ("size", ctypes.c_int), ("m_max", ctypes.c_int), ("n", ctypes.c_int64),
+                ("base", ctypes.c_void_p * 8)]
+
+
+class TpExchange:
+    """One rank's view of the tensor-parallel exchange blocks (see ``b200_tp_block`` in include/b200int.h).
+
+    ``TpExchange(comm, m_max, n, device)`` allocates this rank's block in symmetric memory
+    (``torch.distributed._symmetric_memory``) and maps every peer's; ``TpExchange.emulated`` builds the views of
+    ``size`` ranks over blocks that all live on ONE device, for tests that run the ranks' calls one after the
+    other on one stream (every wait then finds its flags already set).
+    """
+
+    def __init__(self, comm: DistributedCommunicator | None, m_max: int, n: int, device, *, _bases=None, _rank=None,
+                 _keep=None):
+        from .._lib import load
+        self.m_max, self.n = int(m_max), int(n)
+        self.nbytes = int(load().b200_tp_block_bytes(self.m_max, self.n))
+        if _bases is None:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            self.size = comm.size
+            self.rank = dist.get_rank(comm.group)
+            self._buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+            self._handle = symm_mem.rendezvous(self._buf, comm.group if comm.group is not None else dist.group.WORLD)
+            bases = [int(p) for p in self._handle.buffer_ptrs]
+        else:
+            self.size, self.rank, self._buf, self._handle = len(_bases), int(_rank), _keep, None
+            bases = list(_bases)
+        self.blk = _TpBlockStruct(self.rank, self.size, self.m_max, self.n, (ctypes.c_void_p * 8)(*(bases + [None] * (8 - len(bases)))))
+        self._p = ctypes.byref(self.blk)
+        if _bases is None:
+            call("b200_tp_block_clear", self._p, stream())
+            torch.cuda.current_stream().synchronize()
+            dist.barrier(group=comm.group)                      # every rank's block is clear before anybody writes
+
+    @classmethod
+    def emulated(cls, size: int, m_max: int, n: int, device="cuda") -> list["TpExchange"]:
+        from .._lib import load
+        nbytes = int(load().b200_tp_block_bytes(int(m_max), int(n)))
+        bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(size)]
+        bases = [b.data_ptr() for b in bufs]
+        return [cls(None, m_max, n, device, _bases=bases, _rank=r, _keep=bufs) for r in range(size)]
+
+    # ---- the four steps of a row-split linear (separately, so that emulated ranks can be interleaved)
+    def absmax_put(self, x2: torch.Tensor) -> None:
+        call("b200_tp_absmax_put", self._p, ptr(x2), x2.stride(0), x2.shape[0], x2.shape[1], stream())
+
+    def quant_wait(self, x2: torch.Tensor):
+        codes = torch.empty(x2.shape, dtype=torch.int8, device=x2.device)
+        absmax = torch.empty(x2.shape[0], dtype=torch.int32, device=x2.device)
+        call("b200_tp_quant_wait", self._p, ptr(x2), x2.stride(0), x2.shape[0], x2.shape[1], ptr(codes), ptr(absmax), stream())
+        return codes, absmax
+
+    def gemm_add(self, codes: torch.Tensor, weight: torch.Tensor) -> None:
+        m, k = codes.shape
+        call("b200_gemm_w8a8_tp", self._p, ptr(codes), ptr(weight), m, weight.shape[0], k, stream())
+
+    def requant_wait(self, absmax: torch.Tensor, w_mul: torch.Tensor, w_shift) -> torch.Tensor:
+        m = absmax.shape[0]
+        out = torch.empty((m, self.n), dtype=torch.int32, device=absmax.device)
+        call("b200_tp_requant_wait", self._p, ptr(absmax), ptr(w_mul), ptr(w_shift), ptr(out), m, stream())
+        return out
+
+    @staticmethod
+    def _rows(x_q15_local: torch.Tensor) -> torch.Tensor:
+        assert_q15(x_q15_local, "x_q15_local")
+        require_cuda(x_q15_local)
+        x2 = x_q15_local.reshape(-1, x_q15_local.shape[-1])
+        if x2.stride(1) != 1 or x2.stride(0) % 4 or x2.data_ptr() % 16:
+            x2 = x2.contiguous()
+        return x2
+
+    def fits(self, rows: int, n: int) -> bool:
+        return 0 < rows <= min(256, self.m_max) and n == self.n
+
+    def row_parallel_q15(self, method: W8A8Int8LinearMethod, layer, x_q15_local: torch.Tensor) -> torch.Tensor:
+        """`row_parallel_q15` without a collective call: same bits."""
+        if getattr(layer, "weight_mul", None) is None:
+            method.process_weights_after_loading(layer)
+        x2 = self._rows(x_q15_local)
+        self.absmax_put(x2)
+        codes, absmax = self.quant_wait(x2)
+        self.gemm_add(codes, layer.weight)
+        return self.requant_wait(absmax, layer.weight_mul, layer.weight_shift)
+
+    def all_gather(self, src: torch.Tensor) -> torch.Tensor:
+        """int32 [words] from every rank -> int32 [size, words] (words <= 2 * m_max)."""
+        require_cuda(src)
+        s = src.reshape(-1).to(torch.int32).contiguous()
+        out = torch.empty((self.size, s.numel()), dtype=torch.int32, device=s.device)
+        call("b200_tp_all_gather", self._p, ptr(s), s.numel(), ptr(out), stream())
+        return out
+
+    @staticmethod
+    def status(reset: bool = True) -> int:
+        """0, or channel + 1 of the first wait that ran out since the last reset (synchronises)."""
+        v = ctypes.c_int(0)
+        call("b200_tp_status", ctypes.byref(v), int(reset))
+        return int(v.value)
+
+    @staticmethod
+    def set_timeout_us(us: int) -> None:
+        call("b200_tp_set_timeout_us", int(us))

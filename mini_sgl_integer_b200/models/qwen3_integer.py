@@ -19,6 +19,7 @@ from ..attention import Int8PagedKVCache
 from ..distributed import DistributedCommunicator
 from ..kernel import fixed_point as fp
 from ..layers.decoder_layer import AttnBatch, Qwen3DecoderLayerInteger, _Linear
+from ..layers.tp_linear import TpExchange
 from ..layers.w8a8_int8 import W8A8Int8LinearMethod
 
 
@@ -86,6 +87,22 @@ def merge_sharded_argmax(values: torch.Tensor, indices: torch.Tensor) -> torch.T
     return ids.min(dim=0).values.to(torch.int32)
 
 
+def check_device_status() -> None:
+    """Raises if a bounded wait inside a GEMM kernel (operand / accumulator hand-over) or inside a tensor-parallel
+    exchange kernel (a peer's signal) has expired since the last check.  Both reads synchronise with the device:
+    call it where the step's tokens have just been copied to the host anyway."""
+    import ctypes
+    st = ctypes.c_int(0)
+    call("b200_gemm_status", ctypes.byref(st), 1)
+    if st.value:
+        raise RuntimeError(f"a wait inside a W8A8 GEMM kernel expired (code {st.value}: 1 loader, 2 MMA issuer, "
+                           "3 epilogue, 4 accumulator hand-back); the step's results are not valid")
+    call("b200_tp_status", ctypes.byref(st), 1)
+    if st.value:
+        raise RuntimeError(f"a tensor-parallel wait expired on channel {st.value - 1} (0 absmax, 1 sums, 2 gather): "
+                           "a peer rank did not arrive; the step's results are not valid")
+
+
 class DecodeBatch:
     """Device-resident state of a decode batch: page table, lengths and the per-step views derived from them.
 
@@ -117,28 +134,32 @@ class Qwen3ModelInteger:
     """embed_tokens -> layers -> final norm, activations in Q15.16 / int8 codes."""
 
     def __init__(self, cfg: Qwen3IntegerConfig, weights: dict, pool: Int8PagedKVCache,
-                 comm: Optional[DistributedCommunicator] = None):
+                 comm: Optional[DistributedCommunicator] = None, exchange: Optional[TpExchange] = None):
         """``weights``: "embed" bf16 [vocab, hidden]; "layers": list of per-layer dicts (see
         Qwen3DecoderLayerInteger); "final_norm" int32 [hidden] (Q15.16).
 
         Under tensor parallelism ``cfg`` carries this rank's head counts and intermediate size, the layer
         weights are this rank's shards, and "embed" holds this rank's block of vocabulary rows starting at
         ``weights["vocab_start"]`` (VocabParallelEmbedding, layers/embedding.py:14-42): ids of other ranks give
-        zero rows and the sum over ranks restores the embedding."""
+        zero rows and the sum over ranks restores the embedding.  With ``weights["embed_replicated"]`` every
+        rank holds the whole table and no sum is needed (a decode step then has no collective call when the
+        layers run on an ``exchange``)."""
         self.cfg, self.w, self.pool = cfg, weights, pool
         self.comm = comm if comm is not None else DistributedCommunicator()
-        self.vocab_start = int(weights.get("vocab_start", 0))
+        self.exchange = exchange
+        self.embed_replicated = bool(weights.get("embed_replicated", False))
+        self.vocab_start = 0 if self.embed_replicated else int(weights.get("vocab_start", 0))
         self.cache = rope_cache_q15(cfg.max_pos, cfg.rope_base, cfg.head_dim).to(pool.device)
         self.layers = [
             Qwen3DecoderLayerInteger(i, cfg.num_qo_heads, cfg.num_kv_heads, cfg.hidden, cfg.inter, weights["layers"][i],
-                                     self.cache, pool, cfg.hadamard_block, comm)
+                                     self.cache, pool, cfg.hadamard_block, comm, exchange=exchange)
             for i in range(cfg.num_layers)
         ]
 
     def forward(self, input_ids: torch.Tensor, batch: AttnBatch):
         """Returns the final norm's output as int8 codes [tokens, hidden] with the per-token absmax [tokens]."""
         x = embedding_to_fixed(self.w["embed"], input_ids, self.vocab_start)
-        if self.comm.size > 1:
+        if self.comm.size > 1 and not self.embed_replicated:
             x = self.comm.all_reduce(x)
         residual = None
         for layer in self.layers:
@@ -149,12 +170,13 @@ class Qwen3ModelInteger:
 
 class Qwen3ForCausalLMInteger:
     def __init__(self, cfg: Qwen3IntegerConfig, weights: dict, pool: Int8PagedKVCache,
-                 comm: Optional[DistributedCommunicator] = None):
+                 comm: Optional[DistributedCommunicator] = None, exchange: Optional[TpExchange] = None):
         """``weights`` additionally holds "lm_head": _Linear with int8 [vocab, hidden] and its channel scales
         (under tensor parallelism this rank's vocabulary rows, ParallelLMHead, layers/embedding.py:46-110)."""
-        self.model = Qwen3ModelInteger(cfg, weights, pool, comm)
+        self.model = Qwen3ModelInteger(cfg, weights, pool, comm, exchange)
         self.comm = self.model.comm
-        self.vocab_start = self.model.vocab_start
+        self.exchange = exchange
+        self.vocab_start = int(weights.get("vocab_start", 0))          # of the lm_head rows
         self.lm_head = weights["lm_head"]
         self.method = W8A8Int8LinearMethod()
 
@@ -167,17 +189,48 @@ class Qwen3ForCausalLMInteger:
             codes, absmax = codes.index_select(0, idx), absmax.index_select(0, idx)
         return self.method.apply_quantised(self.lm_head, codes, absmax)
 
+    check_status = staticmethod(check_device_status)
+
     def greedy(self, input_ids: torch.Tensor, batch: AttnBatch, last_indices: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Next token ids int32 [rows] (integer arg-max, lowest index on ties).  With a sharded vocabulary every
         rank takes the arg-max of its rows and the (value, id) pairs are merged - two tiny all-gathers instead
         of the reference's all-gather of the full logits (layers/embedding.py:100-110)."""
         logits = self.forward(input_ids, batch, last_indices)
-        if self.comm.size == 1:
+        ranks = self.exchange.size if self.exchange is not None else self.comm.size
+        if ranks == 1:
             return argmax_int32(logits)
         idx, val = argmax_int32(logits, index_offset=self.vocab_start, return_values=True)
         rows = idx.shape[0]
-        both = self.comm.all_gather(torch.stack((val, idx)).reshape(1, 2, rows))        # [ranks, 2, rows]
+        if self.exchange is not None and 2 * rows <= 2 * self.exchange.m_max:
+            both = self.exchange.all_gather(torch.stack((val, idx))).view(ranks, 2, rows)   # over peer memory
+        else:
+            both = self.comm.all_gather(torch.stack((val, idx)).reshape(1, 2, rows))        # [ranks, 2, rows]
         return merge_sharded_argmax(both[:, 0], both[:, 1])
+
+
+def shard_layer_weights(lw: dict, rank: int, size: int, num_qo_heads: int, num_kv_heads: int, inter: int,
+                        head_dim: int = 128) -> dict:
+    """Rank ``rank``'s tensor-parallel shard of one layer's weight dict (see Qwen3DecoderLayerInteger): the q | k | v
+    and gate | up output channels of the local heads / columns, the input features of o / down, as the reference
+    shards and merges them at load time (models/weight.py:12-52)."""
+    hq, hk, il = num_qo_heads // size, num_kv_heads // size, inter // size
+    dev = lw["qkv"].weight.device
+    ar = lambda a, b: torch.arange(a, b, device=dev)
+
+    def rows(l, idx):
+        return _Linear(l.weight[idx].contiguous(), weight_mul=l.weight_mul[idx].contiguous(),
+                       weight_shift=l.weight_shift[idx].contiguous())
+
+    def cols(l, per):
+        return _Linear(l.weight[:, rank * per:(rank + 1) * per].contiguous(), weight_mul=l.weight_mul, weight_shift=l.weight_shift)
+    k0, v0 = num_qo_heads * head_dim, (num_qo_heads + num_kv_heads) * head_dim
+    out = dict(lw)
+    out["qkv"] = rows(lw["qkv"], torch.cat([ar(rank * hq * head_dim, (rank + 1) * hq * head_dim),
+                                            ar(k0 + rank * hk * head_dim, k0 + (rank + 1) * hk * head_dim),
+                                            ar(v0 + rank * hk * head_dim, v0 + (rank + 1) * hk * head_dim)]))
+    out["gate_up"] = rows(lw["gate_up"], torch.cat([ar(rank * il, (rank + 1) * il), inter + ar(rank * il, (rank + 1) * il)]))
+    out["o"], out["down"] = cols(lw["o"], hq * head_dim), cols(lw["down"], il)
+    return out
 
 
 def random_weights(cfg: Qwen3IntegerConfig, seed: int, device="cuda", qk_norm: bool = True,

@@ -139,6 +139,29 @@ def q15_to_bf16_bits(out_q15: np.ndarray) -> np.ndarray:
     return rounded.astype(np.uint16).view(np.int16)
 
 
+def quantize_per_tensor_int8_ms(x_bf16_bits: np.ndarray):
+    """quantize_per_tensor_int8_ms (int8_attention_kernels.py:41-53) for a bf16 tensor given as raw uint16 bits.
+
+    The maximum, its clamp at 1e-8 and log2 / ceil / 31 - e are bf16 operations in the reference (the tensor's
+    dtype), the multiplier and the codes fp32.  Returns (codes int8, multiplier int, shift int).
+    """
+    bits = np.asarray(x_bf16_bits).view(np.uint16)
+    x = (bits.astype(np.uint32) << 16).view(np.float32)
+
+    def bf16(v):
+        u = np.float32(v).reshape(1).view(np.uint32).astype(np.uint64)
+        r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+        return r.astype(np.uint32).view(np.float32)[0]
+    max_abs = max(np.float32(np.abs(x).max()) if x.size else np.float32(0), bf16(1e-8))
+    e = np.ceil(bf16(np.log2(np.float32(max_abs))))
+    shift = int(bf16(np.float32(31.0) - e))
+    mult_f = np.float32(max_abs) * np.float32(2.0) ** np.float32(shift)
+    multiplier = int(min(mult_f, np.float32(2**31 - 1)))
+    multiplier = min(multiplier, 2**31 - 1)
+    q = np.clip(np.rint((x / np.float32(max_abs)) * np.float32(127.0)), -128, 127).astype(np.int8)
+    return q, multiplier, shift + 7
+
+
 # --------------------------------------------------------------------------- paged pool
 def absmax_to_mul_shift(m):
     """Fixed-point form of the per-row int8 scale m / (127 * 65536) (build-defined).

@@ -262,7 +262,7 @@ def per_token_quant_from_q15(x: np.ndarray):
     neg = _wrap32(-(x2.astype(np.int64)))
     m = np.maximum(np.where(x2 < 0, neg, x2).max(axis=1, keepdims=True), 1).astype(np.int32)
     q = (x2.astype(np.float32) * np.float32(127.0)) / m.astype(np.float32)
-    q = np.clip(np.rint(q).astype(np.int32), -128, 127).astype(np.int8)
+    q = np.clip(np.rint(q), -128, 127).astype(np.int8)          # clamp first: a row's -2^31 gives a quotient beyond int32
     scale = m.astype(np.float32) / np.float32(127.0 * float(FIXED_POINT_SCALE))
     lead = x.shape[:-1] + (1,)
     return q.reshape(x.shape), scale.reshape(lead), m.reshape(lead)

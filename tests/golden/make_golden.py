@@ -221,6 +221,31 @@ def main() -> None:
         put(f"static_codes_{i}", c8)
     put("static_in", sq); put("static_scales", np.array([0.013671875, 0.05, 1e-3], dtype=np.float32))
 
+    # per-token quant of rows that hold -2^31 (its |x| wraps, so it never enters the absmax and its code clamps
+    # to -128) next to mid-size values: row absmax below 2^22, above it, and just below 2^31
+    g3 = torch.Generator().manual_seed(3)
+    qi = torch.randint(-(2**20), 2**20, (4, 64), generator=g3, dtype=torch.int32)
+    qi[1] = torch.randint(-(2**27), 2**27, (64,), generator=g3, dtype=torch.int32)
+    qi[2] = torch.randint(-(2**31) + 1, 2**31 - 1, (64,), generator=g3, dtype=torch.int64).to(torch.int32)
+    qi[3] = 0
+    for r in range(4):
+        qi[r, 7 + r] = -(2**31)
+    qi[0, 40] = -(2**31)
+    i8, isc = per_token_quant_int8_from_q15(qi)
+    put("quant_intmin_in", qi); put("quant_intmin_codes", i8); put("quant_intmin_scale", isc)
+
+    # the same quantiser at other magnitudes: a maximum just above a power of two (its bf16 log2 rounds down to the
+    # integer, and the multiplier then exceeds int32: the x86 conversion stored here wraps to -2^31 where a CUDA
+    # device saturates at 2^31 - 1), a small one, a large one, and an all-zero tensor (clamped at 1e-8)
+    g4 = torch.Generator().manual_seed(4)
+    for i, (mult, peak) in enumerate(((1.0, 16.125), (1.0 / 300.0, None), (1000.0, None), (0.0, None))):
+        t = (torch.randn(33, 128, generator=g4) * mult).to(torch.bfloat16)
+        if peak is not None:
+            t = t.clamp(-8, 8); t[3, 5] = peak
+        c8, cm, cs = quantize_per_tensor_int8_ms(t)
+        put(f"ptq{i}_in_bf16_bits", t.view(torch.int16)); put(f"ptq{i}_codes", c8)
+        put(f"ptq{i}_ms", np.array([int(cm), int(cs)], dtype=np.int64))
+
     np.savez_compressed(os.path.join(HERE, "ref_vectors.npz"), **vec)
     with open(os.path.join(HERE, "ref_hashes.json"), "w") as fjs:
         json.dump(hashes, fjs, indent=1, sort_keys=True)

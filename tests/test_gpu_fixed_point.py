@@ -72,6 +72,42 @@ def test_golden_quant_edges(fp, golden):
     eq(host(q), golden["quant_edge_codes"]); eq(host(s), golden["quant_edge_scale"])
 
 
+def test_golden_quant_rows_holding_int_min(fp, golden):
+    """Rows with -2^31 beside ordinary values: the code is -128 on every quantising path (row absmax below 2^22,
+    above it, near 2^31, and a row that is otherwise zero)."""
+    x = golden["quant_intmin_in"]
+    q, s = fp.per_token_quant_int8_from_q15(dev(x))
+    eq(host(q), golden["quant_intmin_codes"]); eq(host(s), golden["quant_intmin_scale"])
+    # the same rows as V heads on their way into the pool, and quantised with a given absmax
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    from mini_sgl_integer_b200.layers.tp_linear import quant_given_absmax
+    from oracle import attention as oattn
+    rows = np.concatenate([x, x], axis=1)                              # [4, 128]: one 128-wide head row per token
+    pool = Int8PagedKVCache(1, 1, 128, 2, "cuda")
+    loc = np.array([3, 16, 17, 31], dtype=np.int32)
+    pool.store_kv(dev(rows), dev(rows), dev(loc), 0)
+    ref = oattn.PagedKV(2, 1, 128)
+    ref.store_q15(loc, rows, rows)
+    eq(host(pool.k_cache(0)), ref.k_codes); eq(host(pool.v_cache(0)), ref.v_codes); eq(host(pool.meta(0)), ref.meta)
+    want, _, m = ofp.per_token_quant_from_q15(rows)
+    eq(host(quant_given_absmax(dev(rows), dev(m.reshape(-1)))), want)
+
+
+def test_golden_per_tensor_quantiser(golden):
+    """quantize_per_tensor_int8_ms (the reference's prefill quantiser) on the device: codes, multiplier, shift."""
+    from mini_sgl_integer_b200.attention import quantize_per_tensor_int8_ms
+    for key in ("ptq", "ptq0", "ptq1", "ptq2", "ptq3"):
+        bits = golden[f"{key}_in_bf16_bits"]
+        q, mul, shift = quantize_per_tensor_int8_ms(dev(bits).view(torch.bfloat16))
+        eq(host(q), golden[f"{key}_codes"])
+        want_mul, want_shift = (int(v) for v in golden[f"{key}_ms"])
+        assert int(shift) == want_shift, key
+        # ptq0: the multiplier exceeds int32; the x86 fixture wrapped, a CUDA device (the reference's too) saturates
+        assert int(mul) == (2**31 - 1 if key == "ptq0" else want_mul), key
+    with pytest.raises(TypeError):
+        quantize_per_tensor_int8_ms(torch.zeros(4, device="cuda"))
+
+
 def _cache(pos, rows, n=4096):
     c = np.zeros((n, rows.shape[1]), dtype=np.int32)
     c[pos] = rows

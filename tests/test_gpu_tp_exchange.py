@@ -1,0 +1,118 @@
+"""The tensor-parallel exchange kernels on ONE GPU: the calls of 2, 4 or 8 ranks are issued one after the other on
+one stream over exchange blocks that all live on this device, so every wait finds its flags already set.  The
+row-split linear must give the bits of the unsplit linear (the oracle's), repeatedly (both halves of the blocks
+get reused and cleared), and a wait that nothing satisfies must end by itself with a status code."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as oattn
+from oracle import fixed_point as ofp
+from oracle import linear as olin
+
+pytestmark = pytest.mark.gpu
+
+
+def d(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _case(seed, m, n, k):
+    rng = np.random.default_rng(seed)
+    x = np.clip(np.rint(rng.normal(0, 2**16, (m, k))), -(2**24), 2**24).astype(np.int32)
+    x[0, :] = 0                                                     # an all-zero row: absmax 1
+    w8 = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    wm = rng.integers(2**29, 2**30, n).astype(np.int32)
+    ws = rng.integers(30, 34, n).astype(np.int32)
+    codes, _, absmax = ofp.per_token_quant_from_q15(x)
+    xm, xs = oattn.absmax_to_mul_shift(absmax.reshape(-1))
+    want = olin.requant_q15(olin.int32_accumulate(codes, w8), xm, xs, wm, ws)
+    return x, w8, wm, ws, want
+
+
+@pytest.mark.parametrize("size", [1, 2, 4, 8])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (33, 1028, 1024), (256, 1024, 2048)])
+def test_row_split_linear_over_exchange_blocks(size, m, n, k):
+    from mini_sgl_integer_b200.layers.tp_linear import TpExchange
+    x, w8, wm, ws, want = _case(size * 1000 + m, m, n, k)
+    ks = k // size
+    ranks = TpExchange.emulated(size, 256, n)
+    xs_ = [d(x[:, r * ks:(r + 1) * ks]) for r in range(size)]
+    w_ = [d(w8[:, r * ks:(r + 1) * ks]) for r in range(size)]
+    wm_d, ws_d = d(wm), d(ws)
+    for rnd in range(3):
+        for r in range(size):
+            ranks[r].absmax_put(xs_[r])
+        q = [ranks[r].quant_wait(xs_[r]) for r in range(size)]
+        for r in range(size):
+            ranks[r].gemm_add(q[r][0], w_[r])
+        outs = [ranks[r].requant_wait(q[r][1], wm_d, ws_d) for r in range(size)]
+        for r in range(size):
+            np.testing.assert_array_equal(outs[r].cpu().numpy(), want, err_msg=f"round {rnd}, rank {r}")
+    assert TpExchange.status() == 0
+    # everything that was accumulated into has been cleared again
+    for r in range(size):
+        body = ranks[r]._buf[r].view(torch.int32)[64 + 64:]          # past the header and the flag words
+        assert int(body.abs().max()) == 0
+
+
+def test_all_gather_over_exchange_blocks():
+    from mini_sgl_integer_b200.layers.tp_linear import TpExchange
+    size, words = 4, 37
+    ranks = TpExchange.emulated(size, 32, 64)
+    rng = np.random.default_rng(1)
+    for rnd in range(3):
+        src = rng.integers(-2**31, 2**31, (size, words), dtype=np.int64).astype(np.int32)
+        # a rank's gather kernel signals and then waits for everybody: with the ranks emulated one after the other
+        # only the LAST rank's call finds all slots filled, so the earlier calls are issued with a short time limit
+        TpExchange.set_timeout_us(2000)
+        outs = [ranks[r].all_gather(d(src[r])) for r in range(size)]
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(outs[size - 1].cpu().numpy(), src, err_msg=f"round {rnd}")
+    assert TpExchange.status() == 3                                   # the early ranks' waits ran out (channel 2)
+    TpExchange.set_timeout_us(2_000_000)
+    assert TpExchange.status() == 0
+
+
+def test_wait_that_nothing_satisfies_ends_with_a_status():
+    """Rank 0 of two: its peer never signals.  The consumer kernel gives up after the time limit, the context stays
+    usable, and the status word names the channel."""
+    from mini_sgl_integer_b200.layers.tp_linear import TpExchange
+    ranks = TpExchange.emulated(2, 16, 64)
+    x = d(np.arange(16 * 64, dtype=np.int32).reshape(16, 64))
+    TpExchange.set_timeout_us(20_000)
+    try:
+        ranks[0].absmax_put(x)
+        codes, absmax = ranks[0].quant_wait(x)
+        torch.cuda.synchronize()
+        assert TpExchange.status() == 1
+        assert TpExchange.status() == 0                              # cleared by the read above
+        assert codes.shape == (16, 64) and int(absmax[15]) == 16 * 64 - 1   # rank 0's own maxima were there
+    finally:
+        TpExchange.set_timeout_us(2_000_000)
+
+
+@pytest.mark.parametrize("n_peers", [1, 2])
+@pytest.mark.parametrize("m,n,k", [(1, 384, 512), (33, 1028, 1024), (256, 4096, 2048)])
+def test_gemm_reduce_peers_adds_into_every_buffer(n_peers, m, n, k):
+    """b200_gemm_w8a8_reduce_peers with the peers' accumulators on this device: every buffer receives the exact
+    int32 accumulators once per call (split and unsplit tiles, ragged n), also on top of earlier contents."""
+    from mini_sgl_integer_b200._lib import call, ptr, stream
+    rng = np.random.default_rng(7 * m + n_peers)
+    x8 = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    w8 = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    acc = olin.int32_accumulate(x8, w8)
+    bufs = [torch.zeros((m, n), dtype=torch.int32, device="cuda") for _ in range(n_peers)]
+    arr = (ctypes.c_void_p * n_peers)(*[b.data_ptr() for b in bufs])
+    xd, wd = d(x8), d(w8)
+    for rnd in range(3):
+        call("b200_gemm_w8a8_reduce_peers", ptr(xd), ptr(wd), arr, n_peers, m, n, k, stream())
+        for b in bufs:
+            np.testing.assert_array_equal(b.cpu().numpy(), acc * (rnd + 1))
+    st = ctypes.c_int(0)
+    call("b200_gemm_status", ctypes.byref(st), 1)
+    assert st.value == 0

@@ -198,3 +198,26 @@ def test_static_input_scale_quant_matches_reference(golden):
     x = golden["static_in"]
     for i, scale in enumerate(golden["static_scales"]):
         np.testing.assert_array_equal(ofp.static_quant_from_q15(x, scale), golden[f"static_codes_{i}"])
+
+
+def test_quant_rows_holding_int_min(golden):
+    """-2^31 never enters the row's absmax (|x| wraps) and its code clamps to -128, whatever the row's magnitude."""
+    q, s, m = ofp.per_token_quant_from_q15(golden["quant_intmin_in"])
+    assert np.array_equal(q, golden["quant_intmin_codes"])
+    assert np.array_equal(s.reshape(-1), golden["quant_intmin_scale"].reshape(-1))
+    assert (q[golden["quant_intmin_in"] == -(2**31)] == -128).all() and int(m[3, 0]) == 1
+
+
+def test_per_tensor_quantiser_matches_reference(golden):
+    """quantize_per_tensor_int8_ms, the quantiser of the reference's prefill path: codes, multiplier and shift."""
+    for key in ("ptq", "ptq0", "ptq1", "ptq2", "ptq3"):
+        q, mul, shift = oattn.quantize_per_tensor_int8_ms(golden[f"{key}_in_bf16_bits"])
+        assert np.array_equal(q, golden[f"{key}_codes"]), key
+        want_mul, want_shift = (int(v) for v in golden[f"{key}_ms"])
+        assert shift == want_shift, key
+        if key == "ptq0":
+            # the maximum 16.125 has a bf16 log2 of exactly 4, so the multiplier is 16.125 * 2^27 > int32: the
+            # fixture (made on x86) holds the wrapped -2^31, a CUDA device saturates; the oracle follows the device
+            assert want_mul == -(2**31) and mul == 2**31 - 1
+        else:
+            assert mul == want_mul, key

@@ -8,6 +8,7 @@ import pytest
 import torch
 
 from attn_util import device_pool, make_case
+from oracle import attention as oattn
 
 pytestmark = pytest.mark.gpu
 
@@ -62,6 +63,27 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point():
         want, got = _both(case, pool, longest)
         for w, g in zip(want, got):
             np.testing.assert_array_equal(g, w)
+
+
+def test_matches_the_oracle_and_leaves_device_memory_alone():
+    """One batch against the CPU oracle (Q15.16 output, int8 codes and their absmax), and the amount of free device
+    memory before and after a call that is not the first one on the device: the call allocates nothing."""
+    from mini_sgl_integer_b200._lib import call, ptr, stream
+    case = make_case(75, [130, 17, 1, 640], 8, 2, 64)
+    pool = device_pool(case, 64, 2)
+    keep, head, tail, (batch, q_heads) = _args(case, pool, 640)
+    out = _outputs(batch, q_heads)
+    call("b200_attn_paged_static", *head, ptr(out[0]), ptr(out[1]), ptr(out[2]), *tail, stream())   # set-up call
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    call("b200_attn_paged_static", *head, ptr(out[0]), ptr(out[1]), ptr(out[2]), *tail, stream())
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    want = oattn.paged_attention(case["q8"], case["qm"], case["qs"], case["pool"], case["tables"], case["kv_lens"], [1] * batch)
+    codes, absmax = oattn.quant_heads_int8(want)
+    np.testing.assert_array_equal(out[0].cpu().numpy(), want)
+    np.testing.assert_array_equal(out[1].cpu().numpy(), codes)
+    np.testing.assert_array_equal(out[2].cpu().numpy(), absmax)
 
 
 def test_same_call_twice_gives_the_same_answer():
