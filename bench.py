@@ -386,7 +386,8 @@ def build_parity_case(dev, comm, exch, full_layer0, cache, rank, world):
     batch = AttnBatch(t((lens - 1).astype(np.int32)), t(out_loc), t(table), t(lens.astype(np.int32)), None, 256)
     x = (torch.randn(T, HID, device=dev, generator=g) * 30000.0).round().to(torch.int32)
     res = (torch.randn(T, HID, device=dev, generator=g) * 30000.0).round().to(torch.int32)
-    full = Qwen3DecoderLayerInteger(0, HQ, HK, HID, INTER, full_layer0, cache, pool_full)
+    from mini_sgl_integer_b200.distributed import DistributedCommunicator
+    full = Qwen3DecoderLayerInteger(0, HQ, HK, HID, INTER, full_layer0, cache, pool_full, comm=DistributedCommunicator(single=True))
     want, want_res = full.forward_q15(x, res, batch)
     tp = Qwen3DecoderLayerInteger(0, HQ // world, hk, HID, INTER // world, shard_layer_weights(full_layer0, rank, world, HQ, HK, INTER),
                                   cache, pool_tp, comm=comm, exchange=exch)

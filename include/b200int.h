@@ -331,15 +331,20 @@ B200_API int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, int
  * seen from the calling process, base[rank] the caller's own.  Clear the own block once with
  * b200_tp_block_clear and make sure (host barrier) that every rank has done so before the first exchange.
  * All ranks must issue the same sequence of these calls.  A row-split linear is
- *     b200_tp_absmax_put   the token's absmax over this rank's K-slice, folded into every rank's block
- *     b200_tp_quant_wait   waits for all ranks, quantises the slice with the agreed absmax
- *     b200_gemm_w8a8_tp    partial sums added straight from tensor memory into every rank's block
- *     b200_tp_requant_wait waits for all ranks, applies the epilogue of b200_gemm_w8a8 to the sum
+ *     b200_tp_absmax_put      the token's absmax over this rank's K-slice, folded into every rank's block
+ *     b200_tp_quant_wait      waits for all ranks, quantises the slice with the agreed absmax
+ *     b200_gemm_w8a8_tp       partial sums; every token row is stored (16-byte stores) only into the block of
+ *                             the rank that owns the row (rank = row / ceil(m / size))
+ *     b200_tp_requant_scatter waits for all ranks, adds the partial sums of the rows it owns, applies the
+ *                             epilogue of b200_gemm_w8a8 and stores the finished rows into every rank's block
+ *     b200_tp_collect         waits for all ranks, copies the m finished rows to out_q15 int32 [m, n]
+ * With one or two ranks the last three steps are two: b200_gemm_w8a8_tp stores every row into every rank's block
+ * (the same bytes at two ranks) and b200_tp_requant_direct finishes all m rows into out_q15.
  * and gives the bits of b200_gemm_w8a8 on the whole K on one GPU.  b200_tp_all_gather exchanges up to
  * 2 * m_max words per rank (dst int32 [size][words], rank order).  Producer kernels end with a signal,
  * consumer kernels start with a wait that is bounded (default 2 s, b200_tp_set_timeout_us): on expiry the
- * kernel carries on with what the block holds and b200_tp_status reports channel + 1 (1 absmax, 2 sums,
- * 3 gather).  Kernels only: a step made of these calls can be captured in a CUDA graph.  x: int32 rows with
+ * kernel carries on with what the block holds and b200_tp_status reports 1 (absmax exchange), 2 (sums),
+ * 3 (gather) or 4 (finished rows).  Kernels only: a step made of these calls can be captured in a CUDA graph.  x: int32 rows with
  * the given pitch (elements); k and n multiples of 4; rows, m <= m_max (and <= 256 for the GEMM). */
 typedef struct {
   int rank;        /* this process's rank, 0 .. size-1 */
@@ -354,10 +359,17 @@ B200_API int b200_tp_absmax_put(const b200_tp_block* blk, const int32_t* x, int6
                                 b200_stream_t s);
 B200_API int b200_tp_quant_wait(const b200_tp_block* blk, const int32_t* x, int64_t pitch, int rows, int k,
                                 int8_t* codes, int32_t* absmax_out, b200_stream_t s);
+/* b200_tp_absmax_put + b200_tp_quant_wait in one launch (rows <= 512): a row's CTA delivers, waits for the
+ * peers' words of the same row and quantises; one kernel less in the step, same words and counters. */
+B200_API int b200_tp_absmax_quant(const b200_tp_block* blk, const int32_t* x, int64_t pitch, int rows, int k,
+                                  int8_t* codes, int32_t* absmax_out, b200_stream_t s);
 B200_API int b200_gemm_w8a8_tp(const b200_tp_block* blk, const int8_t* x8, const int8_t* w8, int64_t m, int64_t n,
                                int64_t k, b200_stream_t s);
-B200_API int b200_tp_requant_wait(const b200_tp_block* blk, const int32_t* absmax, const int32_t* w_mul,
-                                  const int32_t* w_shift, int32_t* out_q15, int m, b200_stream_t s);
+B200_API int b200_tp_requant_scatter(const b200_tp_block* blk, const int32_t* absmax, const int32_t* w_mul,
+                                     const int32_t* w_shift, int m, b200_stream_t s);
+B200_API int b200_tp_collect(const b200_tp_block* blk, int32_t* out_q15, int m, b200_stream_t s);
+B200_API int b200_tp_requant_direct(const b200_tp_block* blk, const int32_t* absmax, const int32_t* w_mul,
+                                    const int32_t* w_shift, int32_t* out_q15, int m, b200_stream_t s);
 B200_API int b200_tp_all_gather(const b200_tp_block* blk, const int32_t* src, int words, int32_t* dst,
                                 b200_stream_t s);
 B200_API int b200_tp_status(int* out_host, int reset);        /* synchronises with the device */

@@ -54,8 +54,11 @@ SIGNATURES: dict[str, list] = {
     "b200_tp_block_clear": [P, P],
     "b200_tp_absmax_put": [P, P, L, I, I, P],
     "b200_tp_quant_wait": [P, P, L, I, I, P, P, P],
+    "b200_tp_absmax_quant": [P, P, L, I, I, P, P, P],
     "b200_gemm_w8a8_tp": [P, P, P, L, L, L, P],
-    "b200_tp_requant_wait": [P, P, P, P, P, I, P],
+    "b200_tp_requant_scatter": [P, P, P, P, I, P],
+    "b200_tp_collect": [P, P, I, P],
+    "b200_tp_requant_direct": [P, P, P, P, P, I, P],
     "b200_tp_all_gather": [P, P, I, P, P],
     "b200_tp_status": [P, I],
     "b200_tp_set_timeout_us": [L],

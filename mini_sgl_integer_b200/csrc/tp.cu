@@ -1,11 +1,11 @@
 // Tensor-parallel exchange steps of the row-split linears over NVLink peer memory (decode sizes).
 //
 // A row-split linear (o_proj, down_proj) on `size` ranks gives the bits of one GPU when the ranks
-//   1. agree on every token's absmax            (atomicMax into every rank's block, channel 0),
+//   1. agree on every token's absmax            (one word per rank and token stored into every rank's block),
 //   2. quantise their K-slice with it,
-//   3. add their exact int32 partial sums       (red.global from the GEMM epilogue, channel 1),
-//   4. requantise the sum once.
-// Steps 1 and 3 write straight into the peers' memory; a producer kernel ends with a signal (its last CTA
+//   3. add their exact int32 partial sums       (each token row is sent to one owner rank, channel 1),
+//   4. requantise the sum once and hand the finished rows to everybody (channel 3).
+// Steps 1, 3 and 4 write straight into the peers' memory; a producer kernel ends with a signal (its last CTA
 // stores the channel's new epoch into every rank's flag word), the consumer kernel begins with a bounded
 // wait on those flags.  No collective library call, no host synchronisation: a decode step that uses these
 // kernels is an ordinary stream of launches and can be captured in a CUDA graph on every rank.
@@ -21,7 +21,7 @@ static __device__ int g_tp_status = 0;                             // 0 = fine, 
 static __device__ unsigned long long g_tp_timeout_ns = 2000000000ull;
 
 // Waits until every rank's signal number `epoch` on channel ch has arrived: threads 0 .. size-1 poll one
-// source each; the caller follows with a CTA barrier.
+// source each; the caller follows with a CTA barrier and reads the peers' data past L1 (__ldcg).
 __device__ __forceinline__ void tp_wait_flags(const TpView& v, int ch, int epoch) {
   if ((int)threadIdx.x < v.size) {
     const int32_t* f = v.base[v.rank] + kTpHdrWords + ch * kTpMaxRanks + threadIdx.x;
@@ -32,56 +32,81 @@ __device__ __forceinline__ void tp_wait_flags(const TpView& v, int ch, int epoch
           atomicCAS(&g_tp_status, 0, ch + 1);
           break;
         }
-        __nanosleep(64);
+        __nanosleep(32);
       }
     }
   }
 }
 
-// ---------------------------------------------------------------------------- step 1: absmax agreement
-// One CTA per token row of this rank's slice x [rows, k] (row pitch in elements): the row's max(1, max|x|)
-// is folded into amax[half][row] of every rank.  Signals channel 0.
+// ---------------------------------------------------------------------------- steps 1 + 2: absmax agreement, quantisation
+// The absmax of a token row over this rank's K-slice is max(1, max|x|) >= 1, so it doubles as its own arrival
+// flag: rank r stores it with one 4-byte store into word [half][row][r] of every rank's block, and a row is
+// complete when all `size` words of the row are non-zero - no fence, no separate flag.  The agreed absmax is
+// their maximum; the reader clears the words.  The half alternates with a per-rank call counter (header word
+// 4) advanced by the last CTA of the reading kernel.
+__device__ __forceinline__ int tp_row_absmax(const int4* __restrict__ xr, int nvec, int* red32) {
+  int m = 0;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const int4 a = xr[i];
+    m = max(max(m, abs_wrap(a.x)), max(abs_wrap(a.y), max(abs_wrap(a.z), abs_wrap(a.w))));
+  }
+  return max(1, block_max(m, red32));
+}
+
+// Thread 0 of the row's CTA: waits for all ranks' words of the row (bounded), returns their maximum, clears them
+// and counts the CTA; the last CTA of the launch advances the call counter.
+__device__ __forceinline__ int tp_row_agree(const TpView& v, int32_t* words) {
+  int agreed = 1;
+  const unsigned long long t0 = tp_now_ns(), limit = g_tp_timeout_ns;
+  for (int src = 0; src < v.size; ++src) {
+    int a = tp_ld_acquire(words + src);
+    while (a == 0) {
+      if (tp_now_ns() - t0 > limit) {
+        atomicCAS(&g_tp_status, 0, 1);
+        break;
+      }
+      __nanosleep(32);
+      a = tp_ld_acquire(words + src);
+    }
+    agreed = max(agreed, a);
+    words[src] = 0;
+  }
+  int32_t* hdr = v.base[v.rank];
+  if (atomicAdd(reinterpret_cast<unsigned*>(hdr + 12), 1u) + 1 == gridDim.x) {
+    hdr[12] = 0;
+    hdr[4] += 1;                    // read by the next launch, after this one has ended
+  }
+  return agreed;
+}
+
+// One CTA per token row of this rank's slice x [rows, k] (row pitch in elements): delivers the row's absmax.
 __global__ void __launch_bounds__(256)
 tp_absmax_put_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pitch, int k) {
   __shared__ int red32[33];
   const TpLayout l = tp_layout(v.m_max, v.n);
-  const int half = *reinterpret_cast<volatile int32_t*>(v.base[v.rank] + 0) & 1;
+  const int half = *reinterpret_cast<volatile int32_t*>(v.base[v.rank] + 4) & 1;
   const int row = blockIdx.x;
-  const int4* xr = reinterpret_cast<const int4*>(x + (int64_t)row * pitch);
-  int m = 0;
-  for (int i = threadIdx.x; i < (k >> 2); i += blockDim.x) {
-    const int4 a = xr[i];
-    m = max(max(m, abs_wrap(a.x)), max(abs_wrap(a.y), max(abs_wrap(a.z), abs_wrap(a.w))));
-  }
-  m = max(1, block_max(m, red32));
-  if ((int)threadIdx.x < v.size) {
-    atomicMax(v.base[threadIdx.x] + l.amax + (int64_t)half * v.m_max + row, m);
-    __threadfence_system();
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) tp_signal_if_last(v, 0, gridDim.x);
+  const int m = tp_row_absmax(reinterpret_cast<const int4*>(x + (int64_t)row * pitch), k >> 2, red32);
+  if ((int)threadIdx.x < v.size)
+    tp_st_relaxed(v.base[threadIdx.x] + l.amax + ((int64_t)half * v.m_max + row) * kTpMaxRanks + v.rank, m);
 }
 
-// ---------------------------------------------------------------------------- step 2: quantise with the agreed absmax
-// One CTA per row: waits for every rank's channel-0 signal, reads the agreed absmax, writes the int8 codes of
-// this rank's slice and the absmax (for the requant), and clears the word for its next use.
+// One CTA per row: waits for every rank's absmax of the row, writes the int8 codes of this rank's slice and the
+// agreed absmax (for the requant).
 __global__ void __launch_bounds__(256)
 tp_quant_wait_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pitch, int k,
                      int8_t* __restrict__ codes, int32_t* __restrict__ absmax_out) {
+  __shared__ int agreed;
   const TpLayout l = tp_layout(v.m_max, v.n);
   int32_t* hdr = v.base[v.rank];
-  const int epoch = *reinterpret_cast<volatile int32_t*>(hdr + 0);     // the signal this step's producer sent
-  const int half = (epoch - 1) & 1;
-  tp_wait_flags(v, 0, epoch);
-  __syncthreads();
+  const int half = *reinterpret_cast<volatile int32_t*>(hdr + 4) & 1;
   const int row = blockIdx.x;
-  int32_t* word = hdr + l.amax + (int64_t)half * v.m_max + row;
-  const int m = max(1, tp_ld_acquire(word));
-  __syncthreads();                                   // everybody has read the word before it is cleared
   if (threadIdx.x == 0) {
-    absmax_out[row] = m;
-    *word = 0;
+    agreed = tp_row_agree(v, hdr + l.amax + ((int64_t)half * v.m_max + row) * kTpMaxRanks);
+    absmax_out[row] = agreed;
   }
+  __syncthreads();
+  const int m = agreed;
   const float mf = __int2float_rn(m), my = __frcp_rn(mf);
   const int4* xr = reinterpret_cast<const int4*>(x + (int64_t)row * pitch);
   unsigned* co = reinterpret_cast<unsigned*>(codes + (int64_t)row * k);
@@ -92,45 +117,148 @@ tp_quant_wait_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pitc
   }
 }
 
-// ---------------------------------------------------------------------------- step 4: requantise the summed accumulators
-// Waits for every rank's channel-1 signal (sent by the GEMM kernels), applies the fixed-point epilogue to
-// acc[half] and clears it.  Four consecutive channels of one token per thread.
+// Both in one launch: a CTA delivers its row's absmax, waits for the peers' words of the SAME row and quantises.
+// A CTA depends only on the peers' CTAs of its row, which never wait before they deliver, so there is no
+// grid-wide dependency; all rows' CTAs must be able to run at once (rows <= 512).
+__global__ void __launch_bounds__(256)
+tp_absmax_quant_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pitch, int k,
+                       int8_t* __restrict__ codes, int32_t* __restrict__ absmax_out) {
+  __shared__ int red32[33];
+  __shared__ int agreed;
+  const TpLayout l = tp_layout(v.m_max, v.n);
+  int32_t* hdr = v.base[v.rank];
+  const int half = *reinterpret_cast<volatile int32_t*>(hdr + 4) & 1;
+  const int row = blockIdx.x;
+  const int4* xr = reinterpret_cast<const int4*>(x + (int64_t)row * pitch);
+  // the row stays in registers between the two passes (up to 8 vectors per thread), the rest is read again
+  constexpr int kKeep = 8;
+  int4 keep[kKeep];
+  const int nvec = k >> 2;
+  int m = 0;
+#pragma unroll
+  for (int j = 0; j < kKeep; ++j) {
+    const int i = threadIdx.x + j * 256;
+    keep[j] = i < nvec ? xr[i] : make_int4(0, 0, 0, 0);
+    m = max(max(m, abs_wrap(keep[j].x)), max(abs_wrap(keep[j].y), max(abs_wrap(keep[j].z), abs_wrap(keep[j].w))));
+  }
+  for (int i = threadIdx.x + kKeep * 256; i < nvec; i += 256) {
+    const int4 a = xr[i];
+    m = max(max(m, abs_wrap(a.x)), max(abs_wrap(a.y), max(abs_wrap(a.z), abs_wrap(a.w))));
+  }
+  m = max(1, block_max(m, red32));
+  const int64_t words = l.amax + ((int64_t)half * v.m_max + row) * kTpMaxRanks;
+  if ((int)threadIdx.x < v.size) tp_st_relaxed(v.base[threadIdx.x] + words + v.rank, m);
+  __syncthreads();                               // this rank's own word is out before thread 0 starts to wait
+  if (threadIdx.x == 0) {
+    agreed = tp_row_agree(v, hdr + words);
+    absmax_out[row] = agreed;
+  }
+  __syncthreads();
+  const int a = agreed;
+  const float mf = __int2float_rn(a), my = __frcp_rn(mf);
+  unsigned* co = reinterpret_cast<unsigned*>(codes + (int64_t)row * k);
+#pragma unroll
+  for (int j = 0; j < kKeep; ++j) {
+    const int i = threadIdx.x + j * 256;
+    if (i < nvec)
+      co[i] = pack4(quant_code_fast(keep[j].x, mf, my), quant_code_fast(keep[j].y, mf, my), quant_code_fast(keep[j].z, mf, my),
+                    quant_code_fast(keep[j].w, mf, my));
+  }
+  for (int i = threadIdx.x + kKeep * 256; i < nvec; i += 256) {
+    const int4 b = xr[i];
+    co[i] = pack4(quant_code_fast(b.x, mf, my), quant_code_fast(b.y, mf, my), quant_code_fast(b.z, mf, my),
+                  quant_code_fast(b.w, mf, my));
+  }
+}
+
+// ---------------------------------------------------------------------------- step 4: add, requantise, hand out
+// The rank owns the token rows [rank * rpr, (rank + 1) * rpr), rpr = ceil(m / size).  After every rank's channel-1
+// signal (sent by the GEMM kernels) the slots rs[half][src] hold all ranks' partial sums of those rows: add them,
+// apply the fixed-point epilogue and store the finished Q15.16 row into `out` of EVERY rank.  Signals channel 3.
 __device__ __forceinline__ int tp_requant_one(int acc, int cm, int s) {
   if (s > 0 && s < 63) return sat32(((long long)acc * (long long)cm + (1LL << (s - 1))) >> s);
   return sat32(mul_shift64((long long)acc, (long long)cm, s));
 }
 
+// DIRECT: every rank holds all ranks' partial sums of all rows and writes the finished rows to `dst` (the caller's
+// tensor); otherwise the rank finishes the rows it owns, stores them into every rank's `out` and signals channel 3.
+template <bool DIRECT>
 __global__ void __launch_bounds__(256)
-tp_requant_wait_kernel(const TpView v, const int32_t* __restrict__ absmax, const int32_t* __restrict__ w_mul,
-                       const int32_t* __restrict__ w_shift, int32_t* __restrict__ out, int m, int n) {
+tp_requant_scatter_kernel(const TpView v, const int32_t* __restrict__ absmax, const int32_t* __restrict__ w_mul,
+                          const int32_t* __restrict__ w_shift, int32_t* __restrict__ dst, int m, int n) {
   const TpLayout l = tp_layout(v.m_max, v.n);
   int32_t* hdr = v.base[v.rank];
   const int epoch = *reinterpret_cast<volatile int32_t*>(hdr + 1);
   const int half = (epoch - 1) & 1;
   tp_wait_flags(v, 1, epoch);
   __syncthreads();
-  int32_t* acc = hdr + l.acc + (int64_t)half * l.acc_half;
+  const int rpr = tp_rows_per_rank(m, v.size), cap = tp_rows_per_rank(v.m_max, v.size);
+  const int row0 = DIRECT ? 0 : v.rank * rpr, rows = max(0, min(m, row0 + rpr) - row0);
+  const int32_t* rs = hdr + l.rs + (int64_t)half * l.rs_half;
+  const int64_t out_off = l.out + (int64_t)half * l.acc_half;
   const int nvec = n >> 2;
-  const int64_t total = (int64_t)m * nvec;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int t = (int)(i / nvec);
-    const int c = (int)(i - (int64_t)t * nvec) * 4;
-    int xm, xs;
-    absmax_to_ms_dev(__ldg(absmax + t), &xm, &xs);
-    xs -= 48;
-    int4* ap = reinterpret_cast<int4*>(acc + (int64_t)t * n + c);
-    const int4 a = __ldcg(ap);                        // written by peers: read from L2, not a stale L1 line
-    *ap = make_int4(0, 0, 0, 0);
-    const int4 wm = __ldg(reinterpret_cast<const int4*>(w_mul + c));
-    int4 ws = make_int4(31, 31, 31, 31);
-    if (w_shift) ws = __ldg(reinterpret_cast<const int4*>(w_shift + c));
-    int4 r;
-    r.x = tp_requant_one(a.x, __mulhi(xm, wm.x), xs + ws.x);
-    r.y = tp_requant_one(a.y, __mulhi(xm, wm.y), xs + ws.y);
-    r.z = tp_requant_one(a.z, __mulhi(xm, wm.z), xs + ws.z);
-    r.w = tp_requant_one(a.w, __mulhi(xm, wm.w), xs + ws.w);
-    *reinterpret_cast<int4*>(out + (int64_t)t * n + c) = r;
+  const int64_t total = (int64_t)rows * nvec;
+  constexpr int kBatch = 4;                     // independent loads in flight per thread
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i0 < total; i0 += stride * kBatch) {
+    int4 a[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int64_t i = i0 + j * stride;
+      a[j] = make_int4(0, 0, 0, 0);
+      if (i < total) {
+        const int tl = (int)(i / nvec);
+        const int c = (int)(i - (int64_t)tl * nvec) * 4;
+        for (int src = 0; src < v.size; ++src) {
+          const int4 b = __ldcg(reinterpret_cast<const int4*>(rs + ((int64_t)src * cap + tl) * n + c));   // written by peers: L2
+          a[j].x += b.x; a[j].y += b.y; a[j].z += b.z; a[j].w += b.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int64_t i = i0 + j * stride;
+      if (i >= total) continue;
+      const int tl = (int)(i / nvec);
+      const int c = (int)(i - (int64_t)tl * nvec) * 4;
+      const int t = row0 + tl;
+      int xm, xs;
+      absmax_to_ms_dev(__ldg(absmax + t), &xm, &xs);
+      xs -= 48;
+      const int4 wm = __ldg(reinterpret_cast<const int4*>(w_mul + c));
+      int4 ws = make_int4(31, 31, 31, 31);
+      if (w_shift) ws = __ldg(reinterpret_cast<const int4*>(w_shift + c));
+      int4 r;
+      r.x = tp_requant_one(a[j].x, __mulhi(xm, wm.x), xs + ws.x);
+      r.y = tp_requant_one(a[j].y, __mulhi(xm, wm.y), xs + ws.y);
+      r.z = tp_requant_one(a[j].z, __mulhi(xm, wm.z), xs + ws.z);
+      r.w = tp_requant_one(a[j].w, __mulhi(xm, wm.w), xs + ws.w);
+      if (DIRECT) {
+        *reinterpret_cast<int4*>(dst + (int64_t)t * n + c) = r;
+      } else {
+        for (int d = 0; d < v.size; ++d) *reinterpret_cast<int4*>(v.base[d] + out_off + (int64_t)t * n + c) = r;
+      }
+    }
   }
+  if (!DIRECT) {
+    __syncthreads();
+    if (threadIdx.x == 0) tp_signal_if_last(v, 3, gridDim.x, total > 0);
+  }
+}
+
+// ---------------------------------------------------------------------------- step 5: collect the finished rows
+// Waits for every rank's channel-3 signal and copies out[half] (all m rows) to the caller's tensor.
+__global__ void __launch_bounds__(256)
+tp_collect_kernel(const TpView v, int32_t* __restrict__ dst, int m, int n) {
+  const TpLayout l = tp_layout(v.m_max, v.n);
+  const int32_t* hdr = v.base[v.rank];
+  const int half = (*reinterpret_cast<const volatile int32_t*>(hdr + 1) - 1) & 1;
+  tp_wait_flags(v, 3, *reinterpret_cast<const volatile int32_t*>(hdr + 3));
+  __syncthreads();
+  const int4* src = reinterpret_cast<const int4*>(hdr + l.out + (int64_t)half * l.acc_half);
+  const int64_t total = (int64_t)m * (n >> 2);
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    reinterpret_cast<int4*>(dst)[i] = __ldcg(src + i);
 }
 
 // ---------------------------------------------------------------------------- small all-gather (channel 2)
@@ -145,7 +273,6 @@ tp_gather_kernel(const TpView v, const int32_t* __restrict__ src, int words, int
   const int64_t slot = l.gather + ((int64_t)half * kTpMaxRanks + v.rank) * l.gather_slot;
   for (int r = 0; r < v.size; ++r)
     for (int i = threadIdx.x; i < words; i += blockDim.x) v.base[r][slot + i] = src[i];
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) tp_signal_if_last(v, 2, 1);
   __syncthreads();
@@ -217,19 +344,66 @@ extern "C" int b200_tp_quant_wait(const b200_tp_block* blk, const int32_t* x, in
   return check_launch("tp_quant_wait");
 }
 
-extern "C" int b200_tp_requant_wait(const b200_tp_block* blk, const int32_t* absmax, const int32_t* w_mul,
-                                    const int32_t* w_shift, int32_t* out_q15, int m, b200_stream_t s) {
+extern "C" int b200_tp_absmax_quant(const b200_tp_block* blk, const int32_t* x, int64_t pitch, int rows, int k,
+                                    int8_t* codes, int32_t* absmax_out, b200_stream_t s) {
   TpView v;
-  int rc = view_of(blk, &v, "tp_requant_wait");
+  int rc = view_of(blk, &v, "tp_absmax_quant");
   if (rc != B200_OK) return rc;
-  B200_REQUIRE(absmax && w_mul && out_q15, B200_E_NULL, "tp_requant_wait: null pointer");
-  B200_REQUIRE(m > 0 && m <= v.m_max, B200_E_SHAPE, "tp_requant_wait: m=%d (1..%d)", m, v.m_max);
+  B200_REQUIRE(x && codes && absmax_out, B200_E_NULL, "tp_absmax_quant: null pointer");
+  B200_REQUIRE(rows > 0 && rows <= v.m_max && k > 0 && k % 4 == 0 && pitch >= k && pitch % 4 == 0, B200_E_SHAPE,
+               "tp_absmax_quant: rows=%d (1..%d) k=%d pitch=%lld", rows, v.m_max, k, (long long)pitch);
+  // every CTA waits for its peers' CTAs of the same row: all rows' CTAs must be able to run at once
+  B200_REQUIRE(rows <= 512, B200_E_UNSUPPORTED, "tp_absmax_quant: rows=%d (at most 512; use tp_absmax_put + tp_quant_wait beyond)", rows);
+  B200_REQUIRE(aligned16(x) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0, B200_E_ALIGN,
+               "tp_absmax_quant: x must be 16-byte aligned, codes 4-byte");
+  tp_absmax_quant_kernel<<<rows, 256, 0, (cudaStream_t)s>>>(v, x, pitch, k, codes, absmax_out);
+  return check_launch("tp_absmax_quant");
+}
+
+extern "C" int b200_tp_requant_scatter(const b200_tp_block* blk, const int32_t* absmax, const int32_t* w_mul,
+                                       const int32_t* w_shift, int m, b200_stream_t s) {
+  TpView v;
+  int rc = view_of(blk, &v, "tp_requant_scatter");
+  if (rc != B200_OK) return rc;
+  B200_REQUIRE(absmax && w_mul, B200_E_NULL, "tp_requant_scatter: null pointer");
+  B200_REQUIRE(m > 0 && m <= v.m_max, B200_E_SHAPE, "tp_requant_scatter: m=%d (1..%d)", m, v.m_max);
+  B200_REQUIRE(aligned16(w_mul) && aligned16(w_shift), B200_E_ALIGN, "tp_requant_scatter: w_mul and w_shift must be 16-byte aligned");
+  B200_REQUIRE(!tp_direct(v.size), B200_E_UNSUPPORTED, "tp_requant_scatter: %d ranks exchange directly: use tp_requant_direct", v.size);
+  // few CTAs: each ends with a system-scope fence, and many of those at once are slow
+  const int64_t vecs = (int64_t)tp_rows_per_rank(m, v.size) * (v.n / 4);
+  const int grid = (int)((vecs + 1023) / 1024 < 148 ? (vecs + 1023) / 1024 : 148);
+  tp_requant_scatter_kernel<false><<<grid < 1 ? 1 : grid, 256, 0, (cudaStream_t)s>>>(v, absmax, w_mul, w_shift, nullptr, m, (int)v.n);
+  return check_launch("tp_requant_scatter");
+}
+
+extern "C" int b200_tp_requant_direct(const b200_tp_block* blk, const int32_t* absmax, const int32_t* w_mul,
+                                      const int32_t* w_shift, int32_t* out_q15, int m, b200_stream_t s) {
+  TpView v;
+  int rc = view_of(blk, &v, "tp_requant_direct");
+  if (rc != B200_OK) return rc;
+  B200_REQUIRE(absmax && w_mul && out_q15, B200_E_NULL, "tp_requant_direct: null pointer");
+  B200_REQUIRE(m > 0 && m <= v.m_max, B200_E_SHAPE, "tp_requant_direct: m=%d (1..%d)", m, v.m_max);
+  B200_REQUIRE(tp_direct(v.size), B200_E_UNSUPPORTED, "tp_requant_direct: %d ranks exchange through row owners: use tp_requant_scatter + tp_collect", v.size);
   B200_REQUIRE(aligned16(w_mul) && aligned16(w_shift) && aligned16(out_q15), B200_E_ALIGN,
-               "tp_requant_wait: w_mul, w_shift and out must be 16-byte aligned");
+               "tp_requant_direct: w_mul, w_shift and out must be 16-byte aligned");
   const int64_t vecs = (int64_t)m * (v.n / 4);
-  const int grid = (int)((vecs + 255) / 256 < 1184 ? (vecs + 255) / 256 : 1184);
-  tp_requant_wait_kernel<<<grid, 256, 0, (cudaStream_t)s>>>(v, absmax, w_mul, w_shift, out_q15, m, (int)v.n);
-  return check_launch("tp_requant_wait");
+  const int grid = (int)((vecs + 1023) / 1024 < 592 ? (vecs + 1023) / 1024 : 592);
+  tp_requant_scatter_kernel<true><<<grid < 1 ? 1 : grid, 256, 0, (cudaStream_t)s>>>(v, absmax, w_mul, w_shift, out_q15, m, (int)v.n);
+  return check_launch("tp_requant_direct");
+}
+
+extern "C" int b200_tp_collect(const b200_tp_block* blk, int32_t* out_q15, int m, b200_stream_t s) {
+  TpView v;
+  int rc = view_of(blk, &v, "tp_collect");
+  if (rc != B200_OK) return rc;
+  B200_REQUIRE(out_q15, B200_E_NULL, "tp_collect: null pointer");
+  B200_REQUIRE(m > 0 && m <= v.m_max, B200_E_SHAPE, "tp_collect: m=%d (1..%d)", m, v.m_max);
+  B200_REQUIRE(!tp_direct(v.size), B200_E_UNSUPPORTED, "tp_collect: %d ranks exchange directly: use tp_requant_direct", v.size);
+  B200_REQUIRE(aligned16(out_q15), B200_E_ALIGN, "tp_collect: out must be 16-byte aligned");
+  const int64_t vecs = (int64_t)m * (v.n / 4);
+  const int grid = (int)((vecs + 255) / 256 < 592 ? (vecs + 255) / 256 : 592);
+  tp_collect_kernel<<<grid, 256, 0, (cudaStream_t)s>>>(v, out_q15, m, (int)v.n);
+  return check_launch("tp_collect");
 }
 
 extern "C" int b200_tp_all_gather(const b200_tp_block* blk, const int32_t* src, int words, int32_t* dst,

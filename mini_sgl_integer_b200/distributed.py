@@ -62,11 +62,16 @@ class DistributedCommunicator:
     With a world of one every call returns its argument unchanged, as the reference does (impl.py:27-28).
     """
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, single: bool = False):
+        """``single``: a communicator of one rank whatever process group exists (an unsplit layer built inside a
+        multi-rank job, e.g. for a parity check)."""
         self.group = group
+        self.single = bool(single)
 
     @property
     def size(self) -> int:
+        if self.single:
+            return 1
         return dist.get_world_size(self.group) if dist.is_initialized() else 1
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:

@@ -174,7 +174,7 @@ class TpExchange:
         bases = [b.data_ptr() for b in bufs]
         return [cls(None, m_max, n, device, _bases=bases, _rank=r, _keep=bufs) for r in range(size)]
 
-    # ---- the four steps of a row-split linear (separately, so that emulated ranks can be interleaved)
+    # ---- the five steps of a row-split linear (separately, so that emulated ranks can be interleaved)
     def absmax_put(self, x2: torch.Tensor) -> None:
         call("b200_tp_absmax_put", self._p, ptr(x2), x2.stride(0), x2.shape[0], x2.shape[1], stream())
 
@@ -184,14 +184,34 @@ class TpExchange:
         call("b200_tp_quant_wait", self._p, ptr(x2), x2.stride(0), x2.shape[0], x2.shape[1], ptr(codes), ptr(absmax), stream())
         return codes, absmax
 
+    def absmax_quant(self, x2: torch.Tensor):
+        """absmax_put + quant_wait in one launch (the ranks meet per token row)."""
+        codes = torch.empty(x2.shape, dtype=torch.int8, device=x2.device)
+        absmax = torch.empty(x2.shape[0], dtype=torch.int32, device=x2.device)
+        call("b200_tp_absmax_quant", self._p, ptr(x2), x2.stride(0), x2.shape[0], x2.shape[1], ptr(codes), ptr(absmax), stream())
+        return codes, absmax
+
     def gemm_add(self, codes: torch.Tensor, weight: torch.Tensor) -> None:
         m, k = codes.shape
         call("b200_gemm_w8a8_tp", self._p, ptr(codes), ptr(weight), m, weight.shape[0], k, stream())
 
-    def requant_wait(self, absmax: torch.Tensor, w_mul: torch.Tensor, w_shift) -> torch.Tensor:
+    def requant_scatter(self, absmax: torch.Tensor, w_mul: torch.Tensor, w_shift) -> None:
+        call("b200_tp_requant_scatter", self._p, ptr(absmax), ptr(w_mul), ptr(w_shift), absmax.shape[0], stream())
+
+    def requant_direct(self, absmax: torch.Tensor, w_mul: torch.Tensor, w_shift) -> torch.Tensor:
+        """One or two ranks: every rank has received all partial sums and finishes all rows itself."""
         m = absmax.shape[0]
         out = torch.empty((m, self.n), dtype=torch.int32, device=absmax.device)
-        call("b200_tp_requant_wait", self._p, ptr(absmax), ptr(w_mul), ptr(w_shift), ptr(out), m, stream())
+        call("b200_tp_requant_direct", self._p, ptr(absmax), ptr(w_mul), ptr(w_shift), ptr(out), m, stream())
+        return out
+
+    @property
+    def direct(self) -> bool:
+        return self.size <= 2
+
+    def collect(self, m: int, device) -> torch.Tensor:
+        out = torch.empty((m, self.n), dtype=torch.int32, device=device)
+        call("b200_tp_collect", self._p, ptr(out), m, stream())
         return out
 
     @staticmethod
@@ -211,10 +231,12 @@ class TpExchange:
         if getattr(layer, "weight_mul", None) is None:
             method.process_weights_after_loading(layer)
         x2 = self._rows(x_q15_local)
-        self.absmax_put(x2)
-        codes, absmax = self.quant_wait(x2)
+        codes, absmax = self.absmax_quant(x2)
         self.gemm_add(codes, layer.weight)
-        return self.requant_wait(absmax, layer.weight_mul, layer.weight_shift)
+        if self.direct:
+            return self.requant_direct(absmax, layer.weight_mul, layer.weight_shift)
+        self.requant_scatter(absmax, layer.weight_mul, layer.weight_shift)
+        return self.collect(x2.shape[0], x2.device)
 
     def all_gather(self, src: torch.Tensor) -> torch.Tensor:
         """int32 [words] from every rank -> int32 [size, words] (words <= 2 * m_max)."""

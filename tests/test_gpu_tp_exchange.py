@@ -50,14 +50,36 @@ def test_row_split_linear_over_exchange_blocks(size, m, n, k):
         q = [ranks[r].quant_wait(xs_[r]) for r in range(size)]
         for r in range(size):
             ranks[r].gemm_add(q[r][0], w_[r])
-        outs = [ranks[r].requant_wait(q[r][1], wm_d, ws_d) for r in range(size)]
+        if ranks[0].direct:
+            outs = [ranks[r].requant_direct(q[r][1], wm_d, ws_d) for r in range(size)]
+        else:
+            for r in range(size):
+                ranks[r].requant_scatter(q[r][1], wm_d, ws_d)
+            outs = [ranks[r].collect(m, "cuda") for r in range(size)]
         for r in range(size):
             np.testing.assert_array_equal(outs[r].cpu().numpy(), want, err_msg=f"round {rnd}, rank {r}")
     assert TpExchange.status() == 0
-    # everything that was accumulated into has been cleared again
+    # what is accumulated into (the block counters, the absmax words, the local accumulators) has been cleared again
+    words = ranks[0].nbytes // 4
+    acc_words = 2 * ((256 * n + 63) // 64 * 64)
+    rs_out_words = 2 * ((2 * 256 * n + 63) // 64 * 64) + acc_words
     for r in range(size):
-        body = ranks[r]._buf[r].view(torch.int32)[64 + 64:]          # past the header and the flag words
-        assert int(body.abs().max()) == 0
+        body = ranks[r]._buf[r].view(torch.int32)
+        assert int(body[128:words - rs_out_words].abs().max()) == 0
+
+
+def test_single_rank_exchange_equals_the_plain_linear():
+    """size 1 through the calls the layers make (absmax + quant in one launch): the plain linear's bits."""
+    from mini_sgl_integer_b200.layers.decoder_layer import _Linear
+    from mini_sgl_integer_b200.layers.tp_linear import TpExchange
+    from mini_sgl_integer_b200.layers.w8a8_int8 import W8A8Int8LinearMethod
+    x, w8, wm, ws, want = _case(5, 200, 512, 8192 + 1024)            # rows longer than a CTA keeps in registers
+    ex = TpExchange.emulated(1, 256, 512)[0]
+    layer = _Linear(d(w8), weight_mul=d(wm), weight_shift=d(ws))
+    for _ in range(3):
+        got = ex.row_parallel_q15(W8A8Int8LinearMethod(), layer, d(x))
+        np.testing.assert_array_equal(got.cpu().numpy(), want)
+    assert TpExchange.status() == 0
 
 
 def test_all_gather_over_exchange_blocks():
