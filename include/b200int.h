@@ -191,6 +191,25 @@ B200_API int b200_attn_extend(const int8_t* q, const int32_t* q_mul, const int32
                               int rows, int q_heads, int kv_heads, int64_t num_pages, int max_kv_len,
                               int cluster, b200_stream_t s);
 
+/* ---- Prefill / extend attention for many new tokens per sequence: one CTA per (sequence, KV head, tile of
+ * 128 / (q_heads / kv_heads) consecutive new tokens) with the query rows on the M side of the integer MMA, the
+ * pages of K and V streamed through shared memory once per pass over the keys (three passes for K: the exact
+ * softmax cannot be rescaled, so row maxima, sums and probabilities each recompute the scores; one for V).
+ * Same arithmetic and results as b200_attn_extend, which re-reads all keys for every single query row.
+ * Stands in for Int8Backend._forward_prefill (attention/triton_int8.py:178-212) -> int8_context_attention_fwd
+ * (kernel/triton/int8_attention_kernels.py:229-383); unlike the reference it attends the cached prefix too.
+ *   q int8 [rows, q_heads, 128], the sequences' new tokens back to back; q_mul, q_shift int32 [rows, q_heads];
+ *   kv_lens int32 [batch] (new tokens included, already in the pool); q_lens int32 [batch]; q_start int32
+ *   [batch]: the row of each sequence's first new token; max_q_len bounds every q_lens[i] (it sizes the grid).
+ *   The i-th of n new tokens of a sequence with L keys sees keys 0 .. L - n + i.  Outputs as b200_attn_decode. */
+B200_API int b200_attn_prefill(const int8_t* q, const int32_t* q_mul, const int32_t* q_shift,
+                               const int8_t* k_codes, const int8_t* v_codes, const int32_t* meta,
+                               const int32_t* page_table, int64_t table_pitch, const int32_t* kv_lens,
+                               const int32_t* q_lens, const int32_t* q_start,
+                               int32_t* out_q15, int8_t* out_codes, int32_t* out_absmax,
+                               int batch, int max_q_len, int q_heads, int kv_heads, int64_t num_pages,
+                               int max_kv_len, b200_stream_t s);
+
 /* ---- The same decode / extend attention as a chain of grid-wide passes that meet in a caller-provided
  * workspace (scores, row maxima and sums, reference V scales, int32 output accumulators) instead of
  * inside thread-block clusters: better balanced, any context length.  Same arguments and results as
@@ -333,13 +352,13 @@ B200_API int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, int
  * All ranks must issue the same sequence of these calls.  A row-split linear is
  *     b200_tp_absmax_put      the token's absmax over this rank's K-slice, folded into every rank's block
  *     b200_tp_quant_wait      waits for all ranks, quantises the slice with the agreed absmax
- *     b200_gemm_w8a8_tp       partial sums; every token row is stored (16-byte stores) only into the block of
- *                             the rank that owns the row (rank = row / ceil(m / size))
- *     b200_tp_requant_scatter waits for all ranks, adds the partial sums of the rows it owns, applies the
- *                             epilogue of b200_gemm_w8a8 and stores the finished rows into every rank's block
+ *     b200_gemm_w8a8_tp       this rank's int32 partial sums, accumulated in its own block
+ *     b200_tp_requant_scatter waits for all ranks, fetches (16-byte loads over NVLink) and adds every rank's partial
+ *                             sums of the rows it owns (rank = row / ceil(m / size)), applies the epilogue of
+ *                             b200_gemm_w8a8 and stores the finished rows into every rank's block
  *     b200_tp_collect         waits for all ranks, copies the m finished rows to out_q15 int32 [m, n]
- * With one or two ranks the last three steps are two: b200_gemm_w8a8_tp stores every row into every rank's block
- * (the same bytes at two ranks) and b200_tp_requant_direct finishes all m rows into out_q15.
+ * With one or two ranks the last three steps are two: b200_tp_requant_direct fetches all rows from every rank (the
+ * same bytes at two ranks) and finishes all m rows into out_q15.
  * and gives the bits of b200_gemm_w8a8 on the whole K on one GPU.  b200_tp_all_gather exchanges up to
  * 2 * m_max words per rank (dst int32 [size][words], rank order).  Producer kernels end with a signal,
  * consumer kernels start with a wait that is bounded (default 2 s, b200_tp_set_timeout_us): on expiry the

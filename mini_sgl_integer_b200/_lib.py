@@ -34,6 +34,7 @@ SIGNATURES: dict[str, list] = {
     "b200_kv_store_q15": [P, L, P, L, P, P, P, P, L, I, L, P],
     "b200_kv_store_codes": [P, P, P, P, P, P, P, P, P, P, L, I, L, P],
     "b200_attn_extend": [P, P, P, P, P, P, P, L, P, P, P, P, P, P, I, I, I, L, I, I, P],
+    "b200_attn_prefill": [P, P, P, P, P, P, P, L, P, P, P, P, P, P, I, I, I, I, L, I, P],
     "b200_attn_workspace_bytes": [I, I, I, I],
     "b200_attn_paged_ws": [P, P, P, P, P, P, P, L, P, P, P, P, P, P, I, I, I, L, I, P, ctypes.c_size_t, P],
     "b200_attn_paged_static": [P, P, P, P, P, P, P, L, P, P, P, P, P, P, I, I, I, L, I, P],

@@ -93,6 +93,51 @@ def decode_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
     return o32 if out_q15 else (o8, om)
 
 
+def prefill_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: torch.Tensor, pool: Int8PagedKVCache,
+                                 layer_id: int, page_table: torch.Tensor, kv_lens: torch.Tensor, q_lens: torch.Tensor,
+                                 max_kv_len: int, max_q_len: int, *, out_q15: bool = True, out_int8: bool = False,
+                                 q_start: torch.Tensor | None = None):
+    """Causal attention of newly appended tokens over the cached prefix plus themselves, tiled: one CTA per
+    (sequence, KV head, tile of new tokens) streams the keys once per pass instead of once per query row.
+
+    q8 int8 [sum(q_lens), q_heads, 128] with the sequences back to back; kv_lens int32 [batch] count the new
+    tokens too (they must already be stored in the pool); q_lens int32 [batch]; ``max_q_len`` bounds every
+    q_lens[i] and ``max_kv_len`` every kv_lens[i] (host integers: they size the grid and shared memory, nothing is
+    read back from the device).  ``q_start`` (optional int32 [batch]): the row of each sequence's first new token,
+    by default the exclusive prefix sum of q_lens.  The i-th of the n new tokens of a sequence with L keys sees
+    keys 0 .. L-n+i.  Stands in for Int8Backend._forward_prefill (attention/triton_int8.py:178-212) ->
+    int8_context_attention_fwd (kernel/triton/int8_attention_kernels.py:229-383); unlike the reference it attends
+    the cached prefix.
+    """
+    if q8.dtype != torch.int8:
+        raise TypeError(f"q8 must be int8, got {q8.dtype}")
+    if q8.ndim != 3 or q8.shape[-1] != HEAD_DIM:
+        raise ValueError(f"q8 must be [tokens, q_heads, {HEAD_DIM}], got shape {tuple(q8.shape)}")
+    require_cuda(q8, q_mul, q_shift, page_table, kv_lens, q_lens, q_start)
+    rows, q_heads, _ = q8.shape
+    c = lambda t: t.to(torch.int32).contiguous()
+    q8 = q8.contiguous()
+    q_mul, q_shift, page_table, kv_lens, q_lens = c(q_mul), c(q_shift), c(page_table), c(kv_lens), c(q_lens)
+    batch = kv_lens.shape[0]
+    if page_table.ndim != 2 or page_table.shape[0] != batch or q_lens.shape[0] != batch:
+        raise ValueError(f"page_table [batch, pitch], kv_lens and q_lens [batch] expected, got {tuple(page_table.shape)}, "
+                         f"{tuple(kv_lens.shape)}, {tuple(q_lens.shape)}")
+    if q_start is None:
+        q_start = torch.cumsum(q_lens, 0, dtype=torch.int32) - q_lens
+    q_start = c(q_start)
+    o32 = torch.empty((rows, q_heads, HEAD_DIM), dtype=torch.int32, device=q8.device) if out_q15 else None
+    o8 = torch.empty((rows, q_heads, HEAD_DIM), dtype=torch.int8, device=q8.device) if out_int8 else None
+    om = torch.empty((rows, q_heads), dtype=torch.int32, device=q8.device) if out_int8 else None
+    if rows > 0 and batch > 0:
+        call("b200_attn_prefill", ptr(q8), ptr(q_mul), ptr(q_shift), ptr(pool.k_cache(layer_id)), ptr(pool.v_cache(layer_id)),
+             ptr(pool.meta(layer_id)), ptr(page_table), page_table.stride(0), ptr(kv_lens), ptr(q_lens), ptr(q_start),
+             ptr(o32), ptr(o8), ptr(om), batch, int(min(max_q_len, rows)), q_heads, pool.kv_heads, pool.num_pages,
+             int(max_kv_len), stream())
+    if out_q15 and out_int8:
+        return o32, o8, om
+    return o32 if out_q15 else (o8, om)
+
+
 def extend_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: torch.Tensor,
                                 pool: Int8PagedKVCache, layer_id: int, page_table: torch.Tensor,
                                 kv_lens: torch.Tensor, q_lens: torch.Tensor, max_kv_len: int, *,
@@ -105,6 +150,10 @@ def extend_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
     tokens of a sequence with L keys sees keys 0 .. L-n+i.  Stands in for Int8Backend._forward_prefill
     (attention/triton_int8.py:178-212) -> int8_context_attention_fwd
     (kernel/triton/int8_attention_kernels.py:229-383); unlike the reference it attends the cached prefix.
+
+    ``impl``: "tiled" = `prefill_attention_int8_paged` (the default: keys are streamed once per tile of new
+    tokens); "cluster" = the decode kernel launched once per query row, "split" = its workspace passes (each row
+    re-reads its keys: only for a handful of new tokens per sequence).  All three give the same bits.
     """
     if q8.dtype != torch.int8:
         raise TypeError(f"q8 must be int8, got {q8.dtype}")
@@ -115,8 +164,12 @@ def extend_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
     c = lambda t: t.to(torch.int32).contiguous()
     q8 = q8.contiguous()
     q_mul, q_shift, page_table, kv_lens, q_lens = c(q_mul), c(q_shift), c(page_table), c(kv_lens), c(q_lens)
-    if int(q_lens.sum()) != rows:
-        raise ValueError(f"sum(q_lens)={int(q_lens.sum())} does not match the {rows} query rows")
+    total, longest = (int(v) for v in torch.stack((q_lens.sum(), q_lens.max() if q_lens.numel() else q_lens.sum())).tolist())
+    if total != rows:
+        raise ValueError(f"sum(q_lens)={total} does not match the {rows} query rows")
+    if impl in ("auto", "tiled"):
+        return prefill_attention_int8_paged(q8, q_mul, q_shift, pool, layer_id, page_table, kv_lens, q_lens, max_kv_len,
+                                            longest, out_q15=out_q15, out_int8=out_int8)
     batch = kv_lens.shape[0]
     seq_ids = torch.arange(batch, device=q8.device, dtype=torch.int32)
     row_seq = torch.repeat_interleave(seq_ids, q_lens.to(torch.int64)).to(torch.int32).contiguous()
@@ -127,16 +180,18 @@ def extend_attention_int8_paged(q8: torch.Tensor, q_mul: torch.Tensor, q_shift: 
     o32 = torch.empty((rows, q_heads, HEAD_DIM), dtype=torch.int32, device=q8.device) if out_q15 else None
     o8 = torch.empty((rows, q_heads, HEAD_DIM), dtype=torch.int8, device=q8.device) if out_int8 else None
     om = torch.empty((rows, q_heads), dtype=torch.int32, device=q8.device) if out_int8 else None
-    if impl == "auto":
-        impl = "cluster" if _cluster_fits(q_heads // pool.kv_heads, max_kv_len) else "split"
-    if rows > 0 and impl == "split":
-        _paged_ws(q8, q_mul, q_shift, pool, layer_id, page_table, kv_lens, row_seq, row_limit, o32, o8, om, rows, q_heads,
-                  max_kv_len, workspace)
-    elif rows > 0:
-        call("b200_attn_extend", ptr(q8), ptr(q_mul), ptr(q_shift), ptr(pool.k_cache(layer_id)),
-             ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(page_table), page_table.stride(0),
-             ptr(kv_lens), ptr(row_seq), ptr(row_limit), ptr(o32), ptr(o8), ptr(om), rows, q_heads,
-             pool.kv_heads, pool.num_pages, int(max_kv_len), int(cluster), stream())
+    step = 65535                                            # rows per launch of the row kernels (a grid dimension)
+    for r0 in range(0, rows, step):
+        r1 = min(rows, r0 + step)
+        sl = lambda t: None if t is None else t[r0:r1]
+        if impl == "split":
+            _paged_ws(q8[r0:r1], q_mul[r0:r1], q_shift[r0:r1], pool, layer_id, page_table, kv_lens, row_seq[r0:r1], row_limit[r0:r1],
+                      sl(o32), sl(o8), sl(om), r1 - r0, q_heads, max_kv_len, workspace)
+        else:
+            call("b200_attn_extend", ptr(q8[r0:r1]), ptr(q_mul[r0:r1]), ptr(q_shift[r0:r1]), ptr(pool.k_cache(layer_id)),
+                 ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)), ptr(page_table), page_table.stride(0),
+                 ptr(kv_lens), ptr(row_seq[r0:r1]), ptr(row_limit[r0:r1]), ptr(sl(o32)), ptr(sl(o8)), ptr(sl(om)), r1 - r0, q_heads,
+                 pool.kv_heads, pool.num_pages, int(max_kv_len), int(cluster), stream())
     if out_q15 and out_int8:
         return o32, o8, om
     return o32 if out_q15 else (o8, om)

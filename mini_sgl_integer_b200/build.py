@@ -14,7 +14,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libb200int.so")
-SOURCES = ["api.cu", "rowops.cu", "attn.cu", "attn_split.cu", "gemm.cu", "model_ops.cu", "tp.cu"]
+SOURCES = ["api.cu", "rowops.cu", "attn.cu", "attn_split.cu", "attn_prefill.cu", "gemm.cu", "model_ops.cu", "tp.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

@@ -240,18 +240,12 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   tcgen05_fence_after();
   const unsigned tmem_base = *tmem_slot;
-  // exchange-block mode: word offsets, inside a rank's block, of the local accumulator half and of the
-  // reduce-scatter half in use; this rank's slot inside a peer's reduce-scatter half; rows per owner
-  int64_t tp_acc_off = 0, tp_rs_off = 0;
-  int tp_rpr = 1;
-  bool tp_pushed = false;   // this CTA has stored into peers' blocks (it then owes a system-scope fence)
-  __shared__ int tp_last_part;
+  // exchange-block mode: word offset, inside this rank's block, of the accumulator half in use
+  int64_t tp_acc_off = 0;
   if (WS && p.tp_on) {
     const TpLayout l = tp_layout(p.tp.m_max, p.tp.n);
     const int half = *reinterpret_cast<volatile int32_t*>(p.tp.base[p.tp.rank] + 1) & 1;
     tp_acc_off = l.acc + (int64_t)half * l.acc_half;
-    tp_rs_off = l.rs + (int64_t)half * l.rs_half + (int64_t)p.tp.rank * tp_rows_per_rank(p.tp.m_max, p.tp.size) * p.tp.n;
-    tp_rpr = tp_rows_per_rank(p.M, p.tp.size);
   }
 
   if (warp == 0) {
@@ -352,8 +346,8 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           tmem_ld_32x32(tmem_base + ((unsigned)(q * 32) << 16) + slot * BN + (unsigned)c0, v);
           if (!ok || c0 >= p.M || ch >= p.N || empty_part) continue;
           if (p.tp_on) {
-            // exchange-block mode: this part's sums are added into the rank's OWN accumulators first (L2 atomics);
-            // whoever delivers the last part of the channel block sends the finished block on, see below
+            // exchange-block mode: the parts are added into the rank's OWN accumulators (L2 atomics); the peers fetch
+            // them from there once this kernel has signalled
             int32_t* dst = p.tp.base[p.tp.rank] + tp_acc_off;
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -386,54 +380,6 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty0 + 8 * slot);
-        if (p.tp_on) {
-          // Reduce-scatter step.  The CTA that adds the last part of this block of 128 channels reads the block's
-          // sums back, clears them, and stores every token row into the slot this rank has in the block of the
-          // row's owner: plain 16-byte stores over NVLink, each row crossing once.
-          epilogue_bar_sync();
-          if (et == 0) {
-            __threadfence();        // the epilogue threads' additions (ordered by the barrier) before the arrival count
-            int32_t* cnt = p.tp.base[p.tp.rank] + tp_layout(p.tp.m_max, p.tp.n).nblk + (wt.n_blk & (kTpNblkWords - 1));
-            const int parts = wt.split ? p.splits : 1;
-            const int arrived = atomicAdd(cnt, 1) + 1;
-            tp_last_part = ok && !empty_part && arrived == parts;
-            if (arrived == parts) *cnt = 0;
-            __threadfence();        // the other parts' additions are visible to the reads below (via the barrier)
-          }
-          epilogue_bar_sync();
-          if (tp_last_part) {
-            tp_pushed = true;
-            int32_t* acc = p.tp.base[p.tp.rank] + tp_acc_off;
-            const int col0 = wt.n_blk * kBM;
-            const int items = p.M * (kBM / 4);
-            const bool direct_mode = tp_direct(p.tp.size);
-            constexpr int kBatch = 8;              // loads in flight per thread: the loop is latency-bound otherwise
-            for (int i0 = et; i0 < items; i0 += 32 * kEpiWarps * kBatch) {
-              int4 a[kBatch];
-#pragma unroll
-              for (int j = 0; j < kBatch; ++j) {
-                const int i = i0 + j * 32 * kEpiWarps;
-                const int t = i / (kBM / 4), col = col0 + (i - t * (kBM / 4)) * 4;
-                a[j] = make_int4(0, 0, 0, 0);
-                if (i < items && col < p.N) a[j] = __ldcg(reinterpret_cast<const int4*>(acc + (int64_t)t * p.N + col));
-              }
-#pragma unroll
-              for (int j = 0; j < kBatch; ++j) {
-                const int i = i0 + j * 32 * kEpiWarps;
-                const int t = i / (kBM / 4), col = col0 + (i - t * (kBM / 4)) * 4;
-                if (i >= items || col >= p.N) continue;
-                *reinterpret_cast<int4*>(acc + (int64_t)t * p.N + col) = make_int4(0, 0, 0, 0);
-                if (direct_mode) {
-                  for (int r = 0; r < p.tp.size; ++r)
-                    *reinterpret_cast<int4*>(p.tp.base[r] + tp_rs_off + (int64_t)t * p.N + col) = a[j];
-                } else {
-                  const int owner = t / tp_rpr;
-                  *reinterpret_cast<int4*>(p.tp.base[owner] + tp_rs_off + (int64_t)(t - owner * tp_rpr) * p.N + col) = a[j];
-                }
-              }
-            }
-          }
-        }
         continue;
       }
       const int row = m_blk * kBM + q * 32 + lane;
@@ -492,11 +438,11 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
-  // (tp_pushed is uniform over the epilogue threads; thread 0 is not one of them, so it goes through shared memory)
-  if (WS && p.tp_on) {
-    if (threadIdx.x == 64) tp_last_part = tp_pushed;
-    __syncthreads();
-    if (threadIdx.x == 0) tp_signal_if_last(p.tp, 1, gridDim.x, tp_last_part != 0);
+  // exchange-block mode: nothing was written into a peer's memory, so only the CTA that arrives last pays a
+  // system-scope fence before the flag stores (each CTA orders its own additions with a device-scope fence)
+  if (WS && p.tp_on && threadIdx.x == 0) {
+    __threadfence();
+    tp_signal_if_last(p.tp, 1, gridDim.x, false);
   }
 }
 
@@ -940,9 +886,8 @@ extern "C" int b200_gemm_w8a8_tp(const b200_tp_block* blk, const int8_t* x8, con
   B200_REQUIRE(m >= 1 && m <= 256 && m <= blk->m_max && n == blk->n && k > 0 && k < (1ll << 31), B200_E_UNSUPPORTED,
                "gemm_w8a8_tp: m=%lld (1..min(256, %d)) n=%lld (the block's %lld) k=%lld", (long long)m, blk->m_max,
                (long long)n, (long long)blk->n, (long long)k);
-  B200_REQUIRE(k % 16 == 0 && n % 4 == 0 && (n + kBM - 1) / kBM <= kTpNblkWords, B200_E_UNSUPPORTED,
-               "gemm_w8a8_tp: k=%lld must be a multiple of 16, n=%lld a multiple of 4 and at most %d", (long long)k,
-               (long long)n, kTpNblkWords * kBM);
+  B200_REQUIRE(k % 16 == 0 && n % 4 == 0, B200_E_UNSUPPORTED, "gemm_w8a8_tp: k=%lld must be a multiple of 16, n=%lld of 4",
+               (long long)k, (long long)n);
   B200_REQUIRE(aligned16(x8) && aligned16(w8), B200_E_ALIGN, "gemm_w8a8_tp: operands must be 16-byte aligned");
   GemmParams p;
   p.x_absmax = nullptr; p.x_mul = nullptr; p.x_shift = nullptr; p.w_mul = nullptr; p.w_shift = nullptr;

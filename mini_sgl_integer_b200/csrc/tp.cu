@@ -3,9 +3,9 @@
 // A row-split linear (o_proj, down_proj) on `size` ranks gives the bits of one GPU when the ranks
 //   1. agree on every token's absmax            (one word per rank and token stored into every rank's block),
 //   2. quantise their K-slice with it,
-//   3. add their exact int32 partial sums       (each token row is sent to one owner rank, channel 1),
+//   3. add their exact int32 partial sums       (the owner of a token row fetches them from every rank, channel 1),
 //   4. requantise the sum once and hand the finished rows to everybody (channel 3).
-// Steps 1, 3 and 4 write straight into the peers' memory; a producer kernel ends with a signal (its last CTA
+// Steps 1 and 4 write straight into the peers' memory, step 3 reads from it; a producer kernel ends with a signal (its last CTA
 // stores the channel's new epoch into every rank's flag word), the consumer kernel begins with a bounded
 // wait on those flags.  No collective library call, no host synchronisation: a decode step that uses these
 // kernels is an ordinary stream of launches and can be captured in a CUDA graph on every rank.
@@ -173,8 +173,9 @@ tp_absmax_quant_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pi
 
 // ---------------------------------------------------------------------------- step 4: add, requantise, hand out
 // The rank owns the token rows [rank * rpr, (rank + 1) * rpr), rpr = ceil(m / size).  After every rank's channel-1
-// signal (sent by the GEMM kernels) the slots rs[half][src] hold all ranks' partial sums of those rows: add them,
-// apply the fixed-point epilogue and store the finished Q15.16 row into `out` of EVERY rank.  Signals channel 3.
+// signal (sent by the GEMM kernels) the accumulators acc[half] of all ranks are complete: fetch every rank's partial
+// sums of the own rows, add them, apply the fixed-point epilogue and store the finished Q15.16 row into `out` of
+// EVERY rank.  Signals channel 3.
 __device__ __forceinline__ int tp_requant_one(int acc, int cm, int s) {
   if (s > 0 && s < 63) return sat32(((long long)acc * (long long)cm + (1LL << (s - 1))) >> s);
   return sat32(mul_shift64((long long)acc, (long long)cm, s));
@@ -192,10 +193,18 @@ tp_requant_scatter_kernel(const TpView v, const int32_t* __restrict__ absmax, co
   const int half = (epoch - 1) & 1;
   tp_wait_flags(v, 1, epoch);
   __syncthreads();
-  const int rpr = tp_rows_per_rank(m, v.size), cap = tp_rows_per_rank(v.m_max, v.size);
+  const int rpr = tp_rows_per_rank(m, v.size);
   const int row0 = DIRECT ? 0 : v.rank * rpr, rows = max(0, min(m, row0 + rpr) - row0);
-  const int32_t* rs = hdr + l.rs + (int64_t)half * l.rs_half;
+  const int64_t acc_off = l.acc + (int64_t)half * l.acc_half;
   const int64_t out_off = l.out + (int64_t)half * l.acc_half;
+  // every peer has signalled this exchange, so it has finished reading the accumulator half of the PREVIOUS one:
+  // clear this rank's copy of it for the exchange after this one (all m_max rows; the grid shares the work)
+  {
+    int4* old = reinterpret_cast<int4*>(hdr + l.acc + (int64_t)(half ^ 1) * l.acc_half);
+    const int64_t vecs = (int64_t)v.m_max * (n >> 2);        // all rows: the previous exchange may have had more than m
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < vecs; i += (int64_t)gridDim.x * blockDim.x)
+      old[i] = make_int4(0, 0, 0, 0);
+  }
   const int nvec = n >> 2;
   const int64_t total = (int64_t)rows * nvec;
   constexpr int kBatch = 4;                     // independent loads in flight per thread
@@ -209,8 +218,8 @@ tp_requant_scatter_kernel(const TpView v, const int32_t* __restrict__ absmax, co
       if (i < total) {
         const int tl = (int)(i / nvec);
         const int c = (int)(i - (int64_t)tl * nvec) * 4;
-        for (int src = 0; src < v.size; ++src) {
-          const int4 b = __ldcg(reinterpret_cast<const int4*>(rs + ((int64_t)src * cap + tl) * n + c));   // written by peers: L2
+        for (int src = 0; src < v.size; ++src) {      // every rank's partial sums of the row: 16-byte loads, NVLink for peers
+          const int4 b = __ldcg(reinterpret_cast<const int4*>(v.base[src] + acc_off + (int64_t)(row0 + tl) * n + c));
           a[j].x += b.x; a[j].y += b.y; a[j].z += b.z; a[j].w += b.w;
         }
       }

@@ -10,27 +10,27 @@
 //              [8..11] arrive[ch]   CTAs of the running producer kernel that have finished
 //   flags    [4 channels][8 sources]: flags[ch][src] = the epoch of rank src's last signal on ch
 //            (written by rank src, read by the owner)
-//   nblk     [1024]               owner only: parts of K that have arrived per block of 128 output channels
 //   amax     [2][m_max][8]        per-token absmax of every rank's K-slice: word [.][t][src] is written by rank src
 //                                 with ONE 4-byte store (always >= 1, so the value is its own arrival flag)
 //   gather   [2][8][2 * m_max]    small all-gather slots, one per source rank
-//   acc      [2][m_max * n]       owner only: the rank's own partial sums (its split-K parts are added here)
-//   rs       [2][8][rows_cap * n] reduce-scatter slots: rs[.][src] holds rank src's partial sums of the token
-//                                 rows THIS rank owns (rows_cap = ceil(m_max / size)), written by rank src
+//   acc      [2][m_max * n]       the rank's own int32 partial sums (its GEMM adds its split-K parts here with L2
+//                                 atomics); READ by the peers with 16-byte loads over NVLink
 //   out      [2][m_max * n]       the finished Q15.16 rows, every rank's rows written by their owner
 //
-// A row-split linear moves its int32 partial sums with plain 16-byte stores: every rank sends each token row
-// only to the row's owner (rank t / ceil(m / size)), the owner adds the `size` slots, requantises and stores the
-// finished row into every rank's `out`.  That is (size - 1) / size of the [m, n] matrix out of each rank twice,
-// instead of (size - 1) whole copies as remote atomics.  With two ranks the bytes are the same either way, so
-// every rank receives all rows and finishes them itself: one exchange step instead of two.
+// A row-split linear moves its partial sums by PULL: a GEMM only accumulates locally and signals; the rank that
+// owns a token row (rank t / ceil(m / size)) then fetches the row's partial sums from every rank's `acc`, adds
+// them, requantises and stores the finished row into every rank's `out`.  That is (size - 1) / size of the
+// [m, n] matrix in and out of each rank, instead of (size - 1) whole copies as remote atomics (which ran at about
+// 14 G additions/s over NVLink here).  With one or two ranks every rank fetches all rows and finishes them itself:
+// the same bytes, one exchange step instead of two.  A rank clears an accumulator half one exchange after it was
+// used, when the peers' next signal shows that they have finished reading it.
 //
-// The two halves of amax / gather / acc / rs / out alternate between consecutive exchanges (the half is the
-// parity of a counter in the header: word 4 for the absmax exchange, the channel's epoch for the others);
-// whoever consumes amax or acc clears it afterwards, and the arrival of the NEXT exchange (other half) orders
-// that clearing, and the reads of rs / out, before any peer writes the half again.
+// The two halves of amax / gather / acc / out alternate between consecutive exchanges (the half is the parity
+// of a counter in the header: word 4 for the absmax exchange, the channel's epoch for the others); the arrival
+// of the NEXT exchange (other half) orders the clearing of amax / acc and the reads of out before the half is
+// written again.
 //
-// Channels: 1 = partial sums delivered, 2 = small all-gather, 3 = finished rows delivered (0 is unused: the
+// Channels: 1 = partial sums complete, 2 = small all-gather, 3 = finished rows delivered (0 is unused: the
 // absmax exchange needs no flag).
 #pragma once
 
@@ -45,37 +45,31 @@ constexpr int kTpFlagWords = kTpChannels * kTpMaxRanks;
 
 __host__ __device__ inline int64_t tp_align64(int64_t words) { return (words + 63) & ~int64_t(63); }   // 256 bytes
 
-constexpr int kTpNblkWords = 1024;
-
 struct TpLayout {
-  int64_t flags, nblk, amax, gather, acc, rs, out, total;   // offsets in int32 words from the block's base
+  int64_t flags, amax, gather, acc, out, total;   // offsets in int32 words from the block's base
   int64_t gather_slot;                       // words per (half, source) slot
   int64_t acc_half;                          // words per accumulator half (and per `out` half)
-  int64_t rs_half;                           // words per reduce-scatter half
 };
 
 __host__ __device__ inline TpLayout tp_layout(int m_max, int64_t n) {
   TpLayout l;
   l.flags = kTpHdrWords;
-  l.nblk = l.flags + tp_align64(kTpFlagWords);
-  l.amax = l.nblk + kTpNblkWords;
+  l.amax = l.flags + tp_align64(kTpFlagWords);
   l.gather = l.amax + tp_align64(2 * (int64_t)m_max * kTpMaxRanks);
   l.gather_slot = tp_align64(2 * (int64_t)m_max);
   l.acc = l.gather + 2 * kTpMaxRanks * l.gather_slot;
   l.acc_half = tp_align64((int64_t)m_max * n);
-  l.rs = l.acc + 2 * l.acc_half;
-  l.rs_half = tp_align64(2 * (int64_t)m_max * n);   // size * ceil(m_max / size) rows; two full matrices in direct mode
-  l.out = l.rs + 2 * l.rs_half;
+  l.out = l.acc + 2 * l.acc_half;
   l.total = l.out + 2 * l.acc_half;
   return l;
 }
 
-// Up to kTpDirectRanks ranks every rank receives every rank's partial sums of ALL rows and finishes all rows itself
-// ("direct": one exchange step); beyond, each row goes to one owner rank, which finishes it and hands it out
+// Up to kTpDirectRanks ranks every rank fetches every rank's partial sums of ALL rows and finishes all rows itself
+// ("direct": one exchange step); beyond, each row is finished by one owner rank, which hands it out
 // (reduce-scatter + all-gather: two steps, 1 / size of the bytes each).
 constexpr int kTpDirectRanks = 2;
 __host__ __device__ inline bool tp_direct(int size) { return size <= kTpDirectRanks; }
-// Token rows per owner for a matrix of m rows (all of them in direct mode), and the slot pitch in rows.
+// Token rows per owner for a matrix of m rows (all of them in direct mode).
 __host__ __device__ inline int tp_rows_per_rank(int m, int size) { return tp_direct(size) ? m : (m + size - 1) / size; }
 
 // What a kernel needs of the exchange: plain pointers and sizes, passed by value.

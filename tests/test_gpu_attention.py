@@ -226,6 +226,60 @@ def test_extend_over_prefix_vs_oracle(cluster):
     eq(codes.cpu().numpy(), wc); eq(absmax.cpu().numpy(), wm)
 
 
+@pytest.mark.parametrize("q_heads,kv_heads", [(2, 2), (4, 2), (8, 2), (8, 1)])
+def test_tiled_prefill_vs_oracle(q_heads, kv_heads):
+    """The tiled prefill kernel (query rows on the M side, keys streamed per tile) for every group size: ragged
+    prompts with and without a cached prefix, single new tokens, prompts that end inside a page and inside a
+    tile, Q15.16 and int8 outputs."""
+    kv_lens = [16, 32, 64, 128, 37, 5, 200, 1, 131, 333]
+    q_lens = [16, 16, 16, 16, 9, 5, 1, 1, 131, 70]
+    case = _extend_case(60 + q_heads, kv_lens, q_lens, q_heads, kv_heads, 80)
+    pool = device_pool(case, 80, kv_heads)
+    want = oattn.paged_attention(case["q8"], case["qm"], case["qs"], case["pool"], case["tables"], kv_lens, q_lens)
+    got, codes, absmax = run_extend(case, pool, 512, impl="tiled", out_q15=True, out_int8=True)
+    eq(got.cpu().numpy(), want)
+    wc, wm = oattn.quant_heads_int8(want)
+    eq(codes.cpu().numpy(), wc); eq(absmax.cpu().numpy(), wm)
+    # the row-at-a-time kernels give the same bits
+    eq(run_extend(case, pool, 512, cluster=1, impl="cluster").cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("kv_len,q_len", [(1024, 1024), (3584, 512)])
+def test_tiled_prefill_long_prompts_vs_oracle(kv_len, q_len):
+    """A 1024-token prompt without a prefix, and 512 new tokens over a 3072-token cached prefix."""
+    case = _extend_case(70, [kv_len, 40], [q_len, 40], 8, 2, 240)
+    pool = device_pool(case, 240, 2)
+    want = oattn.paged_attention(case["q8"], case["qm"], case["qs"], case["pool"], case["tables"], [kv_len, 40], [q_len, 40])
+    got = run_extend(case, pool, 3584, impl="tiled").cpu().numpy()
+    eq(got, want)
+    assert np.abs(want).max() > 0
+
+
+def test_tiled_prefill_uniform_scales_and_explicit_row_starts():
+    """Uniform scales (the reference's per-tensor case) through the direct entry point with row offsets that leave
+    gaps between the sequences: rows outside every sequence stay untouched."""
+    from mini_sgl_integer_b200.attention import prefill_attention_int8_paged
+    kv_lens, q_lens = [48, 20, 100], [48, 7, 33]
+    case = _extend_case(80, kv_lens, q_lens, 8, 2, 16, uniform=True)
+    pool = device_pool(case, 16, 2)
+    want = oattn.paged_attention(case["q8"], case["qm"], case["qs"], case["pool"], case["tables"], kv_lens, q_lens)
+    T = sum(q_lens)
+    starts = np.array([3, 60, 70], dtype=np.int32)                       # sequence b's rows begin at starts[b]
+    rows = 110
+    q = np.zeros((rows, 8, 128), dtype=np.int8); qm = np.ones((rows, 8), dtype=np.int32); qs = np.full((rows, 8), 44, dtype=np.int32)
+    src = 0
+    for b, n in enumerate(q_lens):
+        q[starts[b]:starts[b] + n] = case["q8"][src:src + n]; qm[starts[b]:starts[b] + n] = case["qm"][src:src + n]
+        qs[starts[b]:starts[b] + n] = case["qs"][src:src + n]; src += n
+    table = np.pad(case["table"], ((0, 0), (0, 8 - case["table"].shape[1])))
+    out = prefill_attention_int8_paged(d(q), d(qm), d(qs), pool, 0, d(table), d(case["kv_lens"]), d(case["q_lens"]), 128, 48,
+                                       q_start=d(starts))
+    out = out.cpu().numpy()
+    src = 0
+    for b, n in enumerate(q_lens):
+        eq(out[starts[b]:starts[b] + n], want[src:src + n]); src += n
+
+
 def test_extend_without_prefix_reduces_to_reference(golden):
     """Uniform scales, no prefix: the extend kernel reproduces int8_context_attention_fwd bit for bit."""
     from mini_sgl_integer_b200.attention import Int8PagedKVCache, extend_attention_int8_paged
