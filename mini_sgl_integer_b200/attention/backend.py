@@ -22,11 +22,37 @@ import torch
 
 from ..kernel import fixed_point as fp
 from .kv_pool import PAGE_SIZE, Int8PagedKVCache
-from .ops import decode_attention_int8_paged, extend_attention_int8_paged
+from .ops import decode_attention_int8_paged, extend_attention_int8_paged, prefill_attention_int8_paged, qkv_rope_quant_store
+
+
+class BaseAttnMetadata:
+    """attention/base.py:12-15."""
+
+    def get_last_indices(self, bs: int) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class BaseAttnBackend:
+    """The plug-in interface of the reference (attention/base.py:18-35)."""
+
+    def forward(self, q, k, v, layer_id: int, batch) -> torch.Tensor:
+        raise NotImplementedError
+
+    def prepare_metadata(self, batch) -> None:
+        raise NotImplementedError
+
+    def init_capture_graph(self, max_seq_len: int, bs_list: List[int]) -> None:
+        raise NotImplementedError
+
+    def prepare_for_capture(self, batch) -> None:
+        raise NotImplementedError
+
+    def prepare_for_replay(self, batch) -> None:
+        raise NotImplementedError
 
 
 @dataclass
-class Int8Metadata:
+class Int8Metadata(BaseAttnMetadata):
     """What a forward needs besides q/k/v (the reference's Int8Metadata, attention/triton_int8.py:50-64)."""
 
     page_table: torch.Tensor          # int32 [bs, pitch] page ids of the batch's requests
@@ -52,18 +78,30 @@ def token_locations(page_table_rows: torch.Tensor, positions: torch.Tensor, row_
     return (page * PAGE_SIZE + pos % PAGE_SIZE).to(torch.int32)
 
 
-class B200Int8Backend:
+class B200Int8Backend(BaseAttnBackend):
     requires_q_scale_fusion = True     # read by the integer attention layer (models/utils_integer.py:198-208)
 
-    def __init__(self, num_qo_heads: int, num_kv_heads: int, kvcache: Int8PagedKVCache, page_table: torch.Tensor,
-                 tp_size: int = 1, head_dim: int = 128) -> None:
-        """``page_table``: int32 [max_requests, max_pages] of page ids, owned by the engine (the reference keeps
-        it in the global context, engine/engine.py:66-73); rows are addressed by ``req.table_idx``."""
+    def __init__(self, config, kvcache: Int8PagedKVCache, page_table: Optional[torch.Tensor] = None,
+                 tp_size: Optional[int] = None) -> None:
+        """``B200Int8Backend(config, kvcache)`` as the reference constructs its backends (attention/__init__.py:33-37,
+        attention/triton_int8.py:74): ``config`` carries ``num_qo_heads``, ``num_kv_heads`` and ``head_dim`` (a
+        ModelConfig), the rank count comes from the process's tensor-parallel info.
+
+        ``page_table``: int32 [max_requests, max_pages] of PAGE ids (16-token pages); when omitted it is read from
+        the global context at ``prepare_metadata`` time (the reference keeps its table there, engine/engine.py:66-73).
+        Rows are addressed by ``req.table_idx``."""
+        if tp_size is None:
+            from ..distributed import try_get_tp_info
+            info = try_get_tp_info()
+            tp_size = info.size if info is not None else 1
+        num_qo_heads, num_kv_heads = int(config.num_qo_heads), int(config.num_kv_heads)
+        head_dim = int(getattr(config, "head_dim", 128))
         if num_qo_heads % tp_size or num_kv_heads % tp_size:
             raise ValueError("head counts must be divisible by tp_size")
+        self.config = config
         self.kvcache = kvcache
         self.device = kvcache.device
-        self.page_table = page_table
+        self._page_table = page_table
         self.qo_head_local = num_qo_heads // tp_size
         self.kv_head_local = num_kv_heads // tp_size
         self.head_dim = head_dim
@@ -74,7 +112,45 @@ class B200Int8Backend:
         self._cap_kv_lens: Optional[torch.Tensor] = None
         self._cap_order: Optional[torch.Tensor] = None
 
+    @classmethod
+    def from_heads(cls, num_qo_heads: int, num_kv_heads: int, kvcache: Int8PagedKVCache, page_table: torch.Tensor,
+                   tp_size: int = 1, head_dim: int = 128) -> "B200Int8Backend":
+        """The same backend from bare head counts and an explicit page table."""
+        from types import SimpleNamespace
+        return cls(SimpleNamespace(num_qo_heads=num_qo_heads, num_kv_heads=num_kv_heads, head_dim=head_dim), kvcache,
+                   page_table=page_table, tp_size=tp_size)
+
+    @property
+    def page_table(self) -> torch.Tensor:
+        if self._page_table is not None:
+            return self._page_table
+        from ..core import get_global_ctx
+        table = get_global_ctx().page_table
+        if table is None:
+            raise RuntimeError("no page table: pass one to the backend or set it on the global context")
+        return table
+
     # ------------------------------------------------------------------ forward
+    def forward_qkv_q15(self, qkv_q15: torch.Tensor, layer_id: int, batch, cos_sin_cache_q15: torch.Tensor,
+                        q_norm_weight_q15: Optional[torch.Tensor], k_norm_weight_q15: Optional[torch.Tensor]) -> torch.Tensor:
+        """The whole attention block on the qkv projection's Q15.16 output [T, (Hq + 2 Hk) * 128] in two launches:
+        q/k-norm + RoPE + Hadamard rotation + KV store + q quantisation, then the attention kernel.  Same bits as
+        the norms, ``rotary.forward_q15`` and ``forward`` one after the other."""
+        md = batch.attn_metadata
+        if not isinstance(md, Int8Metadata):
+            raise TypeError("batch.attn_metadata was not prepared by this backend")
+        tokens = qkv_q15.shape[0]
+        q8, q_mul, q_shift = qkv_rope_quant_store(batch.positions, qkv_q15, self.qo_head_local, self.kvcache, layer_id,
+                                                  batch.out_loc, cos_sin_cache_q15, q_norm_weight_q15, k_norm_weight_q15)
+        if md.q_lens is None:
+            out = decode_attention_int8_paged(q8, q_mul, q_shift, self.kvcache, layer_id, md.page_table, md.kv_lens,
+                                              md.max_seqlen_k, row_order=md.row_order)
+        else:
+            out = prefill_attention_int8_paged(q8, q_mul, q_shift, self.kvcache, layer_id, md.page_table, md.kv_lens,
+                                               md.q_lens, md.max_seqlen_k, md.max_seqlen_q,
+                                               q_start=None if md.qo_indptr is None else md.qo_indptr[:-1])
+        return out.view(tokens, self.qo_head_local * self.head_dim)
+
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layer_id: int, batch) -> torch.Tensor:
         """q int32 [T, Hq*128] or [T, Hq, 128], k / v int32 [T, Hk*128] (Q15.16).  Returns Q15.16 [T, Hq*128]."""
         md = batch.attn_metadata
@@ -91,8 +167,9 @@ class B200Int8Backend:
             out = decode_attention_int8_paged(q8, q_mul, q_shift, self.kvcache, layer_id, md.page_table, md.kv_lens,
                                               md.max_seqlen_k, row_order=md.row_order)
         else:
-            out = extend_attention_int8_paged(q8, q_mul, q_shift, self.kvcache, layer_id, md.page_table, md.kv_lens,
-                                              md.q_lens, md.max_seqlen_k)
+            out = prefill_attention_int8_paged(q8, q_mul, q_shift, self.kvcache, layer_id, md.page_table, md.kv_lens,
+                                               md.q_lens, md.max_seqlen_k, md.max_seqlen_q,
+                                               q_start=None if md.qo_indptr is None else md.qo_indptr[:-1])
         return out.view(tokens, self.qo_head_local * self.head_dim)
 
     # ------------------------------------------------------------------ metadata

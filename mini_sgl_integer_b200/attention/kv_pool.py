@@ -18,15 +18,27 @@ from __future__ import annotations
 import torch
 
 from .._lib import call, ptr, require_cuda, stream
+from ..kvcache import BaseKVCache
 
 PAGE_SIZE = 16
 HEAD_DIM = 128
 META_WORDS = 40
 
 
-class Int8PagedKVCache:
+class Int8PagedKVCache(BaseKVCache):
     def __init__(self, num_kv_heads: int, num_layers: int, head_dim: int, num_pages: int,
-                 device: torch.device | str = "cuda", tp_size: int = 1) -> None:
+                 device: torch.device | str | torch.dtype = "cuda", tp_size: int | torch.device | str | None = None) -> None:
+        """``Int8PagedKVCache(num_kv_heads, num_layers, head_dim, num_pages, device, tp_size)``, or the argument order
+        of the reference's pool, ``(num_kv_heads, num_layers, head_dim, num_pages, dtype, device)``
+        (kvcache/mha_pool.py:17-25): the dtype must then be torch.int8 and the rank count comes from the
+        process's tensor-parallel info, as there (:26-28).  ``num_pages`` counts 16-token pages."""
+        if isinstance(device, torch.dtype):
+            if device != torch.int8:
+                raise TypeError(f"the int8 pool stores int8 codes, got dtype {device}")
+            from ..distributed import try_get_tp_info
+            info = try_get_tp_info()
+            device, tp_size = tp_size if tp_size is not None else "cuda", (info.size if info is not None else 1)
+        tp_size = 1 if tp_size is None else int(tp_size)
         if head_dim != HEAD_DIM:
             raise NotImplementedError(f"the int8 pool is built for head_dim {HEAD_DIM}, got {head_dim}")
         if num_kv_heads % tp_size != 0:

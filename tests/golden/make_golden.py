@@ -246,6 +246,15 @@ def main() -> None:
         put(f"ptq{i}_in_bf16_bits", t.view(torch.int16)); put(f"ptq{i}_codes", c8)
         put(f"ptq{i}_ms", np.array([int(cm), int(cs)], dtype=np.int64))
 
+    # rotary table with the "llama3" frequency re-scaling (layers/rotary_integer.py:152-187): a few rows
+    from minisgl.layers.rotary_integer import _get_rope_integer
+    l3 = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 64}
+    rot3 = _get_rope_integer(128, 128, 512, 500000.0, l3)
+    put("rope_llama3_rows", rot3._cos_sin_cache_q15[[0, 1, 7, 63, 300, 511]])
+    l3b = dict(l3, low_freq_factor=2.0, high_freq_factor=2.0)
+    put("rope_llama3_step_rows", _get_rope_integer(128, 128, 512, 500000.0, l3b)._cos_sin_cache_q15[[1, 63, 511]])
+
     np.savez_compressed(os.path.join(HERE, "ref_vectors.npz"), **vec)
     with open(os.path.join(HERE, "ref_hashes.json"), "w") as fjs:
         json.dump(hashes, fjs, indent=1, sort_keys=True)

@@ -19,7 +19,7 @@ def batch_of(reqs, phase):
 
 def backend(max_req=8, max_pages=6):
     table = torch.arange(max_req * max_pages, dtype=torch.int32).reshape(max_req, max_pages) * 3 % 50
-    return B200Int8Backend(16, 8, SimpleNamespace(device=torch.device("cpu")), table), table
+    return B200Int8Backend.from_heads(16, 8, SimpleNamespace(device=torch.device("cpu")), table), table
 
 
 def test_prefill_metadata_with_cached_prefixes():

@@ -372,7 +372,7 @@ def test_backend_forward_matches_oracle(phase):
     rq = [SimpleNamespace(table_idx=t, cached_len=c, device_len=dl, extend_len=dl - c) for t, c, dl in reqs]
     batch = SimpleNamespace(reqs=rq, padded_reqs=rq, phase=phase, is_prefill=phase == "prefill", is_decode=phase == "decode",
                             size=len(rq), padded_size=len(rq))
-    be = B200Int8Backend(HQ, HK, pool, d(table))
+    be = B200Int8Backend.from_heads(HQ, HK, pool, d(table))
     be.prepare_metadata(batch)
     batch.out_loc = token_locations(batch.attn_metadata.page_table, d(positions), d(row_of))
     got = be.forward(d(q), d(k), d(v), 0, batch).cpu().numpy()
