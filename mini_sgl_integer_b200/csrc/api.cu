@@ -1,6 +1,7 @@
 // Library-wide pieces of the C ABI: error reporting, version, compiled-in tables.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -19,6 +20,14 @@ void set_error(const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
+}
+
+bool pdl_enabled() {
+  static const int on = [] {
+    const char* v = getenv("B200_PDL");
+    return (v != nullptr && v[0] == '0') ? 0 : 1;
+  }();
+  return on != 0;
 }
 
 int check_launch(const char* what) {

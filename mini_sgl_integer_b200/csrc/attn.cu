@@ -99,6 +99,8 @@ qkv_prepare_kernel(const int32_t* __restrict__ positions, const int32_t* __restr
                    int8_t* __restrict__ k_codes, int8_t* __restrict__ v_codes, int32_t* __restrict__ meta,
                    int8_t* __restrict__ q8, int32_t* __restrict__ q_mul, int32_t* __restrict__ q_shift,
                    int64_t tokens, int q_heads, int kv_heads, int64_t num_pages, int with_fwht) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int heads = q_heads + 2 * kv_heads;
   const int64_t wid = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
@@ -205,6 +207,8 @@ constexpr int kRingSlot = kSlotBytes + 384; // a pair of pages plus their two sc
 template <int G, int kStages>
 __global__ void __launch_bounds__(kDecodeThreads, 2)
 attn_decode_kernel(const DecodeParams p) {
+  pdl_launch_dependents();
+  pdl_wait();          // the queries, lengths and the new K/V rows come from the kernels before this one
   cg::cluster_group cluster = cg::this_cluster();
   const int C = (int)cluster.num_blocks();
   const int rank = (int)cluster.block_rank();
@@ -699,13 +703,15 @@ static int launch_decode(const DecodeParams& p, int batch, int cluster, cudaStre
   cfg.blockDim = dim3(kDecodeThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = cluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<G, kStages>, p);
   if (e != cudaSuccess) {
     set_error("attn_decode: launch: %s", cudaGetErrorString(e));
@@ -771,7 +777,7 @@ extern "C" int b200_qkv_prepare_q15(const int32_t* positions, const int32_t* q, 
   const int64_t warps = tokens * (q_heads + 2 * kv_heads);
   const int64_t blocks = (warps + 7) / 8;
   B200_REQUIRE(blocks < (1ll << 31), B200_E_SHAPE, "qkv_prepare_q15: too many rows");
-  qkv_prepare_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)s>>>(positions, q, q_pitch, k, k_pitch, v, v_pitch, cos_sin,
+  launch_pdl(qkv_prepare_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)s, positions, q, q_pitch, k, k_pitch, v, v_pitch, cos_sin,
                                                                     max_pos, q_norm_w, k_norm_w, out_loc, k_codes, v_codes,
                                                                     meta, q8, q_mul, q_shift, tokens, q_heads, kv_heads,
                                                                     num_pages, with_fwht);

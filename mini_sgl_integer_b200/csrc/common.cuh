@@ -22,11 +22,37 @@ int check_launch(const char* what);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Programmatic dependent launch.  Every kernel of the decode step begins with pdl_launch_dependents() (the next
+// kernel of the stream may be scheduled, and run whatever it does before its own wait, while this one is still
+// running) and executes pdl_wait() before it touches anything an earlier kernel produced or still reads; the wait
+// returns when the preceding kernel has completed and its writes are visible.  launch_pdl() launches with the
+// attribute that allows this overlap (switched off with the environment variable B200_PDL=0); a kernel launched
+// without it, or after a kernel that never triggers, behaves as usual.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // The 1024-entry tables live in luts.cuh; a translation unit that needs them on the device
 // includes that header (each gets its own copy, so no relocatable device code is needed).
 
 // ----------------------------------------------------------------------------- device side
 #define FULL_MASK 0xffffffffu
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ int sat32(long long v) {
   return v > 2147483647LL ? 2147483647 : (v < -2147483648LL ? (int)(-2147483647 - 1) : (int)v);

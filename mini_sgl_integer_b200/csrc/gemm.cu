@@ -236,10 +236,12 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  pdl_launch_dependents();
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const unsigned tmem_base = *tmem_slot;
+  pdl_wait();               // barriers, tensor memory and descriptors are set up; the operands come from earlier kernels
   // exchange-block mode: word offset, inside this rank's block, of the accumulator half in use
   int64_t tp_acc_off = 0;
   if (WS && p.tp_on) {
@@ -531,11 +533,13 @@ gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
+  pdl_launch_dependents();
   tcgen05_fence_before();
   __syncthreads();
   cluster_barrier();       // the peer's barriers exist before anything is signalled across the pair
   tcgen05_fence_after();
   const unsigned tmem_base = *tmem_slot;
+  pdl_wait();              // everything above is independent of the kernels before this one; the operands are not
 
   if (warp == 0) {
     if (lane == 0) {
@@ -645,10 +649,23 @@ gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   }
 }
 
+// Clears columns [0, 4 * vec_cols) of m rows (row pitch in elements) before the split-K parts are added into them.
+__global__ void __launch_bounds__(256)
+zero_cols_kernel(int32_t* __restrict__ base, int m, int vec_cols, int64_t pitch) {
+  pdl_launch_dependents();
+  pdl_wait();               // the buffer may still be read by the kernel before this one
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= (int64_t)m * vec_cols) return;
+  const int64_t r = i / vec_cols;
+  *reinterpret_cast<int4*>(base + r * pitch + (i - r * vec_cols) * 4) = make_int4(0, 0, 0, 0);
+}
+
 // The epilogue on its own, for the split-K parts gathered in `partial` ([M, N] int32; may be `out` itself):
 // four consecutive channels of one token per thread.
 __global__ void __launch_bounds__(256)
 splitk_epilogue_kernel(const int32_t* partial, const GemmParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.y;
   const int c = p.full_blocks * kBM + (blockIdx.x * 256 + threadIdx.x) * 4;   // only the split blocks' columns
   if (c >= p.N) return;
@@ -727,7 +744,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   const int tiles = WS ? p.full_blocks + ((p.N + kBM - 1) / kBM - p.full_blocks) * p.splits
                        : ((p.N + BN - 1) / BN) * ((p.M + kBM - 1) / kBM);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_w8a8_kernel<BN, STAGES, WS><<<grid, kGemmThreads, smem, st>>>(ma, mb, p);
+  launch_pdl(gemm_w8a8_kernel<BN, STAGES, WS>, dim3(grid), dim3(kGemmThreads), smem, st, ma, mb, p);
   return check_launch("gemm_w8a8");
 }
 
@@ -743,7 +760,7 @@ static int launch_gemm_2sm(const CUtensorMap& ma, const CUtensorMap& mb, const G
   }
   const int tiles = ((p.N + BN - 1) / BN) * ((p.M + 2 * kBM - 1) / (2 * kBM));
   const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-  gemm_w8a8_2sm_kernel<STAGES><<<2 * pairs, kGemmThreads2, smem, st>>>(ma, mb, p);
+  launch_pdl(gemm_w8a8_2sm_kernel<STAGES>, dim3(2 * pairs), dim3(kGemmThreads2), smem, st, ma, mb, p);
   return check_launch("gemm_w8a8 (two-CTA tiles)");
 }
 
@@ -789,9 +806,17 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
       // the parts are added into the exact-accumulator output if the caller wants it, else into the
       // Q15.16 output buffer itself, which the epilogue kernel then rewrites in place
       p.partial = acc_out ? acc_out : out_q15;
-      cudaError_t e = cudaMemset2DAsync(p.partial + col0, (size_t)n * sizeof(int32_t), 0, (size_t)(n - col0) * sizeof(int32_t),
-                                        (size_t)m, st);
-      B200_REQUIRE(e == cudaSuccess, B200_E_CUDA, "gemm_w8a8: cudaMemset2DAsync: %s", cudaGetErrorString(e));
+      // (a kernel rather than a memset node: it takes part in the programmatic launch chain of the step)
+      if ((n - col0) % 4 == 0 && col0 % 4 == 0 && n % 4 == 0) {
+        const int64_t vecs = (int64_t)m * ((n - col0) / 4);
+        launch_pdl(zero_cols_kernel, dim3((unsigned)((vecs + 255) / 256)), dim3(256), 0, st, p.partial + col0, (int)m, (int)((n - col0) / 4), (int64_t)n);
+        int rcz = check_launch("gemm_w8a8 (clearing the partial sums)");
+        if (rcz != B200_OK) return rcz;
+      } else {
+        cudaError_t e = cudaMemset2DAsync(p.partial + col0, (size_t)n * sizeof(int32_t), 0, (size_t)(n - col0) * sizeof(int32_t),
+                                          (size_t)m, st);
+        B200_REQUIRE(e == cudaSuccess, B200_E_CUDA, "gemm_w8a8: cudaMemset2DAsync: %s", cudaGetErrorString(e));
+      }
     }
     const int bn = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
     B200_REQUIRE(make_map(&ma, w8, n, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for w8");
@@ -804,7 +829,7 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
       default: rc = launch_gemm<32, 10, true>(ma, mb, p, st); break;
     }
     if (rc != B200_OK || splits == 1 || !out_q15) return rc;
-    splitk_epilogue_kernel<<<dim3((unsigned)((n - col0 + 1023) / 1024), (unsigned)m), 256, 0, st>>>(p.partial, p);
+    launch_pdl(splitk_epilogue_kernel, dim3((unsigned)((n - col0 + 1023) / 1024), (unsigned)m), dim3(256), 0, st, (const int32_t*)p.partial, p);
     return check_launch("gemm_w8a8 (split-K epilogue)");
   }
   B200_REQUIRE(make_map(&ma, x8, m, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");

@@ -22,6 +22,8 @@ __device__ __forceinline__ int bf16_bits_to_q15(unsigned short b) {
 __global__ void __launch_bounds__(256)
 embedding_q15_kernel(const uint16_t* __restrict__ table, const int32_t* __restrict__ ids, int32_t* __restrict__ out,
                      int64_t rows, int hidden, int64_t vocab_start, int64_t vocab_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -58,6 +60,8 @@ __global__ void __launch_bounds__(kArgmaxThreads)
 argmax_rows_kernel(const int32_t* __restrict__ logits, int64_t pitch, int64_t n, int32_t index_offset,
                    int32_t* __restrict__ out_idx, int32_t* __restrict__ out_val) {
   __shared__ unsigned long long red[kArgmaxThreads / 32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int32_t* row = logits + (int64_t)blockIdx.x * pitch;
   unsigned long long best = 0ull;      // below every real key: an index < 2^31 makes the low word >= 2^31
   const int64_t n4 = n / 4;
@@ -105,6 +109,8 @@ argmax_rows_kernel(const int32_t* __restrict__ logits, int64_t pitch, int64_t n,
 __global__ void decode_prepare_kernel(const int32_t* __restrict__ page_table, int64_t pitch, int32_t* __restrict__ seq_lens,
                                       int32_t* __restrict__ positions, int32_t* __restrict__ out_loc,
                                       int32_t* __restrict__ kv_lens, int batch, int max_len) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= batch) return;
   int pos = seq_lens[b];
@@ -173,7 +179,7 @@ extern "C" int b200_embedding_bf16_q15(const uint16_t* table, const int32_t* ids
   B200_REQUIRE(aligned16(table) && aligned16(out), B200_E_ALIGN, "embedding: table and out must be 16-byte aligned");
   const int64_t blocks = (rows + 7) / 8;
   B200_REQUIRE(blocks < (1ll << 31), B200_E_SHAPE, "embedding: too many rows");
-  embedding_q15_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)s>>>(table, ids, out, rows, hidden, vocab_start, vocab_rows);
+  launch_pdl(embedding_q15_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)s, table, ids, out, rows, hidden, vocab_start, vocab_rows);
   return check_launch("embedding_bf16_q15");
 }
 
@@ -185,7 +191,7 @@ extern "C" int b200_argmax_i32(const int32_t* logits, int64_t rows, int64_t n, i
   B200_REQUIRE(logits && out_idx, B200_E_NULL, "argmax: null pointer");
   B200_REQUIRE(aligned16(logits) && pitch % 4 == 0, B200_E_ALIGN, "argmax: rows must be 16-byte aligned (pitch a multiple of 4)");
   B200_REQUIRE(rows < (1ll << 31), B200_E_SHAPE, "argmax: too many rows");
-  argmax_rows_kernel<<<(unsigned)rows, kArgmaxThreads, 0, (cudaStream_t)s>>>(logits, pitch, n, index_offset, out_idx, out_val);
+  launch_pdl(argmax_rows_kernel, dim3((unsigned)rows), dim3(kArgmaxThreads), 0, (cudaStream_t)s, logits, pitch, n, index_offset, out_idx, out_val);
   return check_launch("argmax_i32");
 }
 
@@ -195,8 +201,8 @@ extern "C" int b200_decode_prepare(const int32_t* page_table, int64_t table_pitc
                "decode_prepare: batch=%d max_len=%d table_pitch=%lld", batch, max_len, (long long)table_pitch);
   if (batch == 0) return B200_OK;
   B200_REQUIRE(page_table && seq_lens && positions && out_loc && kv_lens, B200_E_NULL, "decode_prepare: null pointer");
-  decode_prepare_kernel<<<(batch + 127) / 128, 128, 0, (cudaStream_t)s>>>(page_table, table_pitch, seq_lens, positions, out_loc,
-                                                                        kv_lens, batch, max_len);
+  launch_pdl(decode_prepare_kernel, dim3((batch + 127) / 128), dim3(128), 0, (cudaStream_t)s, page_table, table_pitch, seq_lens, positions, out_loc,
+             kv_lens, batch, max_len);
   return check_launch("decode_prepare");
 }
 

@@ -60,6 +60,8 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
                     float* __restrict__ scale, int32_t* __restrict__ absmax, int H) {
   __shared__ long long red64[33];
   __shared__ int red32[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const int nvec = H >> 2;
   const int4* xr = reinterpret_cast<const int4*>(x + row * H);
@@ -152,6 +154,8 @@ __global__ void __launch_bounds__(1024)
 quant_rows_kernel(const int32_t* __restrict__ x, int8_t* __restrict__ codes,
                   float* __restrict__ scale, int32_t* __restrict__ absmax, int K) {
   __shared__ int red32[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const int nvec = K >> 2;
   const int4* xr = reinterpret_cast<const int4*>(x + row * K);
@@ -400,6 +404,7 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   __shared__ int red32[33];
   int32_t* lut = rowbuf + (QUANT ? I : 0);
   const uint16_t* sneg_tab = reinterpret_cast<const uint16_t*>(lut);
+  pdl_launch_dependents();
   if (TABLE) {
     const int4* src = reinterpret_cast<const int4*>(g_silu_sneg);      // 19457 entries: 2432 int4 + one entry
     for (int i = threadIdx.x; i < kSnegEntries / 8; i += blockDim.x) reinterpret_cast<int4*>(lut)[i] = src[i];
@@ -407,6 +412,7 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   } else {
     for (int i = threadIdx.x; i < 1024; i += blockDim.x) lut[i] = g_exp2_silu_lut[i];
   }
+  pdl_wait();                          // the tables above do not depend on the preceding kernel; gate_up does
   __syncthreads();
 
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -676,11 +682,11 @@ extern "C" int b200_rmsnorm_q15(const int32_t* x, const int32_t* residual, const
                    aligned16(norm_out) && ((uintptr_t)codes & 3u) == 0,
                B200_E_ALIGN, "rmsnorm_q15: int32 buffers must be 16-byte aligned (codes 4-byte)");
   if ((hidden >> 2) == p.threads * p.vpt) {
-    DISPATCH_VPT(p.vpt, (rmsnorm_rows_kernel<V, true><<<(unsigned)rows, p.threads, 0, (cudaStream_t)s>>>(
-                            x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
+    DISPATCH_VPT(p.vpt, (launch_pdl(rmsnorm_rows_kernel<V, true>, dim3((unsigned)rows), dim3(p.threads), 0, (cudaStream_t)s,
+                                    x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
   } else {
-    DISPATCH_VPT(p.vpt, (rmsnorm_rows_kernel<V, false><<<(unsigned)rows, p.threads, 0, (cudaStream_t)s>>>(
-                            x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
+    DISPATCH_VPT(p.vpt, (launch_pdl(rmsnorm_rows_kernel<V, false>, dim3((unsigned)rows), dim3(p.threads), 0, (cudaStream_t)s,
+                                    x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
   }
   return check_launch("rmsnorm_q15");
 }
@@ -696,8 +702,8 @@ extern "C" int b200_per_token_quant_q15(const int32_t* x, int8_t* codes, float* 
   if (rows == 0) return B200_OK;
   B200_REQUIRE(aligned16(x) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN,
                "per_token_quant_q15: x must be 16-byte aligned, codes 4-byte");
-  DISPATCH_VPT(p.vpt, (quant_rows_kernel<V><<<(unsigned)rows, p.threads, 0, (cudaStream_t)s>>>(
-                          x, codes, scale, absmax, k)));
+  DISPATCH_VPT(p.vpt, (launch_pdl(quant_rows_kernel<V>, dim3((unsigned)rows), dim3(p.threads), 0, (cudaStream_t)s,
+                                  x, codes, scale, absmax, k)));
   return check_launch("per_token_quant_q15");
 }
 
@@ -724,7 +730,7 @@ static int launch_silu(const int32_t* gu, int32_t* q15, int8_t* codes, float* sc
       set_error("silu_mul_q15: cudaFuncSetAttribute: %s", cudaGetErrorString(e));                          \
       return B200_E_CUDA;                                                                                  \
     }                                                                                                      \
-    silu_rows_kernel<F, Q, T><<<grid, threads, smem, st>>>(gu, q15, codes, scale, absmax, rows, inter);    \
+    launch_pdl(silu_rows_kernel<F, Q, T>, dim3(grid), dim3(threads), smem, st, gu, q15, codes, scale, absmax, rows, inter);    \
   } while (0)
 #define B200_SILU_LAUNCH_T(F, Q) do { if (table) B200_SILU_LAUNCH(F, Q, true); else B200_SILU_LAUNCH(F, Q, false); } while (0)
   if (fwht && quant) B200_SILU_LAUNCH_T(true, true);
