@@ -27,7 +27,7 @@ The script prints ONE JSON line:
 
 `--impl reference` times only that CPU port (the reference's Python/torch code cannot travel with this
 repository; its arithmetic is restated in oracle/).  Other workloads (`--workload attn|gemm|rowops|prefill|
-tp_layer`) print the same kind of line for one component.
+tp_layer|tp_linear`) print the same kind of line for one component.
 """
 from __future__ import annotations
 
@@ -756,13 +756,100 @@ def run_tp_layer(args) -> None:
         dist.destroy_process_group()
 
 
+def run_tp_linear(args) -> None:
+    """One row-split linear of the 8B shape (M = batch, N 4096, K 4096 or 12288 split over the ranks) in its
+    pieces, each replayed from a CUDA graph of 20 repetitions: microseconds per call for the exchange-block form, its
+    steps alone, the same work on one GPU without any exchange, and the NCCL form (eager)."""
+    import torch
+    import torch.distributed as dist
+    from mini_sgl_integer_b200.distributed import DistributedCommunicator
+    from mini_sgl_integer_b200.kernel.fixed_point import absmax_to_mul_shift
+    from mini_sgl_integer_b200.layers.decoder_layer import _Linear
+    from mini_sgl_integer_b200.layers.tp_linear import TpExchange, quant_given_absmax, requant_q15, row_absmax_q15, row_parallel_q15
+    from mini_sgl_integer_b200.layers.w8a8_int8 import W8A8Int8LinearMethod, int8_gemm_q15
+    rank, world, local = env_ranks()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    comm, method = DistributedCommunicator(), W8A8Int8LinearMethod()
+    M, N = args.batch, MODEL_CFG["hidden"]
+    res = {}
+    for name, K in (("o", MODEL_CFG["hidden"] // world), ("down", MODEL_CFG["inter"] // world)):
+        ex = TpExchange(comm, M, N, dev) if world > 1 else TpExchange.emulated(1, M, N, dev)[0]
+        g = torch.Generator(device=dev).manual_seed(1)
+        x = (torch.randn(M, K, device=dev, generator=g) * 30000).round().to(torch.int32)
+        w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=g)
+        wm = torch.randint(2**29, 2**30, (N,), dtype=torch.int32, device=dev, generator=g)
+        layer = _Linear(w, weight_mul=wm, weight_shift=torch.full((N,), 31, dtype=torch.int32, device=dev))
+        c0, a0 = ex.absmax_quant(x)
+
+        def finish():
+            if ex.direct:
+                return ex.requant_direct(a0, wm, None)
+            ex.requant_scatter(a0, wm, None)
+            return ex.collect(M, dev)
+
+        def local_linear():
+            a = row_absmax_q15(x); c = quant_given_absmax(x, a)
+            acc = int8_gemm_q15(c, None, None, w, None, want_q15=False, want_acc=True)
+            xm, xs = absmax_to_mul_shift(a)
+            return requant_q15(acc, xm, xs, wm, None)
+        cases = [("exchange", lambda: ex.row_parallel_q15(method, layer, x), True), ("absmax+quant", lambda: ex.absmax_quant(x), True),
+                 ("gemm", lambda: ex.gemm_add(c0, w), True), ("gemm+finish", lambda: (ex.gemm_add(c0, w), finish()), True),
+                 ("one_gpu_same_work", local_linear, True)]
+        if world > 1:
+            cases.append(("nccl_eager", lambda: row_parallel_q15(method, layer, x, comm), False))
+        for label, fn, graphable in cases:
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            reps = 20
+            if graphable:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    fn()
+                torch.cuda.current_stream().wait_stream(side)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    for _ in range(reps):
+                        fn()
+                run = graph.replay
+            else:
+                def run():
+                    for _ in range(reps):
+                        fn()
+            run()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                run()
+            e1.record()
+            torch.cuda.synchronize()
+            res[f"{name}.{label}"] = round(e0.elapsed_time(e1) / (5 * reps) * 1e3, 1)
+        if TpExchange.status() != 0:
+            raise SystemExit("a cross-rank wait ran out")
+    if rank == 0:
+        print(json.dumps({"metric": "microseconds per row-split linear (8B shape)", "n_gpus": world, "unit": "us", "M": M, "N": N,
+                          "value": res["o.exchange"], "higher_is_better": False, "phases_us": res}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="model", choices=["model", "attn", "rowops", "gemm", "prefill", "tp_layer"],
+    ap.add_argument("--workload", default="model", choices=["model", "attn", "rowops", "gemm", "prefill", "tp_layer", "tp_linear"],
                     help="model = the decode step of the 8B-shaped model, tensor-parallel over the launched ranks (default); "
                          "the others time one component")
     ap.add_argument("--batch", type=int, default=MODEL_CFG["batch"], help="decode batch of --workload model")
@@ -779,7 +866,7 @@ def main() -> None:
         run_reference(args)
     else:
         {"model": run_model, "attn": run_attn, "rowops": run_rowops, "gemm": run_gemm, "prefill": run_prefill,
-         "tp_layer": run_tp_layer}[args.workload](args)
+         "tp_layer": run_tp_layer, "tp_linear": run_tp_linear}[args.workload](args)
 
 
 if __name__ == "__main__":

@@ -4,6 +4,8 @@
 // its reductions, so every input element is read from HBM once.
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "luts.cuh"
 #include "rope.cuh"
@@ -236,8 +238,16 @@ __global__ void requant_kernel(const int32_t* acc, const int32_t* __restrict__ x
 struct RowPlan {
   int threads, vpt;
 };
-static bool plan_rows(int width, RowPlan* p) {
+static bool plan_rows(int width, RowPlan* p, int64_t rows = 1 << 30) {
   const int nvec = width >> 2;
+  // Few rows (a decode batch) leave most SMs with one or two CTAs: spread each row over up to 1024 threads, which
+  // shortens the dependent chain load -> reduce -> reduce -> store of a row; many rows keep 256 threads per CTA.
+  if (rows <= 1024 && nvec > 256 && std::getenv("B200_ROWS_NARROW") == nullptr) {
+    const int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
+    p->threads = threads;
+    p->vpt = (nvec + threads - 1) / threads;
+    if (p->vpt <= 8) return true;
+  }
   if (nvec <= 256) {
     p->threads = ((nvec + 31) / 32) * 32;
     p->vpt = 1;
@@ -676,7 +686,7 @@ extern "C" int b200_rmsnorm_q15(const int32_t* x, const int32_t* residual, const
                "rmsnorm_q15: rows=%lld hidden=%d", (long long)rows, hidden);
   B200_REQUIRE(hidden % 4 == 0, B200_E_UNSUPPORTED, "rmsnorm_q15: hidden=%d is not a multiple of 4", hidden);
   RowPlan p;
-  B200_REQUIRE(plan_rows(hidden, &p), B200_E_UNSUPPORTED, "rmsnorm_q15: hidden=%d exceeds 32768", hidden);
+  B200_REQUIRE(plan_rows(hidden, &p, rows), B200_E_UNSUPPORTED, "rmsnorm_q15: hidden=%d exceeds 32768", hidden);
   if (rows == 0) return B200_OK;
   B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(residual) && aligned16(residual_out) &&
                    aligned16(norm_out) && ((uintptr_t)codes & 3u) == 0,
@@ -698,7 +708,7 @@ extern "C" int b200_per_token_quant_q15(const int32_t* x, int8_t* codes, float* 
                "per_token_quant_q15: rows=%lld k=%d", (long long)rows, k);
   B200_REQUIRE(k % 4 == 0, B200_E_UNSUPPORTED, "per_token_quant_q15: k=%d is not a multiple of 4", k);
   RowPlan p;
-  B200_REQUIRE(plan_rows(k, &p), B200_E_UNSUPPORTED, "per_token_quant_q15: k=%d exceeds 32768", k);
+  B200_REQUIRE(plan_rows(k, &p, rows), B200_E_UNSUPPORTED, "per_token_quant_q15: k=%d exceeds 32768", k);
   if (rows == 0) return B200_OK;
   B200_REQUIRE(aligned16(x) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN,
                "per_token_quant_q15: x must be 16-byte aligned, codes 4-byte");

@@ -35,8 +35,9 @@ def _case(seed, m, n, k):
 
 
 @pytest.mark.parametrize("size", [1, 2, 4, 8])
-@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (33, 1028, 1024), (256, 1024, 2048)])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (33, 1028, 1024), (256, 1024, 2048), (8, 5120, 8192)])
 def test_row_split_linear_over_exchange_blocks(size, m, n, k):
+    """The last shape is the o-projection of the 32B-shaped model (hidden 5120, 64 x 128 input features) on 8 tokens."""
     from mini_sgl_integer_b200.layers.tp_linear import TpExchange
     x, w8, wm, ws, want = _case(size * 1000 + m, m, n, k)
     ks = k // size
