@@ -432,6 +432,7 @@ def run_model(args) -> None:
         flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         tp_parity = "ok" if int(flag) == 1 else "mismatch"
+        check_device_status()   # a peer that never arrived: every later wait would run out too, so stop at once
     wl = random_weights(Qwen3IntegerConfig(max(L - 1, 0), HID, hq, hk, inter, 128), seed=1000 + rank, device=dev,
                         generate_on_device=True)
     weights = {"embed": wf["embed"], "embed_replicated": True, "final_norm": wf["final_norm"],
@@ -473,6 +474,7 @@ def run_model(args) -> None:
         step()                                              # loads modules, sizes attributes (outside the capture)
     torch.cuda.current_stream().wait_stream(side)
     barrier()
+    check_device_status()       # a tensor-parallel wait that ran out in the very first step: stop here, not after the run
     calls0 = _lib.CALLS
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
@@ -732,6 +734,114 @@ def run_prefill(args) -> None:
                    {"gpu_launches": args.steps, "kernels": {"prefill_attn": r}})
 
 
+def run_offline(args) -> None:
+    """Configuration 4 as a run: R requests with prompts U[100, 1024] are prefilled for real (tiled prefill attention over
+    their own pages, chunks of at most `--chunk-tokens` prompt tokens per forward), then decoded greedily together for
+    `--decode-steps` steps from a CUDA graph.  Reports prefill, decode and overall tokens/s of the 8B-shaped model on one
+    GPU and checks batch invariance: the first requests run again on their own must generate the same token ids, bit
+    for bit (integer arithmetic with per-token scales has no cross-request term)."""
+    import torch
+    from mini_sgl_integer_b200.attention import Int8PagedKVCache
+    from mini_sgl_integer_b200.layers.decoder_layer import AttnBatch
+    from mini_sgl_integer_b200.models import (DecodeBatch, Qwen3ForCausalLMInteger, Qwen3IntegerConfig, argmax_int32,
+                                              check_device_status, random_weights)
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    c = MODEL_CFG
+    HID, HQ, HK, INTER, VOCAB, L = c["hidden"], c["q_heads"], c["kv_heads"], c["inter"], c["vocab"], args.model_layers
+    R, D = args.batch, args.decode_steps
+    rng = np.random.default_rng(33)
+    prompt_lens = rng.integers(100, 1025, R)
+    ids = rng.integers(0, VOCAB, int(prompt_lens.sum())).astype(np.int32)
+    starts = np.concatenate([[0], np.cumsum(prompt_lens)])
+    max_len = int(-(-(int(prompt_lens.max()) + D + 1) // 16) * 16)
+    table, P = page_tables(rng, prompt_lens + D + 1, max_len // 16)
+    cfg = Qwen3IntegerConfig(L, HID, HQ, HK, INTER, VOCAB, max_pos=4096)
+    weights = random_weights(cfg, seed=4, device=dev, generate_on_device=True)
+    d_table = torch.from_numpy(table).to(dev)
+
+    def run(req, pool):
+        """Prefill + D decode steps of the requests `req` (indices); returns generated ids [D + 1, len(req)] and times."""
+        lm = Qwen3ForCausalLMInteger(cfg, weights, pool)
+        first = torch.empty(len(req), dtype=torch.int32, device=dev)
+        chunks, cur, tok = [], [], 0
+        for j, r in enumerate(req):                          # whole prompts per chunk, up to chunk_tokens tokens
+            if cur and tok + prompt_lens[r] > args.chunk_tokens:
+                chunks.append(cur); cur, tok = [], 0
+            cur.append(j); tok += int(prompt_lens[r])
+        chunks.append(cur)
+        batches = []
+        for ch in chunks:
+            rr = [req[j] for j in ch]
+            lens = prompt_lens[rr].astype(np.int32)
+            pos = np.concatenate([np.arange(n) for n in lens]).astype(np.int32)
+            loc = np.concatenate([table[r][np.arange(n) // 16] * 16 + np.arange(n) % 16 for r, n in zip(rr, lens)]).astype(np.int32)
+            tok_ids = np.concatenate([ids[starts[r]:starts[r + 1]] for r in rr])
+            t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+            batches.append((torch.tensor(ch, device=dev), t(tok_ids), AttnBatch(t(pos), t(loc), d_table[rr].contiguous(), t(lens), t(lens), max_len),
+                            t((np.cumsum(lens) - 1).astype(np.int32))))
+        torch.cuda.synchronize()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        for slot, tok_ids, ab, last in batches:
+            first[slot] = lm.greedy(tok_ids, ab, last)
+        e[1].record()
+        state = DecodeBatch(d_table[req].contiguous(), torch.from_numpy(prompt_lens[req].astype(np.int32)).to(dev), max_len)
+        out = torch.empty((D + 1, len(req)), dtype=torch.int32, device=dev)
+        out[0] = first
+        cur_t = first.clone()
+        step_no = torch.zeros(1, dtype=torch.int64, device=dev)
+
+        def step():
+            cur_t.copy_(lm.greedy(cur_t, state.advance()))
+            step_no.add_(1)
+            out.index_copy_(0, step_no, cur_t.view(1, -1))
+        step()                                               # eager; counts as the first decode step
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ea.record()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):                        # host work only (nothing runs): left out of the decode time
+            step()
+        eb.record()
+        for _ in range(D - 1):
+            graph.replay()
+        e[2].record()
+        torch.cuda.synchronize()
+        check_device_status()
+        return out.cpu().numpy(), e[0].elapsed_time(e[1]), e[1].elapsed_time(ea) + eb.elapsed_time(e[2])
+
+    pool = Int8PagedKVCache(HK, L, 128, P, dev)
+    sub = list(range(min(4, R)))
+    ids_sub, _, _ = run(sub, pool)                           # also the warm-up of every kernel shape class
+    sampler = ClockSampler(0)
+    t0 = time.perf_counter()
+    ids_all, pre_ms, dec_ms = run(list(range(R)), pool)
+    clocks = sampler.stop(t0, time.perf_counter())
+    invariant = bool(np.array_equal(ids_all[:, :len(sub)], ids_sub))
+    n_prompt, n_gen = int(prompt_lens.sum()), R * D
+    total_ms = pre_ms + dec_ms
+    per_layer_w = (HQ + 2 * HK) * 128 * HID + HID * HQ * 128 + 2 * INTER * HID + HID * INTER
+    lens_dec = prompt_lens + D / 2.0
+    dec_bytes = (L * per_layer_w + VOCAB * HID) + float(lens_dec.sum()) * HK * 266 * L
+    peak, how = measured_peak()
+    ach = dec_bytes / (dec_ms / D * 1e-3) / 1e9
+    gemm_ops = 2.0 * n_prompt * (L * per_layer_w)
+    component_line("offline run, prompts U[100,1024] + greedy decode, integer-only W8A8 Qwen3-8B-shaped model (tokens/s, prompt + generated)",
+                   (n_prompt + n_gen) / (total_ms * 1e-3), "tokens/s", total_ms, args,
+                   {"workload": f"{R} requests, prompts U[100,1024] ({n_prompt} tokens) prefilled in chunks of <= {args.chunk_tokens} tokens, "
+                                f"then {D} greedy decode steps of all requests (CUDA graph); Qwen3-8B shape, {L} layers, one GPU",
+                    "prefill_tok_s": n_prompt / (pre_ms * 1e-3), "prefill_ms": pre_ms, "prefill_gemm_TOPS": gemm_ops / (pre_ms * 1e-3) / 1e12,
+                    "decode_tok_s": n_gen / (dec_ms * 1e-3), "decode_ms_per_step": dec_ms / D,
+                    "batch_invariance": "ok" if invariant else "mismatch",
+                    "batch_invariance_note": f"requests 0..{len(sub) - 1} run alone generate the ids they generate inside the batch of {R}",
+                    "l2": "weights + KV per decode step exceed L2; prefill chunks stream the weights once per chunk"},
+                   {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                    "peak_source": how, "note": "decode phase: weights + KV bytes per step over the mean decode step time"},
+                   {"clocks": clocks, "gpu_launches": None, "data": "synthetic (seeded prompts and random-init weights)"})
+    if not invariant:
+        raise SystemExit("offline run: token ids depend on the batch composition")
+
+
 def run_tp_layer(args) -> None:
     import torch
     import torch.distributed as dist
@@ -849,11 +959,13 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="model", choices=["model", "attn", "rowops", "gemm", "prefill", "tp_layer", "tp_linear"],
+    ap.add_argument("--workload", default="model", choices=["model", "attn", "rowops", "gemm", "prefill", "offline", "tp_layer", "tp_linear"],
                     help="model = the decode step of the 8B-shaped model, tensor-parallel over the launched ranks (default); "
                          "the others time one component")
     ap.add_argument("--batch", type=int, default=MODEL_CFG["batch"], help="decode batch of --workload model")
     ap.add_argument("--model-layers", type=int, default=MODEL_CFG["layers"], help="layers of --workload model (fewer: profiler captures)")
+    ap.add_argument("--decode-steps", type=int, default=64, help="offline: greedy decode steps after the prefill")
+    ap.add_argument("--chunk-tokens", type=int, default=8192, help="offline: most prompt tokens per prefill forward")
     ap.add_argument("--no-kernels", action="store_true", help="model on one GPU: skip the component records")
     ap.add_argument("--no-tp32b", action="store_true", help="model on several GPUs: skip the 32B-shaped layer record")
     ap.add_argument("--cluster", type=int, default=0, help="attn: CTAs per (sequence, KV head); 0 = library default")
@@ -865,7 +977,7 @@ def main() -> None:
     if args.impl == "reference":
         run_reference(args)
     else:
-        {"model": run_model, "attn": run_attn, "rowops": run_rowops, "gemm": run_gemm, "prefill": run_prefill,
+        {"model": run_model, "attn": run_attn, "rowops": run_rowops, "gemm": run_gemm, "prefill": run_prefill, "offline": run_offline,
          "tp_layer": run_tp_layer, "tp_linear": run_tp_linear}[args.workload](args)
 
 

@@ -313,6 +313,35 @@ B200_API int b200_gemm_w8a8_absmax(const int8_t* x8, const int8_t* w8, const int
                                    const int32_t* w_mul, const int32_t* w_shift, int32_t* out_q15,
                                    int32_t* acc_out, int64_t m, int64_t n, int64_t k, b200_stream_t s);
 
+/* ---- The linear with its requantisation left to the kernel that consumes it ("pending" linear), for decode steps
+ * where a launch costs as much as the work in it.  `zero_ws` is an int32 [m, n] workspace that the caller keeps and
+ * that is ALL ZERO whenever no call is using it (allocate it zeroed once):
+ *   b200_gemm_w8a8_absmax_ws  the linear of b200_gemm_w8a8_absmax; split-K parts are added into zero_ws without a
+ *                             clearing launch and the requantising kernel zeroes what it read.  out_q15 != zero_ws.
+ *   b200_gemm_w8a8_acc_ws     leaves the exact accumulators in zero_ws; exactly one of the two calls below must then
+ *                             consume them (they zero the buffer again) before zero_ws is reused.
+ *   b200_rmsnorm_q15_pending  b200_rmsnorm_q15 with x = the Q15.16 result of that linear, computed on the fly from
+ *                             (acc, x_absmax int32 [rows], w_mul, w_shift int32 [hidden]): the same bits as
+ *                             b200_gemm_w8a8_absmax followed by b200_rmsnorm_q15, in two launches instead of four.
+ *   b200_qkv_prepare_pending  b200_qkv_prepare_q15 on the pending qkv linear (acc int32 [tokens, (q_heads + 2 kv_heads)
+ *                             * 128], q | k | v heads side by side).
+ * No reference counterpart: the reference materialises every linear's output (layers/quantization/w8a8_int8.py:242-286)
+ * before RMSNorm (models/integer/qwen3_integer.py:62-80) or q/k-norm + RoPE (models/utils_integer.py:209-227) read it. */
+B200_API int b200_gemm_w8a8_absmax_ws(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax, const int32_t* w_mul,
+                                      const int32_t* w_shift, int32_t* out_q15, int32_t* zero_ws, int64_t m, int64_t n,
+                                      int64_t k, b200_stream_t s);
+B200_API int b200_gemm_w8a8_acc_ws(const int8_t* x8, const int8_t* w8, int32_t* zero_ws, int64_t m, int64_t n, int64_t k,
+                                   b200_stream_t s);
+B200_API int b200_rmsnorm_q15_pending(int32_t* acc, const int32_t* x_absmax, const int32_t* w_mul, const int32_t* w_shift,
+                                      const int32_t* residual, const int32_t* weight, int32_t* residual_out,
+                                      int32_t* norm_out, int8_t* codes, float* scale, int32_t* absmax, int64_t rows,
+                                      int hidden, b200_stream_t s);
+B200_API int b200_qkv_prepare_pending(const int32_t* positions, int32_t* acc, const int32_t* x_absmax, const int32_t* w_mul,
+                                      const int32_t* w_shift, const int32_t* cos_sin, int max_pos, const int32_t* q_norm_w,
+                                      const int32_t* k_norm_w, const int32_t* out_loc, int8_t* k_codes, int8_t* v_codes,
+                                      int32_t* meta, int8_t* q8, int32_t* q_mul, int32_t* q_shift, int64_t tokens,
+                                      int q_heads, int kv_heads, int64_t num_pages, int with_fwht, b200_stream_t s);
+
 /* ---- Pieces of the W8A8 linear for tensor-parallel row-split layers, where the int32 partial
  * sums of the ranks are added (all-reduce) between the GEMM and its epilogue.  They stand in for
  * the per-rank quant + GEMM + all-reduce of LinearOProj / LinearRowParallel

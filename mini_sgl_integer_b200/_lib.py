@@ -46,6 +46,10 @@ SIGNATURES: dict[str, list] = {
     "b200_gemm_w8a8": [P, P, P, P, P, P, P, P, L, L, L, P],
     "b200_gemm_w8a8_absmax": [P, P, P, P, P, P, P, L, L, L, P],
     "b200_gemm_w8a8_reduce_peers": [P, P, P, I, L, L, L, P],
+    "b200_gemm_w8a8_absmax_ws": [P, P, P, P, P, P, P, L, L, L, P],
+    "b200_gemm_w8a8_acc_ws": [P, P, P, L, L, L, P],
+    "b200_rmsnorm_q15_pending": [P, P, P, P, P, P, P, P, P, P, P, L, I, P],
+    "b200_qkv_prepare_pending": [P, P, P, P, P, P, I, P, P, P, P, P, P, P, P, P, L, I, I, L, I, P],
     "b200_gemm_status": [P, I],
     "b200_quant_given_absmax_q15": [P, P, P, L, I, P],
     "b200_requant_q15": [P, P, P, P, P, P, L, L, P],

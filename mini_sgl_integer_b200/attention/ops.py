@@ -208,9 +208,28 @@ def qkv_rope_quant_store(positions: torch.Tensor, qkv_q15: torch.Tensor, q_heads
     Returns (q8 int8 [tokens, q_heads, 128], q_mul, q_shift int32 [tokens, q_heads]).  Same bits as
     qk_norm_rope_fwht -> pool.store_kv -> per_token_quant_int8_from_q15 -> absmax_to_mul_shift
     (models/utils_integer.py:209-227, attention/triton_int8.py:125)."""
+    from ..kernel.pending import PendingLinear
+    hk = pool.kv_heads
+    if isinstance(qkv_q15, PendingLinear):
+        # the qkv linear's accumulators: requantised by the kernel while it loads them (and zeroed behind it)
+        pl = qkv_q15
+        tokens = pl.acc.shape[0]
+        if pl.acc.shape[1] != (q_heads + 2 * hk) * HEAD_DIM:
+            raise ValueError(f"qkv width {pl.acc.shape[1]} != (q_heads + 2*kv_heads)*{HEAD_DIM}")
+        require_cuda(positions, pl.acc, out_loc, cos_sin_cache_q15, q_norm_weight, k_norm_weight)
+        c = lambda t: None if t is None else t.to(torch.int32).contiguous()
+        q8 = torch.empty((tokens, q_heads, HEAD_DIM), dtype=torch.int8, device=pl.acc.device)
+        q_mul = torch.empty((tokens, q_heads), dtype=torch.int32, device=pl.acc.device)
+        q_shift = torch.empty_like(q_mul)
+        cache = c(cos_sin_cache_q15)
+        if tokens:
+            call("b200_qkv_prepare_pending", ptr(c(positions)), ptr(pl.acc), ptr(pl.x_absmax), ptr(pl.weight_mul),
+                 ptr(pl.weight_shift), ptr(cache), cache.shape[0], ptr(c(q_norm_weight)), ptr(c(k_norm_weight)),
+                 ptr(c(out_loc)), ptr(pool.k_cache(layer_id)), ptr(pool.v_cache(layer_id)), ptr(pool.meta(layer_id)),
+                 ptr(q8), ptr(q_mul), ptr(q_shift), tokens, q_heads, hk, pool.num_pages, int(with_fwht), stream())
+        return q8, q_mul, q_shift
     if qkv_q15.dtype != torch.int32 or qkv_q15.ndim != 2:
         raise TypeError(f"qkv_q15 must be int32 [tokens, width], got {qkv_q15.dtype} {tuple(qkv_q15.shape)}")
-    hk = pool.kv_heads
     if qkv_q15.shape[1] != (q_heads + 2 * hk) * HEAD_DIM:
         raise ValueError(f"qkv width {qkv_q15.shape[1]} != (q_heads + 2*kv_heads)*{HEAD_DIM}")
     require_cuda(positions, qkv_q15, out_loc, cos_sin_cache_q15, q_norm_weight, k_norm_weight)

@@ -91,6 +91,9 @@ kv_store_kernel(const void* __restrict__ k_in, int64_t k_pitch, const void* __re
 // (multiplier, shift); k heads the same and go straight into their page; v heads are quantised and stored
 // in operand order.  Same arithmetic, row by row, as qk_rope_kernel, quant_rows_kernel, absmax_to_ms_kernel
 // and kv_store_kernel<true> run one after the other.
+// PENDING: q, k and v are null and the rows come from the qkv linear's exact accumulators ([tokens, heads * 128],
+// q | k | v heads side by side), requantised while they are loaded and zeroed behind.
+template <bool PENDING>
 __global__ void __launch_bounds__(256)
 qkv_prepare_kernel(const int32_t* __restrict__ positions, const int32_t* __restrict__ q, int64_t q_pitch,
                    const int32_t* __restrict__ k, int64_t k_pitch, const int32_t* __restrict__ v, int64_t v_pitch,
@@ -98,7 +101,7 @@ qkv_prepare_kernel(const int32_t* __restrict__ positions, const int32_t* __restr
                    const int32_t* __restrict__ k_norm_w, const int32_t* __restrict__ out_loc,
                    int8_t* __restrict__ k_codes, int8_t* __restrict__ v_codes, int32_t* __restrict__ meta,
                    int8_t* __restrict__ q8, int32_t* __restrict__ q_mul, int32_t* __restrict__ q_shift,
-                   int64_t tokens, int q_heads, int kv_heads, int64_t num_pages, int with_fwht) {
+                   int64_t tokens, int q_heads, int kv_heads, int64_t num_pages, int with_fwht, const PendingLinear pl) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -111,15 +114,43 @@ qkv_prepare_kernel(const int32_t* __restrict__ positions, const int32_t* __restr
   const int64_t pid = loc >> 4;
   const int tok = (int)(loc & 15);
   const bool in_pool = loc >= 0 && pid < num_pages;     // out-of-pool locations are dropped, never written
+  int pxm = 0, pxs = 0;
+  int4 pv = make_int4(0, 0, 0, 0);
+  int2 plo = make_int2(0, 0), phi = make_int2(0, 0);
+  if (PENDING) {     // taken (and zeroed) before any early return: the buffer must be all zero afterwards
+    absmax_to_ms_dev(__ldg(pl.x_absmax + t), &pxm, &pxs);
+    pxs -= 48;
+    if (h < q_heads + kv_heads) {
+      plo = pending_take2(pl, t, heads * kD, h * kD + 2 * lane, pxm, pxs);
+      phi = pending_take2(pl, t, heads * kD, h * kD + 64 + 2 * lane, pxm, pxs);
+    } else {
+      pv = pending_take4(pl, t, heads * kD, h * kD + 4 * lane, pxm, pxs);
+    }
+  }
   if (h < q_heads + kv_heads) {
     const bool is_q = h < q_heads;
     const int hh = is_q ? h : h - q_heads;
-    if (!is_q && !in_pool) return;
-    const int32_t* src = is_q ? q + t * q_pitch + (int64_t)hh * kD : k + t * k_pitch + (int64_t)hh * kD;
+    if (!is_q && !in_pool) {
+      if (PENDING) {   // dropped, but the buffer must still be all zero afterwards
+        pending_clear2(pl, t, heads * kD, h * kD + 2 * lane);
+        pending_clear2(pl, t, heads * kD, h * kD + 64 + 2 * lane);
+      }
+      return;
+    }
     int a0, a1, b0, b1;
-    rope_row(src, is_q ? q_norm_w : k_norm_w, positions[t], cos_sin, max_pos, with_fwht, lane, a0, a1, b0, b1);
+    if (PENDING) {
+      rope_row_vals(plo, phi, is_q ? q_norm_w : k_norm_w, positions[t], cos_sin, max_pos, with_fwht, lane, a0, a1, b0, b1);
+    } else {
+      const int32_t* src = is_q ? q + t * q_pitch + (int64_t)hh * kD : k + t * k_pitch + (int64_t)hh * kD;
+      rope_row(src, is_q ? q_norm_w : k_norm_w, positions[t], cos_sin, max_pos, with_fwht, lane, a0, a1, b0, b1);
+    }
     int m = max(max(0, abs_wrap(a0)), max(abs_wrap(a1), max(abs_wrap(b0), abs_wrap(b1))));
     m = max(1, warp_max(m));
+    if (PENDING) {   // after a reduction over the loaded values: zeros for the next GEMM's partial sums
+      __syncwarp();
+      pending_clear2(pl, t, heads * kD, h * kD + 2 * lane);
+      pending_clear2(pl, t, heads * kD, h * kD + 64 + 2 * lane);
+    }
     const float mf = __int2float_rn(m), my = __frcp_rn(mf);
     const unsigned lo = (unsigned)(quant_code_fast(a0, mf, my) & 0xff) | ((unsigned)(quant_code_fast(a1, mf, my) & 0xff) << 8);
     const unsigned hi = (unsigned)(quant_code_fast(b0, mf, my) & 0xff) | ((unsigned)(quant_code_fast(b1, mf, my) & 0xff) << 8);
@@ -141,11 +172,18 @@ qkv_prepare_kernel(const int32_t* __restrict__ positions, const int32_t* __restr
     reinterpret_cast<unsigned short*>(row)[lane] = (unsigned short)lo;            // elements 2l, 2l+1
     reinterpret_cast<unsigned short*>(row + 64)[lane] = (unsigned short)hi;       // elements 64+2l, 64+2l+1
   } else {
-    if (!in_pool) return;
+    if (!in_pool) {
+      if (PENDING) pending_clear4(pl, t, heads * kD, h * kD + 4 * lane);
+      return;
+    }
     const int hh = h - q_heads - kv_heads;
-    const int4 b = *reinterpret_cast<const int4*>(v + t * v_pitch + (int64_t)hh * kD + 4 * lane);
+    const int4 b = PENDING ? pv : *reinterpret_cast<const int4*>(v + t * v_pitch + (int64_t)hh * kD + 4 * lane);
     int mv = max(max(0, abs_wrap(b.x)), max(abs_wrap(b.y), max(abs_wrap(b.z), abs_wrap(b.w))));
     mv = max(1, warp_max(mv));
+    if (PENDING) {
+      __syncwarp();
+      pending_clear4(pl, t, heads * kD, h * kD + 4 * lane);
+    }
     const float fv = __int2float_rn(mv), yv = __frcp_rn(fv);
     const unsigned vw = pack4(quant_code_fast(b.x, fv, yv), quant_code_fast(b.y, fv, yv), quant_code_fast(b.z, fv, yv),
                               quant_code_fast(b.w, fv, yv));
@@ -777,11 +815,37 @@ extern "C" int b200_qkv_prepare_q15(const int32_t* positions, const int32_t* q, 
   const int64_t warps = tokens * (q_heads + 2 * kv_heads);
   const int64_t blocks = (warps + 7) / 8;
   B200_REQUIRE(blocks < (1ll << 31), B200_E_SHAPE, "qkv_prepare_q15: too many rows");
-  launch_pdl(qkv_prepare_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)s, positions, q, q_pitch, k, k_pitch, v, v_pitch, cos_sin,
+  const PendingLinear none = {nullptr, nullptr, nullptr, nullptr};
+  launch_pdl(qkv_prepare_kernel<false>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)s, positions, q, q_pitch, k, k_pitch, v, v_pitch, cos_sin,
                                                                     max_pos, q_norm_w, k_norm_w, out_loc, k_codes, v_codes,
                                                                     meta, q8, q_mul, q_shift, tokens, q_heads, kv_heads,
-                                                                    num_pages, with_fwht);
+                                                                    num_pages, with_fwht, none);
   return check_launch("qkv_prepare_q15");
+}
+
+extern "C" int b200_qkv_prepare_pending(const int32_t* positions, int32_t* acc, const int32_t* x_absmax, const int32_t* w_mul,
+                                        const int32_t* w_shift, const int32_t* cos_sin, int max_pos, const int32_t* q_norm_w,
+                                        const int32_t* k_norm_w, const int32_t* out_loc, int8_t* k_codes, int8_t* v_codes,
+                                        int32_t* meta, int8_t* q8, int32_t* q_mul, int32_t* q_shift, int64_t tokens,
+                                        int q_heads, int kv_heads, int64_t num_pages, int with_fwht, b200_stream_t s) {
+  B200_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && max_pos > 0 && num_pages > 0, B200_E_SHAPE,
+               "qkv_prepare_pending: tokens=%lld q_heads=%d kv_heads=%d max_pos=%d num_pages=%lld", (long long)tokens,
+               q_heads, kv_heads, max_pos, (long long)num_pages);
+  if (tokens == 0) return B200_OK;
+  B200_REQUIRE(positions && acc && x_absmax && w_mul && cos_sin && out_loc && k_codes && v_codes && meta && q8 && q_mul &&
+                   q_shift, B200_E_NULL, "qkv_prepare_pending: null pointer");
+  auto a8 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; };
+  B200_REQUIRE(aligned16(acc) && aligned16(w_mul) && aligned16(w_shift) && a8(cos_sin) && a8(q_norm_w) && a8(k_norm_w) &&
+                   aligned16(k_codes) && aligned16(v_codes) && aligned16(meta) && (reinterpret_cast<uintptr_t>(q8) & 3u) == 0,
+               B200_E_ALIGN, "qkv_prepare_pending: acc, scales and pool buffers 16-byte, norm weights 8-byte, q8 4-byte aligned");
+  const int64_t warps = tokens * (q_heads + 2 * kv_heads);
+  const int64_t blocks = (warps + 7) / 8;
+  B200_REQUIRE(blocks < (1ll << 31), B200_E_SHAPE, "qkv_prepare_pending: too many rows");
+  const PendingLinear pl = {acc, x_absmax, w_mul, w_shift};
+  launch_pdl(qkv_prepare_kernel<true>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)s, positions, (const int32_t*)nullptr,
+             (int64_t)0, (const int32_t*)nullptr, (int64_t)0, (const int32_t*)nullptr, (int64_t)0, cos_sin, max_pos, q_norm_w,
+             k_norm_w, out_loc, k_codes, v_codes, meta, q8, q_mul, q_shift, tokens, q_heads, kv_heads, num_pages, with_fwht, pl);
+  return check_launch("qkv_prepare_pending");
 }
 
 extern "C" int b200_kv_store_q15(const int32_t* k, int64_t k_pitch, const int32_t* v, int64_t v_pitch,

@@ -219,4 +219,52 @@ __device__ __forceinline__ void absmax_to_ms_dev(int m, int* mul, int* shift) {
   *shift = k + 16;
 }
 
+// The fixed-point epilogue of a W8A8 linear for one exact accumulator: round-half-up shift of acc * cm by s bits,
+// saturated, where cm = (x_mul * w_mul) >> 32 and s = x_shift + w_shift - 48.
+__device__ __forceinline__ int requant_one(int acc, int cm, int s) {
+  if (s > 0 && s < 63) return sat32(((long long)acc * (long long)cm + (1LL << (s - 1))) >> s);
+  return sat32(mul_shift64((long long)acc, (long long)cm, s));
+}
+
+// A linear's output that has not been requantised yet: the exact int32 accumulators [rows, n] (split-K parts already
+// added), the absmax of each token's input row and the weight's per-channel scales.  A row kernel that is handed this
+// instead of Q15.16 values applies the epilogue while it loads and leaves zeros behind, so that the buffer can take
+// the next GEMM's split-K parts without a clearing launch.  The zeros are stored by a separate call placed AFTER a
+// reduction that consumed the loaded values: a store issued right behind the load of the same address waits for
+// the load's miss (measured: the requantising kernel took 12 us instead of 4 with the store in front).
+struct PendingLinear {
+  int32_t* acc;
+  const int32_t* x_absmax;
+  const int32_t* w_mul;
+  const int32_t* w_shift;     // nullable: 31 everywhere
+};
+
+__device__ __forceinline__ int2 pending_take2(const PendingLinear& pl, int64_t row, int n, int col, int xm, int xs48) {
+  const int2 a = *reinterpret_cast<const int2*>(pl.acc + row * n + col);
+  const int2 wm = __ldg(reinterpret_cast<const int2*>(pl.w_mul + col));
+  int2 ws = make_int2(31, 31);
+  if (pl.w_shift) ws = __ldg(reinterpret_cast<const int2*>(pl.w_shift + col));
+  return make_int2(requant_one(a.x, __mulhi(xm, wm.x), xs48 + ws.x), requant_one(a.y, __mulhi(xm, wm.y), xs48 + ws.y));
+}
+
+__device__ __forceinline__ void pending_clear2(const PendingLinear& pl, int64_t row, int n, int col) {
+  *reinterpret_cast<int2*>(pl.acc + row * n + col) = make_int2(0, 0);
+}
+__device__ __forceinline__ void pending_clear4(const PendingLinear& pl, int64_t row, int n, int col) {
+  *reinterpret_cast<int4*>(pl.acc + row * n + col) = make_int4(0, 0, 0, 0);
+}
+
+__device__ __forceinline__ int4 pending_take4(const PendingLinear& pl, int64_t row, int n, int col, int xm, int xs48) {
+  const int4 a = *reinterpret_cast<const int4*>(pl.acc + row * n + col);
+  const int4 wm = __ldg(reinterpret_cast<const int4*>(pl.w_mul + col));
+  int4 ws = make_int4(31, 31, 31, 31);
+  if (pl.w_shift) ws = __ldg(reinterpret_cast<const int4*>(pl.w_shift + col));
+  int4 r;
+  r.x = requant_one(a.x, __mulhi(xm, wm.x), xs48 + ws.x);
+  r.y = requant_one(a.y, __mulhi(xm, wm.y), xs48 + ws.y);
+  r.z = requant_one(a.z, __mulhi(xm, wm.z), xs48 + ws.z);
+  r.w = requant_one(a.w, __mulhi(xm, wm.w), xs48 + ws.w);
+  return r;
+}
+
 }  // namespace b200

@@ -123,6 +123,7 @@ struct GemmParams {
   int full_blocks;          // weights-stationary mode: the first full_blocks blocks of weight rows are never split
                             // (one tile each, finished in the GEMM kernel); `splits` applies to the blocks after them
   int32_t* partial;         // splits > 1: int32 [M, N] that the parts are added into (zeroed before the launch)
+  int split_col0;           // first output channel that belongs to a split block
   int n_peers;              // > 0: tensor-parallel reduction - every part is added into each of these [M, N] buffers
   int32_t* peer[8];         //      (this rank's and its peers', mapped into this process: NVLink peer memory)
   int tp_on;                // the peers' buffers are the accumulator halves of tensor-parallel exchange blocks: the
@@ -150,11 +151,6 @@ __device__ __forceinline__ WsTile ws_tile(const GemmParams& p, int tile, int num
   t.kb1 = min(num_kb, t.kb0 + kb_per);
   t.split = p.splits > 1;
   return t;
-}
-
-__device__ __forceinline__ int requant_one(int acc, int cm, int s) {
-  if (s > 0 && s < 63) return sat32(((long long)acc * (long long)cm + (1LL << (s - 1))) >> s);
-  return sat32(mul_shift64((long long)acc, (long long)cm, s));
 }
 
 constexpr int kStagePitch = 20;   // ints per staged row of 16: 16-byte aligned, conflict-free for int4 both ways
@@ -649,6 +645,170 @@ gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   }
 }
 
+// The two-CTA kernel with the operands swapped, for 129..256 tokens (decode batches): the pair's 256 accumulator rows
+// are WEIGHT rows, the 256 columns are tokens.  Each CTA stages its own 128 weight rows and HALF of the token tile per
+// k-block (32 KB instead of the 48 KB of the one-CTA weights-stationary tile, whose CTAs each re-read all tokens):
+// at these sizes the time goes into moving operands from L2 into shared memory, not into MMAs.  Tiles follow the
+// weights-stationary list in blocks of 256 weight rows: whole-K tiles for the first full_blocks, `splits` parts of K
+// for the rest, whose partial sums are added into `partial` with reductions (a warp's 32 lanes are 32 consecutive
+// channels of one token: one 128-byte reduction per instruction).
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads2, 1)
+gemm_w8a8_2sm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                        const GemmParams p) {
+  constexpr int BN = 256;                      // token columns of the pair's tile; each CTA stages BN / 2 token rows
+  constexpr int kABytes = kBM * kBK;           // 128 weight rows
+  constexpr int kBBytes = (BN / 2) * kBK;      // 128 token rows
+  constexpr int kStageBytes = kABytes + kBBytes;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * kStageBytes);   // full[S], empty[S], tfull[2], tempty[2]
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 4);
+  int32_t* tok_scale = reinterpret_cast<int32_t*>(tmem_slot + 4);               // [2 slots][mul BN | shift BN] per token
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+  const int w_blocks = (p.N + 2 * kBM - 1) / (2 * kBM);
+  const int num_tiles = p.full_blocks + (w_blocks - p.full_blocks) * p.splits;
+  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const unsigned tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull0 + 8 * s, 1);
+      mbar_init(tempty0 + 8 * s, 2 * kEpiWarps2);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  pdl_launch_dependents();
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_barrier();
+  tcgen05_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      unsigned it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const WsTile t = ws_tile(p, tile, num_kb);
+        for (int kb = t.kb0; kb < t.kb1; ++kb, ++it) {
+          const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
+          ok = mbar_wait(empty0 + 8 * s, ph ^ 1, 1);
+          if (!ok) break;
+          if (leader) mbar_expect_tx(full0 + 8 * s, 2 * kStageBytes);
+          const unsigned a_dst = smem_u32(tiles + s * kStageBytes);
+          const unsigned lbar = (full0 + 8 * s) & kPeerBitMask;
+          tma_load_2d_2sm(a_dst, &map_w, kb * kBK, t.n_blk * 2 * kBM + (int)rank * kBM, lbar);
+          tma_load_2d_2sm(a_dst + kABytes, &map_x, kb * kBK, (int)rank * (BN / 2), lbar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr unsigned idesc = make_idesc(2 * kBM, BN);
+      unsigned it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++lt) {
+        const unsigned slot = lt & 1, aph = (lt >> 1) & 1;
+        ok = mbar_wait(tempty0 + 8 * slot, aph ^ 1, 4);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const unsigned tmem_d = tmem_base + slot * BN;
+        const WsTile t = ws_tile(p, tile, num_kb);
+        for (int kb = t.kb0; kb < t.kb1; ++kb, ++it) {
+          const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
+          ok = mbar_wait(full0 + 8 * s, ph, 2);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const unsigned a_addr = smem_u32(tiles + s * kStageBytes);
+          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_i8_2sm(tmem_d, da + (uint64_t)(k * kUmmaK >> 4), db + (uint64_t)(k * kUmmaK >> 4), idesc,
+                        (kb > t.kb0 || k > 0) ? 1u : 0u);
+          tcgen05_commit_pair(empty0 + 8 * s);
+        }
+        if (ok) tcgen05_commit_pair(tfull0 + 8 * slot);   // nothing is released after an expired wait
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int part = (warp - 2) >> 2;          // which of the interleaved 32-token chunks this warp takes
+    const int et = threadIdx.x - 64;
+    unsigned lt = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++lt) {
+      const WsTile t = ws_tile(p, tile, num_kb);
+      const unsigned slot = lt & 1, aph = (lt >> 1) & 1;
+      const int ch = t.n_blk * 2 * kBM + (int)rank * kBM + q * 32 + lane;
+      const bool direct = !t.split;
+      const bool empty_part = t.kb0 >= t.kb1;      // a part of K with no k-blocks: nothing was accumulated
+      int32_t* cs = tok_scale + slot * 2 * BN;
+      if (direct && p.out_q15) {
+        for (int c = et; c < BN; c += 32 * kEpiWarps2) {
+          const int tk = min(c, p.M - 1);
+          int tm, ts;
+          if (p.x_absmax) absmax_to_ms_dev(__ldg(p.x_absmax + tk), &tm, &ts);
+          else { tm = __ldg(p.x_mul + tk); ts = __ldg(p.x_shift + tk); }
+          cs[c] = tm;
+          cs[BN + c] = ts - 48;
+        }
+      }
+      int wm = 0, ws = 0;
+      if (ch < p.N && direct && p.out_q15) { wm = __ldg(p.w_mul + ch); ws = p.w_shift ? __ldg(p.w_shift + ch) : 31; }
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps2) : "memory");
+      if (ok) ok = mbar_wait(tfull0 + 8 * slot, aph, 3);
+      tcgen05_fence_after();
+#pragma unroll 1
+      for (int c0 = part * 32; c0 < BN; c0 += 32 * (kEpiWarps2 / 4)) {
+        if (!ok || c0 >= p.M || empty_part) continue;   // warp-uniform
+        int v[32];
+        tmem_ld_32x32(tmem_base + ((unsigned)(q * 32) << 16) + slot * BN + (unsigned)c0, v);
+        if (ch >= p.N) continue;
+        if (!direct) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < p.M) atomicAdd(p.partial + (int64_t)(c0 + j) * p.N + ch, v[j]);   // result unused: a reduction
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (c0 + j < p.M) {
+              const int64_t o = (int64_t)(c0 + j) * p.N + ch;
+              if (p.acc_out) p.acc_out[o] = v[j];
+              if (p.out_q15) p.out_q15[o] = requant_one(v[j], __mulhi(cs[c0 + j], wm), cs[BN + c0 + j] + ws);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(tempty0 + 8 * slot);
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_barrier();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+  }
+}
+
 // Clears columns [0, 4 * vec_cols) of m rows (row pitch in elements) before the split-K parts are added into them.
 __global__ void __launch_bounds__(256)
 zero_cols_kernel(int32_t* __restrict__ base, int m, int vec_cols, int64_t pitch) {
@@ -661,13 +821,14 @@ zero_cols_kernel(int32_t* __restrict__ base, int m, int vec_cols, int64_t pitch)
 }
 
 // The epilogue on its own, for the split-K parts gathered in `partial` ([M, N] int32; may be `out` itself):
-// four consecutive channels of one token per thread.
+// four consecutive channels of one token per thread.  With `clear` the sums are zeroed once read: `partial` is then a
+// workspace that stays zero between calls, and no clearing launch is needed in front of the next GEMM.
 __global__ void __launch_bounds__(256)
-splitk_epilogue_kernel(const int32_t* partial, const GemmParams p) {
+splitk_epilogue_kernel(int32_t* partial, const GemmParams p, int clear) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.y;
-  const int c = p.full_blocks * kBM + (blockIdx.x * 256 + threadIdx.x) * 4;   // only the split blocks' columns
+  const int c = p.split_col0 + (blockIdx.x * 256 + threadIdx.x) * 4;   // only the split blocks' columns
   if (c >= p.N) return;
   int xm, xs;
   if (p.x_absmax) absmax_to_ms_dev(__ldg(p.x_absmax + t), &xm, &xs);
@@ -685,10 +846,14 @@ splitk_epilogue_kernel(const int32_t* partial, const GemmParams p) {
     r.z = requant_one(a.z, __mulhi(xm, wm.z), xs + ws.z);
     r.w = requant_one(a.w, __mulhi(xm, wm.w), xs + ws.w);
     *reinterpret_cast<int4*>(p.out_q15 + o) = r;
+    // behind the result's store: a store issued right behind the load of the same address waits for the load's miss
+    if (clear) *reinterpret_cast<int4*>(partial + o) = make_int4(0, 0, 0, 0);
   } else {
-    for (int j = 0; j < 4 && c + j < p.N; ++j)
-      p.out_q15[o + j] = requant_one(partial[o + j], __mulhi(xm, __ldg(p.w_mul + c + j)),
-                                     xs + (p.w_shift ? __ldg(p.w_shift + c + j) : 31));
+    for (int j = 0; j < 4 && c + j < p.N; ++j) {
+      const int a = partial[o + j];
+      if (clear) partial[o + j] = 0;
+      p.out_q15[o + j] = requant_one(a, __mulhi(xm, __ldg(p.w_mul + c + j)), xs + (p.w_shift ? __ldg(p.w_shift + c + j) : 31));
+    }
   }
 }
 
@@ -764,13 +929,41 @@ static int launch_gemm_2sm(const CUtensorMap& ma, const CUtensorMap& mb, const G
   return check_launch("gemm_w8a8 (two-CTA tiles)");
 }
 
+template <int STAGES>
+static int launch_gemm_2sm_ws(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t st) {
+  constexpr int BN = 256;
+  constexpr size_t smem = (size_t)STAGES * (kBM * kBK + (BN / 2) * kBK) + 1024 + (2 * STAGES + 4) * 8 + 16 + 4 * BN * 4;
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  cudaError_t e = cudaFuncSetAttribute(gemm_w8a8_2sm_ws_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_error("gemm_w8a8: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    return B200_E_CUDA;
+  }
+  const int tiles = p.full_blocks + ((p.N + 2 * kBM - 1) / (2 * kBM) - p.full_blocks) * p.splits;
+  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  launch_pdl(gemm_w8a8_2sm_ws_kernel<STAGES>, dim3(2 * pairs), dim3(kGemmThreads2), smem, st, mw, mx, p);
+  return check_launch("gemm_w8a8 (two-CTA weights-stationary tiles)");
+}
+
+static bool pair_ws_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("B200_GEMM_PAIR_WS");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
 }  // namespace b200
 
 using namespace b200;
 
 static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax, const int32_t* x_mul,
                      const int32_t* x_shift, const int32_t* w_mul, const int32_t* w_shift, int32_t* out_q15,
-                     int32_t* acc_out, int64_t m, int64_t n, int64_t k, b200_stream_t s) {
+                     int32_t* acc_out, int64_t m, int64_t n, int64_t k, b200_stream_t s, int32_t* zero_ws = nullptr) {
+  // zero_ws: a caller-kept [m, n] int32 workspace that is all zero on entry; split-K parts are added into it without
+  // a clearing launch.  With a Q15.16 output the requantising kernel zeroes it again; with acc_out == zero_ws (no
+  // Q15.16 output) it holds the exact accumulators on return and whoever consumes them clears it.
   B200_REQUIRE(x8 && w8, B200_E_NULL, "gemm_w8a8: x8 or w8 is null");
   B200_REQUIRE(out_q15 || acc_out, B200_E_NULL, "gemm_w8a8: no output requested");
   B200_REQUIRE(!out_q15 || (((x_mul && x_shift) || x_absmax) && w_mul), B200_E_NULL,
@@ -785,29 +978,36 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
   GemmParams p;
   p.x_absmax = x_absmax; p.x_mul = x_mul; p.x_shift = x_shift; p.w_mul = w_mul; p.w_shift = w_shift;
   p.out_q15 = out_q15; p.acc_out = acc_out; p.M = (int)m; p.N = (int)n; p.K = (int)k;
-  p.splits = 1; p.full_blocks = 0; p.partial = nullptr; p.n_peers = 0; p.tp_on = 0;
+  p.splits = 1; p.full_blocks = 0; p.partial = nullptr; p.n_peers = 0; p.tp_on = 0; p.split_col0 = 0;
   cudaStream_t st = (cudaStream_t)s;
-  const int w_blocks = (int)((n + kBM - 1) / kBM), num_kb = (int)((k + kBK - 1) / kBK);
-  if (m <= 128 || (m <= 256 && w_blocks < sm_count())) {
-    // decode sizes: weights-stationary, K split so that about one CTA per SM streams the weights
-    // (256 tokens against a weight matrix with at least one 128-row block per SM do as well on the other path)
-    // With more blocks than SMs the whole waves run unsplit and only the blocks of the last, partial wave are
+  const int num_kb = (int)((k + kBK - 1) / kBK);
+  // 129..256 tokens: CTA pairs on blocks of 256 weight rows (each CTA stages half of the tokens); fewer tokens: single
+  // CTAs on blocks of 128 weight rows with a token tile as narrow as the batch
+  const bool pair_ws = m > 128 && m <= 256 && pair_ws_enabled();
+  const int block_rows = pair_ws ? 2 * kBM : kBM, units = pair_ws ? sm_count() / 2 : sm_count();
+  const int w_blocks = (int)((n + block_rows - 1) / block_rows);
+  if (pair_ws || m <= 128 || (m <= 256 && w_blocks < sm_count())) {
+    // decode sizes: weights-stationary, K split so that about one CTA (pair) per SM (pair) streams the weights
+    // With more blocks than units the whole waves run unsplit and only the blocks of the last, partial wave are
     // split, so that it costs a fraction of a wave instead of a whole one.
-    const int tail = w_blocks % sm_count();
-    const int split_blocks = w_blocks < sm_count() ? w_blocks : tail;
-    int splits = split_blocks > 0 ? sm_count() / split_blocks : 1;
+    const int tail = w_blocks % units;
+    const int split_blocks = w_blocks < units ? w_blocks : tail;
+    int splits = split_blocks > 0 ? units / split_blocks : 1;
     splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
     while (splits > 1 && num_kb / splits < 4) --splits;
     while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;   // no empty part
     p.splits = splits;
     p.full_blocks = splits > 1 ? w_blocks - split_blocks : 0;
-    const int64_t col0 = (int64_t)p.full_blocks * kBM;     // first column that parts are added into
+    const int64_t col0 = (int64_t)p.full_blocks * block_rows;     // first column that parts are added into
+    p.split_col0 = (int)col0;
     if (splits > 1) {
       // the parts are added into the exact-accumulator output if the caller wants it, else into the
       // Q15.16 output buffer itself, which the epilogue kernel then rewrites in place
-      p.partial = acc_out ? acc_out : out_q15;
+      p.partial = zero_ws ? zero_ws : (acc_out ? acc_out : out_q15);
       // (a kernel rather than a memset node: it takes part in the programmatic launch chain of the step)
-      if ((n - col0) % 4 == 0 && col0 % 4 == 0 && n % 4 == 0) {
+      if (zero_ws) {
+        // already zero
+      } else if ((n - col0) % 4 == 0 && col0 % 4 == 0 && n % 4 == 0) {
         const int64_t vecs = (int64_t)m * ((n - col0) / 4);
         launch_pdl(zero_cols_kernel, dim3((unsigned)((vecs + 255) / 256)), dim3(256), 0, st, p.partial + col0, (int)m, (int)((n - col0) / 4), (int64_t)n);
         int rcz = check_launch("gemm_w8a8 (clearing the partial sums)");
@@ -820,16 +1020,18 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
     }
     const int bn = m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256));
     B200_REQUIRE(make_map(&ma, w8, n, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for w8");
-    B200_REQUIRE(make_map(&mb, x8, m, k, bn), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");
+    B200_REQUIRE(make_map(&mb, x8, m, k, pair_ws ? kBM : bn), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");
     int rc;
-    switch (bn) {
+    if (pair_ws) {
+      rc = launch_gemm_2sm_ws<6>(ma, mb, p, st);
+    } else switch (bn) {
       case 256: rc = launch_gemm<256, 4, true>(ma, mb, p, st); break;
       case 128: rc = launch_gemm<128, 6, true>(ma, mb, p, st); break;
       case 64: rc = launch_gemm<64, 8, true>(ma, mb, p, st); break;
       default: rc = launch_gemm<32, 10, true>(ma, mb, p, st); break;
     }
     if (rc != B200_OK || splits == 1 || !out_q15) return rc;
-    launch_pdl(splitk_epilogue_kernel, dim3((unsigned)((n - col0 + 1023) / 1024), (unsigned)m), dim3(256), 0, st, (const int32_t*)p.partial, p);
+    launch_pdl(splitk_epilogue_kernel, dim3((unsigned)((n - col0 + 1023) / 1024), (unsigned)m), dim3(256), 0, st, p.partial, p, zero_ws ? 1 : 0);
     return check_launch("gemm_w8a8 (split-K epilogue)");
   }
   B200_REQUIRE(make_map(&ma, x8, m, k, kBM), B200_E_CUDA, "gemm_w8a8: cuTensorMapEncodeTiled failed for x8");
@@ -865,6 +1067,21 @@ extern "C" int b200_gemm_w8a8_absmax(const int8_t* x8, const int8_t* w8, const i
   return gemm_impl(x8, w8, x_absmax, nullptr, nullptr, w_mul, w_shift, out_q15, acc_out, m, n, k, s);
 }
 
+extern "C" int b200_gemm_w8a8_absmax_ws(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax, const int32_t* w_mul,
+                                        const int32_t* w_shift, int32_t* out_q15, int32_t* zero_ws, int64_t m, int64_t n,
+                                        int64_t k, b200_stream_t s) {
+  B200_REQUIRE(x_absmax && out_q15 && zero_ws, B200_E_NULL, "gemm_w8a8_absmax_ws: null pointer");
+  B200_REQUIRE(aligned16(zero_ws) && zero_ws != out_q15, B200_E_ALIGN,
+               "gemm_w8a8_absmax_ws: the workspace must be 16-byte aligned and distinct from the output");
+  return gemm_impl(x8, w8, x_absmax, nullptr, nullptr, w_mul, w_shift, out_q15, nullptr, m, n, k, s, zero_ws);
+}
+
+extern "C" int b200_gemm_w8a8_acc_ws(const int8_t* x8, const int8_t* w8, int32_t* zero_ws, int64_t m, int64_t n, int64_t k,
+                                     b200_stream_t s) {
+  B200_REQUIRE(zero_ws, B200_E_NULL, "gemm_w8a8_acc_ws: the workspace is null");
+  return gemm_impl(x8, w8, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, zero_ws, m, n, k, s, zero_ws);
+}
+
 extern "C" int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, int32_t* const* peer_acc, int n_peers,
                                            int64_t m, int64_t n, int64_t k, b200_stream_t s) {
   B200_REQUIRE(x8 && w8 && peer_acc, B200_E_NULL, "gemm_w8a8_reduce_peers: null pointer");
@@ -876,7 +1093,7 @@ extern "C" int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, i
   B200_REQUIRE(aligned16(x8) && aligned16(w8), B200_E_ALIGN, "gemm_w8a8_reduce_peers: operands must be 16-byte aligned");
   GemmParams p;
   p.x_absmax = nullptr; p.x_mul = nullptr; p.x_shift = nullptr; p.w_mul = nullptr; p.w_shift = nullptr;
-  p.out_q15 = nullptr; p.acc_out = nullptr; p.M = (int)m; p.N = (int)n; p.K = (int)k; p.partial = nullptr;
+  p.out_q15 = nullptr; p.acc_out = nullptr; p.M = (int)m; p.N = (int)n; p.K = (int)k; p.partial = nullptr; p.split_col0 = 0;
   p.n_peers = n_peers;
   p.tp_on = 0;
   for (int r = 0; r < 8; ++r) {
@@ -916,7 +1133,7 @@ extern "C" int b200_gemm_w8a8_tp(const b200_tp_block* blk, const int8_t* x8, con
   B200_REQUIRE(aligned16(x8) && aligned16(w8), B200_E_ALIGN, "gemm_w8a8_tp: operands must be 16-byte aligned");
   GemmParams p;
   p.x_absmax = nullptr; p.x_mul = nullptr; p.x_shift = nullptr; p.w_mul = nullptr; p.w_shift = nullptr;
-  p.out_q15 = nullptr; p.acc_out = nullptr; p.M = (int)m; p.N = (int)n; p.K = (int)k; p.partial = nullptr;
+  p.out_q15 = nullptr; p.acc_out = nullptr; p.M = (int)m; p.N = (int)n; p.K = (int)k; p.partial = nullptr; p.split_col0 = 0;
   p.n_peers = 0;
   p.tp_on = 1;
   p.tp.rank = blk->rank; p.tp.size = blk->size; p.tp.m_max = blk->m_max; p.tp.n = blk->n;

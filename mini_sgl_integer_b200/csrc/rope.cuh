@@ -12,12 +12,10 @@ __device__ __forceinline__ int fwht_scale(int y, int kq15) {
 
 // Lane l ends up with elements 2l, 2l+1 (a0, a1) and 64+2l, 64+2l+1 (b0, b1) of the row, so that the
 // rotate-half pairs (j, j+64) sit in one thread.  nw: per-head RMSNorm weight (nullable).
-__device__ __forceinline__ void rope_row(const int32_t* __restrict__ src, const int32_t* __restrict__ nw, int pos_in,
-                                         const int32_t* __restrict__ cos_sin, int max_pos, int with_fwht, int lane,
-                                         int& a0, int& a1, int& b0, int& b1) {
-  int2 lo = *reinterpret_cast<const int2*>(src + 2 * lane);
-  int2 hi = *reinterpret_cast<const int2*>(src + 64 + 2 * lane);
-
+// (lo, hi): the lane's four values of the row as loaded.
+__device__ __forceinline__ void rope_row_vals(int2 lo, int2 hi, const int32_t* __restrict__ nw, int pos_in,
+                                              const int32_t* __restrict__ cos_sin, int max_pos, int with_fwht, int lane,
+                                              int& a0, int& a1, int& b0, int& b1) {
   if (nw != nullptr) {  // per-head fixed-point RMSNorm over the 128 values
     int m = max(max(0, abs_wrap(lo.x)), max(abs_wrap(lo.y), max(abs_wrap(hi.x), abs_wrap(hi.y))));
     m = warp_max(m);
@@ -61,6 +59,14 @@ __device__ __forceinline__ void rope_row(const int32_t* __restrict__ src, const 
     a0 = fwht_scale(t0, 2896); b0 = fwht_scale(u0, 2896);
     a1 = fwht_scale(t1, 2896); b1 = fwht_scale(u1, 2896);
   }
+}
+
+__device__ __forceinline__ void rope_row(const int32_t* __restrict__ src, const int32_t* __restrict__ nw, int pos_in,
+                                         const int32_t* __restrict__ cos_sin, int max_pos, int with_fwht, int lane,
+                                         int& a0, int& a1, int& b0, int& b1) {
+  const int2 lo = *reinterpret_cast<const int2*>(src + 2 * lane);
+  const int2 hi = *reinterpret_cast<const int2*>(src + 64 + 2 * lane);
+  rope_row_vals(lo, hi, nw, pos_in, cos_sin, max_pos, with_fwht, lane, a0, a1, b0, b1);
 }
 
 }  // namespace b200

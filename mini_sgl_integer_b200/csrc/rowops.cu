@@ -54,21 +54,27 @@ static int elementwise_grid(int64_t n, int threads) {
 // ============================================================================ RMSNorm rows
 // One CTA per row; thread t owns int4 vectors t, t+T, ... (VPT of them).
 // FULL: the row is exactly blockDim.x * VPT vectors long (no bounds checks on the vector index).
-template <int VPT, bool FULL>
+// PENDING: x is null and the row comes from a linear's exact accumulators, requantised while it is loaded.
+template <int VPT, bool FULL, bool PENDING = false>
 __global__ void __launch_bounds__(1024)
 rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ res,
                     const int32_t* __restrict__ w, int32_t* __restrict__ res_out,
                     int32_t* __restrict__ norm_out, int8_t* __restrict__ codes,
-                    float* __restrict__ scale, int32_t* __restrict__ absmax, int H) {
+                    float* __restrict__ scale, int32_t* __restrict__ absmax, int H, const PendingLinear pl) {
   __shared__ long long red64[33];
   __shared__ int red32[33];
   pdl_launch_dependents();
   pdl_wait();
   const int64_t row = blockIdx.x;
   const int nvec = H >> 2;
-  const int4* xr = reinterpret_cast<const int4*>(x + row * H);
+  const int4* xr = PENDING ? nullptr : reinterpret_cast<const int4*>(x + row * H);
   const int4* rr = res ? reinterpret_cast<const int4*>(res + row * H) : nullptr;
   int4* ro = res ? reinterpret_cast<int4*>(res_out + row * H) : nullptr;
+  int pxm = 0, pxs = 0;
+  if (PENDING) {
+    absmax_to_ms_dev(__ldg(pl.x_absmax + row), &pxm, &pxs);
+    pxs -= 48;
+  }
 
   int4 v[VPT];
   int m = 0;
@@ -77,7 +83,8 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
     const int idx = threadIdx.x + i * blockDim.x;
     int4 a = make_int4(0, 0, 0, 0);
     if (FULL || idx < nvec) {
-      a = __ldcs(xr + idx);
+      if (PENDING) a = pending_take4(pl, row, H, idx * 4, pxm, pxs);
+      else a = __ldcs(xr + idx);
       if (rr) {
         int4 b = __ldcs(rr + idx);
         a.x = (int)((unsigned)a.x + (unsigned)b.x);
@@ -91,6 +98,13 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
     m = max(max(m, abs_wrap(a.x)), max(abs_wrap(a.y), max(abs_wrap(a.z), abs_wrap(a.w))));
   }
   m = block_max(m, red32);
+  if (PENDING) {   // the accumulators have arrived (the reduction used them): leave zeros behind
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      if (FULL || idx < nvec) pending_clear4(pl, row, H, idx * 4);
+    }
+  }
   const NormRow nr = norm_row_from_absmax(m);
 
   long long S = 0;
@@ -691,14 +705,46 @@ extern "C" int b200_rmsnorm_q15(const int32_t* x, const int32_t* residual, const
   B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(residual) && aligned16(residual_out) &&
                    aligned16(norm_out) && ((uintptr_t)codes & 3u) == 0,
                B200_E_ALIGN, "rmsnorm_q15: int32 buffers must be 16-byte aligned (codes 4-byte)");
+  const PendingLinear none = {nullptr, nullptr, nullptr, nullptr};
   if ((hidden >> 2) == p.threads * p.vpt) {
     DISPATCH_VPT(p.vpt, (launch_pdl(rmsnorm_rows_kernel<V, true>, dim3((unsigned)rows), dim3(p.threads), 0, (cudaStream_t)s,
-                                    x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
+                                    x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden, none)));
   } else {
     DISPATCH_VPT(p.vpt, (launch_pdl(rmsnorm_rows_kernel<V, false>, dim3((unsigned)rows), dim3(p.threads), 0, (cudaStream_t)s,
-                                    x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden)));
+                                    x, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden, none)));
   }
   return check_launch("rmsnorm_q15");
+}
+
+extern "C" int b200_rmsnorm_q15_pending(int32_t* acc, const int32_t* x_absmax, const int32_t* w_mul, const int32_t* w_shift,
+                                        const int32_t* residual, const int32_t* weight, int32_t* residual_out,
+                                        int32_t* norm_out, int8_t* codes, float* scale, int32_t* absmax, int64_t rows,
+                                        int hidden, b200_stream_t s) {
+  B200_REQUIRE(acc && x_absmax && w_mul && weight, B200_E_NULL, "rmsnorm_q15_pending: acc, x_absmax, w_mul or weight is null");
+  B200_REQUIRE((residual == nullptr) == (residual_out == nullptr), B200_E_NULL,
+               "rmsnorm_q15_pending: residual and residual_out must be given together");
+  const bool q = codes != nullptr;
+  B200_REQUIRE(q == (scale != nullptr) && q == (absmax != nullptr), B200_E_NULL,
+               "rmsnorm_q15_pending: codes, scale and absmax must be given together");
+  B200_REQUIRE(norm_out || q, B200_E_NULL, "rmsnorm_q15_pending: no output requested");
+  B200_REQUIRE(rows >= 0 && rows < (1ll << 31) && hidden > 0, B200_E_SHAPE,
+               "rmsnorm_q15_pending: rows=%lld hidden=%d", (long long)rows, hidden);
+  B200_REQUIRE(hidden % 4 == 0, B200_E_UNSUPPORTED, "rmsnorm_q15_pending: hidden=%d is not a multiple of 4", hidden);
+  RowPlan p;
+  B200_REQUIRE(plan_rows(hidden, &p, rows), B200_E_UNSUPPORTED, "rmsnorm_q15_pending: hidden=%d exceeds 32768", hidden);
+  if (rows == 0) return B200_OK;
+  B200_REQUIRE(aligned16(acc) && aligned16(w_mul) && aligned16(w_shift) && aligned16(weight) && aligned16(residual) &&
+                   aligned16(residual_out) && aligned16(norm_out) && ((uintptr_t)codes & 3u) == 0,
+               B200_E_ALIGN, "rmsnorm_q15_pending: int32 buffers must be 16-byte aligned (codes 4-byte)");
+  const PendingLinear pl = {acc, x_absmax, w_mul, w_shift};
+  if ((hidden >> 2) == p.threads * p.vpt) {
+    DISPATCH_VPT(p.vpt, (launch_pdl(rmsnorm_rows_kernel<V, true, true>, dim3((unsigned)rows), dim3(p.threads), 0, (cudaStream_t)s,
+                                    (const int32_t*)nullptr, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden, pl)));
+  } else {
+    DISPATCH_VPT(p.vpt, (launch_pdl(rmsnorm_rows_kernel<V, false, true>, dim3((unsigned)rows), dim3(p.threads), 0, (cudaStream_t)s,
+                                    (const int32_t*)nullptr, residual, weight, residual_out, norm_out, codes, scale, absmax, hidden, pl)));
+  }
+  return check_launch("rmsnorm_q15_pending");
 }
 
 extern "C" int b200_per_token_quant_q15(const int32_t* x, int8_t* codes, float* scale,

@@ -314,6 +314,9 @@ def fused_add_rmsnorm_quant(x: torch.Tensor, residual: torch.Tensor | None, weig
     Returns (codes int8, scale fp32 [..., 1], absmax int32 [..., 1], residual_out or None,
     normalised Q15.16 or None).
     """
+    from .pending import PendingLinear
+    if isinstance(x, PendingLinear):
+        return _fused_add_rmsnorm_quant_pending(x, residual, weight, want_norm)
     assert_q15(x, "x")
     assert_q15(weight, "weight")
     hidden = _norm_args(x, weight)
@@ -335,6 +338,31 @@ def fused_add_rmsnorm_quant(x: torch.Tensor, residual: torch.Tensor | None, weig
     norm = torch.empty_like(xc) if want_norm else None
     call("b200_rmsnorm_q15", ptr(xc), ptr(rc), ptr(weight.contiguous()), ptr(res_out), ptr(norm), ptr(codes),
          ptr(scale), ptr(absmax), rows, hidden, stream())
+    return codes, scale, absmax, res_out, norm
+
+
+def _fused_add_rmsnorm_quant_pending(x, residual: torch.Tensor | None, weight: torch.Tensor, want_norm: bool):
+    """fused_add_rmsnorm_quant on a linear whose requantisation is still pending (kernel/pending.py): the kernel
+    applies the linear's fixed-point epilogue while it loads the row and zeroes the accumulators behind it."""
+    assert_q15(weight, "weight")
+    rows, hidden = x.acc.shape
+    if weight.ndim != 1 or weight.shape[0] != hidden:
+        raise ValueError(f"weight must be [{hidden}], got {tuple(weight.shape)}")
+    require_cuda(x.acc, residual, weight)
+    rc = res_out = None
+    if residual is not None:
+        assert_q15(residual, "residual")
+        if tuple(residual.shape) != (rows, hidden):
+            raise ValueError("residual and x must have same shape")
+        rc = residual.contiguous()
+        res_out = torch.empty_like(rc)
+    dev = x.acc.device
+    codes = torch.empty((rows, hidden), dtype=torch.int8, device=dev)
+    scale = torch.empty((rows, 1), dtype=torch.float32, device=dev)
+    absmax = torch.empty((rows, 1), dtype=torch.int32, device=dev)
+    norm = torch.empty((rows, hidden), dtype=torch.int32, device=dev) if want_norm else None
+    call("b200_rmsnorm_q15_pending", ptr(x.acc), ptr(x.x_absmax), ptr(x.weight_mul), ptr(x.weight_shift), ptr(rc),
+         ptr(weight.contiguous()), ptr(res_out), ptr(norm), ptr(codes), ptr(scale), ptr(absmax), rows, hidden, stream())
     return codes, scale, absmax, res_out, norm
 
 

@@ -9,6 +9,7 @@ reference's bf16 bridge (models/utils_integer.py:222-227).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -16,9 +17,13 @@ import torch
 
 from ..attention import Int8PagedKVCache, decode_attention_int8_paged, extend_attention_int8_paged, qkv_rope_quant_store
 from ..kernel import fixed_point as fp
+from ..kernel.pending import PENDING_MAX_ROWS, PendingLinear
 from ..distributed import DistributedCommunicator
 from .tp_linear import PeerReduceBuffers, TpExchange, row_parallel_q15, row_parallel_q15_fused
 from .w8a8_int8 import W8A8Int8LinearMethod
+
+
+_PENDING_ON = os.environ.get("B200_PENDING", "1") != "0"       # "0": every linear materialises its Q15.16 output
 
 
 @dataclass
@@ -72,18 +77,26 @@ class Qwen3DecoderLayerInteger:
         # no collective call in the layer (decode sizes; larger batches fall back to NCCL)
         self.exchange = exchange
 
-    def forward_q15(self, x_q15: torch.Tensor, residual_q15: Optional[torch.Tensor], batch: AttnBatch,
-                    trace: Optional[dict] = None):
-        """Returns (x_out, residual_out), both Q15.16 int32 [tokens, hidden]."""
-        fp.assert_q15(x_q15, "x_q15")
+    def forward_q15(self, x_q15, residual_q15: Optional[torch.Tensor], batch: AttnBatch,
+                    trace: Optional[dict] = None, defer_down: bool = False):
+        """Returns (x_out, residual_out), both Q15.16 int32 [tokens, hidden].
+
+        At decode sizes on one GPU the qkv and o projections are left pending (kernel/pending.py) and finished by
+        the kernels that read them; with ``defer_down`` the down projection is returned pending too, for the next
+        layer's (or the final) add + RMSNorm + quant, and ``x_q15`` may be such a pending linear."""
+        pending_in = isinstance(x_q15, PendingLinear)
+        if not pending_in:
+            fp.assert_q15(x_q15, "x_q15")
         t = trace if trace is not None else {}
         w, m = self.w, self.method
         T = x_q15.shape[0]
+        tp = self.comm.size > 1 or (self.exchange is not None and self.exchange.size > 1)
+        defer = trace is None and not tp and 0 < T <= PENDING_MAX_ROWS and _PENDING_ON
         # input_layernorm (+ residual add) -> int8 codes for qkv_proj
         codes, _, absmax, res, _ = fp.fused_add_rmsnorm_quant(x_q15, residual_q15, w["input_norm"])
         residual = res if residual_q15 is not None else x_q15
         t["ln1_codes"], t["ln1_absmax"] = codes, absmax
-        qkv = m.apply_quantised(w["qkv"], codes, absmax)
+        qkv = m.apply_pending(w["qkv"], codes, absmax) if defer else m.apply_quantised(w["qkv"], codes, absmax)
         t["qkv"] = qkv
         qd, kd = self.hq * 128, self.hk * 128
         if trace is None:
@@ -107,14 +120,19 @@ class Qwen3DecoderLayerInteger:
             attn = extend_attention_int8_paged(q8, q_mul, q_shift, self.pool, self.layer_id, batch.page_table,
                                                batch.kv_lens, batch.q_lens, batch.max_kv_len)
         t["attn"] = attn
-        tp = self.comm.size > 1 or (self.exchange is not None and self.exchange.size > 1)
         if self.exchange is not None and self.exchange.fits(T, self.hidden):
             rowp = lambda l, x: self.exchange.row_parallel_q15(m, l, x)
         elif self.peer_buffers is not None:
             rowp = lambda l, x: row_parallel_q15_fused(m, l, x, self.comm, self.peer_buffers)
         else:
             rowp = lambda l, x: row_parallel_q15(m, l, x, self.comm)
-        o = rowp(w["o"], attn.view(T, qd)) if tp else m.apply_weights_q15(w["o"], attn.view(T, qd))
+        if tp:
+            o = rowp(w["o"], attn.view(T, qd))
+        elif defer and getattr(w["o"], "input_scale", None) is None:
+            a_codes, _, a_absmax = fp.per_token_quant_int8_from_q15(attn.view(T, qd), return_absmax=True)
+            o = m.apply_pending(w["o"], a_codes, a_absmax)
+        else:
+            o = m.apply_weights_q15(w["o"], attn.view(T, qd))
         t["o"] = o
         # post_attention_layernorm (+ residual add) -> codes for gate_up_proj
         codes, _, absmax, residual, _ = fp.fused_add_rmsnorm_quant(o, residual, w["post_norm"])
@@ -126,6 +144,6 @@ class Qwen3DecoderLayerInteger:
         else:
             codes, _, absmax, _ = fp.silu_mul_fwht_quant(gate_up, self.hadamard_block)
             t["act_codes"], t["act_absmax"] = codes, absmax
-            down = m.apply_quantised(w["down"], codes, absmax)
+            down = (m.apply_pending if defer and defer_down else m.apply_quantised)(w["down"], codes, absmax)
         t["down"] = down
         return down, residual

@@ -21,6 +21,7 @@ import torch
 
 from .._lib import call, ptr, require_cuda, stream
 from ..kernel.fixed_point import absmax_to_mul_shift, assert_q15, per_token_quant_int8_from_q15
+from ..kernel.pending import PENDING_MAX_ROWS, PendingLinear, zero_workspace
 
 __all__ = ["W8A8Int8LinearMethod", "int8_gemm_q15", "weight_scale_to_mul_shift", "per_token_quant_int8_from_q15",
            "per_tensor_quant_int8_static_from_q15"]
@@ -140,11 +141,32 @@ class W8A8Int8LinearMethod:
         """The GEMM half of apply_weights_q15 for activations already quantised by a fused row kernel."""
         if getattr(layer, "weight_mul", None) is None:
             self.process_weights_after_loading(layer)
-        out = int8_gemm_q15(codes.reshape(-1, codes.shape[-1]), None, None, layer.weight, layer.weight_mul,
-                            layer.weight_shift, x_absmax=absmax.reshape(-1))
+        x8 = codes.reshape(-1, codes.shape[-1])
+        m, n = x8.shape[0], layer.weight.shape[0]
+        if 0 < m <= PENDING_MAX_ROWS and x8.is_contiguous() and layer.weight.is_contiguous() and layer.weight_shift is not None:
+            # decode sizes: split-K parts go into a workspace that is kept zero, which saves the clearing launch
+            out = torch.empty((m, n), dtype=torch.int32, device=x8.device)
+            require_cuda(x8, layer.weight, absmax, layer.weight_mul, layer.weight_shift)
+            call("b200_gemm_w8a8_absmax_ws", ptr(x8), ptr(layer.weight), ptr(absmax.reshape(-1).to(torch.int32).contiguous()), ptr(layer.weight_mul),
+                 ptr(layer.weight_shift), ptr(out), ptr(zero_workspace(x8.device, m, n)), m, n, x8.shape[1], stream())
+        else:
+            out = int8_gemm_q15(x8, None, None, layer.weight, layer.weight_mul, layer.weight_shift, x_absmax=absmax.reshape(-1))
         if bias is not None:
             out = self._add_bias(out, bias)
         return out
+
+    def apply_pending(self, layer, codes: torch.Tensor, absmax: torch.Tensor) -> PendingLinear:
+        """apply_quantised without the requantisation: the exact accumulators stay in a zero workspace and the next
+        row kernel (fused_add_rmsnorm_quant, qkv_rope_quant_store) finishes the linear while it loads them."""
+        if getattr(layer, "weight_mul", None) is None:
+            self.process_weights_after_loading(layer)
+        x8 = codes.reshape(-1, codes.shape[-1]).contiguous()
+        require_cuda(x8, layer.weight, absmax, layer.weight_mul, layer.weight_shift)
+        m, n = x8.shape[0], layer.weight.shape[0]
+        ws = zero_workspace(x8.device, m, n)
+        if m:
+            call("b200_gemm_w8a8_acc_ws", ptr(x8), ptr(layer.weight.contiguous()), ptr(ws), m, n, x8.shape[1], stream())
+        return PendingLinear(ws, absmax.reshape(-1).to(torch.int32).contiguous(), layer.weight_mul, layer.weight_shift)
 
     @staticmethod
     def _add_bias(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:

@@ -163,7 +163,7 @@ class Qwen3ModelInteger:
             x = self.comm.all_reduce(x)
         residual = None
         for layer in self.layers:
-            x, residual = layer.forward_q15(x, residual, batch)
+            x, residual = layer.forward_q15(x, residual, batch, defer_down=True)
         codes, _, absmax, _, _ = fp.fused_add_rmsnorm_quant(x, residual, self.w["final_norm"])
         return codes, absmax
 

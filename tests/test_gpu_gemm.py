@@ -75,6 +75,13 @@ def test_decode_sizes_without_accumulator_output(M, N, K):
         np.testing.assert_array_equal(out.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 24576, 4096), (200, 19208, 2048), (129, 132, 512), (256, 256, 8192), (177, 6144, 4096)])
+def test_pair_weights_stationary_tiles(M, N, K):
+    """129..256 tokens run on CTA pairs over blocks of 256 weight rows with half of the tokens staged per CTA: unsplit
+    waves followed by a split tail, a ragged last block, a single block with the deepest split, both outputs."""
+    run_case(M, N, K, M + N + K, per_channel_shift=True)
+
+
 @pytest.mark.parametrize("M,N,K", [(300, 512, 1024), (64, 1024, 2048), (256, 20000, 256)])
 def test_token_scale_from_absmax(M, N, K):
     """The entry point that takes the row kernels' integer absmax derives the same (multiplier, shift)."""

@@ -56,6 +56,23 @@ def _run_case(seed, kv_lens, q_lens, decode, hq, hk, hid, inter, num_pages, wide
     layer2 = Qwen3DecoderLayerInteger(1, hq, hk, hid, inter, device_layer_weights(w), d(cache), pool2)
     fx, fres = layer2.forward_q15(d(x), d(res), batch)
     _same("x_out (fused path)", fx, want_x); _same("residual_out (fused path)", fres, want_res)
+    _same("pool.k (fused path)", pool2.k_cache(1), ref_pool.k_codes); _same("pool.v (fused path)", pool2.v_cache(1), ref_pool.v_codes)
+    _same("pool.meta (fused path)", pool2.meta(1), ref_pool.meta)
+    # the down projection handed over pending: the next add + RMSNorm + quant finishes it, and so does materialise()
+    from mini_sgl_integer_b200.kernel import fixed_point as fp
+    from mini_sgl_integer_b200.kernel.pending import PendingLinear, _workspaces
+    px, pres = layer2.forward_q15(d(x), d(res), batch, defer_down=True)
+    if T <= 256:
+        assert isinstance(px, PendingLinear)
+        got = fp.fused_add_rmsnorm_quant(px, pres, d(w["input_norm"]), want_norm=True)
+        want = fp.fused_add_rmsnorm_quant(d(want_x), d(want_res), d(w["input_norm"]), want_norm=True)
+        for name, g, wv in zip(("codes", "scale", "absmax", "residual", "norm"), got, want):
+            assert torch.equal(g, wv), f"pending down -> norm: {name}"
+        px, _ = layer2.forward_q15(d(x), d(res), batch, defer_down=True)
+        _same("x_out (materialised)", px.materialise(), want_x)
+        assert all(int(b.abs().max()) == 0 for b in _workspaces.values())        # every workspace is zero again
+    else:
+        _same("x_out (defer_down at a size that is not deferred)", px, want_x)
     assert np.abs(want_x).max() > 0 and np.abs(wt["attn"]).max() > 0
     assert np.abs(want_x).max() < 2**31 - 1           # the case exercises the arithmetic, not the saturation rails
 

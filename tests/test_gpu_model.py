@@ -73,15 +73,29 @@ def test_decode_prepare_advances_on_device():
 
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_prefill_then_greedy_decode_matches_oracle(use_graph):
+    _prefill_then_decode(use_graph, (L, HID, HQ, HK, INTER, VOCAB), [5, 17, 32], 4, wide=False)
+
+
+def test_prefill_then_greedy_decode_8b_shaped_layers():
+    """Two layers of the Qwen3-8B shape (hidden 4096, 32 q / 8 kv heads, intermediate 12288) under a small vocabulary:
+    prefill of three short prompts and two greedy decode steps, token ids, logits and pools against the oracle."""
+    _prefill_then_decode(False, (2, 4096, 32, 8, 12288, 2048), [3, 9, 5], 2, wide=True)
+
+
+def _prefill_then_decode(use_graph, shape, prompt_lens, steps, wide):
     from mini_sgl_integer_b200.attention import Int8PagedKVCache
     from mini_sgl_integer_b200.layers.decoder_layer import AttnBatch
     from mini_sgl_integer_b200.models import DecodeBatch, Qwen3ForCausalLMInteger, Qwen3IntegerConfig, random_weights, rope_cache_q15
+    L, HID, HQ, HK, INTER, VOCAB = shape
     cfg = Qwen3IntegerConfig(L, HID, HQ, HK, INTER, VOCAB, max_pos=128)
     w = random_weights(cfg, seed=11)
+    if wide:       # channel shifts that keep the activations of a hidden size of several thousand inside Q15.16
+        for lw in w["layers"]:
+            lw["qkv"].weight_shift += 1; lw["o"].weight_shift += 1
+            lw["gate_up"].weight_shift += 2; lw["down"].weight_shift += 2
     hw = host_weights(w)
     rng = np.random.default_rng(5)
-    prompt_lens = [5, 17, 32]
-    steps, P, max_len = 4, 16, 64
+    P, max_len = 16, 64
     B = len(prompt_lens)
     perm = rng.permutation(P)
     pitch = max_len // 16
@@ -150,3 +164,4 @@ def test_prefill_then_greedy_decode_matches_oracle(use_graph):
     for i in range(L):
         np.testing.assert_array_equal(pool.k_cache(i).cpu().numpy(), pools[i].k_codes)
         np.testing.assert_array_equal(pool.meta(i).cpu().numpy(), pools[i].meta)
+    assert 0 < np.abs(want_logits[-1]).max() < 2**31 - 1          # the case exercises the arithmetic, not the rails
