@@ -395,6 +395,17 @@ def build_parity_case(dev, comm, exch, full_layer0, cache, rank, world):
     for _ in range(3):                                       # three rounds: both halves of the exchange blocks
         got, got_res = tp.forward_q15(x, res, batch)
         ok = ok and bool(torch.equal(got, want)) and bool(torch.equal(got_res, want_res))
+    # the form the model step uses: codes in, codes out, every row finished and normalised by its owner
+    from mini_sgl_integer_b200.kernel import fixed_point as fp
+    next_w = full_layer0["post_norm"]                        # any norm weight will do for the norm after the layer
+    w_codes, _, w_absmax, w_res3, _ = fp.fused_add_rmsnorm_quant(want, want_res, next_w)
+    in_codes, _, in_absmax, res1, _ = fp.fused_add_rmsnorm_quant(x, res, full_layer0["input_norm"])
+    own = exch.owner_rows(T)
+    for _ in range(3):
+        resid = res1.clone()
+        g_codes, g_absmax = tp.forward_codes(in_codes, in_absmax.reshape(-1), resid, batch, next_w)
+        ok = ok and bool(torch.equal(g_codes, w_codes)) and bool(torch.equal(g_absmax, w_absmax.reshape(-1)))
+        ok = ok and bool(torch.equal(resid[own], w_res3[own]))
     return ok and int(want.abs().max()) > 0
 
 
@@ -625,7 +636,14 @@ def tp32b_layer(dev, comm, rank, world, args):
     g = torch.Generator(device=dev).manual_seed(13)
     x = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
     res = (torch.randn(B, HID, device=dev, generator=g) * 4096.0).round().to(torch.int32)
-    run = lambda: layer.forward_q15(x, res, batch)
+    if world > 1:
+        # the form the model step uses between two norms: codes in, codes out, rows finished by their owners
+        from mini_sgl_integer_b200.kernel import fixed_point as fp
+        codes_in, _, absmax_in, resid, _ = fp.fused_add_rmsnorm_quant(x, res, w["input_norm"])
+        absmax_in = absmax_in.reshape(-1)
+        run = lambda: layer.forward_codes(codes_in, absmax_in, resid, batch, w["input_norm"])
+    else:
+        run = lambda: layer.forward_q15(x, res, batch)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):

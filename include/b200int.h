@@ -418,6 +418,18 @@ B200_API int b200_tp_requant_scatter(const b200_tp_block* blk, const int32_t* ab
 B200_API int b200_tp_collect(const b200_tp_block* blk, int32_t* out_q15, int m, b200_stream_t s);
 B200_API int b200_tp_requant_direct(const b200_tp_block* blk, const int32_t* absmax, const int32_t* w_mul,
                                     const int32_t* w_shift, int32_t* out_q15, int m, b200_stream_t s);
+/* The row-split linear fused with the (residual add +) RMSNorm + per-token quantisation that follows it in the decoder
+ * layer (o_proj -> post_attention_layernorm, down_proj -> the next input_layernorm / the final norm;
+ * models/integer/qwen3_integer.py:62-80): after b200_gemm_w8a8_tp the rank that owns a token row (row / ceil(m / size))
+ * fetches the row's partial sums from every rank, requantises, adds `residual` (int32 [m, n], updated in place for the
+ * OWN rows only; nullable = no add), normalises with norm_weight, quantises, and stores the int8 codes and the absmax
+ * of the row into every rank's block.  b200_tp_collect_codes waits for all owners and copies codes int8 [m, n] and
+ * absmax int32 [m] out.  Same bits as b200_tp_requant_scatter + b200_tp_collect + b200_rmsnorm_q15 on every rank, with a
+ * quarter of the bytes exchanged and the norm computed once per row instead of once per rank.  n % 16 == 0. */
+B200_API int b200_tp_owner_norm(const b200_tp_block* blk, const int32_t* x_absmax, const int32_t* w_mul,
+                                const int32_t* w_shift, int32_t* residual, const int32_t* norm_weight, int m,
+                                b200_stream_t s);
+B200_API int b200_tp_collect_codes(const b200_tp_block* blk, int8_t* codes, int32_t* absmax, int m, b200_stream_t s);
 B200_API int b200_tp_all_gather(const b200_tp_block* blk, const int32_t* src, int words, int32_t* dst,
                                 b200_stream_t s);
 B200_API int b200_tp_status(int* out_host, int reset);        /* synchronises with the device */

@@ -13,6 +13,7 @@
 // Every wait gives up after a time limit (default 2 s), records the channel in a status word that the host
 // can read, and lets the kernel finish on whatever the block holds: a missing peer costs a wrong result and
 // an error code, never a hung GPU.
+#include "luts.cuh"
 #include "tp_block.cuh"
 
 namespace b200 {
@@ -270,6 +271,138 @@ tp_collect_kernel(const TpView v, int32_t* __restrict__ dst, int m, int n) {
     reinterpret_cast<int4*>(dst)[i] = __ldcg(src + i);
 }
 
+// ---------------------------------------------------------------------------- steps 4 + 5 fused with the following norm
+// The row-split linears of a decoder layer are each followed by (residual add +) RMSNorm + per-token quantisation,
+// and the next linears only need the int8 codes and the absmax of that.  So the rank that owns a token row does it
+// all: fetch the row's partial sums from every rank, requantise, add the residual (kept by the owner only: nobody
+// else needs that row's residual again as long as ownership does not move), normalise, quantise, and store the
+// CODES (a quarter of the Q15.16 bytes) and the absmax into every rank's `out` half.  Signals channel 3.
+// One CTA per owned row; the arithmetic is that of splitk_epilogue_kernel followed by rmsnorm_rows_kernel.
+__host__ __device__ inline int tp_owner_rows(int m, int size) { return (m + size - 1) / size; }
+__host__ __device__ inline int64_t tp_codes_absmax_off(int m_max, int64_t n) { return tp_align64((int64_t)m_max * n / 4); }
+
+template <int VPT>
+__global__ void __launch_bounds__(1024)
+tp_owner_norm_kernel(const TpView v, const int32_t* __restrict__ x_absmax, const int32_t* __restrict__ w_mul,
+                     const int32_t* __restrict__ w_shift, int32_t* __restrict__ residual, const int32_t* __restrict__ norm_w,
+                     int m, int n) {
+  __shared__ long long red64[33];
+  __shared__ int red32[33];
+  const TpLayout l = tp_layout(v.m_max, v.n);
+  int32_t* hdr = v.base[v.rank];
+  const int epoch = *reinterpret_cast<volatile int32_t*>(hdr + 1);
+  const int half = (epoch - 1) & 1;
+  tp_wait_flags(v, 1, epoch);
+  __syncthreads();
+  const int rpr = tp_owner_rows(m, v.size);
+  const int row0 = v.rank * rpr, rows = max(0, min(m, row0 + rpr) - row0);
+  const int64_t acc_off = l.acc + (int64_t)half * l.acc_half;
+  const int64_t out_off = l.out + (int64_t)half * l.acc_half;
+  {   // every peer has signalled this exchange, so it has finished reading the accumulator half of the previous one
+    int4* old = reinterpret_cast<int4*>(hdr + l.acc + (int64_t)(half ^ 1) * l.acc_half);
+    const int64_t vecs = (int64_t)v.m_max * (n >> 2);
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < vecs; i += (int64_t)gridDim.x * blockDim.x)
+      old[i] = make_int4(0, 0, 0, 0);
+  }
+  if ((int)blockIdx.x < rows) {
+    const int t = row0 + blockIdx.x;
+    const int nvec = n >> 2;
+    int xm, xs;
+    absmax_to_ms_dev(__ldg(x_absmax + t), &xm, &xs);
+    xs -= 48;
+    int4 val[VPT];
+    int mx = 0;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      int4 a = make_int4(0, 0, 0, 0);
+      if (idx < nvec) {
+        for (int src = 0; src < v.size; ++src) {
+          const int4 b = __ldcg(reinterpret_cast<const int4*>(v.base[src] + acc_off + (int64_t)t * n) + idx);
+          a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        const int4 wm = __ldg(reinterpret_cast<const int4*>(w_mul) + idx);
+        int4 ws = make_int4(31, 31, 31, 31);
+        if (w_shift) ws = __ldg(reinterpret_cast<const int4*>(w_shift) + idx);
+        a.x = tp_requant_one(a.x, __mulhi(xm, wm.x), xs + ws.x);
+        a.y = tp_requant_one(a.y, __mulhi(xm, wm.y), xs + ws.y);
+        a.z = tp_requant_one(a.z, __mulhi(xm, wm.z), xs + ws.z);
+        a.w = tp_requant_one(a.w, __mulhi(xm, wm.w), xs + ws.w);
+        if (residual) {
+          int4* rr = reinterpret_cast<int4*>(residual + (int64_t)t * n) + idx;
+          const int4 b = *rr;
+          a.x = (int)((unsigned)a.x + (unsigned)b.x);
+          a.y = (int)((unsigned)a.y + (unsigned)b.y);
+          a.z = (int)((unsigned)a.z + (unsigned)b.z);
+          a.w = (int)((unsigned)a.w + (unsigned)b.w);
+          *rr = a;
+        }
+      }
+      val[i] = a;
+      mx = max(max(mx, abs_wrap(a.x)), max(abs_wrap(a.y), max(abs_wrap(a.z), abs_wrap(a.w))));
+    }
+    mx = block_max(mx, red32);
+    const NormRow nr = norm_row_from_absmax(mx);
+    long long S = 0;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      S += (long long)norm_normalised_sq(val[i].x, nr.p) + (long long)norm_normalised_sq(val[i].y, nr.p) +
+           (long long)norm_normalised_sq(val[i].z, nr.p) + (long long)norm_normalised_sq(val[i].w, nr.p);
+    S = block_sum64(S, red64);
+    const int inv = norm_inv_sqrt(S, n, g_inv_sqrt_lut);
+    int m2 = 0;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      if (idx < nvec) {
+        const int4 ww = __ldg(reinterpret_cast<const int4*>(norm_w) + idx);
+        int4 o;
+        o.x = nr.zero ? 0 : norm_apply(val[i].x, inv, ww.x, nr.p);
+        o.y = nr.zero ? 0 : norm_apply(val[i].y, inv, ww.y, nr.p);
+        o.z = nr.zero ? 0 : norm_apply(val[i].z, inv, ww.z, nr.p);
+        o.w = nr.zero ? 0 : norm_apply(val[i].w, inv, ww.w, nr.p);
+        val[i] = o;
+        m2 = max(max(m2, abs_wrap(o.x)), max(abs_wrap(o.y), max(abs_wrap(o.z), abs_wrap(o.w))));
+      }
+    }
+    m2 = max(1, block_max(m2, red32));
+    const float mf = __int2float_rn(m2), my = __frcp_rn(mf);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      if (idx < nvec) {
+        const unsigned c4 = pack4(quant_code_fast(val[i].x, mf, my), quant_code_fast(val[i].y, mf, my),
+                                  quant_code_fast(val[i].z, mf, my), quant_code_fast(val[i].w, mf, my));
+        for (int d = 0; d < v.size; ++d)
+          reinterpret_cast<unsigned*>(v.base[d] + out_off)[(int64_t)t * nvec + idx] = c4;
+      }
+    }
+    if (threadIdx.x == 0) {
+      const int64_t ao = out_off + tp_codes_absmax_off(v.m_max, v.n) + t;
+      for (int d = 0; d < v.size; ++d) v.base[d][ao] = m2;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) tp_signal_if_last(v, 3, gridDim.x, (int)blockIdx.x < rows);
+}
+
+// Waits for every rank's channel-3 signal and copies the codes and the absmax of all m rows out of the block.
+__global__ void __launch_bounds__(256)
+tp_collect_codes_kernel(const TpView v, int8_t* __restrict__ codes, int32_t* __restrict__ absmax, int m, int n) {
+  const TpLayout l = tp_layout(v.m_max, v.n);
+  const int32_t* hdr = v.base[v.rank];
+  const int half = (*reinterpret_cast<const volatile int32_t*>(hdr + 1) - 1) & 1;
+  tp_wait_flags(v, 3, *reinterpret_cast<const volatile int32_t*>(hdr + 3));
+  __syncthreads();
+  const int32_t* out = hdr + l.out + (int64_t)half * l.acc_half;
+  const int64_t total = (int64_t)m * n / 16;                       // 16-byte vectors of codes
+  const int4* src = reinterpret_cast<const int4*>(out);
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    reinterpret_cast<int4*>(codes)[i] = __ldcg(src + i);
+  const int32_t* am = out + tp_codes_absmax_off(v.m_max, v.n);
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < m; i += gridDim.x * blockDim.x) absmax[i] = __ldcg(am + i);
+}
+
 // ---------------------------------------------------------------------------- small all-gather (channel 2)
 // One CTA: stores `words` int32 of src into slot [half][rank] of every rank's block, signals, waits for
 // every rank's signal and copies the `size` slots, in rank order, to dst [size][words].
@@ -413,6 +546,46 @@ extern "C" int b200_tp_collect(const b200_tp_block* blk, int32_t* out_q15, int m
   const int grid = (int)((vecs + 255) / 256 < 592 ? (vecs + 255) / 256 : 592);
   tp_collect_kernel<<<grid, 256, 0, (cudaStream_t)s>>>(v, out_q15, m, (int)v.n);
   return check_launch("tp_collect");
+}
+
+extern "C" int b200_tp_owner_norm(const b200_tp_block* blk, const int32_t* x_absmax, const int32_t* w_mul, const int32_t* w_shift,
+                                  int32_t* residual, const int32_t* norm_weight, int m, b200_stream_t s) {
+  TpView v;
+  int rc = view_of(blk, &v, "tp_owner_norm");
+  if (rc != B200_OK) return rc;
+  B200_REQUIRE(x_absmax && w_mul && norm_weight, B200_E_NULL, "tp_owner_norm: null pointer");
+  B200_REQUIRE(m > 0 && m <= v.m_max, B200_E_SHAPE, "tp_owner_norm: m=%d (1..%d)", m, v.m_max);
+  B200_REQUIRE(v.n % 16 == 0 && v.n <= 32768, B200_E_UNSUPPORTED, "tp_owner_norm: n=%lld must be a multiple of 16, at most 32768",
+               (long long)v.n);
+  B200_REQUIRE(aligned16(w_mul) && aligned16(w_shift) && aligned16(residual) && aligned16(norm_weight), B200_E_ALIGN,
+               "tp_owner_norm: w_mul, w_shift, residual and norm_weight must be 16-byte aligned");
+  const int nvec = (int)(v.n / 4);
+  int threads = ((nvec + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  const int vpt = (nvec + threads - 1) / threads;
+  const int grid = tp_owner_rows(m, v.size);
+  cudaStream_t st = (cudaStream_t)s;
+  switch (vpt) {
+    case 1: tp_owner_norm_kernel<1><<<grid, threads, 0, st>>>(v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
+    case 2: tp_owner_norm_kernel<2><<<grid, threads, 0, st>>>(v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
+    case 3: case 4: tp_owner_norm_kernel<4><<<grid, threads, 0, st>>>(v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
+    default: tp_owner_norm_kernel<8><<<grid, threads, 0, st>>>(v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
+  }
+  return check_launch("tp_owner_norm");
+}
+
+extern "C" int b200_tp_collect_codes(const b200_tp_block* blk, int8_t* codes, int32_t* absmax, int m, b200_stream_t s) {
+  TpView v;
+  int rc = view_of(blk, &v, "tp_collect_codes");
+  if (rc != B200_OK) return rc;
+  B200_REQUIRE(codes && absmax, B200_E_NULL, "tp_collect_codes: null pointer");
+  B200_REQUIRE(m > 0 && m <= v.m_max, B200_E_SHAPE, "tp_collect_codes: m=%d (1..%d)", m, v.m_max);
+  B200_REQUIRE(v.n % 16 == 0, B200_E_UNSUPPORTED, "tp_collect_codes: n=%lld must be a multiple of 16", (long long)v.n);
+  B200_REQUIRE(aligned16(codes), B200_E_ALIGN, "tp_collect_codes: codes must be 16-byte aligned");
+  const int64_t vecs = (int64_t)m * v.n / 16;
+  const int grid = (int)((vecs + 255) / 256 < 296 ? (vecs + 255) / 256 : 296);
+  tp_collect_codes_kernel<<<grid < 1 ? 1 : grid, 256, 0, (cudaStream_t)s>>>(v, codes, absmax, m, (int)v.n);
+  return check_launch("tp_collect_codes");
 }
 
 extern "C" int b200_tp_all_gather(const b200_tp_block* blk, const int32_t* src, int words, int32_t* dst,

@@ -77,6 +77,29 @@ class Qwen3DecoderLayerInteger:
         # no collective call in the layer (decode sizes; larger batches fall back to NCCL)
         self.exchange = exchange
 
+    def forward_codes(self, codes: torch.Tensor, absmax: torch.Tensor, residual: torch.Tensor, batch: AttnBatch,
+                      next_norm_weight: torch.Tensor):
+        """The layer between two norms, for tensor-parallel steps on an exchange block: takes the int8 codes and
+        absmax of ITS input norm (all token rows) and returns those of the NEXT norm (``next_norm_weight``: the next
+        layer's input_layernorm or the model's final norm).  Each row-split linear is finished, added to the
+        residual, normalised and quantised by the rank that owns the token row (``exchange.owner_rows``);
+        ``residual`` int32 [tokens, hidden] is updated in place for the own rows only.  Same bits as forward_q15
+        followed by the next layer's fused add + RMSNorm + quant."""
+        w, m, T = self.w, self.method, codes.shape[0]
+        qkv = m.apply_pending(w["qkv"], codes, absmax) if T <= PENDING_MAX_ROWS and _PENDING_ON else m.apply_quantised(w["qkv"], codes, absmax)
+        q8, q_mul, q_shift = qkv_rope_quant_store(batch.positions, qkv, self.hq, self.pool, self.layer_id, batch.out_loc,
+                                                  self.cache, w.get("q_norm"), w.get("k_norm"))
+        if batch.q_lens is None:
+            attn = decode_attention_int8_paged(q8, q_mul, q_shift, self.pool, self.layer_id, batch.page_table,
+                                               batch.kv_lens, batch.max_kv_len, row_order=batch.row_order)
+        else:
+            attn = extend_attention_int8_paged(q8, q_mul, q_shift, self.pool, self.layer_id, batch.page_table,
+                                               batch.kv_lens, batch.q_lens, batch.max_kv_len)
+        codes, absmax = self.exchange.row_parallel_norm_quant(m, w["o"], attn.view(T, self.hq * 128), residual, w["post_norm"])
+        gate_up = m.apply_quantised(w["gate_up"], codes, absmax)
+        act = fp.silu_mul_fwht_q15(gate_up, self.hadamard_block)
+        return self.exchange.row_parallel_norm_quant(m, w["down"], act, residual, next_norm_weight)
+
     def forward_q15(self, x_q15, residual_q15: Optional[torch.Tensor], batch: AttnBatch,
                     trace: Optional[dict] = None, defer_down: bool = False):
         """Returns (x_out, residual_out), both Q15.16 int32 [tokens, hidden].

@@ -19,6 +19,7 @@ contains no collective call at all and can be captured in a CUDA graph on every 
 from __future__ import annotations
 
 import ctypes
+from typing import Optional
 
 import torch
 
@@ -237,6 +238,40 @@ class TpExchange:
             return self.requant_direct(absmax, layer.weight_mul, layer.weight_shift)
         self.requant_scatter(absmax, layer.weight_mul, layer.weight_shift)
         return self.collect(x2.shape[0], x2.device)
+
+    # ---- the row-split linear fused with the add + RMSNorm + quant that follows it (row owners)
+    def owner_norm(self, absmax: torch.Tensor, w_mul: torch.Tensor, w_shift, residual, norm_weight: torch.Tensor) -> None:
+        call("b200_tp_owner_norm", self._p, ptr(absmax), ptr(w_mul), ptr(w_shift), ptr(residual), ptr(norm_weight),
+             absmax.shape[0], stream())
+
+    def collect_codes(self, m: int, device):
+        codes = torch.empty((m, self.n), dtype=torch.int8, device=device)
+        absmax = torch.empty(m, dtype=torch.int32, device=device)
+        call("b200_tp_collect_codes", self._p, ptr(codes), ptr(absmax), m, stream())
+        return codes, absmax
+
+    def owner_rows(self, m: int) -> slice:
+        """The token rows of an [m, n] matrix that this rank finishes (and whose residual it keeps)."""
+        rpr = (m + self.size - 1) // self.size
+        return slice(min(m, self.rank * rpr), min(m, (self.rank + 1) * rpr))
+
+    def row_parallel_norm_quant(self, method: W8A8Int8LinearMethod, layer, x_q15_local: torch.Tensor,
+                                residual: Optional[torch.Tensor], norm_weight: torch.Tensor):
+        """Row-split linear -> (+ residual) -> RMSNorm -> per-token int8 quant without a collective call.
+
+        ``residual`` int32 [rows, n] is updated in place for this rank's ``owner_rows`` only (the other rows go
+        stale: their owners keep them).  Returns (codes int8 [rows, n], absmax int32 [rows]) of ALL rows: the bits of
+        ``fused_add_rmsnorm_quant(row_parallel_q15(...), residual, norm_weight)`` computed on every rank."""
+        if getattr(layer, "weight_mul", None) is None:
+            method.process_weights_after_loading(layer)
+        x2 = self._rows(x_q15_local)
+        if residual is not None and (residual.dtype != torch.int32 or not residual.is_contiguous()
+                                     or tuple(residual.shape) != (x2.shape[0], self.n)):
+            raise ValueError("residual must be a contiguous int32 [rows, n] tensor (it is updated in place)")
+        codes, absmax = self.absmax_quant(x2)
+        self.gemm_add(codes, layer.weight)
+        self.owner_norm(absmax, layer.weight_mul, layer.weight_shift, residual, norm_weight.contiguous())
+        return self.collect_codes(x2.shape[0], x2.device)
 
     def all_gather(self, src: torch.Tensor) -> torch.Tensor:
         """int32 [words] from every rank -> int32 [size, words] (words <= 2 * m_max)."""

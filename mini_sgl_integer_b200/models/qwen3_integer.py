@@ -161,6 +161,17 @@ class Qwen3ModelInteger:
         x = embedding_to_fixed(self.w["embed"], input_ids, self.vocab_start)
         if self.comm.size > 1 and not self.embed_replicated:
             x = self.comm.all_reduce(x)
+        T = x.shape[0]
+        if self.exchange is not None and self.exchange.size > 1 and self.exchange.fits(T, self.cfg.hidden) and self.layers:
+            # tensor parallel on an exchange block: the rows of the residual stream have owners, and every row-split
+            # linear is finished together with the norm that follows it (Qwen3DecoderLayerInteger.forward_codes)
+            codes, _, absmax, _, _ = fp.fused_add_rmsnorm_quant(x, None, self.layers[0].w["input_norm"])
+            absmax = absmax.reshape(-1)
+            residual = x.contiguous()                       # layer 0's residual is its input; updated in place from here on
+            for i, layer in enumerate(self.layers):
+                nw = self.layers[i + 1].w["input_norm"] if i + 1 < len(self.layers) else self.w["final_norm"]
+                codes, absmax = layer.forward_codes(codes, absmax, residual, batch, nw)
+            return codes, absmax
         residual = None
         for layer in self.layers:
             x, residual = layer.forward_q15(x, residual, batch, defer_down=True)

@@ -70,6 +70,58 @@ def test_row_split_linear_over_exchange_blocks(size, m, n, k):
         assert int(acc[0].abs().max()) == 0 or int(acc[1].abs().max()) == 0
 
 
+@pytest.mark.parametrize("size", [1, 2, 4, 8])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (33, 1040, 1024), (256, 4096, 2048), (8, 5120, 8192), (5, 8192 + 64, 512)])
+def test_row_split_linear_finished_and_normalised_by_row_owners(size, m, n, k):
+    """The row-split linear fused with the residual add + RMSNorm + quant that follows it: every token row is finished
+    by one owner rank, all ranks receive the codes and the absmax of all rows (the oracle's bits), and an owner's
+    residual rows are updated in place.  Three rounds reuse and clear both halves of the blocks."""
+    from mini_sgl_integer_b200.layers.tp_linear import TpExchange
+    x, w8, wm, ws, lin = _case(size * 77 + m, m, n, k)
+    rng = np.random.default_rng(n + size)
+    res = np.clip(np.rint(rng.normal(0, 2**15, (m, n))), -(2**23), 2**23).astype(np.int32)
+    nw = rng.integers(2**11, 2**15, n).astype(np.int32)
+    norm, summed = ofp.fused_add_rmsnorm_v2(res, lin, nw)
+    want_codes, _, want_absmax = ofp.per_token_quant_from_q15(norm)
+    ks = k // size
+    ranks = TpExchange.emulated(size, 256, n)
+    xs_ = [d(x[:, r * ks:(r + 1) * ks]) for r in range(size)]
+    w_ = [d(w8[:, r * ks:(r + 1) * ks]) for r in range(size)]
+    wm_d, ws_d, nw_d = d(wm), d(ws), d(nw)
+    for rnd in range(3):
+        resid = [d(res) for _ in range(size)]
+        for r in range(size):
+            ranks[r].absmax_put(xs_[r])
+        q = [ranks[r].quant_wait(xs_[r]) for r in range(size)]
+        for r in range(size):
+            ranks[r].gemm_add(q[r][0], w_[r])
+        for r in range(size):
+            ranks[r].owner_norm(q[r][1], wm_d, ws_d, resid[r], nw_d)
+        for r in range(size):
+            codes, absmax = ranks[r].collect_codes(m, "cuda")
+            np.testing.assert_array_equal(codes.cpu().numpy(), want_codes, err_msg=f"codes, round {rnd}, rank {r}")
+            np.testing.assert_array_equal(absmax.cpu().numpy(), want_absmax.reshape(-1), err_msg=f"absmax, round {rnd}, rank {r}")
+            own = ranks[r].owner_rows(m)
+            np.testing.assert_array_equal(resid[r][own].cpu().numpy(), summed[own], err_msg=f"residual, round {rnd}, rank {r}")
+            other = np.ones(m, bool); other[own] = False
+            np.testing.assert_array_equal(resid[r].cpu().numpy()[other], res[other])       # the other rows are not touched
+    assert TpExchange.status() == 0
+    # without a residual: the norm of the linear's output alone
+    norm0 = ofp.rmsnorm_v2(lin, nw)
+    c0, _, a0 = ofp.per_token_quant_from_q15(norm0)
+    for r in range(size):
+        ranks[r].absmax_put(xs_[r])
+    q = [ranks[r].quant_wait(xs_[r]) for r in range(size)]
+    for r in range(size):
+        ranks[r].gemm_add(q[r][0], w_[r])
+    for r in range(size):
+        ranks[r].owner_norm(q[r][1], wm_d, ws_d, None, nw_d)
+    codes, absmax = ranks[size - 1].collect_codes(m, "cuda")
+    np.testing.assert_array_equal(codes.cpu().numpy(), c0)
+    np.testing.assert_array_equal(absmax.cpu().numpy(), a0.reshape(-1))
+    assert TpExchange.status() == 0
+
+
 def test_single_rank_exchange_equals_the_plain_linear():
     """size 1 through the calls the layers make (absmax + quant in one launch): the plain linear's bits."""
     from mini_sgl_integer_b200.layers.decoder_layer import _Linear
