@@ -63,8 +63,9 @@ __device__ __forceinline__ int pf_exp(int score, int row_max) {
   return __ldg(&g_exp2_attn_lut[((unsigned)prod) >> 22]) >> min(31, 13 - (int)(prod >> 32));
 }
 
-template <int G>
-__global__ void __launch_bounds__(kPfThreads, 1)
+// kMinBlocks: CTAs per SM the register budget is cut for.
+template <int G, int kMinBlocks = 1>
+__global__ void __launch_bounds__(kPfThreads, kMinBlocks)
 attn_prefill_kernel(const PrefillParams p) {
   constexpr int TQ = kPfRows / G;                    // new tokens per tile
   const int b = blockIdx.z, kh = blockIdx.y;
@@ -360,12 +361,29 @@ static int launch_prefill(const PrefillParams& p, int batch, int max_q_len, cuda
     set_error("attn_prefill: max_kv_len=%d needs %zu bytes of shared memory for the page list", p.max_kv_len, smem);
     return B200_E_UNSUPPORTED;
   }
+  // Two CTAs per SM (a budget of 128 registers, some spilled) while the page list leaves room: the kernel waits on
+  // dependent integer arithmetic, and four warps per scheduler hide more of it than two (1.73 -> 1.58 ms on 16
+  // prompts of U[100,1024] tokens).  B200_PREFILL_OCC2=0 keeps one CTA of 250 registers per SM.
+  static int occ2 = -1;
+  if (occ2 < 0) {
+    const char* ev = getenv("B200_PREFILL_OCC2");
+    occ2 = (ev && ev[0] == '0') ? 0 : 1;
+  }
+  const int tiles = (max_q_len + TQ - 1) / TQ;
+  if (occ2 == 1 && smem <= 100 * 1024) {
+    cudaError_t e2 = cudaFuncSetAttribute(attn_prefill_kernel<G, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e2 != cudaSuccess) {
+      set_error("attn_prefill: cudaFuncSetAttribute: %s", cudaGetErrorString(e2));
+      return B200_E_CUDA;
+    }
+    attn_prefill_kernel<G, 2><<<dim3(tiles, p.kv_heads, batch), kPfThreads, smem, st>>>(p);
+    return check_launch("attn_prefill");
+  }
   cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_error("attn_prefill: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return B200_E_CUDA;
   }
-  const int tiles = (max_q_len + TQ - 1) / TQ;
   attn_prefill_kernel<G><<<dim3(tiles, p.kv_heads, batch), kPfThreads, smem, st>>>(p);
   return check_launch("attn_prefill");
 }
