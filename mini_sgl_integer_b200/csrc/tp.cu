@@ -83,6 +83,8 @@ __device__ __forceinline__ int tp_row_agree(const TpView& v, int32_t* words) {
 // One CTA per token row of this rank's slice x [rows, k] (row pitch in elements): delivers the row's absmax.
 __global__ void __launch_bounds__(256)
 tp_absmax_put_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pitch, int k) {
+  pdl_launch_dependents();
+  pdl_wait();          // what this kernel reads comes from the kernels before it (and from the peers, see below)
   __shared__ int red32[33];
   const TpLayout l = tp_layout(v.m_max, v.n);
   const int half = *reinterpret_cast<volatile int32_t*>(v.base[v.rank] + 4) & 1;
@@ -97,6 +99,8 @@ tp_absmax_put_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pitc
 __global__ void __launch_bounds__(256)
 tp_quant_wait_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pitch, int k,
                      int8_t* __restrict__ codes, int32_t* __restrict__ absmax_out) {
+  pdl_launch_dependents();
+  pdl_wait();          // what this kernel reads comes from the kernels before it (and from the peers, see below)
   __shared__ int agreed;
   const TpLayout l = tp_layout(v.m_max, v.n);
   int32_t* hdr = v.base[v.rank];
@@ -124,6 +128,8 @@ tp_quant_wait_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pitc
 __global__ void __launch_bounds__(256)
 tp_absmax_quant_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pitch, int k,
                        int8_t* __restrict__ codes, int32_t* __restrict__ absmax_out) {
+  pdl_launch_dependents();
+  pdl_wait();          // what this kernel reads comes from the kernels before it (and from the peers, see below)
   __shared__ int red32[33];
   __shared__ int agreed;
   const TpLayout l = tp_layout(v.m_max, v.n);
@@ -188,6 +194,8 @@ template <bool DIRECT>
 __global__ void __launch_bounds__(256)
 tp_requant_scatter_kernel(const TpView v, const int32_t* __restrict__ absmax, const int32_t* __restrict__ w_mul,
                           const int32_t* __restrict__ w_shift, int32_t* __restrict__ dst, int m, int n) {
+  pdl_launch_dependents();
+  pdl_wait();          // what this kernel reads comes from the kernels before it (and from the peers, see below)
   const TpLayout l = tp_layout(v.m_max, v.n);
   int32_t* hdr = v.base[v.rank];
   const int epoch = *reinterpret_cast<volatile int32_t*>(hdr + 1);
@@ -260,6 +268,8 @@ tp_requant_scatter_kernel(const TpView v, const int32_t* __restrict__ absmax, co
 // Waits for every rank's channel-3 signal and copies out[half] (all m rows) to the caller's tensor.
 __global__ void __launch_bounds__(256)
 tp_collect_kernel(const TpView v, int32_t* __restrict__ dst, int m, int n) {
+  pdl_launch_dependents();
+  pdl_wait();          // what this kernel reads comes from the kernels before it (and from the peers, see below)
   const TpLayout l = tp_layout(v.m_max, v.n);
   const int32_t* hdr = v.base[v.rank];
   const int half = (*reinterpret_cast<const volatile int32_t*>(hdr + 1) - 1) & 1;
@@ -286,6 +296,8 @@ __global__ void __launch_bounds__(1024)
 tp_owner_norm_kernel(const TpView v, const int32_t* __restrict__ x_absmax, const int32_t* __restrict__ w_mul,
                      const int32_t* __restrict__ w_shift, int32_t* __restrict__ residual, const int32_t* __restrict__ norm_w,
                      int m, int n) {
+  pdl_launch_dependents();
+  pdl_wait();          // what this kernel reads comes from the kernels before it (and from the peers, see below)
   __shared__ long long red64[33];
   __shared__ int red32[33];
   const TpLayout l = tp_layout(v.m_max, v.n);
@@ -389,6 +401,8 @@ tp_owner_norm_kernel(const TpView v, const int32_t* __restrict__ x_absmax, const
 // Waits for every rank's channel-3 signal and copies the codes and the absmax of all m rows out of the block.
 __global__ void __launch_bounds__(256)
 tp_collect_codes_kernel(const TpView v, int8_t* __restrict__ codes, int32_t* __restrict__ absmax, int m, int n) {
+  pdl_launch_dependents();
+  pdl_wait();          // what this kernel reads comes from the kernels before it (and from the peers, see below)
   const TpLayout l = tp_layout(v.m_max, v.n);
   const int32_t* hdr = v.base[v.rank];
   const int half = (*reinterpret_cast<const volatile int32_t*>(hdr + 1) - 1) & 1;
@@ -408,6 +422,8 @@ tp_collect_codes_kernel(const TpView v, int8_t* __restrict__ codes, int32_t* __r
 // every rank's signal and copies the `size` slots, in rank order, to dst [size][words].
 __global__ void __launch_bounds__(256)
 tp_gather_kernel(const TpView v, const int32_t* __restrict__ src, int words, int32_t* __restrict__ dst) {
+  pdl_launch_dependents();
+  pdl_wait();          // what this kernel reads comes from the kernels before it (and from the peers, see below)
   const TpLayout l = tp_layout(v.m_max, v.n);
   int32_t* hdr = v.base[v.rank];
   const int e0 = *reinterpret_cast<volatile int32_t*>(hdr + 2);
@@ -468,7 +484,7 @@ extern "C" int b200_tp_absmax_put(const b200_tp_block* blk, const int32_t* x, in
   B200_REQUIRE(rows > 0 && rows <= v.m_max && k > 0 && k % 4 == 0 && pitch >= k && pitch % 4 == 0, B200_E_SHAPE,
                "tp_absmax_put: rows=%d (1..%d) k=%d pitch=%lld", rows, v.m_max, k, (long long)pitch);
   B200_REQUIRE(aligned16(x), B200_E_ALIGN, "tp_absmax_put: x must be 16-byte aligned");
-  tp_absmax_put_kernel<<<rows, 256, 0, (cudaStream_t)s>>>(v, x, pitch, k);
+  launch_pdl(tp_absmax_put_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)s, v, x, pitch, k);
   return check_launch("tp_absmax_put");
 }
 
@@ -482,7 +498,7 @@ extern "C" int b200_tp_quant_wait(const b200_tp_block* blk, const int32_t* x, in
                "tp_quant_wait: rows=%d (1..%d) k=%d pitch=%lld", rows, v.m_max, k, (long long)pitch);
   B200_REQUIRE(aligned16(x) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0, B200_E_ALIGN,
                "tp_quant_wait: x must be 16-byte aligned, codes 4-byte");
-  tp_quant_wait_kernel<<<rows, 256, 0, (cudaStream_t)s>>>(v, x, pitch, k, codes, absmax_out);
+  launch_pdl(tp_quant_wait_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)s, v, x, pitch, k, codes, absmax_out);
   return check_launch("tp_quant_wait");
 }
 
@@ -498,7 +514,7 @@ extern "C" int b200_tp_absmax_quant(const b200_tp_block* blk, const int32_t* x, 
   B200_REQUIRE(rows <= 512, B200_E_UNSUPPORTED, "tp_absmax_quant: rows=%d (at most 512; use tp_absmax_put + tp_quant_wait beyond)", rows);
   B200_REQUIRE(aligned16(x) && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0, B200_E_ALIGN,
                "tp_absmax_quant: x must be 16-byte aligned, codes 4-byte");
-  tp_absmax_quant_kernel<<<rows, 256, 0, (cudaStream_t)s>>>(v, x, pitch, k, codes, absmax_out);
+  launch_pdl(tp_absmax_quant_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)s, v, x, pitch, k, codes, absmax_out);
   return check_launch("tp_absmax_quant");
 }
 
@@ -514,7 +530,7 @@ extern "C" int b200_tp_requant_scatter(const b200_tp_block* blk, const int32_t* 
   // few CTAs: each ends with a system-scope fence, and many of those at once are slow
   const int64_t vecs = (int64_t)tp_rows_per_rank(m, v.size) * (v.n / 4);
   const int grid = (int)((vecs + 1023) / 1024 < 148 ? (vecs + 1023) / 1024 : 148);
-  tp_requant_scatter_kernel<false><<<grid < 1 ? 1 : grid, 256, 0, (cudaStream_t)s>>>(v, absmax, w_mul, w_shift, nullptr, m, (int)v.n);
+  launch_pdl(tp_requant_scatter_kernel<false>, dim3(grid < 1 ? 1 : grid), dim3(256), 0, (cudaStream_t)s, v, absmax, w_mul, w_shift, (int32_t*)nullptr, m, (int)v.n);
   return check_launch("tp_requant_scatter");
 }
 
@@ -530,7 +546,7 @@ extern "C" int b200_tp_requant_direct(const b200_tp_block* blk, const int32_t* a
                "tp_requant_direct: w_mul, w_shift and out must be 16-byte aligned");
   const int64_t vecs = (int64_t)m * (v.n / 4);
   const int grid = (int)((vecs + 1023) / 1024 < 592 ? (vecs + 1023) / 1024 : 592);
-  tp_requant_scatter_kernel<true><<<grid < 1 ? 1 : grid, 256, 0, (cudaStream_t)s>>>(v, absmax, w_mul, w_shift, out_q15, m, (int)v.n);
+  launch_pdl(tp_requant_scatter_kernel<true>, dim3(grid < 1 ? 1 : grid), dim3(256), 0, (cudaStream_t)s, v, absmax, w_mul, w_shift, out_q15, m, (int)v.n);
   return check_launch("tp_requant_direct");
 }
 
@@ -544,7 +560,7 @@ extern "C" int b200_tp_collect(const b200_tp_block* blk, int32_t* out_q15, int m
   B200_REQUIRE(aligned16(out_q15), B200_E_ALIGN, "tp_collect: out must be 16-byte aligned");
   const int64_t vecs = (int64_t)m * (v.n / 4);
   const int grid = (int)((vecs + 255) / 256 < 592 ? (vecs + 255) / 256 : 592);
-  tp_collect_kernel<<<grid, 256, 0, (cudaStream_t)s>>>(v, out_q15, m, (int)v.n);
+  launch_pdl(tp_collect_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)s, v, out_q15, m, (int)v.n);
   return check_launch("tp_collect");
 }
 
@@ -566,10 +582,10 @@ extern "C" int b200_tp_owner_norm(const b200_tp_block* blk, const int32_t* x_abs
   const int grid = tp_owner_rows(m, v.size);
   cudaStream_t st = (cudaStream_t)s;
   switch (vpt) {
-    case 1: tp_owner_norm_kernel<1><<<grid, threads, 0, st>>>(v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
-    case 2: tp_owner_norm_kernel<2><<<grid, threads, 0, st>>>(v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
-    case 3: case 4: tp_owner_norm_kernel<4><<<grid, threads, 0, st>>>(v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
-    default: tp_owner_norm_kernel<8><<<grid, threads, 0, st>>>(v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
+    case 1: launch_pdl(tp_owner_norm_kernel<1>, dim3(grid), dim3(threads), 0, st, v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
+    case 2: launch_pdl(tp_owner_norm_kernel<2>, dim3(grid), dim3(threads), 0, st, v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
+    case 3: case 4: launch_pdl(tp_owner_norm_kernel<4>, dim3(grid), dim3(threads), 0, st, v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
+    default: launch_pdl(tp_owner_norm_kernel<8>, dim3(grid), dim3(threads), 0, st, v, x_absmax, w_mul, w_shift, residual, norm_weight, m, (int)v.n); break;
   }
   return check_launch("tp_owner_norm");
 }
@@ -584,7 +600,7 @@ extern "C" int b200_tp_collect_codes(const b200_tp_block* blk, int8_t* codes, in
   B200_REQUIRE(aligned16(codes), B200_E_ALIGN, "tp_collect_codes: codes must be 16-byte aligned");
   const int64_t vecs = (int64_t)m * v.n / 16;
   const int grid = (int)((vecs + 255) / 256 < 296 ? (vecs + 255) / 256 : 296);
-  tp_collect_codes_kernel<<<grid < 1 ? 1 : grid, 256, 0, (cudaStream_t)s>>>(v, codes, absmax, m, (int)v.n);
+  launch_pdl(tp_collect_codes_kernel, dim3(grid < 1 ? 1 : grid), dim3(256), 0, (cudaStream_t)s, v, codes, absmax, m, (int)v.n);
   return check_launch("tp_collect_codes");
 }
 
@@ -595,7 +611,7 @@ extern "C" int b200_tp_all_gather(const b200_tp_block* blk, const int32_t* src, 
   if (rc != B200_OK) return rc;
   B200_REQUIRE(src && dst, B200_E_NULL, "tp_all_gather: null pointer");
   B200_REQUIRE(words > 0 && words <= 2 * v.m_max, B200_E_SHAPE, "tp_all_gather: words=%d (1..%d)", words, 2 * v.m_max);
-  tp_gather_kernel<<<1, 256, 0, (cudaStream_t)s>>>(v, src, words, dst);
+  launch_pdl(tp_gather_kernel, dim3(1), dim3(256), 0, (cudaStream_t)s, v, src, words, dst);
   return check_launch("tp_all_gather");
 }
 
