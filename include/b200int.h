@@ -429,6 +429,12 @@ B200_API int b200_tp_requant_direct(const b200_tp_block* blk, const int32_t* abs
 B200_API int b200_tp_owner_norm(const b200_tp_block* blk, const int32_t* x_absmax, const int32_t* w_mul,
                                 const int32_t* w_shift, int32_t* residual, const int32_t* norm_weight, int m,
                                 b200_stream_t s);
+/* SiLU(gate) * up + blocked Walsh-Hadamard rotation of this rank's columns fused with the absmax agreement and the
+ * quantisation of b200_tp_absmax_quant: what GatedMLPInteger does between gate_up_proj and down_proj
+ * (models/utils_integer.py:99-121) when down_proj is row-split.  gate_up int32 [rows, 2 * inter] (this rank's gate |
+ * up columns), codes int8 [rows, inter], absmax int32 [rows] (the agreed value).  rows <= 256, inter % 128 == 0. */
+B200_API int b200_tp_silu_absmax_quant(const b200_tp_block* blk, const int32_t* gate_up, int8_t* codes, int32_t* absmax,
+                                       int rows, int inter, int fwht_block, b200_stream_t s);
 B200_API int b200_tp_collect_codes(const b200_tp_block* blk, int8_t* codes, int32_t* absmax, int m, b200_stream_t s);
 B200_API int b200_tp_all_gather(const b200_tp_block* blk, const int32_t* src, int words, int32_t* dst,
                                 b200_stream_t s);

@@ -67,6 +67,7 @@ SIGNATURES: dict[str, list] = {
     "b200_tp_all_gather": [P, P, I, P, P],
     "b200_tp_owner_norm": [P, P, P, P, P, P, I, P],
     "b200_tp_collect_codes": [P, P, P, I, P],
+    "b200_tp_silu_absmax_quant": [P, P, P, P, I, I, I, P],
     "b200_tp_status": [P, I],
     "b200_tp_set_timeout_us": [L],
 }

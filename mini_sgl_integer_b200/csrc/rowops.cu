@@ -9,6 +9,7 @@
 #include "common.cuh"
 #include "luts.cuh"
 #include "rope.cuh"
+#include "tp_block.cuh"
 
 namespace b200 {
 
@@ -419,13 +420,17 @@ __device__ __forceinline__ void fwht128_group_nosat(int (&val)[16], int lane8) {
 // the whole row are parked in shared memory until the row's absmax is known, then quantised from there: gate
 // and up are read from HBM once.  TABLE: the sigmoid term comes from the 38 KB direct table instead of the exp2
 // table, a shift and an exact division (used whenever the row buffer leaves room for it).
-template <bool FWHT, bool QUANT, bool TABLE>
+// TP: the row is this rank's slice of a token whose absmax spans all ranks' columns (the input of a row-split
+// linear): between the two phases the CTA takes part in the absmax agreement over the exchange blocks (one CTA per
+// row, all of them resident), quantises with the agreed value and reports it; `scale` is not written.
+template <bool FWHT, bool QUANT, bool TABLE, bool TP = false>
 __global__ void __launch_bounds__(512, 2)
 silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_out,
                  int8_t* __restrict__ codes, float* __restrict__ scale,
-                 int32_t* __restrict__ absmax, int64_t rows, int I) {
+                 int32_t* __restrict__ absmax, int64_t rows, int I, const TpAgree agree) {
   extern __shared__ __align__(16) int32_t rowbuf[];   // QUANT: [I] results of the row; then the table
   __shared__ int red32[33];
+  __shared__ int agree_slot;
   int32_t* lut = rowbuf + (QUANT ? I : 0);
   const uint16_t* sneg_tab = reinterpret_cast<const uint16_t*>(lut);
   pdl_launch_dependents();
@@ -501,6 +506,7 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   }
   if (!QUANT) continue;
   m = max(1, block_max(m, red32));     // its barriers also order the rowbuf writes before the reads
+  if (TP) m = tp_agree_cta(agree, (int)row, m, &agree_slot);
   const float mf = __int2float_rn(m);
   const float my = __frcp_rn(mf);
   unsigned* co = reinterpret_cast<unsigned*>(codes + row * (int64_t)I);
@@ -518,7 +524,7 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
     }
   }
   if (threadIdx.x == 0) {
-    scale[row] = quant_scale(mf);
+    if (!TP) scale[row] = quant_scale(mf);
     absmax[row] = m;
   }
   __syncthreads();                     // the row buffer and the reduction scratch are reused by the next row
@@ -786,7 +792,7 @@ static int launch_silu(const int32_t* gu, int32_t* q15, int8_t* codes, float* sc
       set_error("silu_mul_q15: cudaFuncSetAttribute: %s", cudaGetErrorString(e));                          \
       return B200_E_CUDA;                                                                                  \
     }                                                                                                      \
-    launch_pdl(silu_rows_kernel<F, Q, T>, dim3(grid), dim3(threads), smem, st, gu, q15, codes, scale, absmax, rows, inter);    \
+    launch_pdl(silu_rows_kernel<F, Q, T>, dim3(grid), dim3(threads), smem, st, gu, q15, codes, scale, absmax, rows, inter, TpAgree{});    \
   } while (0)
 #define B200_SILU_LAUNCH_T(F, Q) do { if (table) B200_SILU_LAUNCH(F, Q, true); else B200_SILU_LAUNCH(F, Q, false); } while (0)
   if (fwht && quant) B200_SILU_LAUNCH_T(true, true);
@@ -823,6 +829,45 @@ extern "C" int b200_silu_mul_q15(const int32_t* gate_up, int32_t* q15_out, int8_
     return check_launch("silu_mul_q15");
   }
   return launch_silu(gate_up, q15_out, codes, scale, absmax, rows, inter, fwht_block == 128, st);
+}
+
+extern "C" int b200_tp_silu_absmax_quant(const b200_tp_block* blk, const int32_t* gate_up, int8_t* codes, int32_t* absmax,
+                                         int rows, int inter, int fwht_block, b200_stream_t s) {
+  TpAgree agree;
+  int rc = tp_agree_of(blk, &agree, "tp_silu_absmax_quant");
+  if (rc != B200_OK) return rc;
+  B200_REQUIRE(gate_up && codes && absmax, B200_E_NULL, "tp_silu_absmax_quant: null pointer");
+  // one CTA per row, and every rank's CTA of a row waits for its peers' CTAs of that row: all must be resident
+  B200_REQUIRE(rows > 0 && rows <= agree.m_max && rows <= 256, B200_E_SHAPE, "tp_silu_absmax_quant: rows=%d (1..%d, at most 256)",
+               rows, agree.m_max);
+  B200_REQUIRE(fwht_block == 0 || fwht_block == 128, B200_E_UNSUPPORTED, "tp_silu_absmax_quant: fwht_block=%d (0 or 128)", fwht_block);
+  B200_REQUIRE(inter > 0 && inter % 128 == 0 && inter <= 49152, B200_E_UNSUPPORTED,
+               "tp_silu_absmax_quant: inter=%d must be a multiple of 128 and at most 49152", inter);
+  B200_REQUIRE(aligned16(gate_up) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN,
+               "tp_silu_absmax_quant: gate_up must be 16-byte aligned, codes 4-byte");
+  const int nblocks = inter / 128;
+  int threads = ((nblocks * 8 + 31) / 32) * 32;
+  if (threads > 512) threads = 512;
+  constexpr size_t kTableBytes = ((size_t)kSnegEntries * 2 + 15) / 16 * 16;
+  const size_t row_bytes = (size_t)inter * sizeof(int32_t);
+  const bool table = row_bytes + kTableBytes <= 110 * 1024;
+  const size_t smem = row_bytes + (table ? kTableBytes : 1024 * sizeof(int32_t));
+  cudaStream_t st = (cudaStream_t)s;
+#define B200_SILU_TP_LAUNCH(F, T)                                                                                     \
+  do {                                                                                                                \
+    cudaError_t e = cudaFuncSetAttribute(silu_rows_kernel<F, true, T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                                  \
+    if (e != cudaSuccess) {                                                                                           \
+      set_error("tp_silu_absmax_quant: cudaFuncSetAttribute: %s", cudaGetErrorString(e));                            \
+      return B200_E_CUDA;                                                                                             \
+    }                                                                                                                 \
+    launch_pdl(silu_rows_kernel<F, true, T, true>, dim3((unsigned)rows), dim3(threads), smem, st, gate_up,            \
+               (int32_t*)nullptr, codes, (float*)nullptr, absmax, (int64_t)rows, inter, agree);                       \
+  } while (0)
+  if (fwht_block == 128) { if (table) B200_SILU_TP_LAUNCH(true, true); else B200_SILU_TP_LAUNCH(true, false); }
+  else { if (table) B200_SILU_TP_LAUNCH(false, true); else B200_SILU_TP_LAUNCH(false, false); }
+#undef B200_SILU_TP_LAUNCH
+  return check_launch("tp_silu_absmax_quant");
 }
 
 extern "C" int b200_fwht_q15(const int32_t* x, int32_t* out, int64_t rows, int n, int normalize,

@@ -457,6 +457,21 @@ static int view_of(const b200_tp_block* blk, TpView* v, const char* name) {
   return B200_OK;
 }
 
+int tp_agree_of(const ::b200_tp_block* blk, TpAgree* out, const char* name) {
+  TpView v;
+  int rc = view_of(blk, &v, name);
+  if (rc != B200_OK) return rc;
+  out->rank = v.rank; out->size = v.size; out->m_max = v.m_max;
+  out->amax_off = tp_layout(v.m_max, v.n).amax;
+  for (int r = 0; r < kTpMaxRanks; ++r) out->base[r] = v.base[r];
+  void *st = nullptr, *to = nullptr;
+  B200_REQUIRE(cudaGetSymbolAddress(&st, g_tp_status) == cudaSuccess && cudaGetSymbolAddress(&to, g_tp_timeout_ns) == cudaSuccess,
+               B200_E_CUDA, "%s: cudaGetSymbolAddress failed", name);
+  out->status = reinterpret_cast<int*>(st);
+  out->timeout_ns = reinterpret_cast<const unsigned long long*>(to);
+  return B200_OK;
+}
+
 }  // namespace b200
 
 using namespace b200;

@@ -112,4 +112,52 @@ __device__ __forceinline__ void tp_signal_if_last(const TpView& v, int ch, unsig
   }
 }
 
+// What a kernel of another translation unit needs to take part in the absmax agreement (steps 1 + 2 of the exchange)
+// for the row it has just produced: the blocks, and where the status word and the time limit live.
+struct TpAgree {
+  int rank, size, m_max;
+  int64_t amax_off;                   // word offset of amax[0][0][0] inside a block
+  int32_t* base[kTpMaxRanks];
+  int* status;
+  const unsigned long long* timeout_ns;
+};
+
+// Called by ALL threads of the CTA that owns token row `row` (one CTA per row, gridDim.x rows): delivers the row's
+// local absmax (>= 1) to every rank, waits (bounded) for every rank's word of the row, clears them and returns the
+// maximum.  `slot` is one int of shared memory.
+__device__ __forceinline__ int tp_agree_cta(const TpAgree& a, int row, int local, int* slot) {
+  int32_t* hdr = a.base[a.rank];
+  const int half = *reinterpret_cast<volatile int32_t*>(hdr + 4) & 1;
+  const int64_t words = a.amax_off + ((int64_t)half * a.m_max + row) * kTpMaxRanks;
+  if ((int)threadIdx.x < a.size) tp_st_relaxed(a.base[threadIdx.x] + words + a.rank, local);
+  __syncthreads();                               // this rank's own word is out before thread 0 starts to wait
+  if (threadIdx.x == 0) {
+    int agreed = 1;
+    const unsigned long long t0 = tp_now_ns(), limit = *a.timeout_ns;
+    for (int src = 0; src < a.size; ++src) {
+      int w = tp_ld_acquire(hdr + words + src);
+      while (w == 0) {
+        if (tp_now_ns() - t0 > limit) {
+          atomicCAS(a.status, 0, 1);
+          break;
+        }
+        __nanosleep(32);
+        w = tp_ld_acquire(hdr + words + src);
+      }
+      agreed = max(agreed, w);
+      hdr[words + src] = 0;
+    }
+    if (atomicAdd(reinterpret_cast<unsigned*>(hdr + 12), 1u) + 1 == gridDim.x) {
+      hdr[12] = 0;
+      hdr[4] += 1;                    // read by the next launch, after this one has ended
+    }
+    *slot = agreed;
+  }
+  __syncthreads();
+  return *slot;
+}
+
+// Host side (tp.cu): fills `out` from a block descriptor; returns a status code and sets the error string.
+int tp_agree_of(const ::b200_tp_block* blk, TpAgree* out, const char* name);
+
 }  // namespace b200

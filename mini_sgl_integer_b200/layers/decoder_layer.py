@@ -97,6 +97,10 @@ class Qwen3DecoderLayerInteger:
                                                batch.kv_lens, batch.q_lens, batch.max_kv_len)
         codes, absmax = self.exchange.row_parallel_norm_quant(m, w["o"], attn.view(T, self.hq * 128), residual, w["post_norm"])
         gate_up = m.apply_quantised(w["gate_up"], codes, absmax)
+        if self.inter % 128 == 0 and T <= 256 and self.hadamard_block in (0, 128):
+            # SiLU * up, rotation, the ranks' absmax agreement and the quantisation in one launch
+            q = self.exchange.silu_absmax_quant(gate_up, self.hadamard_block)
+            return self.exchange.row_parallel_norm_quant(m, w["down"], None, residual, next_norm_weight, quantised=q)
         act = fp.silu_mul_fwht_q15(gate_up, self.hadamard_block)
         return self.exchange.row_parallel_norm_quant(m, w["down"], act, residual, next_norm_weight)
 

@@ -255,23 +255,42 @@ class TpExchange:
         rpr = (m + self.size - 1) // self.size
         return slice(min(m, self.rank * rpr), min(m, (self.rank + 1) * rpr))
 
+    def silu_absmax_quant(self, gate_up: torch.Tensor, fwht_block: int = 128):
+        """SiLU(gate) * up -> blocked FWHT of this rank's columns -> absmax agreement -> int8 codes, one launch
+        (silu_mul_fwht_q15 + absmax_quant).  Returns (codes int8 [rows, inter], agreed absmax int32 [rows])."""
+        require_cuda(gate_up)
+        if gate_up.dtype != torch.int32 or gate_up.ndim != 2:
+            raise TypeError(f"gate_up must be int32 [tokens, 2*inter], got {gate_up.dtype} {tuple(gate_up.shape)}")
+        g = gate_up.contiguous()
+        rows, inter = g.shape[0], g.shape[1] // 2
+        codes = torch.empty((rows, inter), dtype=torch.int8, device=g.device)
+        absmax = torch.empty(rows, dtype=torch.int32, device=g.device)
+        call("b200_tp_silu_absmax_quant", self._p, ptr(g), ptr(codes), ptr(absmax), rows, inter, int(fwht_block), stream())
+        return codes, absmax
+
     def row_parallel_norm_quant(self, method: W8A8Int8LinearMethod, layer, x_q15_local: torch.Tensor,
-                                residual: Optional[torch.Tensor], norm_weight: torch.Tensor):
+                                residual: Optional[torch.Tensor], norm_weight: torch.Tensor, *, quantised=None):
         """Row-split linear -> (+ residual) -> RMSNorm -> per-token int8 quant without a collective call.
 
         ``residual`` int32 [rows, n] is updated in place for this rank's ``owner_rows`` only (the other rows go
         stale: their owners keep them).  Returns (codes int8 [rows, n], absmax int32 [rows]) of ALL rows: the bits of
-        ``fused_add_rmsnorm_quant(row_parallel_q15(...), residual, norm_weight)`` computed on every rank."""
+        ``fused_add_rmsnorm_quant(row_parallel_q15(...), residual, norm_weight)`` computed on every rank.
+        ``quantised``: the input already as (codes, agreed absmax) instead of ``x_q15_local``."""
         if getattr(layer, "weight_mul", None) is None:
             method.process_weights_after_loading(layer)
-        x2 = self._rows(x_q15_local)
+        if quantised is not None:            # (codes, agreed absmax) of the input, e.g. from silu_absmax_quant
+            codes, absmax = quantised
+            rows, dev = codes.shape[0], codes.device
+        else:
+            x2 = self._rows(x_q15_local)
+            rows, dev = x2.shape[0], x2.device
+            codes, absmax = self.absmax_quant(x2)
         if residual is not None and (residual.dtype != torch.int32 or not residual.is_contiguous()
-                                     or tuple(residual.shape) != (x2.shape[0], self.n)):
+                                     or tuple(residual.shape) != (rows, self.n)):
             raise ValueError("residual must be a contiguous int32 [rows, n] tensor (it is updated in place)")
-        codes, absmax = self.absmax_quant(x2)
         self.gemm_add(codes, layer.weight)
         self.owner_norm(absmax, layer.weight_mul, layer.weight_shift, residual, norm_weight.contiguous())
-        return self.collect_codes(x2.shape[0], x2.device)
+        return self.collect_codes(rows, dev)
 
     def all_gather(self, src: torch.Tensor) -> torch.Tensor:
         """int32 [words] from every rank -> int32 [size, words] (words <= 2 * m_max)."""

@@ -122,6 +122,39 @@ def test_row_split_linear_finished_and_normalised_by_row_owners(size, m, n, k):
     assert TpExchange.status() == 0
 
 
+@pytest.mark.parametrize("size", [1, 3])
+@pytest.mark.parametrize("rows,inter,block", [(5, 256, 128), (64, 3072, 128), (9, 1536, 0), (3, 12288, 128)])
+def test_silu_fused_with_the_absmax_agreement(size, rows, inter, block):
+    """SiLU * up + rotation + agreement + quant in one launch.  The ranks' calls are issued one after the other, so
+    only the LAST rank's kernel finds every rank's word (the earlier ones run into a short time limit); its codes
+    must be the oracle's codes of its slice under the maximum of all slices' absmax."""
+    from mini_sgl_integer_b200.layers.tp_linear import TpExchange
+    rng = np.random.default_rng(rows + inter + size)
+    gus = [np.clip(np.rint(rng.normal(0, 2**17, (rows, 2 * inter))), -(2**22), 2**22).astype(np.int32) for _ in range(size)]
+    gus[0][:, :] //= 7                                    # one rank with clearly smaller values
+    acts = []
+    for gu in gus:
+        a = ofp.silu_and_mul(gu)
+        acts.append(ofp.blockwise_fwht_q15(a, block) if block else a)
+    agreed = np.maximum(1, np.max([np.abs(a.astype(np.int64)).max(axis=1) for a in acts], axis=0)).astype(np.int32)
+    last = size - 1
+    # the oracle's per-token quant of the row [own slice | a column holding the agreed absmax]
+    want = ofp.per_token_quant_from_q15(np.concatenate([acts[last], agreed.reshape(-1, 1)], axis=1))[0][:, :-1]
+    for rnd in range(2):
+        ranks = TpExchange.emulated(size, 64, 256)        # fresh blocks: the early ranks leave stale words behind
+        TpExchange.set_timeout_us(2000)
+        try:
+            outs = [ranks[r].silu_absmax_quant(d(gus[r]), block) for r in range(size)]
+            torch.cuda.synchronize()
+        finally:
+            TpExchange.set_timeout_us(2_000_000)
+        codes, absmax = outs[last]
+        np.testing.assert_array_equal(absmax.cpu().numpy(), agreed)
+        np.testing.assert_array_equal(codes.cpu().numpy(), want)
+    assert TpExchange.status() == (1 if size > 1 else 0)   # the early ranks' waits ran out (channel 0)
+    assert TpExchange.status() == 0
+
+
 def test_single_rank_exchange_equals_the_plain_linear():
     """size 1 through the calls the layers make (absmax + quant in one launch): the plain linear's bits."""
     from mini_sgl_integer_b200.layers.decoder_layer import _Linear
