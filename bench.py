@@ -331,6 +331,9 @@ def rowops_micro(dev, rows=16384, launches=20):
     return rec, (x, r, w, gu)
 
 
+PREFILL_NCU_TRAFFIC_BYTES = 52994560 + 80477696      # one launch of the prefill workload below, from its ncu capture
+
+
 def prefill_micro(dev, launches=5):
     """Prefill attention on prompts of the offline run's shape: 16 prompts of U[100, 1024] tokens, 32 q / 8 kv heads."""
     import torch
@@ -354,9 +357,13 @@ def prefill_micro(dev, launches=5):
     pairs = float((lens.astype(np.float64) * (lens + 1) / 2).sum()) * Hq
     ops = pairs * 128 * 2 * 2                                   # QK^T and PV, causal half
     kv_bytes = float(lens.sum()) * Hkv * 266
+    algo_bytes = kv_bytes + T * Hq * 128 * (1 + 4) + T * Hq * 8          # K/V once, int8 queries in, Q15.16 rows out, scales
     return {"workload": "16 prompts of U[100,1024] tokens, 32q/8kv heads, causal, no cached prefix", "tokens": T, "ms": ms,
             "ms_median": med, "tok_s": T / (ms * 1e-3), "int8_TOPS_algorithmic": ops / ms / 1e9,
-            "kv_bytes_once": kv_bytes, "score_elements": pairs}
+            "kv_bytes_once": kv_bytes, "score_elements": pairs, "algorithmic_bytes": algo_bytes,
+            "traffic": PREFILL_NCU_TRAFFIC_BYTES, "traffic_over_algorithmic": PREFILL_NCU_TRAFFIC_BYTES / algo_bytes,
+            "traffic_source": "ncu capture of attn_prefill_kernel<4> on this workload (dram__bytes_read.sum + dram__bytes_write.sum), "
+                              "not re-measured by this run"}
 
 
 # ----------------------------------------------------------------------------- the model step (default workload)
