@@ -20,7 +20,7 @@ import torch
 
 from .._lib import call, ptr, stream
 
-__all__ = ["PendingLinear", "zero_workspace", "workspace_scope", "PENDING_MAX_ROWS"]
+__all__ = ["PendingLinear", "zero_workspace", "workspace_scope", "reset_workspaces", "PENDING_MAX_ROWS"]
 
 PENDING_MAX_ROWS = 256          # the GEMM splits K (and needs a zeroed buffer) up to this many token rows
 
@@ -54,6 +54,13 @@ def zero_workspace(device: torch.device, rows: int, n: int) -> torch.Tensor:
         buf = torch.zeros((cap, n), dtype=torch.int32, device=device)
         _workspaces[key] = buf
     return buf[:rows]
+
+
+def reset_workspaces() -> None:
+    """Zeroes every workspace: after an exception between a pending linear and its consumer (the one situation that
+    leaves a buffer dirty), before the buffers are used again."""
+    for buf in _workspaces.values():
+        buf.zero_()
 
 
 @dataclass

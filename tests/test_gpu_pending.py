@@ -119,3 +119,16 @@ def test_qkv_preparation_on_a_pending_linear(tokens, hq, hk):
     assert torch.equal(pool_a.k_cache(0), pool_b.k_cache(0)) and torch.equal(pool_a.v_cache(0), pool_b.v_cache(0))
     assert torch.equal(pool_a.meta(0), pool_b.meta(0))
     assert _workspaces_zero()
+
+
+def test_a_pending_linear_that_nobody_consumed_is_cleared_by_reset():
+    from mini_sgl_integer_b200.kernel.pending import reset_workspaces, workspace_scope
+    from mini_sgl_integer_b200.layers.w8a8_int8 import W8A8Int8LinearMethod
+    codes, absmax, w8, wm, ws, acc, q15 = _linear_case(3, 40, 512, 1024)
+    layer, meth = _layer(w8, wm, ws), W8A8Int8LinearMethod()
+    with workspace_scope("scratch"):                         # a buffer set of its own: the default one stays clean
+        pend = meth.apply_pending(layer, d(codes), d(absmax))
+        assert int(pend.acc.abs().max()) > 0 and not _workspaces_zero()
+    reset_workspaces()
+    assert _workspaces_zero()
+    np.testing.assert_array_equal(meth.apply_quantised(layer, d(codes), d(absmax)).cpu().numpy(), q15)
