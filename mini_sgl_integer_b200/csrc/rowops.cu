@@ -77,6 +77,19 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
     pxs -= 48;
   }
 
+  // the norm gains do not depend on the row: with few vectors per thread they are requested up front, so that their
+  // latency hides behind the first reduction instead of following the second
+  constexpr bool kEarlyGain = VPT <= 2;
+  const int4* wr = reinterpret_cast<const int4*>(w);
+  int4 gain[kEarlyGain ? VPT : 1];
+  if (kEarlyGain) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      gain[i] = (FULL || idx < nvec) ? __ldg(wr + idx) : make_int4(0, 0, 0, 0);
+    }
+  }
+
   int4 v[VPT];
   int m = 0;
 #pragma unroll
@@ -117,14 +130,13 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
   S = block_sum64(S, red64);
   const int inv = norm_inv_sqrt(S, H, g_inv_sqrt_lut);
 
-  const int4* wr = reinterpret_cast<const int4*>(w);
   int4* no = norm_out ? reinterpret_cast<int4*>(norm_out + row * H) : nullptr;
   int m2 = 0;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (FULL || idx < nvec) {
-      const int4 ww = __ldg(wr + idx);
+      const int4 ww = kEarlyGain ? gain[i] : __ldg(wr + idx);
       int4 o;
       o.x = nr.zero ? 0 : norm_apply(v[i].x, inv, ww.x, nr.p);
       o.y = nr.zero ? 0 : norm_apply(v[i].y, inv, ww.y, nr.p);

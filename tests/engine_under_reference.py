@@ -1,6 +1,6 @@
 """Driver for tests/test_gpu_engine_reference.py, run in a fresh process: builds the UNMODIFIED reference's
 ``minisgl.engine.Engine`` (installed under baseline/_ref) with this package's integer model, int8 paged pool and
-attention backend plugged in at the three places the integration notes name, runs one prefill and a few greedy
+attention backend plugged in at three places (backend registry, model factory, pool factory), runs one prefill and a few greedy
 decode steps through ``Engine.forward_batch`` and writes the token ids (and the rotary table the model built) to a file.
 
     python tests/engine_under_reference.py <reference site dir> <model dir> <steps> <out.npz>

@@ -1,5 +1,5 @@
-"""The unmodified reference's Engine (``pip install --target baseline/_ref`` of the reference, see the design notes)
-driving this package's model, pool and attention backend: a tiny int8 Qwen3 checkpoint written as safetensors + a
+"""The unmodified reference's Engine (the reference package installed with ``pip install --no-deps --target
+baseline/_ref``) driving this package's model, pool and attention backend: a tiny int8 Qwen3 checkpoint written as safetensors + a
 Hugging Face config, loaded by the reference's own weight loader (q/k/v and gate/up merged there), one prefill and
 four greedy decode steps through ``Engine.forward_batch``; the token ids must be the oracle's.  Skipped where the
 reference is not installed."""
