@@ -54,30 +54,15 @@ __device__ __forceinline__ int tp_row_absmax(const int4* __restrict__ xr, int nv
   return max(1, block_max(m, red32));
 }
 
-// Thread 0 of the row's CTA: waits for all ranks' words of the row (bounded), returns their maximum, clears them
-// and counts the CTA; the last CTA of the launch advances the call counter.
-__device__ __forceinline__ int tp_row_agree(const TpView& v, int32_t* words) {
-  int agreed = 1;
-  const unsigned long long t0 = tp_now_ns(), limit = g_tp_timeout_ns;
-  for (int src = 0; src < v.size; ++src) {
-    int a = tp_ld_acquire(words + src);
-    while (a == 0) {
-      if (tp_now_ns() - t0 > limit) {
-        atomicCAS(&g_tp_status, 0, 1);
-        break;
-      }
-      __nanosleep(32);
-      a = tp_ld_acquire(words + src);
-    }
-    agreed = max(agreed, a);
-    words[src] = 0;
-  }
-  int32_t* hdr = v.base[v.rank];
-  if (atomicAdd(reinterpret_cast<unsigned*>(hdr + 12), 1u) + 1 == gridDim.x) {
-    hdr[12] = 0;
-    hdr[4] += 1;                    // read by the next launch, after this one has ended
-  }
-  return agreed;
+// The agreement itself is tp_agree_cta (tp_block.cuh); this builds its argument from a view.
+__device__ __forceinline__ TpAgree tp_agree_view(const TpView& v) {
+  TpAgree a;
+  a.rank = v.rank; a.size = v.size; a.m_max = v.m_max;
+  a.amax_off = tp_layout(v.m_max, v.n).amax;
+  for (int r = 0; r < kTpMaxRanks; ++r) a.base[r] = v.base[r];
+  a.status = &g_tp_status;
+  a.timeout_ns = &g_tp_timeout_ns;
+  return a;
 }
 
 // One CTA per token row of this rank's slice x [rows, k] (row pitch in elements): delivers the row's absmax.
@@ -106,12 +91,8 @@ tp_quant_wait_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pitc
   int32_t* hdr = v.base[v.rank];
   const int half = *reinterpret_cast<volatile int32_t*>(hdr + 4) & 1;
   const int row = blockIdx.x;
-  if (threadIdx.x == 0) {
-    agreed = tp_row_agree(v, hdr + l.amax + ((int64_t)half * v.m_max + row) * kTpMaxRanks);
-    absmax_out[row] = agreed;
-  }
-  __syncthreads();
-  const int m = agreed;
+  const int m = tp_agree_cta(tp_agree_view(v), row, 0, &agreed, false);
+  if (threadIdx.x == 0) absmax_out[row] = m;
   const float mf = __int2float_rn(m), my = __frcp_rn(mf);
   const int4* xr = reinterpret_cast<const int4*>(x + (int64_t)row * pitch);
   unsigned* co = reinterpret_cast<unsigned*>(codes + (int64_t)row * k);
@@ -153,15 +134,8 @@ tp_absmax_quant_kernel(const TpView v, const int32_t* __restrict__ x, int64_t pi
     m = max(max(m, abs_wrap(a.x)), max(abs_wrap(a.y), max(abs_wrap(a.z), abs_wrap(a.w))));
   }
   m = max(1, block_max(m, red32));
-  const int64_t words = l.amax + ((int64_t)half * v.m_max + row) * kTpMaxRanks;
-  if ((int)threadIdx.x < v.size) tp_st_relaxed(v.base[threadIdx.x] + words + v.rank, m);
-  __syncthreads();                               // this rank's own word is out before thread 0 starts to wait
-  if (threadIdx.x == 0) {
-    agreed = tp_row_agree(v, hdr + words);
-    absmax_out[row] = agreed;
-  }
-  __syncthreads();
-  const int a = agreed;
+  const int a = tp_agree_cta(tp_agree_view(v), row, m, &agreed);
+  if (threadIdx.x == 0) absmax_out[row] = a;
   const float mf = __int2float_rn(a), my = __frcp_rn(mf);
   unsigned* co = reinterpret_cast<unsigned*>(codes + (int64_t)row * k);
 #pragma unroll

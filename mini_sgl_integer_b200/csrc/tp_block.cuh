@@ -123,37 +123,37 @@ struct TpAgree {
 };
 
 // Called by ALL threads of the CTA that owns token row `row` (one CTA per row, gridDim.x rows): delivers the row's
-// local absmax (>= 1) to every rank, waits (bounded) for every rank's word of the row, clears them and returns the
-// maximum.  `slot` is one int of shared memory.
-__device__ __forceinline__ int tp_agree_cta(const TpAgree& a, int row, int local, int* slot) {
+// local absmax (>= 1) to every rank (`deliver`), waits (bounded) for every rank's word of the row - thread t polls
+// rank t's word, so eight peers cost one poll latency, not eight -, clears them and returns the maximum.  `slot` is
+// one int of shared memory.
+__device__ __forceinline__ int tp_agree_cta(const TpAgree& a, int row, int local, int* slot, bool deliver = true) {
   int32_t* hdr = a.base[a.rank];
   const int half = *reinterpret_cast<volatile int32_t*>(hdr + 4) & 1;
   const int64_t words = a.amax_off + ((int64_t)half * a.m_max + row) * kTpMaxRanks;
-  if ((int)threadIdx.x < a.size) tp_st_relaxed(a.base[threadIdx.x] + words + a.rank, local);
-  __syncthreads();                               // this rank's own word is out before thread 0 starts to wait
-  if (threadIdx.x == 0) {
-    int agreed = 1;
-    const unsigned long long t0 = tp_now_ns(), limit = *a.timeout_ns;
-    for (int src = 0; src < a.size; ++src) {
-      int w = tp_ld_acquire(hdr + words + src);
-      while (w == 0) {
+  if (threadIdx.x == 0) *slot = 1;
+  if (deliver && (int)threadIdx.x < a.size) tp_st_relaxed(a.base[threadIdx.x] + words + a.rank, local);
+  __syncthreads();                               // the slot is initialised; this rank's own word is out
+  if ((int)threadIdx.x < a.size) {
+    int32_t* word = hdr + words + threadIdx.x;
+    int w = tp_ld_acquire(word);
+    if (w == 0) {
+      const unsigned long long t0 = tp_now_ns(), limit = *a.timeout_ns;
+      while ((w = tp_ld_acquire(word)) == 0) {
         if (tp_now_ns() - t0 > limit) {
           atomicCAS(a.status, 0, 1);
           break;
         }
         __nanosleep(32);
-        w = tp_ld_acquire(hdr + words + src);
       }
-      agreed = max(agreed, w);
-      hdr[words + src] = 0;
     }
-    if (atomicAdd(reinterpret_cast<unsigned*>(hdr + 12), 1u) + 1 == gridDim.x) {
-      hdr[12] = 0;
-      hdr[4] += 1;                    // read by the next launch, after this one has ended
-    }
-    *slot = agreed;
+    *word = 0;
+    atomicMax(slot, w);
   }
   __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(reinterpret_cast<unsigned*>(hdr + 12), 1u) + 1 == gridDim.x) {
+    hdr[12] = 0;
+    hdr[4] += 1;                      // read by the next launch, after this one has ended
+  }
   return *slot;
 }
 
