@@ -645,7 +645,7 @@ gemm_w8a8_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   }
 }
 
-// The two-CTA kernel with the operands swapped, for 129..256 tokens (decode batches): the pair's 256 accumulator rows
+// The two-CTA kernel with the operands swapped, for 65..256 tokens (decode batches): the pair's 256 accumulator rows
 // are WEIGHT rows, the 256 columns are tokens.  Each CTA stages its own 128 weight rows and HALF of the token tile per
 // k-block (32 KB instead of the 48 KB of the one-CTA weights-stationary tile, whose CTAs each re-read all tokens):
 // at these sizes the time goes into moving operands from L2 into shared memory, not into MMAs.  Tiles follow the
@@ -981,9 +981,13 @@ static int gemm_impl(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax
   p.splits = 1; p.full_blocks = 0; p.partial = nullptr; p.n_peers = 0; p.tp_on = 0; p.split_col0 = 0;
   cudaStream_t st = (cudaStream_t)s;
   const int num_kb = (int)((k + kBK - 1) / kBK);
-  // 129..256 tokens: CTA pairs on blocks of 256 weight rows (each CTA stages half of the tokens); fewer tokens: single
-  // CTAs on blocks of 128 weight rows with a token tile as narrow as the batch
-  const bool pair_ws = m > 128 && m <= 256 && pair_ws_enabled();
+  // 65..256 tokens: CTA pairs on blocks of 256 weight rows (each CTA stages half of the 256-token tile; rows beyond
+  // the batch are zero fill that costs no traffic); fewer tokens: single CTAs on blocks of 128 weight rows with a
+  // token tile as narrow as the batch.  (Measured on four layers + lm_head of the 8B shape: the pair form wins by
+  // 4 % at 96 and 128 tokens, 1 % at 64, nothing at 48.  B200_GEMM_PAIR_MIN moves the boundary.)
+  static int pair_min = -1;
+  if (pair_min < 0) { const char* e = getenv("B200_GEMM_PAIR_MIN"); pair_min = e ? atoi(e) : 65; }
+  const bool pair_ws = m >= pair_min && m <= 256 && pair_ws_enabled();
   const int block_rows = pair_ws ? 2 * kBM : kBM, units = pair_ws ? sm_count() / 2 : sm_count();
   const int w_blocks = (int)((n + block_rows - 1) / block_rows);
   if (pair_ws || m <= 128 || (m <= 256 && w_blocks < sm_count())) {

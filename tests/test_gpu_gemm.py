@@ -75,9 +75,10 @@ def test_decode_sizes_without_accumulator_output(M, N, K):
         np.testing.assert_array_equal(out.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 24576, 4096), (200, 19208, 2048), (129, 132, 512), (256, 256, 8192), (177, 6144, 4096)])
+@pytest.mark.parametrize("M,N,K", [(256, 24576, 4096), (200, 19208, 2048), (129, 132, 512), (256, 256, 8192), (177, 6144, 4096),
+                                   (65, 4096, 4096), (100, 6144, 1024), (128, 19208, 512)])
 def test_pair_weights_stationary_tiles(M, N, K):
-    """129..256 tokens run on CTA pairs over blocks of 256 weight rows with half of the tokens staged per CTA: unsplit
+    """65..256 tokens run on CTA pairs over blocks of 256 weight rows with half of the tokens staged per CTA: unsplit
     waves followed by a split tail, a ragged last block, a single block with the deepest split, both outputs."""
     run_case(M, N, K, M + N + K, per_channel_shift=True)
 
