@@ -979,6 +979,9 @@ def run_tp_linear(args) -> None:
 
 
 def main() -> None:
+    # NCCL only sets up the process group and runs the barriers / timing reductions around the step (the step itself
+    # has no collective call), so it does not need in-switch reduction; the multi-GPU runs were validated with it off
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
