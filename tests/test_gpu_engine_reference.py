@@ -93,6 +93,8 @@ def test_reference_engine_drives_this_package(tmp_path):
     env = dict(os.environ, MINISGL_INTEGER_MODE="1", PYTHONPATH=ROOT)
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "engine_under_reference.py"), REF, str(tmp_path), str(steps), str(out)],
                           env=env, capture_output=True, text=True, timeout=600)
+    if proc.returncode != 0 and "ddress already in use" in proc.stderr:
+        pytest.skip("the engine's fixed rendezvous port (tcp://127.0.0.1:2333, engine/config.py) is taken on this host")
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
     z = np.load(out)
     assert int(z["calls"]) > 0                                       # the sm_100a library did the work
