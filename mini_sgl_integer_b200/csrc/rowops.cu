@@ -427,6 +427,20 @@ __device__ __forceinline__ void fwht128_group_nosat(int (&val)[16], int lane8) {
   }
 }
 
+// Threads per CTA: an 8-lane group takes one 128-block per iteration, so the groups per CTA should divide the
+// row's blocks without leaving most groups idle in the last iteration (136 blocks on 64 groups: 3 iterations, the
+// last one with 8 groups busy; on 68 groups: 2 full iterations).  Whole warps, at most kSiluMaxThreads.
+constexpr int kSiluMaxThreads = 576;
+static int silu_threads(int nblocks) {
+  const int max_groups = kSiluMaxThreads / 8;
+  if (nblocks <= max_groups) return ((nblocks * 8 + 31) / 32) * 32;
+  int min_slots = 1 << 30;
+  for (int g = max_groups; g >= max_groups / 2; g -= 4) min_slots = min(min_slots, (nblocks + g - 1) / g * g);
+  for (int g = max_groups; g >= max_groups / 2; g -= 4)         // the widest CTA within 6 % of the best fit
+    if ((nblocks + g - 1) / g * g <= min_slots + min_slots / 16) return g * 8;
+  return max_groups * 8;
+}
+
 // One CTA per row at a time (the CTAs walk the rows with the grid as stride, so the tables are staged once per
 // CTA).  An 8-lane group takes the 128-blocks group, group + ngroups, ...; the SiLU*up (+ rotation) results of
 // the whole row are parked in shared memory until the row's absmax is known, then quantised from there: gate
@@ -436,7 +450,7 @@ __device__ __forceinline__ void fwht128_group_nosat(int (&val)[16], int lane8) {
 // linear): between the two phases the CTA takes part in the absmax agreement over the exchange blocks (one CTA per
 // row, all of them resident), quantises with the agreed value and reports it; `scale` is not written.
 template <bool FWHT, bool QUANT, bool TABLE, bool TP = false>
-__global__ void __launch_bounds__(512, 2)
+__global__ void __launch_bounds__(kSiluMaxThreads, 2)
 silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_out,
                  int8_t* __restrict__ codes, float* __restrict__ scale,
                  int32_t* __restrict__ absmax, int64_t rows, int I, const TpAgree agree) {
@@ -785,8 +799,7 @@ static int launch_silu(const int32_t* gu, int32_t* q15, int8_t* codes, float* sc
                        int64_t rows, int inter, bool fwht, cudaStream_t st) {
   const bool quant = codes != nullptr;
   const int nblocks = inter / 128;
-  int threads = ((nblocks * 8 + 31) / 32) * 32;
-  if (threads > 512) threads = 512;
+  const int threads = silu_threads(nblocks);
   // the direct sigmoid table (38 KB) is used when it fits beside the row buffer with two CTAs per SM
   constexpr size_t kTableBytes = ((size_t)kSnegEntries * 2 + 15) / 16 * 16;
   const size_t row_bytes = (size_t)(quant ? inter : 0) * sizeof(int32_t);
@@ -858,8 +871,7 @@ extern "C" int b200_tp_silu_absmax_quant(const b200_tp_block* blk, const int32_t
   B200_REQUIRE(aligned16(gate_up) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN,
                "tp_silu_absmax_quant: gate_up must be 16-byte aligned, codes 4-byte");
   const int nblocks = inter / 128;
-  int threads = ((nblocks * 8 + 31) / 32) * 32;
-  if (threads > 512) threads = 512;
+  const int threads = silu_threads(nblocks);
   constexpr size_t kTableBytes = ((size_t)kSnegEntries * 2 + 15) / 16 * 16;
   const size_t row_bytes = (size_t)inter * sizeof(int32_t);
   const bool table = row_bytes + kTableBytes <= 110 * 1024;
