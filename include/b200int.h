@@ -342,6 +342,22 @@ B200_API int b200_qkv_prepare_pending(const int32_t* positions, int32_t* acc, co
                                       int32_t* meta, int8_t* q8, int32_t* q_mul, int32_t* q_shift, int64_t tokens,
                                       int q_heads, int kv_heads, int64_t num_pages, int with_fwht, b200_stream_t s);
 
+/* ---- gate_up projection with SiLU(gate) * up applied in the GEMM's epilogue (decode batches, m <= 256), and the row
+ * kernel that follows it.  Together they replace gate_up_proj + silu_and_mul_int_only + apply_blockwise_fwht_q15 + the
+ * per-token quant in front of down_proj (GatedMLPInteger.forward_q15, models/utils_integer.py:99-121) with the same bits:
+ *   b200_gemm_gate_up_silu  x8 int8 [m, k], w8 int8 [n2, k] in the checkpoint's merged layout (n2 / 2 gate rows, then
+ *                           n2 / 2 up rows; models/weight.py:86-104), x_absmax int32 [m], w_mul / w_shift int32 [n2]
+ *                           -> act_out int32 [m, n2 / 2] Q15.16.  zero_ws: an all-zero int32 [m, n2] workspace as for
+ *                           b200_gemm_w8a8_absmax_ws (zero again on return).  n2 % 256 == 0, k % 16 == 0.
+ *   b200_fwht_quant_q15     act int32 [rows, inter] -> blocked Walsh-Hadamard rotation (fwht_block 128, or 0 = none) ->
+ *                           per-token int8 codes [rows, inter], scale fp32 [rows], absmax int32 [rows]: the part of
+ *                           b200_silu_mul_q15 behind the activation. */
+B200_API int b200_gemm_gate_up_silu(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax, const int32_t* w_mul,
+                                    const int32_t* w_shift, int32_t* act_out, int32_t* zero_ws, int64_t m, int64_t n2,
+                                    int64_t k, b200_stream_t s);
+B200_API int b200_fwht_quant_q15(const int32_t* act, int8_t* codes, float* scale, int32_t* absmax, int64_t rows, int inter,
+                                 int fwht_block, b200_stream_t s);
+
 /* ---- Pieces of the W8A8 linear for tensor-parallel row-split layers, where the int32 partial
  * sums of the ranks are added (all-reduce) between the GEMM and its epilogue.  They stand in for
  * the per-rank quant + GEMM + all-reduce of LinearOProj / LinearRowParallel

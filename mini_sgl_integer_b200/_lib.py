@@ -48,6 +48,8 @@ SIGNATURES: dict[str, list] = {
     "b200_gemm_w8a8_reduce_peers": [P, P, P, I, L, L, L, P],
     "b200_gemm_w8a8_absmax_ws": [P, P, P, P, P, P, P, L, L, L, P],
     "b200_gemm_w8a8_acc_ws": [P, P, P, L, L, L, P],
+    "b200_gemm_gate_up_silu": [P, P, P, P, P, P, P, L, L, L, P],
+    "b200_fwht_quant_q15": [P, P, P, P, L, I, I, P],
     "b200_rmsnorm_q15_pending": [P, P, P, P, P, P, P, P, P, P, P, L, I, P],
     "b200_qkv_prepare_pending": [P, P, P, P, P, P, I, P, P, P, P, P, P, P, P, P, L, I, I, L, I, P],
     "b200_gemm_status": [P, I],

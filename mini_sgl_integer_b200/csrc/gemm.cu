@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "silu.cuh"
 #include "tp_block.cuh"
 
 namespace b200 {
@@ -809,6 +810,225 @@ gemm_w8a8_2sm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   }
 }
 
+// The gate_up projection with SiLU(gate) * up applied in the epilogue (decode batches, up to 256 tokens).  The weight
+// keeps the checkpoint's layout [gate rows | up rows] (N = 2 I rows); a CTA pair takes 128 activation channels: each
+// CTA stages 64 gate rows AND the 64 up rows of the same channels per k-block (two TMA boxes into one 128-row
+// operand tile), so that after the MMAs its tensor-memory lanes 0..63 hold the gate and lanes 64..127 the up
+// accumulators of the same (channel, token) pairs.  Epilogue warps of lane quarters 2 and 3 requantise their up
+// values and hand them through shared memory to the warps of quarters 0 and 1, which requantise the gate values,
+// apply the fixed-point SiLU * up (direct sigmoid table in shared memory) and store act[token][channel]: half the
+// bytes of the Q15.16 gate_up tensor, and the row kernel that follows only rotates and quantises.  Blocks of the
+// split tail add their parts into `partial` ([M, 2 I], standard columns) and are finished by silu_tail_kernel.
+constexpr int kActStages = 4;
+
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads2, 1)
+gemm_gate_up_silu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                         const GemmParams p) {
+  constexpr int BN = 256;
+  constexpr int kABytes = kBM * kBK;           // 64 gate rows + 64 up rows
+  constexpr int kBBytes = (BN / 2) * kBK;      // 128 token rows
+  constexpr int kStageBytes = kABytes + kBBytes;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * kStageBytes);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * STAGES + 4);
+  int32_t* tok_scale = reinterpret_cast<int32_t*>(tmem_slot + 4);               // [2 slots][mul BN | shift BN] per token
+  uint16_t* sneg_tab = reinterpret_cast<uint16_t*>(tok_scale + 4 * BN);
+  int32_t* hand = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(sneg_tab) + kSiluTableBytes);   // [8 warp pairs][32 tokens][32 lanes]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+  const int I = p.N >> 1;                       // activation channels; a multiple of 128
+  const int w_blocks = I / kBM;
+  const int num_tiles = p.full_blocks + (w_blocks - p.full_blocks) * p.splits;
+  const unsigned full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const unsigned tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull0 + 8 * s, 1);
+      mbar_init(tempty0 + 8 * s, 2 * kEpiWarps2);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  pdl_launch_dependents();
+  silu_stage_table(sneg_tab);                   // constant data: staged before the wait on the preceding kernel
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_barrier();
+  tcgen05_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      unsigned it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const WsTile t = ws_tile(p, tile, num_kb);
+        const int ch0 = t.n_blk * kBM + (int)rank * (kBM / 2);          // first of this CTA's 64 channels
+        for (int kb = t.kb0; kb < t.kb1; ++kb, ++it) {
+          const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
+          ok = mbar_wait(empty0 + 8 * s, ph ^ 1, 1);
+          if (!ok) break;
+          if (leader) mbar_expect_tx(full0 + 8 * s, 2 * kStageBytes);
+          const unsigned a_dst = smem_u32(tiles + s * kStageBytes);
+          const unsigned lbar = (full0 + 8 * s) & kPeerBitMask;
+          tma_load_2d_2sm(a_dst, &map_w, kb * kBK, ch0, lbar);                       // 64 gate rows
+          tma_load_2d_2sm(a_dst + kABytes / 2, &map_w, kb * kBK, I + ch0, lbar);     // the 64 up rows of the same channels
+          tma_load_2d_2sm(a_dst + kABytes, &map_x, kb * kBK, (int)rank * (BN / 2), lbar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr unsigned idesc = make_idesc(2 * kBM, BN);
+      unsigned it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++lt) {
+        const unsigned slot = lt & 1, aph = (lt >> 1) & 1;
+        ok = mbar_wait(tempty0 + 8 * slot, aph ^ 1, 4);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const unsigned tmem_d = tmem_base + slot * BN;
+        const WsTile t = ws_tile(p, tile, num_kb);
+        for (int kb = t.kb0; kb < t.kb1; ++kb, ++it) {
+          const unsigned s = it % STAGES, ph = (it / STAGES) & 1;
+          ok = mbar_wait(full0 + 8 * s, ph, 2);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const unsigned a_addr = smem_u32(tiles + s * kStageBytes);
+          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_i8_2sm(tmem_d, da + (uint64_t)(k * kUmmaK >> 4), db + (uint64_t)(k * kUmmaK >> 4), idesc,
+                        (kb > t.kb0 || k > 0) ? 1u : 0u);
+          tcgen05_commit_pair(empty0 + 8 * s);
+        }
+        if (ok) tcgen05_commit_pair(tfull0 + 8 * slot);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int part = (warp - 2) >> 2;
+    const int et = threadIdx.x - 64;
+    const bool is_up = q >= 2;
+    const int cl = (q & 1) * 32 + lane;                                  // channel inside the CTA's 64
+    const int pair_id = (q & 1) * 4 + part;                              // the gate warp and the up warp of the same lanes
+    int32_t* my_hand = hand + pair_id * 1024;
+    unsigned lt = 0;
+    unsigned okw = 1;                                                    // agreed by all epilogue threads, see below
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++lt) {
+      const WsTile t = ws_tile(p, tile, num_kb);
+      const unsigned slot = lt & 1, aph = (lt >> 1) & 1;
+      const int chan = t.n_blk * kBM + (int)rank * (kBM / 2) + cl;       // < I by construction (I % 128 == 0)
+      const int wrow = is_up ? I + chan : chan;                          // weight row = column of the standard layout
+      const bool direct = !t.split;
+      const bool empty_part = t.kb0 >= t.kb1;
+      int32_t* cs = tok_scale + slot * 2 * BN;
+      if (direct) {
+        for (int c = et; c < BN; c += 32 * kEpiWarps2) {
+          const int tk = min(c, p.M - 1);
+          int tm, ts;
+          absmax_to_ms_dev(__ldg(p.x_absmax + tk), &tm, &ts);
+          cs[c] = tm;
+          cs[BN + c] = ts - 48;
+        }
+      }
+      int wm = 0, ws = 0;
+      if (direct) { wm = __ldg(p.w_mul + wrow); ws = p.w_shift ? __ldg(p.w_shift + wrow) : 31; }
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps2) : "memory");
+      unsigned mine = okw ? (mbar_wait(tfull0 + 8 * slot, aph, 3) ? 1u : 0u) : 0u;
+      // the two warps of a pair meet at barriers below, so whether the accumulator arrived must be ONE decision for
+      // all epilogue threads (a wait that ran out in one warp only would leave its partner at a barrier)
+      asm volatile("{\n.reg .pred pi, po;\nsetp.ne.u32 pi, %1, 0;\nbar.red.and.pred po, 1, %2, pi;\nselp.u32 %0, 1, 0, po;\n}"
+                   : "=r"(okw) : "r"(mine), "n"(32 * kEpiWarps2) : "memory");
+      tcgen05_fence_after();
+#pragma unroll 1
+      for (int c0 = part * 32; c0 < BN; c0 += 32 * (kEpiWarps2 / 4)) {
+        if (!okw || c0 >= p.M || empty_part) continue;                   // uniform over both warps of a pair
+        int v[32];
+        tmem_ld_32x32(tmem_base + ((unsigned)(q * 32) << 16) + slot * BN + (unsigned)c0, v);
+        if (!direct) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < p.M) atomicAdd(p.partial + (int64_t)(c0 + j) * p.N + wrow, v[j]);
+          continue;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = requant_one(v[j], __mulhi(cs[c0 + j], wm), cs[BN + c0 + j] + ws);
+        if (is_up) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) my_hand[j * 32 + lane] = v[j];
+          asm volatile("bar.sync %0, 64;" ::"r"(2 + pair_id) : "memory");       // handed over
+          asm volatile("bar.sync %0, 64;" ::"r"(2 + pair_id) : "memory");       // taken: the buffer may be written again
+        } else {
+          asm volatile("bar.sync %0, 64;" ::"r"(2 + pair_id) : "memory");
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int u = my_hand[j * 32 + lane];
+            if (c0 + j < p.M) p.out_q15[(int64_t)(c0 + j) * I + chan] = silu_mul_elem_table(v[j], u, sneg_tab);
+          }
+          asm volatile("bar.sync %0, 64;" ::"r"(2 + pair_id) : "memory");
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(tempty0 + 8 * slot);
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_barrier();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+  }
+}
+
+// Finishes the split tail of gemm_gate_up_silu_kernel: channels [col0, I) of every token from the summed parts in
+// `partial` ([M, 2 I]: gate at column c, up at column I + c), zeroing what it read; four channels per thread.
+__global__ void __launch_bounds__(256)
+silu_tail_kernel(int32_t* partial, const GemmParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.y;
+  const int I = p.N >> 1;
+  const int c = p.split_col0 + (blockIdx.x * 256 + threadIdx.x) * 4;
+  if (c >= I) return;
+  int xm, xs;
+  absmax_to_ms_dev(__ldg(p.x_absmax + t), &xm, &xs);
+  xs -= 48;
+  int32_t* gp = partial + (int64_t)t * p.N + c;
+  const int4 g = *reinterpret_cast<const int4*>(gp);
+  const int4 u = *reinterpret_cast<const int4*>(gp + I);
+  const int4 gm = __ldg(reinterpret_cast<const int4*>(p.w_mul + c)), um = __ldg(reinterpret_cast<const int4*>(p.w_mul + I + c));
+  int4 gs = make_int4(31, 31, 31, 31), us = gs;
+  if (p.w_shift) { gs = __ldg(reinterpret_cast<const int4*>(p.w_shift + c)); us = __ldg(reinterpret_cast<const int4*>(p.w_shift + I + c)); }
+  int4 r;
+  r.x = silu_mul_elem_table(requant_one(g.x, __mulhi(xm, gm.x), xs + gs.x), requant_one(u.x, __mulhi(xm, um.x), xs + us.x), g_silu_sneg);
+  r.y = silu_mul_elem_table(requant_one(g.y, __mulhi(xm, gm.y), xs + gs.y), requant_one(u.y, __mulhi(xm, um.y), xs + us.y), g_silu_sneg);
+  r.z = silu_mul_elem_table(requant_one(g.z, __mulhi(xm, gm.z), xs + gs.z), requant_one(u.z, __mulhi(xm, um.z), xs + us.z), g_silu_sneg);
+  r.w = silu_mul_elem_table(requant_one(g.w, __mulhi(xm, gm.w), xs + gs.w), requant_one(u.w, __mulhi(xm, um.w), xs + us.w), g_silu_sneg);
+  *reinterpret_cast<int4*>(p.out_q15 + (int64_t)t * I + c) = r;
+  // behind the result's store (a store right behind the load of the same address waits for the load's miss)
+  *reinterpret_cast<int4*>(gp) = make_int4(0, 0, 0, 0);
+  *reinterpret_cast<int4*>(gp + I) = make_int4(0, 0, 0, 0);
+}
+
 // Clears columns [0, 4 * vec_cols) of m rows (row pitch in elements) before the split-K parts are added into them.
 __global__ void __launch_bounds__(256)
 zero_cols_kernel(int32_t* __restrict__ base, int m, int vec_cols, int64_t pitch) {
@@ -1084,6 +1304,51 @@ extern "C" int b200_gemm_w8a8_acc_ws(const int8_t* x8, const int8_t* w8, int32_t
                                      b200_stream_t s) {
   B200_REQUIRE(zero_ws, B200_E_NULL, "gemm_w8a8_acc_ws: the workspace is null");
   return gemm_impl(x8, w8, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, zero_ws, m, n, k, s, zero_ws);
+}
+
+extern "C" int b200_gemm_gate_up_silu(const int8_t* x8, const int8_t* w8, const int32_t* x_absmax, const int32_t* w_mul,
+                                      const int32_t* w_shift, int32_t* act_out, int32_t* zero_ws, int64_t m, int64_t n2,
+                                      int64_t k, b200_stream_t s) {
+  B200_REQUIRE(x8 && w8 && x_absmax && w_mul && act_out && zero_ws, B200_E_NULL, "gemm_gate_up_silu: null pointer");
+  B200_REQUIRE(m >= 0 && m <= 256 && n2 > 0 && k > 0 && n2 < (1ll << 31) && k < (1ll << 31), B200_E_SHAPE,
+               "gemm_gate_up_silu: m=%lld (at most 256) n2=%lld k=%lld", (long long)m, (long long)n2, (long long)k);
+  B200_REQUIRE(n2 % 256 == 0 && k % 16 == 0, B200_E_UNSUPPORTED,
+               "gemm_gate_up_silu: n2=%lld must be a multiple of 256 (128 activation channels per CTA pair), k=%lld of 16",
+               (long long)n2, (long long)k);
+  if (m == 0) return B200_OK;
+  B200_REQUIRE(aligned16(x8) && aligned16(w8) && aligned16(act_out) && aligned16(zero_ws) && aligned16(w_mul) && aligned16(w_shift),
+               B200_E_ALIGN, "gemm_gate_up_silu: buffers must be 16-byte aligned");
+  GemmParams p;
+  p.x_absmax = x_absmax; p.x_mul = nullptr; p.x_shift = nullptr; p.w_mul = w_mul; p.w_shift = w_shift;
+  p.out_q15 = act_out; p.acc_out = nullptr; p.M = (int)m; p.N = (int)n2; p.K = (int)k;
+  p.n_peers = 0; p.tp_on = 0;
+  const int inter = (int)(n2 / 2), w_blocks = inter / kBM, num_kb = (int)((k + kBK - 1) / kBK), units = sm_count() / 2;
+  const int tail = w_blocks % units;
+  const int split_blocks = w_blocks < units ? w_blocks : tail;
+  int splits = split_blocks > 0 ? units / split_blocks : 1;
+  splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
+  while (splits > 1 && num_kb / splits < 4) --splits;
+  while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;
+  p.splits = splits;
+  p.full_blocks = splits > 1 ? w_blocks - split_blocks : 0;
+  p.split_col0 = p.full_blocks * kBM;
+  p.partial = zero_ws;
+  CUtensorMap mw, mx;
+  B200_REQUIRE(make_map(&mw, w8, n2, k, kBM / 2), B200_E_CUDA, "gemm_gate_up_silu: cuTensorMapEncodeTiled failed for w8");
+  B200_REQUIRE(make_map(&mx, x8, m, k, kBM), B200_E_CUDA, "gemm_gate_up_silu: cuTensorMapEncodeTiled failed for x8");
+  constexpr size_t smem = (size_t)kActStages * (kBM * kBK + 128 * kBK) + 1024 + (2 * kActStages + 4) * 8 + 16 + 4 * 256 * 4 +
+                          kSiluTableBytes + 8 * 1024 * 4;
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  cudaError_t e = cudaFuncSetAttribute(gemm_gate_up_silu_kernel<kActStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  B200_REQUIRE(e == cudaSuccess, B200_E_CUDA, "gemm_gate_up_silu: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  cudaStream_t st = (cudaStream_t)s;
+  const int tiles = p.full_blocks + (w_blocks - p.full_blocks) * p.splits;
+  const int pairs = tiles < units ? tiles : units;
+  launch_pdl(gemm_gate_up_silu_kernel<kActStages>, dim3(2 * pairs), dim3(kGemmThreads2), smem, st, mw, mx, p);
+  int rc = check_launch("gemm_gate_up_silu");
+  if (rc != B200_OK || splits == 1) return rc;
+  launch_pdl(silu_tail_kernel, dim3((unsigned)((inter - p.split_col0 + 1023) / 1024), (unsigned)m), dim3(256), 0, st, zero_ws, p);
+  return check_launch("gemm_gate_up_silu (split tail)");
 }
 
 extern "C" int b200_gemm_w8a8_reduce_peers(const int8_t* x8, const int8_t* w8, int32_t* const* peer_acc, int n_peers,

@@ -9,6 +9,7 @@
 #include "common.cuh"
 #include "luts.cuh"
 #include "rope.cuh"
+#include "silu.cuh"
 #include "tp_block.cuh"
 
 namespace b200 {
@@ -307,58 +308,7 @@ static bool plan_rows(int width, RowPlan* p, int64_t rows = 1 << 30) {
     default: { constexpr int V = 8; CALL; } break; \
   }
 
-// ============================================================================ SiLU * up
-// silu_and_mul_int_only_kernel's arithmetic (silu_and_mul_int_only.py:156-226) for one element.
-__device__ __forceinline__ int silu_mul_elem(int g, int u, const int32_t* __restrict__ lut) {
-  const int a = g > 0 ? -g : g;                                  // -|g|, fits int32 for every g
-  const long long prod = (long long)a * 94549LL;                 // -|g| * log2e, Q30.32; y = prod >> 16
-  const int yi = (int)(prod >> 32);                              // y >> 16  (<= 0)
-  const unsigned idx = ((unsigned)prod) >> 22;                   // (y & 0xFFFF) >> 6
-  unsigned E;
-  asm("shr.u32 %0, %1, %2;" : "=r"(E) : "r"((unsigned)lut[idx]), "r"((unsigned)(13 - yi)));  // >= 32 gives 0
-  E = min(E, 65536u);
-  // sneg = floor(E * 2^16 / (2^16 + E)): float estimate (off by at most 1), exact correction
-  const unsigned den = 65536u + E;
-  const unsigned num = E << 16;                                  // wraps only for E == 2^16 (handled below)
-  // E and den are below 2^23, so they convert to float exactly by being placed in the mantissa of 2^23
-  // (an OR and an FP add instead of the conversion unit), and the estimate goes back the same way
-  // (rounded to nearest instead of truncated: still within one of the quotient).
-  const float Ef = __uint_as_float(0x4B000000u | E) - 8388608.0f;
-  const float denf = __uint_as_float(0x4B000000u | den) - 8388608.0f;
-  unsigned sneg = __float_as_uint(__fdividef(Ef * 65536.0f, denf) + 8388608.0f) - 0x4B000000u;
-  const int rem = (int)(num - sneg * den);
-  sneg += rem < 0 ? -1 : (rem >= (int)den ? 1 : 0);
-  sneg = (E == 65536u) ? 32768u : sneg;
-  const int sig = (int)(g > 0 ? 65536u - sneg : sneg);           // <= 2^16: 32 x 32 -> 64 bit products below
-  const long long gs = (long long)g * (long long)sig;
-  const int t = (int)__funnelshift_r((unsigned)gs, (unsigned)(gs >> 32), 16);   // (g * sig) >> 16, |t| <= |g|
-  const long long tu = (long long)t * (long long)u;
-  const int hi = (int)(tu >> 32);
-  const int res = (int)__funnelshift_r((unsigned)tu, (unsigned)hi, 16);        // low 32 bits of tu >> 16
-  // tu >> 16 fits int32 iff bits 47..63 of tu all equal the sign bit of the result
-  return (hi >> 15) == (res >> 31) ? res : (hi < 0 ? (int)(-2147483647 - 1) : 2147483647);
-}
-
-// The same element with the sigmoid term read from a direct table: E and s = (E << 16) / (65536 + E) depend only
-// on key = (-|g| * 94549) >> 22 (the exponent's integer part and the 10 table bits), and s is 0 below key -19456.
-#include "silu_sneg.inc"
-constexpr int kSnegEntries = 19457;
-static __device__ __align__(16) const uint16_t g_silu_sneg[kSnegEntries] = {B200_LUT_kSiluSneg};
-
-__device__ __forceinline__ int silu_mul_elem_table(int g, int u, const uint16_t* __restrict__ sneg_tab) {
-  const int a = g > 0 ? -g : g;                                  // -|g|
-  const long long prod = (long long)a * 94549LL;
-  const int key = (int)(prod >> 22) + (kSnegEntries - 1);        // prod >> 22 >= -2^26: fits
-  const unsigned sneg = key < 0 ? 0u : (unsigned)sneg_tab[key];
-  const int sig = (int)(g > 0 ? 65536u - sneg : sneg);
-  const long long gs = (long long)g * (long long)sig;
-  const int t = (int)__funnelshift_r((unsigned)gs, (unsigned)(gs >> 32), 16);
-  const long long tu = (long long)t * (long long)u;
-  const int hi = (int)(tu >> 32);
-  const int res = (int)__funnelshift_r((unsigned)tu, (unsigned)hi, 16);
-  return (hi >> 15) == (res >> 31) ? res : (hi < 0 ? (int)(-2147483647 - 1) : 2147483647);
-}
-
+// ============================================================================ SiLU * up (element arithmetic: silu.cuh)
 // FWHT-128 of a block spread over an 8-lane group: each lane holds 16 values, index
 // i = e + 4*lane8 + 32*k for val[4*k + e] (e = 0..3 inside an int4, k = 0..3).
 // Stage order is the reference's (step 1, 2, 4, ... 64), with saturation at every stage.
@@ -449,7 +399,9 @@ static int silu_threads(int nblocks) {
 // TP: the row is this rank's slice of a token whose absmax spans all ranks' columns (the input of a row-split
 // linear): between the two phases the CTA takes part in the absmax agreement over the exchange blocks (one CTA per
 // row, all of them resident), quantises with the agreed value and reports it; `scale` is not written.
-template <bool FWHT, bool QUANT, bool TABLE, bool TP = false>
+// ACT = false: `gate_up` already holds SiLU(gate) * up, int32 [rows, I] (the gate_up GEMM applied it in its epilogue);
+// the kernel then only rotates and quantises.
+template <bool FWHT, bool QUANT, bool TABLE, bool TP = false, bool ACT = true>
 __global__ void __launch_bounds__(kSiluMaxThreads, 2)
 silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_out,
                  int8_t* __restrict__ codes, float* __restrict__ scale,
@@ -460,10 +412,10 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   int32_t* lut = rowbuf + (QUANT ? I : 0);
   const uint16_t* sneg_tab = reinterpret_cast<const uint16_t*>(lut);
   pdl_launch_dependents();
-  if (TABLE) {
-    const int4* src = reinterpret_cast<const int4*>(g_silu_sneg);      // 19457 entries: 2432 int4 + one entry
-    for (int i = threadIdx.x; i < kSnegEntries / 8; i += blockDim.x) reinterpret_cast<int4*>(lut)[i] = src[i];
-    if (threadIdx.x == 0) reinterpret_cast<uint16_t*>(lut)[kSnegEntries - 1] = g_silu_sneg[kSnegEntries - 1];
+  if (!ACT) {
+    // no table needed
+  } else if (TABLE) {
+    silu_stage_table(reinterpret_cast<uint16_t*>(lut));
   } else {
     for (int i = threadIdx.x; i < 1024; i += blockDim.x) lut[i] = g_exp2_silu_lut[i];
   }
@@ -476,7 +428,7 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   const int ngroups = blockDim.x >> 3;
   const int nblocks = I >> 7;
   const int niter = (nblocks + ngroups - 1) / ngroups;
-  const int32_t* gate = gate_up + row * 2 * (int64_t)I;
+  const int32_t* gate = gate_up + row * (ACT ? 2 : 1) * (int64_t)I;
   const int32_t* up = gate + I;
 
   int m = 0;
@@ -491,9 +443,11 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
       if (live) {
         const int off = b * 128 + k * 32 + lane8 * 4;
         g = __ldcs(reinterpret_cast<const int4*>(gate + off));
-        u = __ldcs(reinterpret_cast<const int4*>(up + off));
+        if (ACT) u = __ldcs(reinterpret_cast<const int4*>(up + off));
       }
-      if (TABLE) {
+      if (!ACT) {
+        val[4 * k + 0] = g.x; val[4 * k + 1] = g.y; val[4 * k + 2] = g.z; val[4 * k + 3] = g.w;
+      } else if (TABLE) {
         val[4 * k + 0] = silu_mul_elem_table(g.x, u.x, sneg_tab);
         val[4 * k + 1] = silu_mul_elem_table(g.y, u.y, sneg_tab);
         val[4 * k + 2] = silu_mul_elem_table(g.z, u.z, sneg_tab);
@@ -854,6 +808,38 @@ extern "C" int b200_silu_mul_q15(const int32_t* gate_up, int32_t* q15_out, int8_
     return check_launch("silu_mul_q15");
   }
   return launch_silu(gate_up, q15_out, codes, scale, absmax, rows, inter, fwht_block == 128, st);
+}
+
+extern "C" int b200_fwht_quant_q15(const int32_t* act, int8_t* codes, float* scale, int32_t* absmax, int64_t rows, int inter,
+                                   int fwht_block, b200_stream_t s) {
+  B200_REQUIRE(act && codes && scale && absmax, B200_E_NULL, "fwht_quant_q15: null pointer");
+  B200_REQUIRE(rows >= 0 && rows < (1ll << 31) && inter > 0, B200_E_SHAPE, "fwht_quant_q15: rows=%lld inter=%d", (long long)rows, inter);
+  B200_REQUIRE(fwht_block == 0 || fwht_block == 128, B200_E_UNSUPPORTED, "fwht_quant_q15: fwht_block=%d (0 or 128)", fwht_block);
+  B200_REQUIRE(inter % 128 == 0 && inter <= 49152, B200_E_UNSUPPORTED,
+               "fwht_quant_q15: inter=%d must be a multiple of 128 and at most 49152", inter);
+  if (rows == 0) return B200_OK;
+  B200_REQUIRE(aligned16(act) && ((uintptr_t)codes & 3u) == 0, B200_E_ALIGN, "fwht_quant_q15: act must be 16-byte aligned, codes 4-byte");
+  const int threads = silu_threads(inter / 128);
+  const size_t smem = (size_t)inter * sizeof(int32_t) + 16;
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    sms = 148;
+  const unsigned grid = (unsigned)(rows < 2 * (int64_t)sms ? rows : 2 * (int64_t)sms);
+  cudaStream_t st = (cudaStream_t)s;
+#define B200_FQ_LAUNCH(F)                                                                                                  \
+  do {                                                                                                                     \
+    cudaError_t e = cudaFuncSetAttribute(silu_rows_kernel<F, true, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                                       \
+    if (e != cudaSuccess) {                                                                                                \
+      set_error("fwht_quant_q15: cudaFuncSetAttribute: %s", cudaGetErrorString(e));                                        \
+      return B200_E_CUDA;                                                                                                  \
+    }                                                                                                                      \
+    launch_pdl(silu_rows_kernel<F, true, true, false, false>, dim3(grid), dim3(threads), smem, st, act, (int32_t*)nullptr, \
+               codes, scale, absmax, rows, inter, TpAgree{});                                                              \
+  } while (0)
+  if (fwht_block == 128) B200_FQ_LAUNCH(true); else B200_FQ_LAUNCH(false);
+#undef B200_FQ_LAUNCH
+  return check_launch("fwht_quant_q15");
 }
 
 extern "C" int b200_tp_silu_absmax_quant(const b200_tp_block* blk, const int32_t* gate_up, int8_t* codes, int32_t* absmax,

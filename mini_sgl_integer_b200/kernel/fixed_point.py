@@ -387,6 +387,22 @@ def silu_mul_fwht_quant(gate_up: torch.Tensor, fwht_block: int = 128, want_q15: 
     return codes, scale, absmax, q15
 
 
+def fwht_quant_q15(act: torch.Tensor, fwht_block: int = 128):
+    """Blocked FWHT -> per-token int8 quant of an activation that already is SiLU(gate) * up (the gate_up GEMM applied
+    it in its epilogue): the second half of silu_mul_fwht_quant.  Returns (codes, scale [..., 1], absmax [..., 1])."""
+    assert_q15(act, "act")
+    if act.ndim != 2:
+        raise ValueError(f"act must be 2D [tokens, inter], got shape {tuple(act.shape)}")
+    require_cuda(act)
+    a = act.contiguous()
+    rows, inter = a.shape
+    codes = torch.empty((rows, inter), dtype=torch.int8, device=a.device)
+    scale = torch.empty((rows, 1), dtype=torch.float32, device=a.device)
+    absmax = torch.empty((rows, 1), dtype=torch.int32, device=a.device)
+    call("b200_fwht_quant_q15", ptr(a), ptr(codes), ptr(scale), ptr(absmax), rows, inter, int(fwht_block), stream())
+    return codes, scale, absmax
+
+
 def silu_mul_fwht_q15(gate_up: torch.Tensor, fwht_block: int = 128) -> torch.Tensor:
     """SiLU(gate) * up -> blocked FWHT, Q15.16 out (no quant): silu_and_mul_int_only + apply_blockwise_fwht_q15."""
     assert_q15(gate_up, "gate_up")
@@ -421,5 +437,5 @@ __all__ = [
     "rope_int_q15", "fwht_int_q15", "rope_fwht_int_q15", "rmsnorm_int_only_v2",
     "fused_add_rmsnorm_int_only_v2", "silu_and_mul_int_only", "apply_blockwise_fwht_q15",
     "per_token_quant_int8_from_q15", "absmax_to_mul_shift", "fused_add_rmsnorm_quant",
-    "silu_mul_fwht_quant", "silu_mul_fwht_q15", "qk_norm_rope_fwht",
+    "silu_mul_fwht_quant", "silu_mul_fwht_q15", "fwht_quant_q15", "qk_norm_rope_fwht",
 ]

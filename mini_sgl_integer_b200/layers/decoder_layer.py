@@ -24,6 +24,10 @@ from .w8a8_int8 import W8A8Int8LinearMethod
 
 
 _PENDING_ON = os.environ.get("B200_PENDING", "1") != "0"       # "0": every linear materialises its Q15.16 output
+# "1": SiLU * up in the gate_up GEMM's epilogue at decode sizes.  Off by default: bit-identical, but measured slower on
+# the 8B shape at batch 256 (the GEMM 33.5 + 6.2 -> 56.6 + 8.1 us for a row kernel that drops from 19.1 to 11.1 us:
+# a CTA pair has 1.3 tiles, so the heavier epilogue is on its critical path instead of under the next tile's MMAs).
+_GATE_UP_SILU_ON = os.environ.get("B200_GATE_UP_SILU", "0") == "1"
 
 
 @dataclass
@@ -164,6 +168,12 @@ class Qwen3DecoderLayerInteger:
         # post_attention_layernorm (+ residual add) -> codes for gate_up_proj
         codes, _, absmax, residual, _ = fp.fused_add_rmsnorm_quant(o, residual, w["post_norm"])
         t["ln2_codes"], t["res2"] = codes, residual
+        if defer and _GATE_UP_SILU_ON and self.hadamard_block in (0, 128) and m.can_fuse_gate_up_silu(w["gate_up"], T):
+            # decode sizes on one GPU: SiLU(gate) * up in the gate_up GEMM's epilogue, then rotation + quant
+            act = m.apply_gate_up_silu(w["gate_up"], codes, absmax)
+            codes, _, absmax = fp.fwht_quant_q15(act, self.hadamard_block)
+            down = (m.apply_pending if defer_down else m.apply_quantised)(w["down"], codes, absmax)
+            return down, residual
         gate_up = m.apply_quantised(w["gate_up"], codes, absmax)
         t["gate_up"] = gate_up
         if tp:   # the token's absmax spans all ranks' columns: rotate locally, agree on the scale, then quantise

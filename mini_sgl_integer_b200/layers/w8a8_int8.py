@@ -155,6 +155,29 @@ class W8A8Int8LinearMethod:
             out = self._add_bias(out, bias)
         return out
 
+    @staticmethod
+    def can_fuse_gate_up_silu(layer, rows: int) -> bool:
+        """Whether ``apply_gate_up_silu`` takes this merged gate_up layer and batch: decode sizes, 128 activation
+        channels per CTA pair, per-channel shifts present."""
+        w = layer.weight
+        return (0 < rows <= PENDING_MAX_ROWS and w.shape[0] % 256 == 0 and w.shape[1] % 16 == 0 and w.is_contiguous()
+                and getattr(layer, "weight_shift", None) is not None and getattr(layer, "input_scale", None) is None)
+
+    def apply_gate_up_silu(self, layer, codes: torch.Tensor, absmax: torch.Tensor) -> torch.Tensor:
+        """The merged gate_up projection with SiLU(gate) * up applied in the GEMM's epilogue: int8 codes [rows, k] ->
+        Q15.16 int32 [rows, inter], the bits of silu_and_mul_q15(apply_quantised(layer, codes, absmax))."""
+        if getattr(layer, "weight_mul", None) is None:
+            self.process_weights_after_loading(layer)
+        x8 = codes.reshape(-1, codes.shape[-1]).contiguous()
+        require_cuda(x8, layer.weight, absmax, layer.weight_mul, layer.weight_shift)
+        m, n2 = x8.shape[0], layer.weight.shape[0]
+        out = torch.empty((m, n2 // 2), dtype=torch.int32, device=x8.device)
+        if m:
+            call("b200_gemm_gate_up_silu", ptr(x8), ptr(layer.weight), ptr(absmax.reshape(-1).to(torch.int32).contiguous()),
+                 ptr(layer.weight_mul), ptr(layer.weight_shift), ptr(out), ptr(zero_workspace(x8.device, m, n2)), m, n2,
+                 x8.shape[1], stream())
+        return out
+
     def apply_pending(self, layer, codes: torch.Tensor, absmax: torch.Tensor) -> PendingLinear:
         """apply_quantised without the requantisation: the exact accumulators stay in a zero workspace and the next
         row kernel (fused_add_rmsnorm_quant, qkv_rope_quant_store) finishes the linear while it loads them."""

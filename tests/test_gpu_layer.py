@@ -90,3 +90,11 @@ def test_decoder_layer_8b_shape_bit_exact(mode):
     kv_lens = [5, 40, 17, 130, 64, 33]
     q_lens = [2, 1, 3, 1, 1, 2] if mode == "extend" else [1] * 6
     _run_case(3, kv_lens, q_lens, mode == "decode", 32, 8, 4096, 12288, 40, wide=True)
+
+
+def test_decoder_layer_with_silu_in_the_gate_up_epilogue(monkeypatch):
+    """The optional form that applies SiLU * up in the gate_up GEMM's epilogue (off by default): the same layer bits."""
+    from mini_sgl_integer_b200.layers import decoder_layer
+    monkeypatch.setattr(decoder_layer, "_GATE_UP_SILU_ON", True)
+    _run_case(0, [16, 32, 64, 128], [1, 1, 1, 1], True, HQ, HK, HID, INTER, 32)
+    _run_case(3, [5, 40, 17, 130, 64, 33], [2, 1, 3, 1, 1, 2], False, 32, 8, 4096, 12288, 40, wide=True)

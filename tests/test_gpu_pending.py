@@ -132,3 +132,28 @@ def test_a_pending_linear_that_nobody_consumed_is_cleared_by_reset():
     reset_workspaces()
     assert _workspaces_zero()
     np.testing.assert_array_equal(meth.apply_quantised(layer, d(codes), d(absmax)).cpu().numpy(), q15)
+
+
+@pytest.mark.parametrize("m,inter,k,block", [(1, 128, 256, 128), (65, 3072, 1024, 128), (200, 12288, 4096, 128), (256, 12288, 4096, 128),
+                                            (33, 9472 + 128, 512, 128), (256, 1536, 2048, 0), (130, 256, 8192, 128)])
+def test_gate_up_with_silu_in_the_epilogue(m, inter, k, block):
+    """gate_up GEMM with SiLU(gate) * up in its epilogue, then rotation + quant: the bits of the unfused chain (GEMM,
+    then the SiLU row kernel) and of the oracle.  Shapes with only whole blocks, with a split tail (96 blocks on 74 CTA
+    pairs), with fewer blocks than pairs (deep splits) and with a single block."""
+    from mini_sgl_integer_b200.kernel import fixed_point as fp
+    from mini_sgl_integer_b200.layers.w8a8_int8 import W8A8Int8LinearMethod
+    codes, absmax, w8, wm, ws, acc, q15 = _linear_case(m + inter + k, m, 2 * inter, k)
+    layer, meth = _layer(w8, wm, ws), W8A8Int8LinearMethod()
+    assert meth.can_fuse_gate_up_silu(layer, m)
+    want_act = ofp.silu_and_mul(q15)
+    want_rot = ofp.blockwise_fwht_q15(want_act, block) if block else want_act
+    want_codes, _, want_absmax = ofp.per_token_quant_from_q15(want_rot)
+    for _ in range(2):
+        act = meth.apply_gate_up_silu(layer, d(codes), d(absmax))
+        np.testing.assert_array_equal(act.cpu().numpy(), want_act)
+        assert _workspaces_zero()
+        got_codes, got_scale, got_absmax = fp.fwht_quant_q15(act, block)
+        np.testing.assert_array_equal(got_codes.cpu().numpy(), want_codes)
+        np.testing.assert_array_equal(got_absmax.cpu().numpy().reshape(-1), want_absmax.reshape(-1))
+    ref = fp.silu_mul_fwht_quant(meth.apply_quantised(layer, d(codes), d(absmax)), block)
+    assert torch.equal(ref[0], got_codes) and torch.equal(ref[1], got_scale) and torch.equal(ref[2], got_absmax)
