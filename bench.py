@@ -472,7 +472,8 @@ def run_model(args) -> None:
     cfg = Qwen3IntegerConfig(L, HID, hq, hk, inter, VOCAB, max_pos=4096)
     pool = Int8PagedKVCache(hk, L, 128, P, dev)
     fill_pool_random(pool, L, torch.Generator(device=dev).manual_seed(5 + rank), v_shift=(36, 40))
-    state = DecodeBatch(torch.from_numpy(table).to(dev), torch.from_numpy(lens.astype(np.int32)).to(dev), max_len)
+    state = DecodeBatch(torch.from_numpy(table).to(dev), torch.from_numpy(lens.astype(np.int32)).to(dev), max_len,
+                        first_wave_rows=max(1, 296 // hk))
     lm = Qwen3ForCausalLMInteger(cfg, weights, pool, comm, exch)
     h_in = torch.from_numpy(rng.integers(0, VOCAB, B).astype(np.int32)).pin_memory()
     h_out = torch.empty(B, dtype=torch.int32).pin_memory()

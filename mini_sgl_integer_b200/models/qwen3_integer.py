@@ -124,11 +124,13 @@ class DecodeBatch:
         # Every sequence grows by one token per step, so the order by length never changes.  Longest first keeps the
         # tail of the attention launch short; but the CTAs of the FIRST wave start together, and rows of similar
         # length then move through their streaming and scalar phases in lock-step, leaving HBM idle in between.
-        # So the first wave (about 296 CTA slots / 8 KV heads = 37 rows) is a sample across the whole length range
-        # (every 7th row of the sorted list), and the other rows follow longest first (145 -> 139 us on the 8B shape).
+        # So the first wave (`first_wave_rows`: about 296 CTA slots / KV heads of this rank, 37 rows for 8 heads) is a
+        # sample across the whole length range (every batch / first_wave_rows-th row of the sorted list), and the other
+        # rows follow longest first (145 -> 139 us on the 8B shape at batch 256).
         desc = torch.argsort(self.seq_lens, descending=True, stable=True)
-        if self.batch > 2 * first_wave_rows:
-            head = desc[0::7][:first_wave_rows]
+        step = self.batch // max(first_wave_rows, 1)
+        if step >= 2:
+            head = desc[0::step][:first_wave_rows]
             keep = torch.ones(self.batch, dtype=torch.bool, device=dev)
             keep[head] = False
             desc = torch.cat((head, desc[keep[desc]]))
