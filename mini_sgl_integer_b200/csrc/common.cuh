@@ -134,38 +134,37 @@ __device__ __forceinline__ int quant_code(int x, float mf) {
   int r = __float2int_rn(q);
   return max(-128, min(127, r));
 }
-// The same code with the division replaced by a multiply and two fused multiply-adds on the
-// row's correctly rounded reciprocal (y = __frcp_rn(mf)): q1 = fma(fma(-mf, a*y, a), y, a*y) is
-// the correctly rounded quotient up to, at worst, a few units in the last place, so it can only
-// disagree with the division after rounding to an integer when it lies within a hair of a
-// half-integer; in that band (2^-10 wide, far above any such error) the true division is used.
+// The same code with the division replaced by a multiply with the row's correctly rounded reciprocal
+// (y = __frcp_rn(mf)): a * y is within a few units in the last place of the quotient (|q| <= 128: an absolute error
+// below 2^-16), so after rounding to an integer it can only disagree with the division when it lies within a hair
+// of a half-integer; in that band (2^-10 wide, far above any such error) the true division is used.
 // Rounding to the nearest-even integer is done by adding 1.5 * 2^23 (-128 <= q <= 127 after the lower clamp).
 __device__ __forceinline__ int quant_code_fast(int x, float mf, float y) {
   const float a = __fmul_rn(__int2float_rn(x), 127.0f);
-  const float q0 = __fmul_rn(a, y);
   // x = -2^31 never enters the row's absmax (its |x| wraps to a negative), so its quotient can lie far below
   // -128: the lower clamp of the reference is kept (an upper one is not needed: every other |x| <= absmax)
-  float q1 = fmaxf(__fmaf_rn(__fmaf_rn(-mf, q0, a), y, q0), -128.0f);
-  float t = __fadd_rn(q1, 12582912.0f);                       // integer part now sits in the mantissa
-  if (fabsf(__fsub_rn(q1, __fsub_rn(t, 12582912.0f))) > 0.4990234375f)   // within 2^-10 of a half-integer
+  const float q = fmaxf(__fmul_rn(a, y), -128.0f);
+  float t = __fadd_rn(q, 12582912.0f);                        // integer part now sits in the mantissa
+  if (fabsf(__fsub_rn(q, __fsub_rn(t, 12582912.0f))) > 0.4990234375f)    // within 2^-10 of a half-integer
     t = __fadd_rn(fmaxf(__fdiv_rn(a, mf), -128.0f), 12582912.0f);
   return __float_as_int(t) - 0x4B400000;
 }
 // quant_code_fast for rows whose absmax is below 2^22: int -> float by placing the value in the mantissa
-// of 1.5 * 2^23 (exact for |x| < 2^22) instead of the conversion unit.
-__device__ __forceinline__ int quant_code_fast_small(int x, float mf, float y) {
+// of 1.5 * 2^23 (exact for |x| < 2^22) instead of the conversion unit, and one multiply with y127 =
+// __fmul_rn(127, __frcp_rn(mf)) for the estimate (one more rounding: still below 2^-15).  Returns a word whose LOW
+// BYTE is the code (the mantissa of 1.5 * 2^23 + q; pack4 takes the low bytes).
+__device__ __forceinline__ unsigned quant_byte_fast_small(int x, float mf, float y127) {
   const float xf = __int_as_float(0x4B400000 + x) - 12582912.0f;
-  const float a = __fmul_rn(xf, 127.0f);
-  const float q0 = __fmul_rn(a, y);
   // -2^31 (not counted in the absmax) comes out of the mantissa trick as -25165824: still far below -128 * absmax / 127
-  float q1 = fmaxf(__fmaf_rn(__fmaf_rn(-mf, q0, a), y, q0), -128.0f);
-  float t = __fadd_rn(q1, 12582912.0f);
-  if (fabsf(__fsub_rn(q1, __fsub_rn(t, 12582912.0f))) > 0.4990234375f)
-    t = __fadd_rn(fmaxf(__fdiv_rn(a, mf), -128.0f), 12582912.0f);
-  return __float_as_int(t) - 0x4B400000;
+  const float q = fmaxf(__fmul_rn(xf, y127), -128.0f);
+  float t = __fadd_rn(q, 12582912.0f);
+  if (fabsf(__fsub_rn(q, __fsub_rn(t, 12582912.0f))) > 0.4990234375f)
+    t = __fadd_rn(fmaxf(__fdiv_rn(__fmul_rn(xf, 127.0f), mf), -128.0f), 12582912.0f);
+  return __float_as_uint(t);
 }
 __device__ __forceinline__ float quant_scale(float mf) { return __fdiv_rn(mf, 8323072.0f); }
 
+// Packs the LOW BYTES of four words (codes, or words from quant_byte_fast_small).
 __device__ __forceinline__ unsigned pack4(int a, int b, int c, int d) {
   // two byte permutes: (a,b) -> low half, (c,d) -> high half, then merge
   const unsigned ab = __byte_perm((unsigned)a, (unsigned)b, 0x0040);

@@ -154,12 +154,13 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
   const float my = __frcp_rn(mf);
   unsigned* co = reinterpret_cast<unsigned*>(codes + row * H);
   if (m2 < (1 << 22)) {   // block-uniform: conversions without the conversion unit
+    const float my127 = __fmul_rn(my, 127.0f);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * blockDim.x;
       if (FULL || idx < nvec) {
-        co[idx] = pack4(quant_code_fast_small(v[i].x, mf, my), quant_code_fast_small(v[i].y, mf, my),
-                        quant_code_fast_small(v[i].z, mf, my), quant_code_fast_small(v[i].w, mf, my));
+        co[idx] = pack4(quant_byte_fast_small(v[i].x, mf, my127), quant_byte_fast_small(v[i].y, mf, my127),
+                        quant_byte_fast_small(v[i].z, mf, my127), quant_byte_fast_small(v[i].w, mf, my127));
       }
     }
   } else {
@@ -342,13 +343,12 @@ __device__ __forceinline__ void fwht128_group(int (&val)[16], int lane8) {
   }
 }
 
-// The n = 128 scale rsr15(y * 2896) in 32-bit arithmetic.  2896 = 16 * 181, so
-// (16a +- 2^14) >> 15 == (a +- 2^10) >> 11 with a = y * 181; splitting y = yh * 2^11 + yl
-// (yl in [0, 2048)) gives yh * 181 + ((yl * 181 +- 2^10) >> 11), all below 2^31.  |result| < |y|.
+// The n = 128 scale rsr15(y * 2896).  2896 = 16 * 181, so (16a +- 2^14) >> 15 == (a +- 2^10) >> 11 with a = y * 181
+// (64 bits), and for y < 0 floor((a - 2^10) / 2^11) == floor((a + 2^10) / 2^11) - 1: one wide multiply-add, one
+// funnel shift (the result fits: |result| < |y|) and the sign word.
 __device__ __forceinline__ int fwht_scale128(int y) {
-  const int yh = y >> 11, yl = y & 2047;
-  const int bias = 1024 - ((y >> 31) & 2048);          // +1024 for y >= 0, -1024 for y < 0
-  return yh * 181 + ((yl * 181 + bias) >> 11);
+  const long long a = (long long)y * 181LL + 1024LL;
+  return (int)__funnelshift_r((unsigned)a, (unsigned)(a >> 32), 11) + (y >> 31);
 }
 
 // FWHT-128 butterflies without saturation: valid when every input satisfies |v| < 2^24, so that
@@ -407,8 +407,9 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
                  int8_t* __restrict__ codes, float* __restrict__ scale,
                  int32_t* __restrict__ absmax, int64_t rows, int I, const TpAgree agree) {
   extern __shared__ __align__(16) int32_t rowbuf[];   // QUANT: [I] results of the row; then the table
-  __shared__ int red32[33];
+  __shared__ int red32[2][32];
   __shared__ int agree_slot;
+  int row_no = 0;
   int32_t* lut = rowbuf + (QUANT ? I : 0);
   const uint16_t* sneg_tab = reinterpret_cast<const uint16_t*>(lut);
   pdl_launch_dependents();
@@ -430,28 +431,70 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   const int niter = (nblocks + ngroups - 1) / ngroups;
   const int32_t* gate = gate_up + row * (ACT ? 2 : 1) * (int64_t)I;
   const int32_t* up = gate + I;
+  if (row + gridDim.x < rows) {        // this CTA's next row on its way into L2 while this one is worked on
+    const char* next = reinterpret_cast<const char*>(gate + (int64_t)gridDim.x * (ACT ? 2 : 1) * I);
+    const int chunks = (ACT ? 2 : 1) * I / 128;                         // of 512 bytes: I is a multiple of 128
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x)
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], 512;" ::"l"(next + (size_t)c * 512) : "memory");
+  }
 
   int m = 0;
   for (int it = 0; it < niter; ++it) {           // uniform trip count: the shuffles need whole warps
     const int b = group + it * ngroups;
     const bool live = b < nblocks;
     int val[16];
-    int big = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      int4 g = make_int4(0, 0, 0, 0), u = make_int4(0, 0, 0, 0);
+    auto load = [&](int k, int4& g, int4& u) {
+      g = make_int4(0, 0, 0, 0);
+      u = make_int4(0, 0, 0, 0);
       if (live) {
         const int off = b * 128 + k * 32 + lane8 * 4;
         g = __ldcs(reinterpret_cast<const int4*>(gate + off));
         if (ACT) u = __ldcs(reinterpret_cast<const int4*>(up + off));
       }
+    };
+    constexpr bool kCheckFirst = ACT && TABLE;     // all 16 gate / up pairs are needed before the first element
+    int4 gq[4], uq[4];
+    if (kCheckFirst) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) load(k, gq[k], uq[k]);
+    }
+    // Warp-uniform: every |gate| and |up| of the warp's four blocks below 2^20 (16.0), so that neither the products
+    // nor the butterflies can saturate (|SiLU * up| < 2^24) and the checks per element are left out.
+    bool small = false;
+    if (kCheckFirst) {
+      int amin = 0, ubig = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        amin = min(min(amin, min(gq[k].x, -gq[k].x)), min(gq[k].y, -gq[k].y));
+        amin = min(min(amin, min(gq[k].z, -gq[k].z)), min(gq[k].w, -gq[k].w));
+        ubig |= (uq[k].x ^ (uq[k].x >> 31)) | (uq[k].y ^ (uq[k].y >> 31)) | (uq[k].z ^ (uq[k].z >> 31)) |
+                (uq[k].w ^ (uq[k].w >> 31));
+      }
+      small = !__any_sync(FULL_MASK, amin <= -(1 << 20) || ubig >= (1 << 20));
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      int4 g, u;
+      if (kCheckFirst) {
+        g = gq[k];
+        u = uq[k];
+      } else {
+        load(k, g, u);
+      }
       if (!ACT) {
         val[4 * k + 0] = g.x; val[4 * k + 1] = g.y; val[4 * k + 2] = g.z; val[4 * k + 3] = g.w;
       } else if (TABLE) {
-        val[4 * k + 0] = silu_mul_elem_table(g.x, u.x, sneg_tab);
-        val[4 * k + 1] = silu_mul_elem_table(g.y, u.y, sneg_tab);
-        val[4 * k + 2] = silu_mul_elem_table(g.z, u.z, sneg_tab);
-        val[4 * k + 3] = silu_mul_elem_table(g.w, u.w, sneg_tab);
+        if (small) {
+          val[4 * k + 0] = silu_mul_elem_table_small(g.x, min(g.x, -g.x), u.x, sneg_tab);
+          val[4 * k + 1] = silu_mul_elem_table_small(g.y, min(g.y, -g.y), u.y, sneg_tab);
+          val[4 * k + 2] = silu_mul_elem_table_small(g.z, min(g.z, -g.z), u.z, sneg_tab);
+          val[4 * k + 3] = silu_mul_elem_table_small(g.w, min(g.w, -g.w), u.w, sneg_tab);
+        } else {
+          val[4 * k + 0] = silu_mul_elem_table(g.x, u.x, sneg_tab);
+          val[4 * k + 1] = silu_mul_elem_table(g.y, u.y, sneg_tab);
+          val[4 * k + 2] = silu_mul_elem_table(g.z, u.z, sneg_tab);
+          val[4 * k + 3] = silu_mul_elem_table(g.w, u.w, sneg_tab);
+        }
       } else {
         val[4 * k + 0] = silu_mul_elem(g.x, u.x, lut);
         val[4 * k + 1] = silu_mul_elem(g.y, u.y, lut);
@@ -460,9 +503,14 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
       }
     }
     if (FWHT) {
+      bool sat = false;
+      if (!small) {
+        int big = 0;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) big |= val[j] ^ (val[j] >> 31);   // >= 2^24 iff some |v| >= 2^24 (-2^24 also passes)
-      if (__any_sync(FULL_MASK, big >= (1 << 24))) {
+        for (int j = 0; j < 16; ++j) big |= val[j] ^ (val[j] >> 31);   // >= 2^24 iff some |v| >= 2^24 (-2^24 also passes)
+        sat = __any_sync(FULL_MASK, big >= (1 << 24));
+      }
+      if (sat) {
         fwht128_group(val, lane8);                // saturating butterflies, the reference's stage order
       } else {
         fwht128_group_nosat(val, lane8);
@@ -485,29 +533,44 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
     }
   }
   if (!QUANT) continue;
-  m = max(1, block_max(m, red32));     // its barriers also order the rowbuf writes before the reads
+  // One barrier per row: the reduction scratch alternates between consecutive rows (a slot is written again only
+  // after the barrier of the row in between, which every reader of its old value has passed), and every thread
+  // quantises exactly the values it parked itself, so warps run on into their next row while others still quantise.
+  {
+    int* red = red32[(row_no++) & 1];
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = warp_max((int)(threadIdx.x & 31) < (int)((blockDim.x + 31) >> 5) ? red[threadIdx.x & 31] : 0);
+    m = max(1, m);
+  }
   if (TP) m = tp_agree_cta(agree, (int)row, m, &agree_slot);
   const float mf = __int2float_rn(m);
   const float my = __frcp_rn(mf);
   unsigned* co = reinterpret_cast<unsigned*>(codes + row * (int64_t)I);
-  if (m < (1 << 22)) {   // the usual case (block-uniform): conversions without the conversion unit
-    for (int i = threadIdx.x; i < (I >> 2); i += blockDim.x) {
+  const bool small_m = m < (1 << 22);    // the usual case (block-uniform): conversions without the conversion unit
+  const float my127 = __fmul_rn(my, 127.0f);
+  for (int it = 0; it < niter; ++it) {
+    const int b = group + it * ngroups;
+    if (b >= nblocks) break;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = b * 32 + k * 8 + lane8;
       const int4 v = reinterpret_cast<const int4*>(rowbuf)[i];
-      co[i] = pack4(quant_code_fast_small(v.x, mf, my), quant_code_fast_small(v.y, mf, my),
-                    quant_code_fast_small(v.z, mf, my), quant_code_fast_small(v.w, mf, my));
-    }
-  } else {
-    for (int i = threadIdx.x; i < (I >> 2); i += blockDim.x) {
-      const int4 v = reinterpret_cast<const int4*>(rowbuf)[i];
-      co[i] = pack4(quant_code_fast(v.x, mf, my), quant_code_fast(v.y, mf, my), quant_code_fast(v.z, mf, my),
-                    quant_code_fast(v.w, mf, my));
+      if (small_m) {
+        co[i] = pack4(quant_byte_fast_small(v.x, mf, my127), quant_byte_fast_small(v.y, mf, my127),
+                      quant_byte_fast_small(v.z, mf, my127), quant_byte_fast_small(v.w, mf, my127));
+      } else {
+        co[i] = pack4(quant_code_fast(v.x, mf, my), quant_code_fast(v.y, mf, my), quant_code_fast(v.z, mf, my),
+                      quant_code_fast(v.w, mf, my));
+      }
     }
   }
   if (threadIdx.x == 0) {
     if (!TP) scale[row] = quant_scale(mf);
     absmax[row] = m;
   }
-  __syncthreads();                     // the row buffer and the reduction scratch are reused by the next row
+  if (TP) __syncthreads();             // the agreement's shared word is reused by the next row
   }
 }
 

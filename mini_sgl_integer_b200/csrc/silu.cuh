@@ -56,6 +56,19 @@ __device__ __forceinline__ int silu_mul_elem_table(int g, int u, const uint16_t*
   return (hi >> 15) == (res >> 31) ? res : (hi < 0 ? (int)(-2147483647 - 1) : 2147483647);
 }
 
+// The same element when |g| < 2^23 and |u| < 2^24 (the caller has checked): no product can saturate (|t| <= |g|, so
+// |t * u| < 2^47).  `a` = -|g|.  With s the table's sigmoid term of -|g|, (g * sig) >> 16 is (a * s) >> 16 for
+// g <= 0 and, for g > 0, (g * 2^16 - g * s) >> 16 = g + ((a * s) >> 16) exactly (the first term is a multiple of
+// 2^16): one form for both signs.  Keys below the table are clamped to entry 0, which is 0.
+__device__ __forceinline__ int silu_mul_elem_table_small(int g, int a, int u, const uint16_t* __restrict__ sneg_tab) {
+  const long long prod = (long long)a * 94549LL;
+  const int key = max((int)(prod >> 22) + (kSnegEntries - 1), 0);
+  const long long as = (long long)a * (long long)(int)sneg_tab[key];
+  const int t = (int)__funnelshift_r((unsigned)as, (unsigned)(as >> 32), 16) + max(g, 0);
+  const long long tu = (long long)t * (long long)u;
+  return (int)__funnelshift_r((unsigned)tu, (unsigned)(tu >> 32), 16);
+}
+
 // Stages the direct sigmoid table (kSnegEntries uint16, 38 KB) into shared memory; all threads of the CTA take part.
 __device__ __forceinline__ void silu_stage_table(uint16_t* dst) {
   const int4* src = reinterpret_cast<const int4*>(g_silu_sneg);      // 19457 entries: 2432 int4 + one entry

@@ -184,6 +184,35 @@ def test_silu_fused_vs_oracle(fp, rows, inter):
     eq(host(codes), q0); eq(host(scale), s0); eq(host(absmax), m0)
 
 
+def test_silu_fused_magnitude_threshold(fp):
+    """Warps whose gate / up magnitudes all lie below 2**20 take a path without saturation checks: values at and
+    around the limit, and single outliers far above it, in some 128-blocks of a row and not in others."""
+    rng = np.random.default_rng(23)
+    rows, inter = 6, 4096
+    x = np.rint(rng.normal(0, 2**17, (rows, 2 * inter))).astype(np.int64)
+    x = np.clip(x, -(2**20) + 1, 2**20 - 1)
+    edge = [2**20 - 1, -(2**20) + 1, 2**20, -(2**20), 2**20 + 1, -(2**20) - 1, 2**23, -(2**23), 2**24, 2**27, -(2**31), 2**31 - 1]
+    for r in range(rows):
+        for j, e in enumerate(edge):
+            blk = (3 * j + r) % (inter // 128)
+            col = blk * 128 + int(rng.integers(0, 128))
+            x[r, col + (inter if (j + r) % 2 else 0)] = e                     # gate half or up half
+            if r == rows - 1:
+                x[r, col], x[r, col + inter] = e, edge[(j + 5) % len(edge)]    # both halves of one element
+    x[0, :] = np.clip(x[0, :], -(2**20) + 1, 2**20 - 1)                        # one row entirely on the short path
+    x[0, 5], x[0, inter + 5] = -(2**20) + 1, 2**20 - 1                         # the largest product the short path sees
+    x[0, 6], x[0, inter + 6] = 2**20 - 1, -(2**20)
+    x = x.astype(np.int32)
+    s = ofp.silu_and_mul(x)
+    f = ofp.blockwise_fwht_q15(s, 128)
+    q, sc, m = ofp.per_token_quant_from_q15(f)
+    codes, scale, absmax, q15 = fp.silu_mul_fwht_quant(dev(x), 128, want_q15=True)
+    eq(host(q15), f); eq(host(codes), q); eq(host(scale), sc); eq(host(absmax), m)
+    q0, s0, m0 = ofp.per_token_quant_from_q15(s)
+    codes, scale, absmax, _ = fp.silu_mul_fwht_quant(dev(x), 0)
+    eq(host(codes), q0); eq(host(absmax), m0)
+
+
 def test_silu_large_magnitudes_and_odd_width(fp):
     rng = np.random.default_rng(11)
     x = rng.integers(-(2**31), 2**31, (4, 2 * 256), dtype=np.int64).astype(np.int32)
