@@ -458,19 +458,21 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
 #pragma unroll
       for (int k = 0; k < 4; ++k) load(k, gq[k], uq[k]);
     }
-    // Warp-uniform: every |gate| and |up| of the warp's four blocks below 2^20 (16.0), so that neither the products
-    // nor the butterflies can saturate (|SiLU * up| < 2^24) and the checks per element are left out.
+    // Warp-uniform: every gate and up of the warp's four blocks in [-2^20, 2^20) (16.0), so that neither the
+    // products nor the butterflies can saturate (|SiLU * up| < 2^24) and the checks per element are left out.
+    // v + 2^20 has a bit above bit 20 exactly when v is outside that range.
     bool small = false;
     if (kCheckFirst) {
-      int amin = 0, ubig = 0;
+      unsigned out = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        amin = min(min(amin, min(gq[k].x, -gq[k].x)), min(gq[k].y, -gq[k].y));
-        amin = min(min(amin, min(gq[k].z, -gq[k].z)), min(gq[k].w, -gq[k].w));
-        ubig |= (uq[k].x ^ (uq[k].x >> 31)) | (uq[k].y ^ (uq[k].y >> 31)) | (uq[k].z ^ (uq[k].z >> 31)) |
-                (uq[k].w ^ (uq[k].w >> 31));
+        constexpr unsigned kOff = 1u << 20;
+        out |= ((unsigned)gq[k].x + kOff) | ((unsigned)uq[k].x + kOff);
+        out |= ((unsigned)gq[k].y + kOff) | ((unsigned)uq[k].y + kOff);
+        out |= ((unsigned)gq[k].z + kOff) | ((unsigned)uq[k].z + kOff);
+        out |= ((unsigned)gq[k].w + kOff) | ((unsigned)uq[k].w + kOff);
       }
-      small = !__any_sync(FULL_MASK, amin <= -(1 << 20) || ubig >= (1 << 20));
+      small = !__any_sync(FULL_MASK, out >= (1u << 21));
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -485,10 +487,10 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
         val[4 * k + 0] = g.x; val[4 * k + 1] = g.y; val[4 * k + 2] = g.z; val[4 * k + 3] = g.w;
       } else if (TABLE) {
         if (small) {
-          val[4 * k + 0] = silu_mul_elem_table_small(g.x, min(g.x, -g.x), u.x, sneg_tab);
-          val[4 * k + 1] = silu_mul_elem_table_small(g.y, min(g.y, -g.y), u.y, sneg_tab);
-          val[4 * k + 2] = silu_mul_elem_table_small(g.z, min(g.z, -g.z), u.z, sneg_tab);
-          val[4 * k + 3] = silu_mul_elem_table_small(g.w, min(g.w, -g.w), u.w, sneg_tab);
+          val[4 * k + 0] = silu_mul_elem_table_small(g.x, u.x, sneg_tab);
+          val[4 * k + 1] = silu_mul_elem_table_small(g.y, u.y, sneg_tab);
+          val[4 * k + 2] = silu_mul_elem_table_small(g.z, u.z, sneg_tab);
+          val[4 * k + 3] = silu_mul_elem_table_small(g.w, u.w, sneg_tab);
         } else {
           val[4 * k + 0] = silu_mul_elem_table(g.x, u.x, sneg_tab);
           val[4 * k + 1] = silu_mul_elem_table(g.y, u.y, sneg_tab);
@@ -528,8 +530,18 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
       }
     }
     if (QUANT) {
+      if (small) {                       // no value can be -2^31 here: the largest and the smallest give the absmax
+        int hi = val[0], lo = val[0];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) m = max(m, abs_wrap(val[j]));
+        for (int j = 1; j < 16; j += 2) {
+          hi = __vimax3_s32(hi, val[j], val[(j + 1) & 15]);
+          lo = __vimin3_s32(lo, val[j], val[(j + 1) & 15]);
+        }
+        m = __vimax3_s32(m, hi, -lo);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) m = max(m, abs_wrap(val[j]));
+      }
     }
   }
   if (!QUANT) continue;

@@ -57,13 +57,17 @@ __device__ __forceinline__ int silu_mul_elem_table(int g, int u, const uint16_t*
 }
 
 // The same element when |g| < 2^23 and |u| < 2^24 (the caller has checked): no product can saturate (|t| <= |g|, so
-// |t * u| < 2^47).  `a` = -|g|.  With s the table's sigmoid term of -|g|, (g * sig) >> 16 is (a * s) >> 16 for
-// g <= 0 and, for g > 0, (g * 2^16 - g * s) >> 16 = g + ((a * s) >> 16) exactly (the first term is a multiple of
-// 2^16): one form for both signs.  Keys below the table are clamped to entry 0, which is 0.
-__device__ __forceinline__ int silu_mul_elem_table_small(int g, int a, int u, const uint16_t* __restrict__ sneg_tab) {
+// |t * u| < 2^47).  With a = -|g| and s the table's sigmoid term of a, (g * sig) >> 16 is (a * s) >> 16 for g <= 0
+// and, for g > 0, (g * 2^16 - g * s) >> 16 = g + ((a * s) >> 16) exactly (the first term is a multiple of 2^16):
+// one form for both signs.  The table's first entry (key -19456, reached from a = kSnegFirstA) is 0 like everything
+// below it, so a is clamped there instead of the key.
+constexpr int kSnegFirstA = -863090;     // the smallest a with (a * 94549) >> 22 >= -(kSnegEntries - 1)
+static_assert(((long long)kSnegFirstA * 94549LL >> 22) == -(kSnegEntries - 1) &&
+              ((long long)(kSnegFirstA - 1) * 94549LL >> 22) == -kSnegEntries, "first key of the sigmoid table");
+__device__ __forceinline__ int silu_mul_elem_table_small(int g, int u, const uint16_t* __restrict__ sneg_tab) {
+  const int a = max(min(g, -g), kSnegFirstA);
   const long long prod = (long long)a * 94549LL;
-  const int key = max((int)(prod >> 22) + (kSnegEntries - 1), 0);
-  const long long as = (long long)a * (long long)(int)sneg_tab[key];
+  const long long as = (long long)a * (long long)(int)sneg_tab[(int)(prod >> 22) + (kSnegEntries - 1)];
   const int t = (int)__funnelshift_r((unsigned)as, (unsigned)(as >> 32), 16) + max(g, 0);
   const long long tu = (long long)t * (long long)u;
   return (int)__funnelshift_r((unsigned)tu, (unsigned)(tu >> 32), 16);
