@@ -149,22 +149,38 @@ __device__ __forceinline__ int quant_code_fast(int x, float mf, float y) {
     t = __fadd_rn(fmaxf(__fdiv_rn(a, mf), -128.0f), 12582912.0f);
   return __float_as_int(t) - 0x4B400000;
 }
-// quant_code_fast for rows whose absmax is below 2^22: int -> float by placing the value in the mantissa
-// of 1.5 * 2^23 (exact for |x| < 2^22) instead of the conversion unit, and one multiply with y127 =
-// __fmul_rn(127, __frcp_rn(mf)) for the estimate (one more rounding: still below 2^-15).  Returns a word whose LOW
-// BYTE is the code (the mantissa of 1.5 * 2^23 + q; pack4 takes the low bytes).
-__device__ __forceinline__ unsigned quant_byte_fast_small(int x, float mf, float y127) {
-  const float xf = __int_as_float(0x4B400000 + x) - 12582912.0f;
-  // -2^31 (not counted in the absmax) comes out of the mantissa trick as -25165824: still far below -128 * absmax / 127
-  const float q = fmaxf(__fmul_rn(xf, y127), -128.0f);
-  float t = __fadd_rn(q, 12582912.0f);
-  if (fabsf(__fsub_rn(q, __fsub_rn(t, 12582912.0f))) > 0.4990234375f)
-    t = __fadd_rn(fmaxf(__fdiv_rn(__fmul_rn(xf, 127.0f), mf), -128.0f), 12582912.0f);
-  return __float_as_uint(t);
-}
 __device__ __forceinline__ float quant_scale(float mf) { return __fdiv_rn(mf, 8323072.0f); }
 
-// Packs the LOW BYTES of four words (codes, or words from quant_byte_fast_small).
+// quant_code_fast for four values of a row whose absmax is below 2^22: int -> float by placing the value in the
+// mantissa of 1.5 * 2^23 (exact for |x| < 2^22) instead of the conversion unit, one multiply with y127 =
+// __fmul_rn(127, __frcp_rn(mf)) for the estimate (one more rounding: still below 2^-15), ONE test for "some value
+// within 2^-10 of a half-integer" and then the division for all four.  The codes are the low bytes of the mantissas
+// of 1.5 * 2^23 + q.  -2^31 (not counted in the absmax) comes out of the mantissa trick as -25165824, still far below
+// -128 * absmax / 127; CLAMP = false leaves out the lower clamp: only for values known not to be -2^31.
+template <bool CLAMP>
+__device__ __forceinline__ unsigned quant4_bytes_fast_small(int4 v, float mf, float y127) {
+  constexpr float kMagic = 12582912.0f;
+  const float x0 = __int_as_float(0x4B400000 + v.x) - kMagic, x1 = __int_as_float(0x4B400000 + v.y) - kMagic;
+  const float x2 = __int_as_float(0x4B400000 + v.z) - kMagic, x3 = __int_as_float(0x4B400000 + v.w) - kMagic;
+  float q0 = __fmul_rn(x0, y127), q1 = __fmul_rn(x1, y127), q2 = __fmul_rn(x2, y127), q3 = __fmul_rn(x3, y127);
+  if (CLAMP) {
+    q0 = fmaxf(q0, -128.0f); q1 = fmaxf(q1, -128.0f); q2 = fmaxf(q2, -128.0f); q3 = fmaxf(q3, -128.0f);
+  }
+  float t0 = __fadd_rn(q0, kMagic), t1 = __fadd_rn(q1, kMagic), t2 = __fadd_rn(q2, kMagic), t3 = __fadd_rn(q3, kMagic);
+  const float d0 = __fsub_rn(q0, __fsub_rn(t0, kMagic)), d1 = __fsub_rn(q1, __fsub_rn(t1, kMagic));
+  const float d2 = __fsub_rn(q2, __fsub_rn(t2, kMagic)), d3 = __fsub_rn(q3, __fsub_rn(t3, kMagic));
+  if (fmaxf(fmaxf(fabsf(d0), fabsf(d1)), fmaxf(fabsf(d2), fabsf(d3))) > 0.4990234375f) {
+    t0 = __fadd_rn(fmaxf(__fdiv_rn(__fmul_rn(x0, 127.0f), mf), -128.0f), kMagic);
+    t1 = __fadd_rn(fmaxf(__fdiv_rn(__fmul_rn(x1, 127.0f), mf), -128.0f), kMagic);
+    t2 = __fadd_rn(fmaxf(__fdiv_rn(__fmul_rn(x2, 127.0f), mf), -128.0f), kMagic);
+    t3 = __fadd_rn(fmaxf(__fdiv_rn(__fmul_rn(x3, 127.0f), mf), -128.0f), kMagic);
+  }
+  const unsigned ab = __byte_perm(__float_as_uint(t0), __float_as_uint(t1), 0x0040);
+  const unsigned cd = __byte_perm(__float_as_uint(t2), __float_as_uint(t3), 0x0040);
+  return __byte_perm(ab, cd, 0x5410);
+}
+
+// Packs the LOW BYTES of four words.
 __device__ __forceinline__ unsigned pack4(int a, int b, int c, int d) {
   // two byte permutes: (a,b) -> low half, (c,d) -> high half, then merge
   const unsigned ab = __byte_perm((unsigned)a, (unsigned)b, 0x0040);

@@ -159,8 +159,7 @@ rmsnorm_rows_kernel(const int32_t* __restrict__ x, const int32_t* __restrict__ r
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * blockDim.x;
       if (FULL || idx < nvec) {
-        co[idx] = pack4(quant_byte_fast_small(v[i].x, mf, my127), quant_byte_fast_small(v[i].y, mf, my127),
-                        quant_byte_fast_small(v[i].z, mf, my127), quant_byte_fast_small(v[i].w, mf, my127));
+        co[idx] = quant4_bytes_fast_small<true>(v[i], mf, my127);
       }
     }
   } else {
@@ -423,12 +422,13 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   pdl_wait();                          // the tables above do not depend on the preceding kernel; gate_up does
   __syncthreads();
 
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
   const int lane8 = threadIdx.x & 7;
   const int group = threadIdx.x >> 3;
   const int ngroups = blockDim.x >> 3;
   const int nblocks = I >> 7;
   const int niter = (nblocks + ngroups - 1) / ngroups;
+
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
   const int32_t* gate = gate_up + row * (ACT ? 2 : 1) * (int64_t)I;
   const int32_t* up = gate + I;
   if (row + gridDim.x < rows) {        // this CTA's next row on its way into L2 while this one is worked on
@@ -439,6 +439,7 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
   }
 
   int m = 0;
+  unsigned small_its = 0;                        // bit `it`: the iteration's values came from the path without saturation
   for (int it = 0; it < niter; ++it) {           // uniform trip count: the shuffles need whole warps
     const int b = group + it * ngroups;
     const bool live = b < nblocks;
@@ -473,6 +474,7 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
         out |= ((unsigned)gq[k].w + kOff) | ((unsigned)uq[k].w + kOff);
       }
       small = !__any_sync(FULL_MASK, out >= (1u << 21));
+      if (it < 32) small_its |= (small ? 1u : 0u) << it;
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -570,8 +572,8 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
       const int i = b * 32 + k * 8 + lane8;
       const int4 v = reinterpret_cast<const int4*>(rowbuf)[i];
       if (small_m) {
-        co[i] = pack4(quant_byte_fast_small(v.x, mf, my127), quant_byte_fast_small(v.y, mf, my127),
-                      quant_byte_fast_small(v.z, mf, my127), quant_byte_fast_small(v.w, mf, my127));
+        co[i] = it < 32 && ((small_its >> it) & 1u) ? quant4_bytes_fast_small<false>(v, mf, my127)
+                                       : quant4_bytes_fast_small<true>(v, mf, my127);
       } else {
         co[i] = pack4(quant_code_fast(v.x, mf, my), quant_code_fast(v.y, mf, my), quant_code_fast(v.z, mf, my),
                       quant_code_fast(v.w, mf, my));
