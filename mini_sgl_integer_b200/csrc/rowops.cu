@@ -440,17 +440,25 @@ silu_rows_kernel(const int32_t* __restrict__ gate_up, int32_t* __restrict__ q15_
 
   int m = 0;
   unsigned small_its = 0;                        // bit `it`: the iteration's values came from the path without saturation
-  for (int it = 0; it < niter; ++it) {           // uniform trip count: the shuffles need whole warps
-    const int b = group + it * ngroups;
+  for (int it = 0; it < niter; ++it) {           // the shuffles need whole warps: a warp leaves when none of its
+    const int b = group + it * ngroups;            // four groups has a block left
     const bool live = b < nblocks;
+    const unsigned live_mask = __ballot_sync(FULL_MASK, live);
+    if (live_mask == 0) break;
+    const bool all_live = live_mask == FULL_MASK;  // the usual case: no zero fill in front of the loads
     int val[16];
     auto load = [&](int k, int4& g, int4& u) {
-      g = make_int4(0, 0, 0, 0);
-      u = make_int4(0, 0, 0, 0);
-      if (live) {
-        const int off = b * 128 + k * 32 + lane8 * 4;
+      const int off = b * 128 + k * 32 + lane8 * 4;
+      if (all_live) {
         g = __ldcs(reinterpret_cast<const int4*>(gate + off));
-        if (ACT) u = __ldcs(reinterpret_cast<const int4*>(up + off));
+        u = ACT ? __ldcs(reinterpret_cast<const int4*>(up + off)) : make_int4(0, 0, 0, 0);
+      } else {
+        g = make_int4(0, 0, 0, 0);
+        u = make_int4(0, 0, 0, 0);
+        if (live) {
+          g = __ldcs(reinterpret_cast<const int4*>(gate + off));
+          if (ACT) u = __ldcs(reinterpret_cast<const int4*>(up + off));
+        }
       }
     };
     constexpr bool kCheckFirst = ACT && TABLE;     // all 16 gate / up pairs are needed before the first element
