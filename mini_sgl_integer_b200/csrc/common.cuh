@@ -134,10 +134,14 @@ __device__ __forceinline__ int quant_code(int x, float mf) {
   int r = __float2int_rn(q);
   return max(-128, min(127, r));
 }
+// |estimate - integer| above this sends a value to the exact division: 0.5 - 2^-13.  The estimates below differ from
+// the reference's rounded quotient by less than 2^-14.7 (three roundings of 2^-24 on |q| <= 128, and the quotient's own),
+// so outside the band both round to the same integer; a band of 2^-10 sent a fifth of the warps there.
+constexpr float kQuantTieBand = 0.4998779296875f;
 // The same code with the division replaced by a multiply with the row's correctly rounded reciprocal
 // (y = __frcp_rn(mf)): a * y is within a few units in the last place of the quotient (|q| <= 128: an absolute error
 // below 2^-16), so after rounding to an integer it can only disagree with the division when it lies within a hair
-// of a half-integer; in that band (2^-10 wide, far above any such error) the true division is used.
+// of a half-integer; in that band (kQuantTieBand, several times any such error) the true division is used.
 // Rounding to the nearest-even integer is done by adding 1.5 * 2^23 (-128 <= q <= 127 after the lower clamp).
 __device__ __forceinline__ int quant_code_fast(int x, float mf, float y) {
   const float a = __fmul_rn(__int2float_rn(x), 127.0f);
@@ -145,7 +149,7 @@ __device__ __forceinline__ int quant_code_fast(int x, float mf, float y) {
   // -128: the lower clamp of the reference is kept (an upper one is not needed: every other |x| <= absmax)
   const float q = fmaxf(__fmul_rn(a, y), -128.0f);
   float t = __fadd_rn(q, 12582912.0f);                        // integer part now sits in the mantissa
-  if (fabsf(__fsub_rn(q, __fsub_rn(t, 12582912.0f))) > 0.4990234375f)    // within 2^-10 of a half-integer
+  if (fabsf(__fsub_rn(q, __fsub_rn(t, 12582912.0f))) > kQuantTieBand)    // close to a half-integer
     t = __fadd_rn(fmaxf(__fdiv_rn(a, mf), -128.0f), 12582912.0f);
   return __float_as_int(t) - 0x4B400000;
 }
@@ -154,7 +158,7 @@ __device__ __forceinline__ float quant_scale(float mf) { return __fdiv_rn(mf, 83
 // quant_code_fast for four values of a row whose absmax is below 2^22: int -> float by placing the value in the
 // mantissa of 1.5 * 2^23 (exact for |x| < 2^22) instead of the conversion unit, one multiply with y127 =
 // __fmul_rn(127, __frcp_rn(mf)) for the estimate (one more rounding: still below 2^-15), ONE test for "some value
-// within 2^-10 of a half-integer" and then the division for all four.  The codes are the low bytes of the mantissas
+// within the tie band of a half-integer" and then the division for all four.  The codes are the low bytes of the mantissas
 // of 1.5 * 2^23 + q.  -2^31 (not counted in the absmax) comes out of the mantissa trick as -25165824, still far below
 // -128 * absmax / 127; CLAMP = false leaves out the lower clamp: only for values known not to be -2^31.
 template <bool CLAMP>
@@ -169,7 +173,7 @@ __device__ __forceinline__ unsigned quant4_bytes_fast_small(int4 v, float mf, fl
   float t0 = __fadd_rn(q0, kMagic), t1 = __fadd_rn(q1, kMagic), t2 = __fadd_rn(q2, kMagic), t3 = __fadd_rn(q3, kMagic);
   const float d0 = __fsub_rn(q0, __fsub_rn(t0, kMagic)), d1 = __fsub_rn(q1, __fsub_rn(t1, kMagic));
   const float d2 = __fsub_rn(q2, __fsub_rn(t2, kMagic)), d3 = __fsub_rn(q3, __fsub_rn(t3, kMagic));
-  if (fmaxf(fmaxf(fabsf(d0), fabsf(d1)), fmaxf(fabsf(d2), fabsf(d3))) > 0.4990234375f) {
+  if (fmaxf(fmaxf(fabsf(d0), fabsf(d1)), fmaxf(fabsf(d2), fabsf(d3))) > kQuantTieBand) {
     t0 = __fadd_rn(fmaxf(__fdiv_rn(__fmul_rn(x0, 127.0f), mf), -128.0f), kMagic);
     t1 = __fadd_rn(fmaxf(__fdiv_rn(__fmul_rn(x1, 127.0f), mf), -128.0f), kMagic);
     t2 = __fadd_rn(fmaxf(__fdiv_rn(__fmul_rn(x2, 127.0f), mf), -128.0f), kMagic);
