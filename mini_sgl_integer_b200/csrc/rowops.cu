@@ -376,18 +376,14 @@ __device__ __forceinline__ void fwht128_group_nosat(int (&val)[16], int lane8) {
   }
 }
 
-// Threads per CTA: an 8-lane group takes one 128-block per iteration, so the groups per CTA should divide the
-// row's blocks without leaving most groups idle in the last iteration (136 blocks on 64 groups: 3 iterations, the
-// last one with 8 groups busy; on 68 groups: 2 full iterations).  Whole warps, at most kSiluMaxThreads.
+// Threads per CTA: an 8-lane group takes one 128-block per iteration; whole warps, at most kSiluMaxThreads (two
+// such CTAs per SM by registers).  Rows with more blocks than groups get the widest CTA: warps that have no block
+// left in the last iteration leave it, so an uneven last pass costs nothing, and more warps hide more latency
+// (136 blocks: 72 groups beat the even 68; 96 blocks at batch 256: 72 + 24 beat 48 + 48).
 constexpr int kSiluMaxThreads = 576;
 static int silu_threads(int nblocks) {
   const int max_groups = kSiluMaxThreads / 8;
-  if (nblocks <= max_groups) return ((nblocks * 8 + 31) / 32) * 32;
-  int min_slots = 1 << 30;
-  for (int g = max_groups; g >= max_groups / 2; g -= 4) min_slots = min(min_slots, (nblocks + g - 1) / g * g);
-  for (int g = max_groups; g >= max_groups / 2; g -= 4)         // the widest CTA within 6 % of the best fit
-    if ((nblocks + g - 1) / g * g <= min_slots + min_slots / 16) return g * 8;
-  return max_groups * 8;
+  return nblocks <= max_groups ? ((nblocks * 8 + 31) / 32) * 32 : max_groups * 8;
 }
 
 // One CTA per row at a time (the CTAs walk the rows with the grid as stride, so the tables are staged once per
