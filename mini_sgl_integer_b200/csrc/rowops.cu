@@ -228,8 +228,9 @@ __global__ void quant_given_absmax_kernel(const int32_t* __restrict__ x, const i
     const float mf = __int2float_rn(max(1, absmax[r]));
     const float my = __frcp_rn(mf);
     const int4 v = reinterpret_cast<const int4*>(x)[i];
-    reinterpret_cast<unsigned*>(codes)[i] = pack4(quant_code_fast(v.x, mf, my), quant_code_fast(v.y, mf, my),
-                                                  quant_code_fast(v.z, mf, my), quant_code_fast(v.w, mf, my));
+    // the given absmax need not bound the row (it is the caller's): the reference's upper clamp is kept here
+    reinterpret_cast<unsigned*>(codes)[i] = pack4(min(127, quant_code_fast(v.x, mf, my)), min(127, quant_code_fast(v.y, mf, my)),
+                                                  min(127, quant_code_fast(v.z, mf, my)), min(127, quant_code_fast(v.w, mf, my)));
   }
 }
 

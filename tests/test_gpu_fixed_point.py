@@ -93,6 +93,20 @@ def test_golden_quant_rows_holding_int_min(fp, golden):
     eq(host(quant_given_absmax(dev(rows), dev(m.reshape(-1)))), want)
 
 
+def test_quant_with_a_given_absmax_below_the_rows_maximum_clamps(fp):
+    """per_token_quant_int8_from_q15's clamp to [-128, 127] (layers/quantization/w8a8_int8.py:122-125) when the caller's
+    absmax does not bound the row: values far beyond it, at the rails, and -2**31."""
+    from mini_sgl_integer_b200.layers.tp_linear import quant_given_absmax
+    rng = np.random.default_rng(31)
+    x = rng.integers(-(2**24), 2**24, (6, 256)).astype(np.int64)
+    x[0, :8] = [2**31 - 1, -(2**31), 2**30, -(2**30), 5 * 2**22, -5 * 2**22, 2**23, -(2**23)]
+    x = x.astype(np.int32)
+    m = np.array([2**22, 1, 7, 2**24, 2**20 + 3, 2**30], dtype=np.int32)
+    q = (x.astype(np.float32) * np.float32(127.0)) / m.astype(np.float32)[:, None]
+    want = np.clip(np.rint(q), -128, 127).astype(np.int8)
+    eq(host(quant_given_absmax(dev(x), dev(m))), want)
+
+
 def test_golden_per_tensor_quantiser(golden):
     """quantize_per_tensor_int8_ms (the reference's prefill quantiser) on the device: codes, multiplier, shift."""
     from mini_sgl_integer_b200.attention import quantize_per_tensor_int8_ms
